@@ -1,0 +1,277 @@
+"""CPU oracle for the Tucker-MoE layer forward (test infrastructure, not product code).
+
+Two independent statements of the same layer:
+
+* ``layer_forward``  -- restates the reference module's forward op by op
+  (reference ``pure_torch_mlx/model.py:68-102`` and its ``RMSNorm`` at
+  ``pure_torch_mlx/model.py:25-27``; second witness
+  ``mamba3_mlx/bench_pytorch_ref.py:107-130``) in the tensor dtype it is given, so that it
+  rounds where the reference rounds.  It is pinned against outputs of the reference module
+  itself: ``tests/golden/make_golden.py`` runs the real module and stores its outputs, and
+  ``tests/test_oracle.py`` checks this function against them bit for bit.
+* ``layer_forward_f64`` -- float64 evaluation in the coefficient-vector algebra
+  ``c = sum_k g_k * U_expert[e_k]``, ``z = sum_a c_a * (h @ core[a])`` that the CUDA kernels
+  use.  It arbitrates when a low-precision reference and the kernels disagree.
+
+Also here: the seeded synthetic input generator for the benchmark configurations and the
+comparison helpers (top-k mismatch classification, relative Frobenius error).
+
+Only ``tests/``, the smoke check and the benchmark's CPU-baseline leg may import this file.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Dict, Optional
+
+import torch
+import torch.nn.functional as F
+
+
+# --------------------------------------------------------------------------------------
+# Factor container
+# --------------------------------------------------------------------------------------
+
+FACTOR_NAMES = ("router_w", "U_in", "inner_norm_w", "U_expert", "core", "U_out", "bias")
+
+
+@dataclass
+class LayerShape:
+    """Sizes of one Tucker-MoE layer (names follow ``pure_torch_mlx/model.py:44-58``)."""
+    d_in: int
+    d_out: int
+    E: int
+    top_k: int
+    r1: int
+    r3: int
+    r2: int
+    eps: float = 1e-6
+
+    def flops_per_token(self) -> int:
+        """Algorithmic FLOPs per token in the coefficient-vector formulation."""
+        return (2 * self.d_in * self.E + 2 * self.d_in * self.r3 + 2 * self.r3 * self.r1 * self.r2
+                + 2 * self.r1 * self.r2 + 2 * self.r2 * self.d_out)
+
+    def factor_elems(self) -> int:
+        return (self.E * self.d_in + self.d_in * self.r3 + self.r3 + self.E * self.r1
+                + self.r1 * self.r3 * self.r2 + self.r2 * self.d_out + self.d_out)
+
+
+# --------------------------------------------------------------------------------------
+# Restatement of the reference forward
+# --------------------------------------------------------------------------------------
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """``x / sqrt(mean(x^2) + eps) * weight`` in x's dtype (model.py:25-27: no fp32 upcast)."""
+    denom = x.pow(2).mean(-1, keepdim=True).add(eps).sqrt()
+    return (x / denom) * weight
+
+
+def _forward_chunk(x_flat: torch.Tensor, f: Dict[str, torch.Tensor], top_k: int, eps: float,
+                   taps: Optional[dict]) -> torch.Tensor:
+    # model.py:75-77 -- raw scores, top-k on the raw scores, softmax over the k winners only
+    scores = F.linear(x_flat, f["router_w"])
+    sel_val, sel_idx = torch.topk(scores, top_k, dim=-1)
+    gates = F.softmax(sel_val, dim=-1)
+    # model.py:80-81 -- shared in-projection, then the inner RMSNorm
+    h = rms_norm(x_flat @ f["U_in"], f["inner_norm_w"], eps)
+    # model.py:87-98 -- per selected expert: mix the core slices, contract, weight, accumulate
+    r2 = f["U_out"].shape[0]
+    acc = h.new_zeros(x_flat.shape[0], r2)
+    for j in range(top_k):
+        coeff = f["U_expert"][sel_idx[:, j]]                       # [T, r1]
+        mixed = torch.einsum("br,rst->bst", coeff, f["core"])      # [T, r3, r2]
+        mid = torch.bmm(h.unsqueeze(1), mixed).squeeze(1)          # [T, r2]
+        acc.add_(gates[:, j].unsqueeze(1) * mid)
+    # model.py:101
+    y = acc @ f["U_out"] + f["bias"]
+    if taps is not None:
+        for name, val in (("scores", scores), ("idx", sel_idx), ("gates", gates), ("h", h),
+                          ("z", acc), ("y", y)):
+            taps.setdefault(name, []).append(val)
+    return y
+
+
+@torch.no_grad()
+def layer_forward(x: torch.Tensor, factors: Dict[str, torch.Tensor], top_k: int, eps: float,
+                  chunk_tokens: int = 256, return_taps: bool = False):
+    """Reference-order forward on CPU.  ``x``: (..., d_in) -> (..., d_out).
+
+    Tokens are processed in chunks because the reference materialises a ``[T, r3, r2]``
+    tensor per selected expert (model.py:95); the layer is token-wise independent so
+    chunking does not change any result.
+    """
+    *batch, d_in = x.shape
+    x_flat = x.reshape(-1, d_in)
+    T = x_flat.shape[0]
+    d_out = factors["U_out"].shape[1]
+    taps: Optional[dict] = {} if return_taps else None
+    outs = []
+    for t0 in range(0, T, chunk_tokens):
+        outs.append(_forward_chunk(x_flat[t0:t0 + chunk_tokens], factors, top_k, eps, taps))
+    y = torch.cat(outs, 0) if outs else x_flat.new_zeros(0, d_out)
+    y = y.reshape(*batch, d_out)
+    if return_taps:
+        merged = {k: torch.cat(v, 0) for k, v in taps.items()} if taps else {}
+        return y, merged
+    return y
+
+
+@torch.no_grad()
+def layer_forward_f64(x: torch.Tensor, factors: Dict[str, torch.Tensor], top_k: int, eps: float,
+                      idx: Optional[torch.Tensor] = None, round_scores_to: Optional[torch.dtype] = None,
+                      chunk_tokens: int = 2048):
+    """float64 forward in the coefficient-vector algebra.
+
+    ``idx`` (optional, [T, k]) forces the selected experts so that outputs can be compared
+    token by token with an implementation that broke a tie differently.
+    ``round_scores_to`` rounds the raw scores to a storage dtype before selection and
+    softmax, which is what the reference does when its parameters are bf16.
+    Returns (y, taps) with taps = idx, gates, c, h, z in float64.
+    """
+    *batch, d_in = x.shape
+    xf = x.reshape(-1, d_in).double()
+    f = {k: v.double() for k, v in factors.items()}
+    T = xf.shape[0]
+    r1, r3, r2 = f["core"].shape
+    core_flat = f["core"].reshape(r1, r3 * r2)
+    ys, taps = [], {"idx": [], "gates": [], "c": [], "h": [], "z": [], "scores": []}
+    for t0 in range(0, T, chunk_tokens):
+        xc = xf[t0:t0 + chunk_tokens]
+        scores = xc @ f["router_w"].t()
+        if round_scores_to is not None:
+            scores = scores.to(round_scores_to).double()
+        if idx is None:
+            sel_val, sel_idx = torch.topk(scores, top_k, dim=-1)
+        else:
+            sel_idx = idx[t0:t0 + chunk_tokens].long()
+            sel_val = torch.gather(scores, 1, sel_idx)
+        gates = torch.softmax(sel_val, -1)
+        c = torch.einsum("tk,tkr->tr", gates, f["U_expert"][sel_idx])         # [t, r1]
+        h = xc @ f["U_in"]
+        h = h / torch.sqrt(h.pow(2).mean(-1, keepdim=True) + eps) * f["inner_norm_w"]
+        # z[t, s] = sum_a c[t, a] * (h[t, :] @ core[a])[s]
+        p = (h @ f["core"].permute(1, 0, 2).reshape(r3, r1 * r2)).reshape(-1, r1, r2)
+        z = torch.einsum("ta,tas->ts", c, p)
+        ys.append(z @ f["U_out"] + f["bias"])
+        for name, val in (("idx", sel_idx), ("gates", gates), ("c", c), ("h", h), ("z", z),
+                          ("scores", scores)):
+            taps[name].append(val)
+    del core_flat
+    d_out = f["U_out"].shape[1]
+    y = torch.cat(ys, 0) if ys else xf.new_zeros(0, d_out)
+    merged = {k: (torch.cat(v, 0) if v else None) for k, v in taps.items()}
+    return y.reshape(*batch, d_out), merged
+
+
+# --------------------------------------------------------------------------------------
+# Seeded synthetic inputs
+# --------------------------------------------------------------------------------------
+
+def make_factors(shape: LayerShape, seed: int, dtype: torch.dtype = torch.float32,
+                 router_std: Optional[float] = 0.02, bias_std: float = 0.0) -> Dict[str, torch.Tensor]:
+    """Seeded factors.  Draw order is fixed: W_r, U_expert, U_in, core, U_out, (bias).
+
+    ``router_std=None`` means ``1/sqrt(d_in)`` so that the logits of N(0,1) inputs are ~N(0,1).
+    All draws are fp32 on a CPU generator and are cast to ``dtype`` afterwards.
+    """
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    s = shape
+    rstd = (1.0 / math.sqrt(s.d_in)) if router_std is None else router_std
+    f = {
+        "router_w": torch.randn(s.E, s.d_in, generator=g) * rstd,
+        "U_expert": torch.randn(s.E, s.r1, generator=g),
+        "U_in": torch.randn(s.d_in, s.r3, generator=g) / math.sqrt(s.d_in),
+        "core": torch.randn(s.r1, s.r3, s.r2, generator=g) / math.sqrt(s.r3),
+        "U_out": torch.randn(s.r2, s.d_out, generator=g) / math.sqrt(s.r2),
+        "inner_norm_w": torch.ones(s.r3),
+    }
+    f["bias"] = (torch.randn(s.d_out, generator=g) * bias_std) if bias_std > 0 else torch.zeros(s.d_out)
+    return {k: v.to(dtype).contiguous() for k, v in f.items()}
+
+
+def make_tokens(T: int, d_in: int, seed: int, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """x ~ N(0,1), fp32 draw on a CPU generator, cast afterwards.  Independent of the factor seed."""
+    g = torch.Generator(device="cpu").manual_seed(seed + 7_000_003)
+    return torch.randn(T, d_in, generator=g).to(dtype).contiguous()
+
+
+def apply_zipf_router_bias(x: torch.Tensor, factors: Dict[str, torch.Tensor], seed: int, s: float = 1.2):
+    """Skewed routing inside the bias-free router API (model.py:60 has ``bias=False``).
+
+    Input channel 0 becomes the constant 1 and ``W_r[:, 0]`` the per-expert bias
+    ``log p_e - mean(log p)`` with ``p_e ~ rank^-s`` under a seeded expert permutation.
+    """
+    E = factors["router_w"].shape[0]
+    g = torch.Generator(device="cpu").manual_seed(seed + 99)
+    perm = torch.randperm(E, generator=g)
+    logp = -s * torch.log(torch.arange(1, E + 1, dtype=torch.float32))
+    logp = logp - logp.mean()
+    b = torch.empty(E)
+    b[perm] = logp
+    factors["router_w"][:, 0] = b.to(factors["router_w"].dtype)
+    x[..., 0] = 1.0
+    return x, factors
+
+
+BENCH_SHAPES = {
+    # name: (LayerShape, T, dtype, factor seed, router_std)
+    "cfg0": (LayerShape(1536, 2304, 8, 2, 4, 256, 1024), 512, torch.float32, 1000, 0.02),
+    "cfg1": (LayerShape(1536, 2304, 8, 2, 4, 256, 1024), 64, torch.bfloat16, 1001, 0.02),
+    "cfg2": (LayerShape(1536, 2304, 64, 2, 4, 256, 1024), 32768, torch.bfloat16, 1002, None),
+    "cfg3": (LayerShape(1536, 2304, 64, 2, 4, 256, 1024), 16384, torch.bfloat16, 1003, 0.02),
+    "cfg4": (LayerShape(3072, 4608, 256, 8, 8, 512, 2048), 131072, torch.bfloat16, 1004, 0.02),
+}
+
+
+# --------------------------------------------------------------------------------------
+# Comparison helpers
+# --------------------------------------------------------------------------------------
+
+def rel_fro(a: torch.Tensor, b: torch.Tensor) -> float:
+    """||a - b||_F / ||b||_F in float64 (0 for two empty tensors)."""
+    a64, b64 = a.double(), b.double()
+    den = float(b64.norm())
+    return float((a64 - b64).norm()) / den if den > 0 else float((a64 - b64).norm())
+
+
+def max_abs(a: torch.Tensor, b: torch.Tensor) -> float:
+    if a.numel() == 0:
+        return 0.0
+    return float((a.double() - b.double()).abs().max())
+
+
+@dataclass
+class TopkReport:
+    tokens: int
+    exact: int                 # ordered index lists identical
+    tie_explained: int         # differ, but every differing position is within `gap` in the checker's scores
+    unexplained: int
+    mismatch_tokens: list = field(default_factory=list)
+
+
+def classify_topk(idx_test: torch.Tensor, idx_ref: torch.Tensor, scores_ref: torch.Tensor,
+                  gap: float) -> TopkReport:
+    """Compare ordered top-k index lists token by token.
+
+    A token whose lists differ counts as tie-explained when, at every position where the
+    two lists disagree, the checker's own scores of the two competing experts are within
+    ``gap`` of each other (fp32: 1e-6; bf16: one unit in the last place of the score).
+    """
+    idx_test = idx_test.long().cpu()
+    idx_ref = idx_ref.long().cpu()
+    s = scores_ref.double().cpu()
+    T = idx_ref.shape[0]
+    same = (idx_test == idx_ref).all(-1)
+    exact = int(same.sum())
+    tie, bad, toks = 0, 0, []
+    for t in torch.nonzero(~same).flatten().tolist():
+        ok = True
+        for j in range(idx_ref.shape[1]):
+            a, b = int(idx_test[t, j]), int(idx_ref[t, j])
+            if a != b and abs(float(s[t, a]) - float(s[t, b])) > gap:
+                ok = False
+        tie += int(ok)
+        bad += int(not ok)
+        toks.append(t)
+    return TopkReport(T, exact, tie, bad, toks)

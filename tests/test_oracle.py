@@ -1,0 +1,59 @@
+"""The CPU oracle against the golden outputs of the real reference module (no GPU needed)."""
+import pytest
+import torch
+
+from golden_cases import ALL_CASES, F32_CASES, load_case
+from oracle.tucker_moe_oracle import (classify_topk, layer_forward, layer_forward_f64, max_abs,
+                                      rel_fro)
+
+
+@pytest.mark.parametrize("name", ALL_CASES)
+def test_restatement_is_bit_exact(name):
+    """The op-by-op restatement reproduces the reference module's output bit for bit."""
+    shape, x, f, dtype, g = load_case(name)
+    y, taps = layer_forward(x, f, shape.top_k, shape.eps, return_taps=True)
+    assert y.shape == g["y"].shape and y.dtype == dtype
+    assert torch.equal(y.float(), g["y"])
+    if x.numel():
+        assert torch.equal(taps["idx"], g["idx"])
+        assert torch.equal(taps["gates"].float(), g["gates"])
+        assert torch.equal(taps["scores"].float(), g["scores"])
+
+
+@pytest.mark.parametrize("chunk", [1, 3, 1000])
+def test_chunking_does_not_change_results(chunk):
+    shape, x, f, _, g = load_case("ragged_e64_k8_f32")
+    y = layer_forward(x, f, shape.top_k, shape.eps, chunk_tokens=chunk)
+    assert max_abs(y, g["y"]) < 5e-5  # BLAS blocks differently per chunk size; |y|max is ~6
+
+
+@pytest.mark.parametrize("name", F32_CASES)
+def test_f64_algebra_matches_reference_fp32(name):
+    """The coefficient-vector algebra in float64 agrees with the fp32 reference to 1e-5 rel-Fro
+    (bound stated for fp32 round-off of the reference itself) with identical selections."""
+    shape, x, f, _, g = load_case(name)
+    y64, taps = layer_forward_f64(x, f, shape.top_k, shape.eps)
+    if x.numel() == 0:
+        assert y64.shape == g["y"].shape
+        return
+    rep = classify_topk(taps["idx"], g["idx"], g["scores"], gap=1e-6)
+    assert rep.unexplained == 0
+    y64b, _ = layer_forward_f64(x, f, shape.top_k, shape.eps, idx=g["idx"])
+    assert rel_fro(y64b, g["y"]) < 1e-5
+
+
+def test_bf16_reference_vs_f64_with_forced_selection():
+    """bf16 reference is low precision end to end; with its own selection forced and scores
+    rounded to bf16, float64 algebra stays within the 2e-2 budget."""
+    shape, x, f, _, g = load_case("cfg2_head_bf16")
+    y64, _ = layer_forward_f64(x, f, shape.top_k, shape.eps, idx=g["idx"], round_scores_to=torch.bfloat16)
+    assert rel_fro(y64, g["y"]) < 2e-2
+
+
+def test_classify_topk_flags_real_mismatch():
+    s = torch.tensor([[0.0, 1.0, 2.0, 3.0]])
+    ref = torch.tensor([[3, 2]])
+    assert classify_topk(torch.tensor([[3, 2]]), ref, s, 1e-6).exact == 1
+    assert classify_topk(torch.tensor([[3, 1]]), ref, s, 1e-6).unexplained == 1
+    s2 = torch.tensor([[0.0, 2.0, 2.0, 3.0]])
+    assert classify_topk(torch.tensor([[3, 1]]), ref, s2, 1e-6).tie_explained == 1
