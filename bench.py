@@ -1,0 +1,359 @@
+"""Benchmark of the Tucker-MoE layer forward on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg2] [--impl ours|reference]
+
+One "step" is one forward of the layer over one batch of synthetic tokens.  The default
+workload is the prefill configuration (T=32768 tokens per GPU, d_in=1536, d_out=2304, E=64,
+top-2, ranks (4,256,1024), bf16).  Tokens are sharded over the GPUs with the factor set
+replicated; there is no collective on the data path, per-GPU work is fixed as N grows (weak
+scaling) and `value` is tokens/s summed over all ranks, timed with CUDA events, max over ranks.
+
+The JSON line also carries
+  roofline      achieved TFLOP/s of the dominant kernel (algorithmic FLOPs / CUDA-event time)
+                against the measured bf16 peak in MEASURED_PEAKS.json
+  e2e           the same metric through the public module call with HOST buffers: pinned
+                host -> device copy of x and device -> host copy of y inside the timed region
+  cpu_baseline  the CPU restatement of the reference layer on this host (rank 0, N=1 only)
+  clocks        SM clock / throttle reasons sampled with nvidia-smi during the timed region
+
+`--impl reference` times the reference algorithm's CPU path (the oracle restatement of
+pure_torch_mlx/model.py:68-102, all host threads) on the same workload, each step a bounded
+token sample.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (oracle shape key, tokens per GPU, description)
+    "cfg2": ("cfg2", 32768, "prefill bf16 T=32768 d_in=1536 d_out=2304 E=64 top2 r=(4,256,1024)"),
+    "cfg0": ("cfg0", 512, "fp32 T=512 d_in=1536 d_out=2304 E=8 top2 r=(4,256,1024)"),
+    "cfg1": ("cfg1", 64, "decode bf16 T=64 d_in=1536 d_out=2304 E=8 top2 r=(4,256,1024)"),
+    "cfg3": ("cfg3", 16384, "bf16 T=16384 E=64 top2"),
+}
+N_INPUT_SETS = 4  # rotating x buffers so that no step re-reads the previous step's lines from L2
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle sampling in the background (read-only queries)."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx, self.proc = gpu_index, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.idx)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        for line in out.strip().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1])); mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_info():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def cpu_reference_rate(workload: str, sample_tokens: int, reps: int):
+    """tokens/s of the CPU restatement of the reference layer on `sample_tokens` tokens of the workload."""
+    from oracle.tucker_moe_oracle import BENCH_SHAPES, layer_forward, make_factors, make_tokens
+    shape, _, dtype, seed, rstd = BENCH_SHAPES[WORKLOADS[workload][0]]
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    f = make_factors(shape, seed, dtype, rstd)
+    x = make_tokens(sample_tokens, shape.d_in, seed, dtype)
+    layer_forward(x[:256], f, shape.top_k, shape.eps, chunk_tokens=64)  # warm-up
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        layer_forward(x, f, shape.top_k, shape.eps, chunk_tokens=64)
+        times.append(time.perf_counter() - t0)
+    dt = min(times)
+    return sample_tokens / dt, threads, dt
+
+
+def run_reference_arm(args):
+    rank, world, _ = dist_info()
+    if rank != 0:
+        return
+    shape_key, T, desc = WORKLOADS[args.workload]
+    sample = min(T, 2048)
+    times = []
+    from oracle.tucker_moe_oracle import BENCH_SHAPES, layer_forward, make_factors, make_tokens
+    shape, _, dtype, seed, rstd = BENCH_SHAPES[shape_key]
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    f = make_factors(shape, seed, dtype, rstd)
+    x = make_tokens(sample, shape.d_in, seed, dtype)
+    for i in range(args.warmup + args.steps):
+        t0 = time.perf_counter()
+        layer_forward(x, f, shape.top_k, shape.eps, chunk_tokens=64)
+        if i >= args.warmup:
+            times.append(time.perf_counter() - t0)
+    total = sum(times)
+    value = sample * args.steps / total
+    line = {
+        "impl": "reference", "metric": "tucker_moe_layer_tokens_per_sec", "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16" if dtype == torch.bfloat16 else "f32", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: {desc}", "tokens_per_step": sample,
+                   "note": "reference algorithm (CPU restatement of pure_torch_mlx/model.py:68-102), "
+                           f"each step a {sample}-token sample of the workload"},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port",
+                         "sample": f"{sample} tokens per step, chunked 64"},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="cfg2", choices=list(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--e2e-steps", type=int, default=8)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--path", type=int, default=0, help="0 auto, 1 CUDA-core, 2 tensor-core")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    rank, world, local = dist_info()
+    if world != args.gpus and world > 1:
+        args.gpus = world
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    import mamba_tuckermoe_b200 as pkg
+    from mamba_tuckermoe_b200 import _lib
+    from oracle.tucker_moe_oracle import BENCH_SHAPES, make_factors, make_tokens
+
+    shape_key, T, desc = WORKLOADS[args.workload]
+    shape, _, dtype, seed, rstd = BENCH_SHAPES[shape_key]
+    peaks = load_peaks()
+    lib = _lib.load()
+
+    cfg = pkg.TuckerMoEConfig(shape.E, shape.top_k, shape.r1, shape.r2, shape.r3, shape.eps)
+    layer = pkg.TuckerMoE(shape.d_in, shape.d_out, cfg)
+    f = make_factors(shape, seed, torch.float32, rstd)
+    layer.load_state_dict({"router.weight": f["router_w"], "U_in": f["U_in"], "inner_norm.weight": f["inner_norm_w"],
+                           "U_expert": f["U_expert"], "core": f["core"], "U_out": f["U_out"], "bias": f["bias"]})
+    layer = layer.to(device=dev, dtype=dtype)
+    layer.path = args.path
+
+    # this rank's token shard: seeded per rank; host copies stay pinned for the end-to-end leg
+    x_host = [make_tokens(T, shape.d_in, seed + 17 * rank + 1000 * i, dtype).pin_memory() for i in range(N_INPUT_SETS)]
+    x_dev = [x.to(dev) for x in x_host]
+    y_host = torch.empty((T, shape.d_out), dtype=dtype).pin_memory()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    with torch.no_grad():
+        for i in range(max(args.warmup, 3)):
+            y = layer(x_dev[i % N_INPUT_SETS])
+        torch.cuda.synchronize()
+        st = pkg.read_device_status(dev)
+        if st[0] != 0:
+            raise RuntimeError(f"device status {st}")
+
+        # ---------------- device-resident timing ----------------
+        sampler = ClockSampler(local)
+        if rank == 0:
+            sampler.start()
+            time.sleep(0.25)
+        barrier()
+        launches0 = lib.tmoe_launch_count()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for i in range(args.steps):
+            y = layer(x_dev[i % N_INPUT_SETS])
+        ev1.record()
+        barrier()
+        launches = lib.tmoe_launch_count() - launches0
+        ms_total = ev0.elapsed_time(ev1)
+        if rank == 0:
+            time.sleep(0.15)
+            clocks = sampler.stop()
+        t_ms = torch.tensor([ms_total], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
+        ms_total = float(t_ms.item())
+        ms_step = ms_total / args.steps
+        value = world * T * args.steps / (ms_total * 1e-3)
+
+        # ---------------- per-kernel timing of the two dominant kernels (stage API) ----------------
+        kern = per_kernel_times(lib, _lib, layer, shape, dtype, x_dev[0], T, args.path)
+
+        # ---------------- end to end with host buffers ----------------
+        e2e_steps = max(2, min(args.e2e_steps, args.steps))
+        for i in range(2):
+            xd = x_host[i % N_INPUT_SETS].to(dev, non_blocking=True)
+            y_host.copy_(layer(xd), non_blocking=True)
+        barrier()
+        ev0.record()
+        for i in range(e2e_steps):
+            xd = x_host[i % N_INPUT_SETS].to(dev, non_blocking=True)
+            y_host.copy_(layer(xd), non_blocking=True)
+        ev1.record()
+        barrier()
+        e_ms = torch.tensor([ev0.elapsed_time(ev1)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(e_ms, op=dist.ReduceOp.MAX)
+        e2e_value = world * T * e2e_steps / (float(e_ms.item()) * 1e-3)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    flops_tok = shape.flops_per_token()
+    dom = kern["dominant"]
+    peak_tf = peaks["bf16_tflops"]
+    roofline = {
+        "bound": "tensor", "kernel": dom["name"], "achieved": dom["tflops"], "peak": peak_tf, "unit": "TFLOP/s",
+        "frac": dom["tflops"] / peak_tf, "traffic": None, "peak_source": f"{peaks['source']} (burst bf16)",
+        "flops_per_launch": dom["flops"], "us_per_launch": dom["us"],
+    }
+    line = {
+        "metric": "tucker_moe_layer_tokens_per_sec", "value": value, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if dtype == torch.bfloat16 else "f32",
+        "data": "synthetic",
+        "config": {"workload": f"{args.workload}: {desc}", "tokens_per_gpu": T, "global_tokens": T * world,
+                   "sharding": f"tokens x{world}, factors replicated, no collective",
+                   "l2": f"{N_INPUT_SETS} rotating input sets; x+z+y per step = "
+                         f"{(T * (shape.d_in + 2 * shape.r2 + shape.d_out) * 2) / 1e6:.0f} MB > 126 MB L2",
+                   "path": {0: "auto", 1: "cuda-core", 2: "tensor-core"}[args.path]},
+        "layer_tflops": value * flops_tok / 1e12 / world,
+        "layer_frac_of_bf16_peak": value * flops_tok / 1e12 / world / peak_tf,
+        "flops_per_token": flops_tok,
+        "roofline": roofline,
+        "kernels": kern["all"],
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": T * shape.d_in * x_host[0].element_size(),
+                "d2h_bytes_per_step": T * shape.d_out * y_host.element_size(), "steps": e2e_steps},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        rate, threads, dt = cpu_reference_rate(args.workload, min(T, 8192), 2)
+        line["cpu_baseline"] = {"value": rate, "unit": "tokens/s", "cores": threads, "kind": "port",
+                                "sample": f"{min(T, 8192)} tokens of the workload, best of 2 ({dt:.2f} s)"}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def per_kernel_times(lib, _lib, layer, shape, dtype, x, T, path, reps=20):
+    """CUDA-event time of each stage through the C-ABI stage entry points, on the current stream."""
+    L = _lib.layer_struct(shape, dtype)
+    rpath = lib.tmoe_resolve_path(C.byref(L), T, path)
+    fd = {"router_w": layer.router.weight, "U_in": layer.U_in, "inner_norm_w": layer.inner_norm.weight,
+          "U_expert": layer.U_expert, "core": layer.core, "U_out": layer.U_out, "bias": layer.bias}
+    F = _lib.factors_struct(fd)
+    ws = _lib.alloc_workspace(L, T, rpath)
+    prep = _lib.alloc_prepared(L, F) if rpath == 2 else None
+    pp = prep.data_ptr() if prep is not None else None
+    zdt = torch.bfloat16 if rpath == 2 else torch.float32
+    z = torch.empty(T, shape.r2, dtype=zdt, device=x.device)
+    y = torch.empty(T, shape.d_out, dtype=dtype, device=x.device)
+    idx = torch.empty(T, shape.top_k, dtype=torch.int32, device=x.device)
+    gates = torch.empty(T, shape.top_k, dtype=torch.float32, device=x.device)
+    c = torch.empty(T, shape.r1, dtype=torch.float32, device=x.device)
+    st = _lib.current_stream_ptr()
+    flush = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device=x.device)
+
+    def t(fn):
+        fn(); torch.cuda.synchronize()
+        evs = []
+        for _ in range(reps):
+            flush.zero_()  # evict L2 between launches
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); rc = fn(); b.record()
+            assert rc == 0, _lib.status_string(rc)
+            evs.append((a, b))
+        torch.cuda.synchronize()
+        return statistics.mean(a.elapsed_time(b) for a, b in evs) * 1e3  # us
+
+    us_router = t(lambda: lib.tmoe_router(C.byref(L), C.byref(F), x.data_ptr(), T, idx.data_ptr(), gates.data_ptr(),
+                                          c.data_ptr(), ws.data_ptr(), ws.numel(), st))
+    us_incore = t(lambda: lib.tmoe_in_core(C.byref(L), C.byref(F), pp, x.data_ptr(), T, c.data_ptr(), z.data_ptr(),
+                                           ws.data_ptr(), ws.numel(), rpath, st))
+    us_out = t(lambda: lib.tmoe_out(C.byref(L), C.byref(F), pp, z.data_ptr(), T, y.data_ptr(), None, ws.data_ptr(),
+                                    ws.numel(), rpath, st))
+    f_in = T * (2 * shape.d_in * shape.r3 + 2 * shape.r3 * shape.r1 * shape.r2 + 2 * shape.r1 * shape.r2)
+    f_out = T * 2 * shape.r2 * shape.d_out
+    allk = {
+        "router_cuda_core": {"us": us_router, "bytes": T * shape.d_in * x.element_size(),
+                             "gbs": T * shape.d_in * x.element_size() / us_router / 1e3},
+        "in_core": {"us": us_incore, "flops": f_in, "tflops": f_in / us_incore / 1e6},
+        "out_gemm": {"us": us_out, "flops": f_out, "tflops": f_out / us_out / 1e6},
+        "path": {1: "cuda-core", 2: "tensor-core"}[rpath],
+    }
+    name = "out_gemm" if us_out >= us_incore else "in_core"
+    dom = dict(allk[name]); dom["name"] = ("tc_" if rpath == 2 else "simt_") + name
+    return {"all": allk, "dominant": dom}
+
+
+if __name__ == "__main__":
+    main()

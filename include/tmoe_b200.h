@@ -1,0 +1,156 @@
+/*
+ * tmoe_b200.h -- C ABI of the B200 (sm_100a) Tucker-MoE layer forward.
+ *
+ * The reference project has no native/FFI interface: its boundary for this path is the
+ * Python class TuckerMoE(d_in, d_out, cfg) with forward(x) (pure_torch_mlx/model.py:41-102).
+ * The entry points below are what a binding for that forward needs; each comment names the
+ * reference lines the entry point replaces.
+ *
+ * Conventions
+ *  - plain C: pointers, integers, floats; no torch / C++ types.  `stream` is a cudaStream_t
+ *    passed as void* (NULL = the legacy default stream).
+ *  - every pointer named "device" is a CUDA device pointer on the current device.
+ *  - functions return 0 (TMOE_OK) or a negative tmoe_status_t; they never throw, never call
+ *    exit(), never synchronise the device (except tmoe_read_device_status) and never allocate
+ *    device memory: the caller passes a workspace sized by tmoe_workspace_bytes().
+ *  - all work is enqueued on `stream`; buffers are borrowed until that work has finished.
+ *  - tensors are dense row-major.  x, y and the seven factors share one dtype (tmoe_dtype_t).
+ */
+#ifndef TMOE_B200_H_
+#define TMOE_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TMOE_ABI_VERSION 1
+#define TMOE_MAX_TOPK 16
+#define TMOE_MAX_R1 64
+
+typedef enum tmoe_status {
+  TMOE_OK = 0,
+  TMOE_ERR_NULL = -1,        /* a required pointer is NULL                               */
+  TMOE_ERR_SHAPE = -2,       /* a size is <= 0, top_k > n_experts, or not a multiple of 8 */
+  TMOE_ERR_DTYPE = -3,       /* dtype is neither TMOE_F32 nor TMOE_BF16                   */
+  TMOE_ERR_ALIGN = -4,       /* a device pointer is not 16-byte aligned                   */
+  TMOE_ERR_WORKSPACE = -5,   /* workspace / prepared buffer too small                     */
+  TMOE_ERR_UNSUPPORTED = -6, /* the requested path does not cover this shape / dtype      */
+  TMOE_ERR_CUDA = -7,        /* a CUDA runtime call or kernel launch failed               */
+  TMOE_ERR_DRIVER = -8,      /* tensor-map encoding is unavailable or failed              */
+  TMOE_ERR_DEVICE_WAIT = -9  /* a bounded wait inside a kernel expired (device status)    */
+} tmoe_status_t;
+
+typedef enum tmoe_dtype { TMOE_F32 = 0, TMOE_BF16 = 1 } tmoe_dtype_t;
+
+/* Which kernels run.  AUTO: tensor-core path for bf16 shapes it covers when T > 64, else SIMT. */
+typedef enum tmoe_path { TMOE_PATH_AUTO = 0, TMOE_PATH_SIMT = 1, TMOE_PATH_TENSOR = 2 } tmoe_path_t;
+
+/* Sizes of one layer; mirrors the constructor arguments TuckerMoE(d_in, d_out, cfg) with
+ * cfg.kmoe_num_experts, kmoe_top_k, kmoe_r1, kmoe_r2, kmoe_r3, rms_norm_eps
+ * (pure_torch_mlx/model.py:54-62). */
+typedef struct tmoe_layer {
+  int32_t d_in, d_out;
+  int32_t n_experts, top_k;
+  int32_t r1, r2, r3;
+  int32_t dtype;  /* tmoe_dtype_t */
+  float eps;      /* inner_norm epsilon */
+} tmoe_layer_t;
+
+/* The seven parameters in the reference's own layouts (pure_torch_mlx/model.py:60-66,
+ * filled by pure_torch_mlx/weights.py:74-81).  Device pointers. */
+typedef struct tmoe_factors {
+  const void *router_w;     /* [n_experts, d_in] */
+  const void *U_in;         /* [d_in, r3]        */
+  const void *inner_norm_w; /* [r3]              */
+  const void *U_expert;     /* [n_experts, r1]   */
+  const void *core;         /* [r1, r3, r2]      */
+  const void *U_out;        /* [r2, d_out]       */
+  const void *bias;         /* [d_out]           */
+} tmoe_factors_t;
+
+/* Optional inputs/outputs; a zeroed struct (or NULL) means "plain module forward".
+ *  - residual/layer_scale: y = residual + layer_scale * (acc @ U_out + bias), the callers'
+ *    epilogue (pure_torch_mlx/model.py:260, 341).  Both or neither; dtype of x; [T,d_out]/[d_out].
+ *  - idx_out/gates_out/c_out: per-token routing results for inspection:
+ *    expert indices [T, top_k] (descending score), gate weights [T, top_k] and the
+ *    coefficient vector c[T, r1] = sum_k gate_k * U_expert[idx_k] (times 1/rms on the
+ *    tensor-core path, see tmoe_in_core). */
+typedef struct tmoe_extras {
+  const void *residual;
+  const void *layer_scale;
+  int32_t *idx_out;
+  float *gates_out;
+  float *c_out;
+} tmoe_extras_t;
+
+/* ABI version of the loaded library (== TMOE_ABI_VERSION of the header it was built from). */
+int tmoe_version(void);
+
+/* Static, human-readable text for a status code. */
+const char *tmoe_status_string(int status);
+
+/* Path that TMOE_PATH_AUTO resolves to for T tokens (TMOE_PATH_SIMT or TMOE_PATH_TENSOR),
+ * or a negative status for an invalid layer. */
+int tmoe_resolve_path(const tmoe_layer_t *layer, int64_t T, int path);
+
+/* Bytes of the re-laid-out factor set used by the tensor-core path (0 when the layer's
+ * shape/dtype is not covered by it), or a negative status. */
+int64_t tmoe_prepared_bytes(const tmoe_layer_t *layer);
+
+/* Re-layout of the factors for the tensor-core path: K-major bf16 copies of U_in, the router
+ * weight, the core (slices interleaved per r2 tile) and U_out, plus fp32 copies of
+ * inner_norm_w, U_expert and bias.  One-time cost per set of parameter values, the analogue
+ * of loading a checkpoint into the module (pure_torch_mlx/weights.py:74-81).  `prepared`
+ * must be 256-byte aligned and tmoe_prepared_bytes() large. */
+int tmoe_prepare_factors(const tmoe_layer_t *layer, const tmoe_factors_t *factors, void *prepared,
+                         int64_t prepared_bytes, void *stream);
+
+/* Bytes of scratch that tmoe_forward / tmoe_router / tmoe_in_core / tmoe_out need for T
+ * tokens on `path`, or a negative status.  The workspace must be 256-byte aligned.  Its
+ * first 256 bytes hold device status words; zero them once after allocation. */
+int64_t tmoe_workspace_bytes(const tmoe_layer_t *layer, int64_t T, int path);
+
+/* Router: scores = x @ router_w^T, top-k of the raw scores, softmax over the k winners
+ * (pure_torch_mlx/model.py:75-77), and c = sum_k gate_k * U_expert[idx_k] (the gather of
+ * model.py:93 folded through the linear core mixing of model.py:95-98).
+ * Outputs (device): idx [T, top_k] int32, gates [T, top_k] fp32, c [T, r1] fp32. */
+int tmoe_router(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const void *x, int64_t T,
+                int32_t *idx, float *gates, float *c, void *workspace, int64_t workspace_bytes,
+                void *stream);
+
+/* In-projection, inner RMSNorm and core contraction:
+ * h = RMSNorm(x @ U_in) (model.py:80-81), z[t] = sum_a c[t,a] * (h[t] @ core[a]) which equals
+ * the per-expert accumulation of model.py:90-98.
+ * SIMT path: c is read, z is fp32 [T, r2].  Tensor-core path (needs `prepared`): c is read,
+ * the row's 1/rms is folded into the coefficients instead of into h, z is bf16 [T, r2]. */
+int tmoe_in_core(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const void *prepared,
+                 const void *x, int64_t T, const float *c, void *z, void *workspace,
+                 int64_t workspace_bytes, int path, void *stream);
+
+/* Out-projection: y = z @ U_out + bias (model.py:101), optionally
+ * y = residual + layer_scale * (...) (model.py:260, 341).  z as written by tmoe_in_core on the
+ * same path; y has the layer dtype, [T, d_out]. */
+int tmoe_out(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const void *prepared,
+             const void *z, int64_t T, void *y, const tmoe_extras_t *extras, void *workspace,
+             int64_t workspace_bytes, int path, void *stream);
+
+/* The whole forward of TuckerMoE.forward (pure_torch_mlx/model.py:68-102) on one stream:
+ * x [T, d_in] -> y [T, d_out].  `prepared` may be NULL when the resolved path is SIMT.
+ * T == 0 is valid and enqueues nothing. */
+int tmoe_forward(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const void *prepared,
+                 const void *x, int64_t T, void *y, const tmoe_extras_t *extras, void *workspace,
+                 int64_t workspace_bytes, int path, void *stream);
+
+/* Synchronises `stream`, reads the workspace's device status word into *device_status
+ * (0, or TMOE_ERR_DEVICE_WAIT with details in the following words) and clears it. */
+int tmoe_read_device_status(void *workspace, int32_t *device_status, void *stream);
+
+/* Number of kernels the library has launched in this process (monotonic counter). */
+int64_t tmoe_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TMOE_B200_H_ */

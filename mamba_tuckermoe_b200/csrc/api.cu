@@ -1,0 +1,271 @@
+// extern "C" entry points declared in include/tmoe_b200.h: validation, workspace carving and
+// dispatch between the CUDA-core path and the tcgen05 tensor-core path.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace tmoe {
+
+unsigned long long g_launch_count = 0;
+
+namespace {
+
+struct WsLayout {
+  int64_t idx, gates, c, scores, h, z, total;
+  bool simt_router_fused;  // CUDA-core path: warp-per-token router (else tiled scores + select)
+  bool tc_router_fused;    // tensor-core path: scores and selection inside the in/core kernel
+};
+
+int check_layer(const tmoe_layer_t *L) {
+  if (!L) return TMOE_ERR_NULL;
+  if (L->dtype != TMOE_F32 && L->dtype != TMOE_BF16) return TMOE_ERR_DTYPE;
+  if (L->d_in <= 0 || L->d_out <= 0 || L->n_experts <= 0 || L->top_k <= 0 || L->r1 <= 0 || L->r2 <= 0 || L->r3 <= 0)
+    return TMOE_ERR_SHAPE;
+  if (L->top_k > L->n_experts || L->top_k > TMOE_MAX_TOPK || L->r1 > TMOE_MAX_R1) return TMOE_ERR_SHAPE;
+  if ((L->d_in | L->d_out | L->r2 | L->r3) & 7) return TMOE_ERR_SHAPE;
+  return TMOE_OK;
+}
+
+int resolve(const tmoe_layer_t &L, int64_t T, int path) {
+  if (path == TMOE_PATH_SIMT) return TMOE_PATH_SIMT;
+  const bool covered = tensor_path_covers(L);
+  if (path == TMOE_PATH_TENSOR) return covered ? (int)TMOE_PATH_TENSOR : (int)TMOE_ERR_UNSUPPORTED;
+  if (path != TMOE_PATH_AUTO) return TMOE_ERR_UNSUPPORTED;
+  return (covered && T > 64) ? TMOE_PATH_TENSOR : TMOE_PATH_SIMT;
+}
+
+WsLayout ws_layout(const tmoe_layer_t &L, int64_t T, int rpath) {
+  WsLayout W{};
+  int64_t off = kStatusBytes;
+  auto take = [&](int64_t bytes) { int64_t o = off; off = align_up(off + bytes, 256); return o; };
+  W.idx = take(T * L.top_k * 4);
+  W.gates = take(T * L.top_k * 4);
+  W.c = take(T * L.r1 * 4);
+  W.simt_router_fused = (L.n_experts <= 32) || (T <= 256);
+  W.tc_router_fused = (align_up(L.n_experts, 16) <= 256) && (L.top_k <= 8);
+  if (rpath == TMOE_PATH_SIMT) {
+    W.scores = W.simt_router_fused ? 0 : take(T * L.n_experts * 4);
+    W.h = take(T * L.r3 * 4);
+    W.z = take(T * L.r2 * 4);
+  } else {
+    W.scores = W.tc_router_fused ? 0 : take(T * L.n_experts * 4);
+    W.h = 0;
+    W.z = take(T * L.r2 * 2);
+  }
+  W.total = off;
+  return W;
+}
+
+bool misaligned(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0; }
+
+int check_factors(const tmoe_factors_t *F) {
+  if (!F) return TMOE_ERR_NULL;
+  const void *ps[7] = {F->router_w, F->U_in, F->inner_norm_w, F->U_expert, F->core, F->U_out, F->bias};
+  for (const void *p : ps) {
+    if (!p) return TMOE_ERR_NULL;
+    if (misaligned(p)) return TMOE_ERR_ALIGN;
+  }
+  return TMOE_OK;
+}
+
+int router_simt(const tmoe_layer_t &L, const tmoe_factors_t &F, const void *x, int64_t T, bool fused, float *scores,
+                int32_t *idx, float *gates, float *c, cudaStream_t st) {
+  if (fused) return launch_router_fused(L, x, F.router_w, F.U_expert, T, idx, gates, c, st);
+  int rc = launch_simt_scores(L, x, F.router_w, T, scores, st);
+  if (rc) return rc;
+  return launch_select(L, scores, F.U_expert, T, idx, gates, c, st);
+}
+
+}  // namespace
+}  // namespace tmoe
+
+using namespace tmoe;
+
+extern "C" {
+
+int tmoe_version(void) { return TMOE_ABI_VERSION; }
+
+const char *tmoe_status_string(int status) {
+  switch (status) {
+    case TMOE_OK: return "ok";
+    case TMOE_ERR_NULL: return "a required pointer is NULL";
+    case TMOE_ERR_SHAPE: return "invalid layer shape (sizes must be positive, d_in/d_out/r2/r3 multiples of 8, top_k <= n_experts)";
+    case TMOE_ERR_DTYPE: return "unsupported dtype (fp32 and bf16 only)";
+    case TMOE_ERR_ALIGN: return "a device pointer is not 16-byte aligned";
+    case TMOE_ERR_WORKSPACE: return "workspace or prepared-factor buffer too small";
+    case TMOE_ERR_UNSUPPORTED: return "the requested path does not cover this shape/dtype";
+    case TMOE_ERR_CUDA: return "a CUDA runtime call or kernel launch failed";
+    case TMOE_ERR_DRIVER: return "tensor-map encoding unavailable or failed";
+    case TMOE_ERR_DEVICE_WAIT: return "a bounded wait inside a kernel expired";
+    default: return "unknown status";
+  }
+}
+
+int tmoe_resolve_path(const tmoe_layer_t *layer, int64_t T, int path) {
+  int rc = check_layer(layer);
+  if (rc) return rc;
+  if (T < 0) return TMOE_ERR_SHAPE;
+  return resolve(*layer, T, path);
+}
+
+int64_t tmoe_prepared_bytes(const tmoe_layer_t *layer) {
+  int rc = check_layer(layer);
+  if (rc) return rc;
+  if (!tensor_path_covers(*layer)) return 0;
+  return prepared_layout(*layer).total;
+}
+
+int tmoe_prepare_factors(const tmoe_layer_t *layer, const tmoe_factors_t *factors, void *prepared,
+                         int64_t prepared_bytes, void *stream) {
+  int rc = check_layer(layer);
+  if (rc) return rc;
+  if ((rc = check_factors(factors))) return rc;
+  if (!prepared) return TMOE_ERR_NULL;
+  if (!tensor_path_covers(*layer)) return TMOE_ERR_UNSUPPORTED;
+  if (reinterpret_cast<uintptr_t>(prepared) & 255) return TMOE_ERR_ALIGN;
+  if (prepared_bytes < prepared_layout(*layer).total) return TMOE_ERR_WORKSPACE;
+  return launch_prepare(*layer, *factors, prepared, (cudaStream_t)stream);
+}
+
+int64_t tmoe_workspace_bytes(const tmoe_layer_t *layer, int64_t T, int path) {
+  int rc = check_layer(layer);
+  if (rc) return rc;
+  if (T < 0) return TMOE_ERR_SHAPE;
+  int rp = resolve(*layer, T, path);
+  if (rp < 0) return rp;
+  return ws_layout(*layer, T, rp).total;
+}
+
+int tmoe_router(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const void *x, int64_t T, int32_t *idx,
+                float *gates, float *c, void *workspace, int64_t workspace_bytes, void *stream) {
+  int rc = check_layer(layer);
+  if (rc) return rc;
+  if ((rc = check_factors(factors))) return rc;
+  if (T < 0) return TMOE_ERR_SHAPE;
+  if (T == 0) return TMOE_OK;
+  if (!x || !idx || !gates || !c || !workspace) return TMOE_ERR_NULL;
+  if (misaligned(x) || (reinterpret_cast<uintptr_t>(workspace) & 255)) return TMOE_ERR_ALIGN;
+  WsLayout W = ws_layout(*layer, T, TMOE_PATH_SIMT);
+  if (workspace_bytes < W.total) return TMOE_ERR_WORKSPACE;
+  char *ws = reinterpret_cast<char *>(workspace);
+  return router_simt(*layer, *factors, x, T, W.simt_router_fused, reinterpret_cast<float *>(ws + W.scores), idx, gates,
+                     c, (cudaStream_t)stream);
+}
+
+int tmoe_in_core(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const void *prepared, const void *x,
+                 int64_t T, const float *c, void *z, void *workspace, int64_t workspace_bytes, int path, void *stream) {
+  int rc = check_layer(layer);
+  if (rc) return rc;
+  if ((rc = check_factors(factors))) return rc;
+  if (T < 0) return TMOE_ERR_SHAPE;
+  if (T == 0) return TMOE_OK;
+  if (!x || !c || !z || !workspace) return TMOE_ERR_NULL;
+  if (misaligned(x) || misaligned(z) || misaligned(c) || (reinterpret_cast<uintptr_t>(workspace) & 255)) return TMOE_ERR_ALIGN;
+  int rp = resolve(*layer, T, path);
+  if (rp < 0) return rp;
+  WsLayout W = ws_layout(*layer, T, rp);
+  if (workspace_bytes < W.total) return TMOE_ERR_WORKSPACE;
+  char *ws = reinterpret_cast<char *>(workspace);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (rp == TMOE_PATH_SIMT) {
+    float *h = reinterpret_cast<float *>(ws + W.h);
+    if ((rc = launch_simt_inproj_norm(*layer, x, factors->U_in, factors->inner_norm_w, T, h, st))) return rc;
+    return launch_simt_core(*layer, h, c, factors->core, T, reinterpret_cast<float *>(z), st);
+  }
+  if (!prepared) return TMOE_ERR_NULL;
+  return launch_tc_in_core(*layer, x, prepared, prepared_layout(*layer), T, 0, c, nullptr, nullptr, nullptr, z,
+                           reinterpret_cast<int32_t *>(ws), st);
+}
+
+int tmoe_out(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const void *prepared, const void *z, int64_t T,
+             void *y, const tmoe_extras_t *extras, void *workspace, int64_t workspace_bytes, int path, void *stream) {
+  int rc = check_layer(layer);
+  if (rc) return rc;
+  if ((rc = check_factors(factors))) return rc;
+  if (T < 0) return TMOE_ERR_SHAPE;
+  if (T == 0) return TMOE_OK;
+  if (!z || !y || !workspace) return TMOE_ERR_NULL;
+  if (misaligned(z) || misaligned(y) || (reinterpret_cast<uintptr_t>(workspace) & 255)) return TMOE_ERR_ALIGN;
+  if (workspace_bytes < kStatusBytes) return TMOE_ERR_WORKSPACE;
+  const void *residual = extras ? extras->residual : nullptr;
+  const void *scale = extras ? extras->layer_scale : nullptr;
+  if ((residual == nullptr) != (scale == nullptr)) return TMOE_ERR_NULL;
+  if (residual && (misaligned(residual) || misaligned(scale))) return TMOE_ERR_ALIGN;
+  int rp = resolve(*layer, T, path);
+  if (rp < 0) return rp;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (rp == TMOE_PATH_SIMT)
+    return launch_simt_out(*layer, reinterpret_cast<const float *>(z), factors->U_out, factors->bias, residual, scale, T,
+                           y, st);
+  if (!prepared) return TMOE_ERR_NULL;
+  PreparedLayout P = prepared_layout(*layer);
+  const char *pb = reinterpret_cast<const char *>(prepared);
+  return launch_tc_out(*layer, z, pb + P.uout_t, reinterpret_cast<const float *>(pb + P.bias), residual, scale, T, y,
+                       reinterpret_cast<int32_t *>(workspace), st);
+}
+
+int tmoe_forward(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const void *prepared, const void *x,
+                 int64_t T, void *y, const tmoe_extras_t *extras, void *workspace, int64_t workspace_bytes, int path,
+                 void *stream) {
+  int rc = check_layer(layer);
+  if (rc) return rc;
+  if ((rc = check_factors(factors))) return rc;
+  if (T < 0) return TMOE_ERR_SHAPE;
+  if (T == 0) return TMOE_OK;
+  if (!x || !y || !workspace) return TMOE_ERR_NULL;
+  if (misaligned(x) || misaligned(y) || (reinterpret_cast<uintptr_t>(workspace) & 255)) return TMOE_ERR_ALIGN;
+  const void *residual = extras ? extras->residual : nullptr;
+  const void *scale = extras ? extras->layer_scale : nullptr;
+  if ((residual == nullptr) != (scale == nullptr)) return TMOE_ERR_NULL;
+  if (residual && (misaligned(residual) || misaligned(scale))) return TMOE_ERR_ALIGN;
+  int rp = resolve(*layer, T, path);
+  if (rp < 0) return rp;
+  const tmoe_layer_t &L = *layer;
+  WsLayout W = ws_layout(L, T, rp);
+  if (workspace_bytes < W.total) return TMOE_ERR_WORKSPACE;
+  char *ws = reinterpret_cast<char *>(workspace);
+  cudaStream_t st = (cudaStream_t)stream;
+  int32_t *idx = (extras && extras->idx_out) ? extras->idx_out : reinterpret_cast<int32_t *>(ws + W.idx);
+  float *gates = (extras && extras->gates_out) ? extras->gates_out : reinterpret_cast<float *>(ws + W.gates);
+  float *c = (extras && extras->c_out) ? extras->c_out : reinterpret_cast<float *>(ws + W.c);
+  float *scores = reinterpret_cast<float *>(ws + W.scores);
+
+  if (rp == TMOE_PATH_SIMT) {
+    float *h = reinterpret_cast<float *>(ws + W.h);
+    float *z = reinterpret_cast<float *>(ws + W.z);
+    if ((rc = router_simt(L, *factors, x, T, W.simt_router_fused, scores, idx, gates, c, st))) return rc;
+    if ((rc = launch_simt_inproj_norm(L, x, factors->U_in, factors->inner_norm_w, T, h, st))) return rc;
+    if ((rc = launch_simt_core(L, h, c, factors->core, T, z, st))) return rc;
+    return launch_simt_out(L, z, factors->U_out, factors->bias, residual, scale, T, y, st);
+  }
+  if (!prepared) return TMOE_ERR_NULL;
+  if (reinterpret_cast<uintptr_t>(prepared) & 255) return TMOE_ERR_ALIGN;
+  PreparedLayout P = prepared_layout(L);
+  const char *pb = reinterpret_cast<const char *>(prepared);
+  void *z = ws + W.z;
+  int32_t *status = reinterpret_cast<int32_t *>(ws);
+  if (W.tc_router_fused) {
+    const bool taps = extras && (extras->idx_out || extras->gates_out || extras->c_out);
+    rc = launch_tc_in_core(L, x, prepared, P, T, 1, nullptr, taps ? extras->idx_out : nullptr,
+                           taps ? extras->gates_out : nullptr, taps ? extras->c_out : nullptr, z, status, st);
+  } else {
+    if ((rc = router_simt(L, *factors, x, T, false, scores, idx, gates, c, st))) return rc;
+    rc = launch_tc_in_core(L, x, prepared, P, T, 0, c, nullptr, nullptr, nullptr, z, status, st);
+  }
+  if (rc) return rc;
+  return launch_tc_out(L, z, pb + P.uout_t, reinterpret_cast<const float *>(pb + P.bias), residual, scale, T, y, status,
+                       st);
+}
+
+int tmoe_read_device_status(void *workspace, int32_t *device_status, void *stream) {
+  if (!workspace || !device_status) return TMOE_ERR_NULL;
+  if (cudaStreamSynchronize((cudaStream_t)stream) != cudaSuccess) return TMOE_ERR_CUDA;
+  int32_t words[4] = {0, 0, 0, 0};
+  if (cudaMemcpy(words, workspace, sizeof(words), cudaMemcpyDeviceToHost) != cudaSuccess) return TMOE_ERR_CUDA;
+  for (int i = 0; i < 4; ++i) device_status[i] = words[i];
+  if (words[0] != 0 && cudaMemset(workspace, 0, kStatusBytes) != cudaSuccess) return TMOE_ERR_CUDA;
+  return TMOE_OK;
+}
+
+int64_t tmoe_launch_count(void) { return (int64_t)__atomic_load_n(&g_launch_count, __ATOMIC_RELAXED); }
+
+}  // extern "C"

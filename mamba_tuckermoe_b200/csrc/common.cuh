@@ -1,0 +1,67 @@
+// Shared host/device helpers for the Tucker-MoE kernels (sm_100a).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "tmoe_b200.h"
+
+namespace tmoe {
+
+using bf16 = __nv_bfloat16;
+
+// ---- workspace status words (first 256 bytes of every workspace) -------------------------
+// word 0: 0 or TMOE_ERR_DEVICE_WAIT; word 1: kernel id; word 2: barrier tag; word 3: block id.
+constexpr int kStatusBytes = 256;
+
+// Counts kernel launches made by this library (read through tmoe_launch_count()).
+extern unsigned long long g_launch_count;
+inline void count_launch(int n = 1) { __atomic_fetch_add(&g_launch_count, (unsigned long long)n, __ATOMIC_RELAXED); }
+
+inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
+
+inline int cuda_ok(cudaError_t e) { return e == cudaSuccess ? TMOE_OK : TMOE_ERR_CUDA; }
+
+// Launch check that does not synchronise: picks up launch-configuration errors only.
+inline int launch_status() { return cuda_ok(cudaGetLastError()); }
+
+// ---- element access -----------------------------------------------------------------------
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+// Round an fp32 value to the storage type and back (what the reference's typed tensors do).
+template <typename T> __device__ __forceinline__ float round_to(float v) { return to_f32(from_f32<T>(v)); }
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t *>(&p);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// Order used for expert selection: higher score first, equal scores -> lower index first.
+__device__ __forceinline__ bool ranks_before(float va, int ia, float vb, int ib) {
+  return (va > vb) || (va == vb && ia < ib);
+}
+
+// Softmax over the k selected scores (sorted descending, so sel_v[0] is the maximum), gate
+// rounding to the storage type, and c[a] = sum_j gate_j * U_expert[idx_j, a].
+// Executed redundantly by every lane of a warp (inputs are warp-uniform); lane `a` keeps c[a].
+template <typename T>
+__device__ __forceinline__ void gates_from_selection(const float *sel_v, int k, float *gate) {
+  float m = sel_v[0], den = 0.f;
+  for (int j = 0; j < k; ++j) { gate[j] = __expf(sel_v[j] - m); den += gate[j]; }
+  float inv = 1.f / den;
+  for (int j = 0; j < k; ++j) gate[j] = round_to<T>(gate[j] * inv);
+}
+
+}  // namespace tmoe

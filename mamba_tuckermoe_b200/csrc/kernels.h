@@ -1,0 +1,51 @@
+// Internal launcher declarations shared by the translation units of the library.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "tmoe_b200.h"
+
+namespace tmoe {
+
+// ---- router.cu ----
+int launch_router_fused(const tmoe_layer_t &L, const void *x, const void *wr, const void *uexp, int64_t T,
+                        int32_t *idx, float *gates, float *c, cudaStream_t st);
+int launch_select(const tmoe_layer_t &L, const float *scores, const void *uexp, int64_t T, int32_t *idx,
+                  float *gates, float *c, cudaStream_t st);
+
+// ---- simt_gemm.cu ----
+// scores[T, E] (fp32) = x @ router_w^T
+int launch_simt_scores(const tmoe_layer_t &L, const void *x, const void *wr, int64_t T, float *scores, cudaStream_t st);
+// h[T, r3] (fp32) = x @ U_in, then in-place inner RMSNorm with weight w (layer dtype)
+int launch_simt_inproj_norm(const tmoe_layer_t &L, const void *x, const void *U_in, const void *w, int64_t T, float *h,
+                            cudaStream_t st);
+// z[T, r2] (fp32) = sum_a c[:, a] * (h @ core[a])
+int launch_simt_core(const tmoe_layer_t &L, const float *h, const float *c, const void *core, int64_t T, float *z,
+                     cudaStream_t st);
+// y[T, d_out] (layer dtype) = z @ U_out + bias, optionally residual + layer_scale * (...)
+int launch_simt_out(const tmoe_layer_t &L, const float *z, const void *U_out, const void *bias, const void *residual,
+                    const void *layer_scale, int64_t T, void *y, cudaStream_t st);
+
+// ---- prepare.cu ----
+struct PreparedLayout {
+  int64_t uin_t, wr_b, g_t, uout_t, normw, bias, uexp, total;  // byte offsets
+  int e_pad, n2, n_tiles2;
+};
+bool tensor_path_covers(const tmoe_layer_t &L);
+PreparedLayout prepared_layout(const tmoe_layer_t &L);
+int launch_prepare(const tmoe_layer_t &L, const tmoe_factors_t &F, void *prepared, cudaStream_t st);
+
+// ---- tc_out_gemm.cu ----
+// y[T, N] = z[T, K] (bf16) @ W_t[N, K]^T (bf16, K-major) + bias (fp32) on tcgen05 tensor cores.
+int launch_tc_out(const tmoe_layer_t &L, const void *z, const void *uout_t, const float *bias, const void *residual,
+                  const void *layer_scale, int64_t T, void *y, int32_t *status, cudaStream_t st);
+
+// ---- tc_in_core.cu ----
+// Fused x@U_in (+ router scores) -> RMS statistics -> h@G tiles with c-weighted epilogue -> z bf16.
+// fuse_router != 0: scores/top-k/softmax/c are computed inside (c_in ignored, taps optional);
+// otherwise c_in [T, r1] is read.
+int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared, const PreparedLayout &P, int64_t T,
+                      int fuse_router, const float *c_in, int32_t *idx_out, float *gates_out, float *c_out, void *z,
+                      int32_t *status, cudaStream_t st);
+
+}  // namespace tmoe

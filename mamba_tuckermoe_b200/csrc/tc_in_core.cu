@@ -1,0 +1,357 @@
+// In-projection, router scores, inner RMSNorm statistics and core contraction in one kernel
+// (subsystem 2, with subsystem 1 folded in when the expert count allows):
+//
+//   phase A   acc_h[128, r3]  = x_tile[128, d_in] @ U_in            (model.py:80)
+//             acc_s[128, E]   = x_tile @ router_w^T                 (model.py:75; same A operand)
+//   epilogue A (thread = token row, TMEM -> registers)
+//             top-k on the bf16-rounded scores, softmax over the winners, c = sum g_k U_expert[e_k]
+//             (model.py:76-77, 93); sum of squares of the row of h; h*w -> bf16 -> shared memory in
+//             the K-major 128-byte-swizzled layout the MMA reads; c *= 1/sqrt(mean(h^2)+eps)
+//             (the RMSNorm scale of model.py:25-27 commutes with the linear core contraction, so it
+//             is applied to the r1 coefficients instead of the r3 values of h)
+//   phase B   for every r2 tile j (n2 = 256/r1 columns):
+//             P[128, r1*n2] = h[128, r3] @ G_j   with the r1 core slices of the tile side by side
+//   epilogue B z[t, j*n2 + s] = sum_a c[t,a] * P[t, a*n2 + s]  in registers -> bf16 -> HBM
+//             (model.py:95-98 for all selected experts at once); P is double-buffered in TMEM so
+//             this runs under the next tile's MMAs and the [T, r1*r2] intermediate never leaves the SM.
+//
+// One CTA per 128-token tile, 6 warps: TMA producer, MMA issuer, 4 epilogue warps.
+// Shared memory: phase A uses a ring of {x tile, U_in^T tile, router tile} stages over the whole
+// 224 KB; after the last phase-A MMA has completed, the first 64 KB become h and the rest becomes a
+// 5-stage ring of 32 KB core tiles.  All mbarrier waits are bounded.
+#include "common.cuh"
+#include "kernels.h"
+#include "ptx.cuh"
+
+namespace tmoe {
+
+using namespace ptx;
+
+constexpr int TM = 128;                    // tokens per CTA
+constexpr int X_TILE_BYTES = TM * 64 * 2;  // 16 KB
+constexpr int H_KBLOCK_BYTES = TM * 64 * 2;
+constexpr int H_REGION_BYTES = 4 * H_KBLOCK_BYTES;  // r3 <= 256
+constexpr int G_STAGE_BYTES = 256 * 64 * 2;         // 32 KB
+constexpr int G_STAGES = 5;
+constexpr int IC_RING_BYTES = H_REGION_BYTES + G_STAGES * G_STAGE_BYTES;  // 224 KB
+constexpr int IC_SMEM_BYTES = IC_RING_BYTES + 1024;
+constexpr int A_STAGES_MAX = 4;
+constexpr int SCORE_COL = 256;  // TMEM column of the router scores during phase A
+constexpr int kKernelInCore = 2;
+constexpr int RK = 8;  // capacity of the in-kernel top-k list
+
+struct InCoreParams {
+  int64_t T;
+  int d_in, r3, r2, E, e_pad, top_k, n_tiles2;
+  float eps;
+  int fuse_router;
+  const float *normw;  // [r3]
+  const float *uexp;   // [E, r1] fp32
+  const float *c_in;   // [T, r1] when !fuse_router
+  int32_t *idx_out;
+  float *gates_out;
+  float *c_out;
+  bf16 *z;  // [T, r2]
+  int32_t *status;
+};
+
+template <int R1>
+__global__ void __launch_bounds__(192, 1)
+tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmU,
+                  const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmG, InCoreParams p) {
+  constexpr int N2 = 256 / R1;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_fullA[A_STAGES_MAX], bar_emptyA[A_STAGES_MAX], bar_fullB[G_STAGES],
+      bar_emptyB[G_STAGES], bar_accA, bar_hready, bar_pfull[2], bar_pempty[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ float wnorm_s[256];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int m0 = blockIdx.x * TM;
+
+  const int u_bytes = p.r3 * 128, w_bytes = p.e_pad * 128;
+  const int stageA_bytes = X_TILE_BYTES + u_bytes + w_bytes;
+  int nA = IC_RING_BYTES / stageA_bytes;
+  nA = nA > A_STAGES_MAX ? A_STAGES_MAX : nA;
+  const int KA = p.d_in / 64;
+  const int KH = p.r3 / 64;
+
+  for (int i = threadIdx.x; i < p.r3; i += blockDim.x) wnorm_s[i] = p.normw[i];
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < A_STAGES_MAX; ++s) { mbar_init(smem_u32(&bar_fullA[s]), 1); mbar_init(smem_u32(&bar_emptyA[s]), 1); }
+    for (int s = 0; s < G_STAGES; ++s) { mbar_init(smem_u32(&bar_fullB[s]), 1); mbar_init(smem_u32(&bar_emptyB[s]), 1); }
+    mbar_init(smem_u32(&bar_accA), 1);
+    mbar_init(smem_u32(&bar_hready), 4);
+    for (int s = 0; s < 2; ++s) { mbar_init(smem_u32(&bar_pfull[s]), 1); mbar_init(smem_u32(&bar_pempty[s]), 4); }
+    fence_mbar_init();
+    prefetch_tmap(&tmX); prefetch_tmap(&tmU); prefetch_tmap(&tmG);
+    if (p.e_pad) prefetch_tmap(&tmW);
+  }
+  if (warp == 1) { tmem_alloc(smem_u32(&tmem_base_s), 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+  const uint32_t ringB = ring + H_REGION_BYTES;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer -------------------------------
+    if (lane == 0) {
+      bool ok = true;
+      for (int kb = 0; kb < KA && ok; ++kb) {
+        const uint32_t s = kb % nA, ph = (kb / nA) & 1;
+        if (!(ok = mbar_wait(smem_u32(&bar_emptyA[s]), ph ^ 1, p.status, kKernelInCore, 2))) break;
+        const uint32_t full = smem_u32(&bar_fullA[s]);
+        mbar_arrive_expect_tx(full, stageA_bytes);
+        const uint32_t sa = ring + s * stageA_bytes;
+        tma_load_2d(sa, &tmX, kb * 64, m0, full);
+        tma_load_2d(sa + X_TILE_BYTES, &tmU, kb * 64, 0, full);
+        if (p.e_pad) tma_load_2d(sa + X_TILE_BYTES + u_bytes, &tmW, kb * 64, 0, full);
+      }
+      // ring A aliases h and the core-tile ring: wait until every phase-A MMA has retired
+      if (ok) ok = mbar_wait(smem_u32(&bar_accA), 0, p.status, kKernelInCore, 3);
+      const int total = p.n_tiles2 * KH;
+      for (int it = 0; it < total && ok; ++it) {
+        const uint32_t s = it % G_STAGES, ph = (it / G_STAGES) & 1;
+        const int j = it / KH, kb = it - j * KH;
+        if (!(ok = mbar_wait(smem_u32(&bar_emptyB[s]), ph ^ 1, p.status, kKernelInCore, 6))) break;
+        const uint32_t full = smem_u32(&bar_fullB[s]);
+        mbar_arrive_expect_tx(full, G_STAGE_BYTES);
+        tma_load_2d(ringB + s * G_STAGE_BYTES, &tmG, kb * 64, j * 256, full);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -------------------------------
+    if (lane == 0) {
+      bool ok = true;
+      const uint32_t idescH = umma_idesc_bf16(TM, p.r3);
+      const uint32_t idescS = umma_idesc_bf16(TM, p.e_pad ? p.e_pad : 16);
+      for (int kb = 0; kb < KA && ok; ++kb) {
+        const uint32_t s = kb % nA, ph = (kb / nA) & 1;
+        if (!(ok = mbar_wait(smem_u32(&bar_fullA[s]), ph, p.status, kKernelInCore, 1))) break;
+        tc_fence_after();
+        const uint32_t sa = ring + s * stageA_bytes;
+        const uint64_t dx = umma_desc_k_sw128(sa), du = umma_desc_k_sw128(sa + X_TILE_BYTES),
+                       dw = umma_desc_k_sw128(sa + X_TILE_BYTES + u_bytes);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          umma_bf16(tmem_base, dx + 2 * k, du + 2 * k, idescH, (kb | k) != 0);
+          if (p.e_pad) umma_bf16(tmem_base + SCORE_COL, dx + 2 * k, dw + 2 * k, idescS, (kb | k) != 0);
+        }
+        umma_commit(smem_u32(&bar_emptyA[s]));
+      }
+      if (ok) umma_commit(smem_u32(&bar_accA));
+      if (ok) ok = mbar_wait(smem_u32(&bar_hready), 0, p.status, kKernelInCore, 4);
+      tc_fence_after();
+      const uint32_t idescP = umma_idesc_bf16(TM, 256);
+      int it = 0;
+      for (int j = 0; j < p.n_tiles2 && ok; ++j) {
+        const uint32_t slot = j & 1, pph = (j >> 1) & 1;
+        if (!(ok = mbar_wait(smem_u32(&bar_pempty[slot]), pph ^ 1, p.status, kKernelInCore, 8))) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + slot * 256;
+        for (int kb = 0; kb < KH; ++kb, ++it) {
+          const uint32_t s = it % G_STAGES, ph = (it / G_STAGES) & 1;
+          if (!(ok = mbar_wait(smem_u32(&bar_fullB[s]), ph, p.status, kKernelInCore, 5))) break;
+          tc_fence_after();
+          const uint64_t dh = umma_desc_k_sw128(ring + kb * H_KBLOCK_BYTES);
+          const uint64_t dg = umma_desc_k_sw128(ringB + s * G_STAGE_BYTES);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) umma_bf16(d_tmem, dh + 2 * k, dg + 2 * k, idescP, (kb | k) != 0);
+          umma_commit(smem_u32(&bar_emptyB[s]));
+        }
+        if (ok) umma_commit(smem_u32(&bar_pfull[slot]));
+      }
+    }
+  } else {
+    // ------------------------------- epilogue warps -------------------------------
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const int64_t grow = (int64_t)m0 + row;
+    const bool live = grow < p.T;
+    const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
+    float c[R1];
+    bool ok = mbar_wait(smem_u32(&bar_accA), 0, p.status, kKernelInCore, 3);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      tc_fence_after();
+      if (p.fuse_router) {
+        // running top-k over the score columns; scores are rounded to bf16 before comparison
+        float sv[RK]; int si[RK];
+#pragma unroll
+        for (int j = 0; j < RK; ++j) { sv[j] = -INFINITY; si[j] = 0x7fffffff; }
+        for (int cc = 0; cc < p.e_pad / 16; ++cc) {
+          uint32_t r[16];
+          tmem_ld16(t_lane + SCORE_COL + cc * 16, r);
+          tmem_ld_wait(r);
+#pragma unroll
+          for (int q = 0; q < 16; ++q) {
+            const int e = cc * 16 + q;
+            if (e < p.E) {
+              float cv = round_to<bf16>(__uint_as_float(r[q])); int ci = e;
+#pragma unroll
+              for (int j = 0; j < RK; ++j) {
+                if (j < p.top_k && ranks_before(cv, ci, sv[j], si[j])) {
+                  const float tv = sv[j]; const int ti = si[j];
+                  sv[j] = cv; si[j] = ci; cv = tv; ci = ti;
+                }
+              }
+            }
+          }
+        }
+        float gate[RK], den = 0.f;
+#pragma unroll
+        for (int j = 0; j < RK; ++j) { gate[j] = (j < p.top_k) ? expf(sv[j] - sv[0]) : 0.f; den += gate[j]; }
+        const float inv = 1.f / den;
+#pragma unroll
+        for (int a = 0; a < R1; ++a) c[a] = 0.f;
+#pragma unroll
+        for (int j = 0; j < RK; ++j) {
+          if (j < p.top_k) {
+            gate[j] = round_to<bf16>(gate[j] * inv);
+            const int e = min(max(si[j], 0), p.E - 1);
+#pragma unroll
+            for (int a = 0; a < R1; ++a) c[a] = fmaf(gate[j], __ldg(p.uexp + e * R1 + a), c[a]);
+            if (live) {
+              if (p.idx_out) p.idx_out[grow * p.top_k + j] = si[j];
+              if (p.gates_out) p.gates_out[grow * p.top_k + j] = gate[j];
+            }
+          }
+        }
+        if (live && p.c_out) {
+#pragma unroll
+          for (int a = 0; a < R1; ++a) p.c_out[grow * R1 + a] = c[a];
+        }
+      } else {
+#pragma unroll
+        for (int a = 0; a < R1; ++a) c[a] = live ? __ldg(p.c_in + grow * R1 + a) : 0.f;
+      }
+      // h row: statistics, weight, bf16, swizzled store (16-byte chunk index XOR row%8 inside 128-byte rows)
+      float ss = 0.f;
+      for (int cc = 0; cc < p.r3 / 32; ++cc) {
+        uint32_t r[32];
+        tmem_ld32(t_lane + cc * 32, r);
+        tmem_ld_wait(r);
+        const uint32_t kblk_base = ring + (cc >> 1) * H_KBLOCK_BYTES + row * 128;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          float v[8];
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const float a = __uint_as_float(r[g * 8 + q]);
+            ss = fmaf(a, a, ss);
+            v[q] = a * wnorm_s[cc * 32 + g * 8 + q];
+          }
+          const uint32_t chunk = (uint32_t)((cc & 1) * 4 + g) ^ (uint32_t)(row & 7);
+          const uint32_t addr = kblk_base + chunk * 16;
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pack_bf16x2(v[0], v[1])),
+                       "r"(pack_bf16x2(v[2], v[3])), "r"(pack_bf16x2(v[4], v[5])), "r"(pack_bf16x2(v[6], v[7]))
+                       : "memory");
+        }
+      }
+      const float inv_rms = 1.f / sqrtf(ss / (float)p.r3 + p.eps);
+#pragma unroll
+      for (int a = 0; a < R1; ++a) c[a] *= inv_rms;
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_hready));
+
+      // epilogue B
+      for (int j = 0; j < p.n_tiles2 && ok; ++j) {
+        const uint32_t slot = j & 1, pph = (j >> 1) & 1;
+        ok = mbar_wait(smem_u32(&bar_pfull[slot]), pph, p.status, kKernelInCore, 7);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t t_p = t_lane + slot * 256;
+#pragma unroll 1
+        for (int sc = 0; sc < N2 / 16; ++sc) {
+          float acc[16];
+#pragma unroll
+          for (int q = 0; q < 16; ++q) acc[q] = 0.f;
+#pragma unroll
+          for (int a = 0; a < R1; a += 2) {
+            uint32_t r0[16], r1v[16];
+            tmem_ld16(t_p + a * N2 + sc * 16, r0);
+            tmem_ld16(t_p + (a + 1) * N2 + sc * 16, r1v);
+            tmem_ld_wait(r0, r1v);
+#pragma unroll
+            for (int q = 0; q < 16; ++q) {
+              acc[q] = fmaf(c[a], __uint_as_float(r0[q]), acc[q]);
+              acc[q] = fmaf(c[a + 1], __uint_as_float(r1v[q]), acc[q]);
+            }
+          }
+          if (live) {
+            bf16 *dst = p.z + grow * p.r2 + (int64_t)j * N2 + sc * 16;
+            uint4 o0, o1;
+            o0.x = pack_bf16x2(acc[0], acc[1]); o0.y = pack_bf16x2(acc[2], acc[3]);
+            o0.z = pack_bf16x2(acc[4], acc[5]); o0.w = pack_bf16x2(acc[6], acc[7]);
+            o1.x = pack_bf16x2(acc[8], acc[9]); o1.y = pack_bf16x2(acc[10], acc[11]);
+            o1.z = pack_bf16x2(acc[12], acc[13]); o1.w = pack_bf16x2(acc[14], acc[15]);
+            *reinterpret_cast<uint4 *>(dst) = o0;
+            *reinterpret_cast<uint4 *>(dst + 8) = o1;
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_pempty[slot]));
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared, const PreparedLayout &P, int64_t T_,
+                      int fuse_router, const float *c_in, int32_t *idx_out, float *gates_out, float *c_out, void *z,
+                      int32_t *status, cudaStream_t st) {
+  const char *base = reinterpret_cast<const char *>(prepared);
+  if (fuse_router && (P.e_pad > 256 || L.top_k > RK)) return TMOE_ERR_UNSUPPORTED;
+  if (!fuse_router && !c_in) return TMOE_ERR_NULL;
+  CUtensorMap tmX, tmU, tmW, tmG;
+  int rc = encode_tmap_bf16_2d(&tmX, x, (uint64_t)T_, (uint64_t)L.d_in, TM);
+  if (rc) return rc;
+  rc = encode_tmap_bf16_2d(&tmU, base + P.uin_t, (uint64_t)L.r3, (uint64_t)L.d_in, (uint32_t)L.r3);
+  if (rc) return rc;
+  // the router tile is only loaded when the scores are computed in-kernel (e_pad <= 256 checked above)
+  rc = encode_tmap_bf16_2d(&tmW, base + P.wr_b, (uint64_t)P.e_pad, (uint64_t)L.d_in,
+                           fuse_router ? (uint32_t)P.e_pad : 16u);
+  if (rc) return rc;
+  rc = encode_tmap_bf16_2d(&tmG, base + P.g_t, (uint64_t)L.r1 * L.r2, (uint64_t)L.r3, 256);
+  if (rc) return rc;
+
+  InCoreParams p{};
+  p.T = T_; p.d_in = L.d_in; p.r3 = L.r3; p.r2 = L.r2; p.E = L.n_experts; p.top_k = L.top_k;
+  p.e_pad = fuse_router ? P.e_pad : 0;
+  p.n_tiles2 = P.n_tiles2; p.eps = L.eps; p.fuse_router = fuse_router;
+  p.normw = reinterpret_cast<const float *>(base + P.normw);
+  p.uexp = reinterpret_cast<const float *>(base + P.uexp);
+  p.c_in = c_in; p.idx_out = idx_out; p.gates_out = gates_out; p.c_out = c_out;
+  p.z = (bf16 *)z; p.status = status;
+  if (X_TILE_BYTES + p.r3 * 128 + p.e_pad * 128 > IC_RING_BYTES) return TMOE_ERR_UNSUPPORTED;
+
+  const unsigned grid = (unsigned)((T_ + TM - 1) / TM);
+  cudaError_t e = cudaSuccess;
+#define TMOE_IC(R)                                                                                              \
+  do {                                                                                                          \
+    e = cudaFuncSetAttribute(tc_in_core_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, IC_SMEM_BYTES); \
+    if (e == cudaSuccess) tc_in_core_kernel<R><<<grid, 192, IC_SMEM_BYTES, st>>>(tmX, tmU, tmW, tmG, p);         \
+  } while (0)
+  if (L.r1 == 2) TMOE_IC(2);
+  else if (L.r1 == 4) TMOE_IC(4);
+  else if (L.r1 == 8) TMOE_IC(8);
+  else return TMOE_ERR_UNSUPPORTED;
+#undef TMOE_IC
+  if (e != cudaSuccess) return TMOE_ERR_CUDA;
+  count_launch();
+  return launch_status();
+}
+
+}  // namespace tmoe

@@ -1,0 +1,230 @@
+// Out-projection on the 5th-generation tensor cores (subsystem 3):
+//   y[T, d_out] = z[T, r2] @ U_out + bias                  (pure_torch_mlx/model.py:101)
+//   optionally   y = residual + layer_scale * (...)         (model.py:260, 341)
+//
+// Persistent warp-specialised kernel, one CTA per SM:
+//   warp 0   TMA producer: {64 x 128} tiles of z and {64 x 256} tiles of U_out^T (K-major bf16,
+//            128-byte swizzle) into a 4-stage shared-memory ring, mbarrier complete_tx.
+//   warp 1   one elected thread issues tcgen05.mma (128 x 256 x 16, bf16 -> fp32) into one of two
+//            256-column TMEM accumulators and commits stage-free / accumulator-full barriers.
+//   warps 2-5 epilogue: tcgen05.ld of the accumulator (thread = output row), bias / residual /
+//            layer-scale in fp32, bf16 pack, 16-byte global stores; runs under the next tile's MMAs.
+// Every mbarrier wait is bounded and reports through the workspace status words.
+#include "common.cuh"
+#include "kernels.h"
+#include "ptx.cuh"
+
+namespace tmoe {
+
+using namespace ptx;
+
+// ------------------------------------------------------------------------------------------
+// Tensor-map encoding through the driver entry point (no link-time dependency on libcuda).
+// ------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) return nullptr;
+    if (q != cudaDriverEntryPointSuccess) return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+int encode_tmap_bf16_2d(CUtensorMap *out, const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return TMOE_ERR_DRIVER;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (cols % 8) || box_rows == 0 || box_rows > 256) return TMOE_ERR_ALIGN;
+  cuuint64_t gdim[2] = {cols, rows};
+  cuuint64_t gstride[1] = {cols * 2};
+  cuuint32_t box[2] = {64, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? TMOE_OK : TMOE_ERR_DRIVER;
+}
+
+// ------------------------------------------------------------------------------------------
+constexpr int OM = 128, ON = 256, OKB = 64, OSTAGES = 4;
+constexpr int O_A_BYTES = OM * OKB * 2;   // 16 KB
+constexpr int O_B_BYTES = ON * OKB * 2;   // 32 KB
+constexpr int O_STAGE_BYTES = O_A_BYTES + O_B_BYTES;
+constexpr int O_SMEM_BYTES = OSTAGES * O_STAGE_BYTES + 1024;
+constexpr int kKernelOut = 3;
+
+struct OutParams {
+  bf16 *y;
+  const float *bias;
+  const bf16 *residual;
+  const bf16 *gamma;
+  int64_t T;
+  int N, K;
+  int num_m, num_n;
+  int32_t *status;
+};
+
+__global__ void __launch_bounds__(192, 1)
+tc_out_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, OutParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[OSTAGES], bar_empty[OSTAGES], bar_tfull[2], bar_tempty[2];
+  __shared__ uint32_t tmem_base_s;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < OSTAGES; ++s) { mbar_init(smem_u32(&bar_full[s]), 1); mbar_init(smem_u32(&bar_empty[s]), 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(smem_u32(&bar_tfull[s]), 1); mbar_init(smem_u32(&bar_tempty[s]), 4); }
+    fence_mbar_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+  }
+  if (warp == 1) { tmem_alloc(smem_u32(&tmem_base_s), 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+
+  const int num_tiles = p.num_m * p.num_n;
+  const int KB = (p.K + OKB - 1) / OKB;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile / p.num_n) * OM, n0 = (tile % p.num_n) * ON;
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const uint32_t s = it % OSTAGES, ph = (it / OSTAGES) & 1;
+          if (!(ok = mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1, p.status, kKernelOut, 2))) break;
+          const uint32_t full = smem_u32(&bar_full[s]);
+          mbar_arrive_expect_tx(full, O_STAGE_BYTES);
+          const uint32_t sa = ring + s * O_STAGE_BYTES;
+          tma_load_2d(sa, &tmA, kb * OKB, m0, full);
+          tma_load_2d(sa + O_A_BYTES, &tmB, kb * OKB, n0, full);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_bf16(OM, ON);
+      uint32_t it = 0, tcount = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+        const uint32_t slot = tcount & 1, aph = (tcount >> 1) & 1;
+        if (!(ok = mbar_wait(smem_u32(&bar_tempty[slot]), aph ^ 1, p.status, kKernelOut, 4))) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + slot * ON;
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const uint32_t s = it % OSTAGES, ph = (it / OSTAGES) & 1;
+          if (!(ok = mbar_wait(smem_u32(&bar_full[s]), ph, p.status, kKernelOut, 1))) break;
+          tc_fence_after();
+          const uint32_t sa = ring + s * O_STAGE_BYTES;
+          const uint64_t da = umma_desc_k_sw128(sa), db = umma_desc_k_sw128(sa + O_A_BYTES);
+#pragma unroll
+          for (int k = 0; k < OKB / 16; ++k)  // +32 bytes (= 2 in >>4 units) per 16-element K step
+            umma_bf16(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+          umma_commit(smem_u32(&bar_empty[s]));
+        }
+        if (ok) umma_commit(smem_u32(&bar_tfull[slot]));
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int row_in_tile = quad * 32 + lane;
+    uint32_t tcount = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+      const int m0 = (tile / p.num_n) * OM, n0 = (tile % p.num_n) * ON;
+      const uint32_t slot = tcount & 1, aph = (tcount >> 1) & 1;
+      ok = mbar_wait(smem_u32(&bar_tfull[slot]), aph, p.status, kKernelOut, 3);
+      ok = __all_sync(0xffffffffu, ok);  // the TMEM loads below are warp-collective
+      if (!ok) break;
+      tc_fence_after();
+      const int64_t row = (int64_t)m0 + row_in_tile;
+      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + slot * ON;
+#pragma unroll 1
+      for (int cc = 0; cc < ON / 32; ++cc) {
+        uint32_t r[32];
+        tmem_ld32(t_row + cc * 32, r);
+        tmem_ld_wait(r);
+        const int col0 = n0 + cc * 32;
+        if (row < p.T) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int col = col0 + g * 8;
+            if (col < p.N) {  // N % 8 == 0, so a group of 8 is entirely in or out
+              float v[8];
+#pragma unroll
+              for (int q = 0; q < 8; ++q) v[q] = __uint_as_float(r[g * 8 + q]);
+              const float4 b0 = __ldg(reinterpret_cast<const float4 *>(p.bias + col));
+              const float4 b1 = __ldg(reinterpret_cast<const float4 *>(p.bias + col + 4));
+              v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+              v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+              if (p.residual) {
+                const uint4 rr = __ldg(reinterpret_cast<const uint4 *>(p.residual + row * p.N + col));
+                const uint4 gg = __ldg(reinterpret_cast<const uint4 *>(p.gamma + col));
+                const uint32_t rw[4] = {rr.x, rr.y, rr.z, rr.w}, gw[4] = {gg.x, gg.y, gg.z, gg.w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  v[2 * q] = __uint_as_float(rw[q] << 16) + __uint_as_float(gw[q] << 16) * v[2 * q];
+                  v[2 * q + 1] = __uint_as_float(rw[q] & 0xffff0000u) + __uint_as_float(gw[q] & 0xffff0000u) * v[2 * q + 1];
+                }
+              }
+              uint4 o;
+              o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
+              o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
+              *reinterpret_cast<uint4 *>(p.y + row * p.N + col) = o;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[slot]));
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+int launch_tc_out(const tmoe_layer_t &L, const void *z, const void *uout_t, const float *bias, const void *residual,
+                  const void *layer_scale, int64_t T_, void *y, int32_t *status, cudaStream_t st) {
+  CUtensorMap tmA, tmB;
+  int rc = encode_tmap_bf16_2d(&tmA, z, (uint64_t)T_, (uint64_t)L.r2, OM);
+  if (rc) return rc;
+  rc = encode_tmap_bf16_2d(&tmB, uout_t, (uint64_t)L.d_out, (uint64_t)L.r2, ON);
+  if (rc) return rc;
+  static bool attr_done[64] = {};
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return TMOE_ERR_CUDA;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return TMOE_ERR_CUDA;
+  if (dev < 64 && !attr_done[dev]) {
+    if (cudaFuncSetAttribute(tc_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, O_SMEM_BYTES) != cudaSuccess)
+      return TMOE_ERR_CUDA;
+    attr_done[dev] = true;
+  }
+  OutParams p{};
+  p.y = (bf16 *)y; p.bias = bias; p.residual = (const bf16 *)residual; p.gamma = (const bf16 *)layer_scale;
+  p.T = T_; p.N = L.d_out; p.K = L.r2;
+  p.num_m = (int)((T_ + OM - 1) / OM); p.num_n = (L.d_out + ON - 1) / ON;
+  p.status = status;
+  const int tiles = p.num_m * p.num_n;
+  const int grid = tiles < sms ? tiles : sms;
+  tc_out_kernel<<<grid, 192, O_SMEM_BYTES, st>>>(tmA, tmB, p);
+  count_launch();
+  return launch_status();
+}
+
+}  // namespace tmoe

@@ -1,0 +1,271 @@
+"""Drop-in replacement for the reference ``TuckerMoE`` layer, forward only, on B200.
+
+Mirrors ``pure_torch_mlx/model.py:41-102``: same constructor ``TuckerMoE(d_in, d_out, cfg)``,
+same parameter names and shapes (so ``state_dict`` keys and the checkpoint loader of
+``pure_torch_mlx/weights.py:74-81`` work unchanged), same ``forward(x: (..., d_in)) -> (..., d_out)``
+and the public ``top_k`` attribute.  ``forward`` calls the torch custom op
+``tmoe_b200::forward`` which hands raw device pointers and the current CUDA stream to the
+C-ABI library; there is no PyTorch or CPU fallback for the computation.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import threading
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+import torch.nn as nn
+
+from . import _lib
+from ._lib import PATH_AUTO, PATH_SIMT, PATH_TENSOR, Extras, Factors, Layer
+
+__all__ = ["TuckerMoE", "TuckerMoEConfig", "RMSNorm", "tucker_moe_forward", "tucker_moe_forward_taps",
+           "PATH_AUTO", "PATH_SIMT", "PATH_TENSOR"]
+
+
+@dataclass
+class TuckerMoEConfig:
+    """The six fields of the reference ``Mamba3Config`` that the layer reads
+    (``pure_torch_mlx/config.py:18-24``, read at ``model.py:56-58,62``), with its defaults.
+    Any object with these attributes (the reference dataclass itself included) is accepted."""
+    kmoe_num_experts: int = 8
+    kmoe_top_k: int = 2
+    kmoe_r1: int = 32
+    kmoe_r2: int = 512
+    kmoe_r3: int = 256
+    rms_norm_eps: float = 1e-5
+
+
+class RMSNorm(nn.Module):
+    """Parameter holder with the reference's attribute names (``model.py:19-27``).  Its forward
+    is only used outside the fused layer (the layer applies the norm inside its kernels)."""
+
+    def __init__(self, dim: int, eps: float = 1e-5):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(dim))
+        self.eps = eps
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        rms = x.pow(2).mean(-1, keepdim=True).add(self.eps).sqrt()
+        return (x / rms) * self.weight
+
+
+_DTYPES = {torch.float32: _lib.TMOE_F32, torch.bfloat16: _lib.TMOE_BF16}
+
+# ------------------------------------------------------------------------------------------
+# per-(device, stream) scratch and per-parameter-set prepared factors
+# ------------------------------------------------------------------------------------------
+_cache_lock = threading.Lock()
+_workspaces = {}   # (device index, stream handle) -> uint8 tensor
+_prepared = {}     # key of the seven parameter tensors -> uint8 tensor
+
+
+def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    with _cache_lock:
+        ws = _workspaces.get(key)
+        if ws is None or ws.numel() < nbytes:
+            # grow geometrically; zero so that the status words start clear
+            ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+            _workspaces[key] = ws
+    return ws
+
+
+def _param_key(tensors) -> tuple:
+    return tuple((t.data_ptr(), t._version, t.dtype, tuple(t.shape)) for t in tensors)
+
+
+def clear_caches() -> None:
+    """Drops cached workspaces and prepared factor sets (e.g. after in-place ``.data`` writes to
+    parameters, which do not bump tensor versions)."""
+    with _cache_lock:
+        _workspaces.clear()
+        _prepared.clear()
+
+
+def _layer_struct(x, router_w, U_in, U_expert, core, U_out, top_k, eps) -> Layer:
+    r1, r3, r2 = core.shape
+    return Layer(int(U_in.shape[0]), int(U_out.shape[1]), int(router_w.shape[0]), int(top_k), int(r1), int(r2),
+                 int(r3), _DTYPES[x.dtype], float(eps))
+
+
+def _validate(x, params, top_k):
+    router_w, U_in, inner_norm_w, U_expert, core, U_out, bias = params
+    if not x.is_cuda:
+        raise RuntimeError("tmoe_b200: the layer forward runs on CUDA tensors only (no CPU fallback)")
+    if x.dtype not in _DTYPES:
+        raise RuntimeError(f"tmoe_b200: unsupported dtype {x.dtype} (float32 and bfloat16 only)")
+    for name, t in zip(("router.weight", "U_in", "inner_norm.weight", "U_expert", "core", "U_out", "bias"), params):
+        if t.device != x.device or t.dtype != x.dtype:
+            raise RuntimeError(f"tmoe_b200: parameter {name} is {t.dtype} on {t.device}, x is {x.dtype} on {x.device}")
+    E, d_in = router_w.shape
+    r1, r3, r2 = core.shape
+    if x.shape[-1] != d_in or U_in.shape != (d_in, r3) or inner_norm_w.shape != (r3,) or \
+            U_expert.shape != (E, r1) or U_out.shape[0] != r2 or bias.shape != (U_out.shape[1],):
+        raise RuntimeError("tmoe_b200: parameter shapes are inconsistent with TuckerMoE's layout")
+    if not 0 < top_k <= E:
+        raise RuntimeError(f"tmoe_b200: top_k={top_k} must be in 1..{E}")
+
+
+def _run(x, router_w, U_in, inner_norm_w, eps, U_expert, core, U_out, bias, top_k, path,
+         residual=None, layer_scale=None, want_taps=False):
+    params = (router_w, U_in, inner_norm_w, U_expert, core, U_out, bias)
+    _validate(x, params, top_k)
+    lib = _lib.load()
+    d_in = x.shape[-1]
+    d_out = U_out.shape[1]
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, d_in)
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    T = x2.shape[0]
+    dev = x.device
+    y = torch.empty((T, d_out), dtype=x.dtype, device=dev)
+    taps = None
+    if T == 0:
+        if want_taps:
+            taps = (torch.empty((0, top_k), dtype=torch.int32, device=dev),
+                    torch.empty((0, top_k), dtype=torch.float32, device=dev),
+                    torch.empty((0, core.shape[0]), dtype=torch.float32, device=dev))
+        return y.reshape(*lead, d_out), taps
+    params = tuple(p if p.is_contiguous() else p.contiguous() for p in params)
+    router_w, U_in, inner_norm_w, U_expert, core, U_out, bias = params
+    layer = _layer_struct(x, router_w, U_in, U_expert, core, U_out, top_k, eps)
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        rpath = _lib.check(lib.tmoe_resolve_path(C.byref(layer), T, path), "tmoe_resolve_path")
+        factors = Factors(*[p.data_ptr() for p in params])
+        prepared_ptr = None
+        if rpath == PATH_TENSOR:
+            key = _param_key(params)
+            with _cache_lock:
+                prep = _prepared.get(key)
+            if prep is None or os.environ.get("TMOE_ALWAYS_PREPARE") == "1":
+                nbytes = _lib.check(lib.tmoe_prepared_bytes(C.byref(layer)), "tmoe_prepared_bytes")
+                prep = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+                _lib.check(lib.tmoe_prepare_factors(C.byref(layer), C.byref(factors), prep.data_ptr(), nbytes, stream),
+                           "tmoe_prepare_factors")
+                with _cache_lock:
+                    if len(_prepared) > 256:
+                        _prepared.clear()
+                    _prepared[key] = prep
+            prepared_ptr = prep.data_ptr()
+        ws_bytes = _lib.check(lib.tmoe_workspace_bytes(C.byref(layer), T, rpath), "tmoe_workspace_bytes")
+        ws = _workspace(dev, ws_bytes)
+        extras = Extras()
+        keep = []
+        if residual is not None:
+            res2 = residual.reshape(-1, d_out).contiguous()
+            ls = layer_scale.contiguous()
+            if res2.shape[0] != T or res2.dtype != x.dtype or ls.dtype != x.dtype or ls.shape != (d_out,):
+                raise RuntimeError("tmoe_b200: residual must be (..., d_out) and layer_scale (d_out,) in x's dtype")
+            extras.residual, extras.layer_scale = res2.data_ptr(), ls.data_ptr()
+            keep += [res2, ls]
+        if want_taps:
+            taps = (torch.empty((T, top_k), dtype=torch.int32, device=dev),
+                    torch.empty((T, top_k), dtype=torch.float32, device=dev),
+                    torch.empty((T, core.shape[0]), dtype=torch.float32, device=dev))
+            extras.idx_out, extras.gates_out, extras.c_out = (t.data_ptr() for t in taps)
+        _lib.check(lib.tmoe_forward(C.byref(layer), C.byref(factors), prepared_ptr, x2.data_ptr(), T, y.data_ptr(),
+                                    C.byref(extras), ws.data_ptr(), ws.numel(), rpath, stream), "tmoe_forward")
+    return y.reshape(*lead, d_out), taps
+
+
+def read_device_status(device=None) -> Tuple[int, int, int, int]:
+    """Synchronises the current stream and returns the four status words of its workspace
+    (all zero unless a bounded wait inside a kernel expired)."""
+    lib = _lib.load()
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    key = (dev.index, torch.cuda.current_stream(dev).cuda_stream)
+    with _cache_lock:
+        ws = _workspaces.get(key)
+    if ws is None:
+        return (0, 0, 0, 0)
+    out = (C.c_int32 * 4)()
+    with torch.cuda.device(dev):
+        _lib.check(lib.tmoe_read_device_status(ws.data_ptr(), out, key[1]), "tmoe_read_device_status")
+    return tuple(int(v) for v in out)
+
+
+# ------------------------------------------------------------------------------------------
+# torch custom op
+# ------------------------------------------------------------------------------------------
+@torch.library.custom_op("tmoe_b200::forward", mutates_args=())
+def _forward_op(x: torch.Tensor, router_w: torch.Tensor, U_in: torch.Tensor, inner_norm_w: torch.Tensor, eps: float,
+                U_expert: torch.Tensor, core: torch.Tensor, U_out: torch.Tensor, bias: torch.Tensor, top_k: int,
+                path: int, residual: Optional[torch.Tensor], layer_scale: Optional[torch.Tensor]) -> torch.Tensor:
+    y, _ = _run(x, router_w, U_in, inner_norm_w, eps, U_expert, core, U_out, bias, top_k, path, residual, layer_scale)
+    return y
+
+
+@_forward_op.register_fake
+def _(x, router_w, U_in, inner_norm_w, eps, U_expert, core, U_out, bias, top_k, path, residual, layer_scale):
+    return x.new_empty((*x.shape[:-1], U_out.shape[1]))
+
+
+def tucker_moe_forward(x, router_w, U_in, inner_norm_w, eps, U_expert, core, U_out, bias, top_k, *, path=PATH_AUTO,
+                       residual=None, layer_scale=None):
+    """Functional form of the layer (parameter order of ``pure_torch_mlx/weights.py:74-81``).
+    With ``residual``/``layer_scale`` it returns ``residual + layer_scale * layer(x)``
+    (the callers' epilogue, ``model.py:260, 341``)."""
+    if (residual is None) != (layer_scale is None):
+        raise RuntimeError("tmoe_b200: residual and layer_scale go together")
+    return torch.ops.tmoe_b200.forward(x, router_w, U_in, inner_norm_w, float(eps), U_expert, core, U_out, bias,
+                                       int(top_k), int(path), residual, layer_scale)
+
+
+def tucker_moe_forward_taps(x, router_w, U_in, inner_norm_w, eps, U_expert, core, U_out, bias, top_k, *,
+                            path=PATH_AUTO):
+    """Forward that also returns the routing results (idx int32 [T,k], gates fp32 [T,k], c fp32 [T,r1])."""
+    y, taps = _run(x, router_w, U_in, inner_norm_w, float(eps), U_expert, core, U_out, bias, int(top_k), int(path),
+                   want_taps=True)
+    return y, taps
+
+
+class TuckerMoE(nn.Module):
+    """Low-rank Tucker-decomposed Mixture-of-Experts, B200 forward.
+
+    Parameter shapes (identical to the reference, ``model.py:44-52``):
+      router.weight (E, d_in)   U_in (d_in, r3)   inner_norm.weight (r3,)   U_expert (E, r1)
+      core (r1, r3, r2)         U_out (r2, d_out)  bias (d_out,)
+    """
+
+    def __init__(self, d_in: int, d_out: int, cfg):
+        super().__init__()
+        E = cfg.kmoe_num_experts
+        r1, r2, r3 = cfg.kmoe_r1, cfg.kmoe_r2, cfg.kmoe_r3
+        self.top_k = cfg.kmoe_top_k
+        self.router = nn.Linear(d_in, E, bias=False)
+        self.U_in = nn.Parameter(torch.empty(d_in, r3))
+        self.inner_norm = RMSNorm(r3, eps=cfg.rms_norm_eps)
+        self.U_expert = nn.Parameter(torch.empty(E, r1))
+        self.core = nn.Parameter(torch.empty(r1, r3, r2))
+        self.U_out = nn.Parameter(torch.empty(r2, d_out))
+        self.bias = nn.Parameter(torch.zeros(d_out))
+        self.path = PATH_AUTO
+
+    def _params(self):
+        return (self.router.weight, self.U_in, self.inner_norm.weight, self.U_expert, self.core, self.U_out, self.bias)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """x: (..., d_in) -> (..., d_out)"""
+        rw, ui, nw, ue, co, uo, b = self._params()
+        return tucker_moe_forward(x, rw, ui, nw, self.inner_norm.eps, ue, co, uo, b, self.top_k, path=self.path)
+
+    def forward_fused_residual(self, x: torch.Tensor, residual: torch.Tensor, layer_scale: torch.Tensor) -> torch.Tensor:
+        """``residual + layer_scale * self(x)`` with the epilogue fused into the out-projection
+        (what the callers compute at ``model.py:259-260`` and ``model.py:340-341``)."""
+        rw, ui, nw, ue, co, uo, b = self._params()
+        return tucker_moe_forward(x, rw, ui, nw, self.inner_norm.eps, ue, co, uo, b, self.top_k, path=self.path,
+                                  residual=residual, layer_scale=layer_scale)
+
+    def forward_with_routing(self, x: torch.Tensor):
+        rw, ui, nw, ue, co, uo, b = self._params()
+        return tucker_moe_forward_taps(x, rw, ui, nw, self.inner_norm.eps, ue, co, uo, b, self.top_k, path=self.path)
+
+    def invalidate_cache(self) -> None:
+        """Call after writing parameters through ``.data`` once the layer has already run
+        (such writes do not change tensor versions, which key the prepared-factor cache)."""
+        clear_caches()

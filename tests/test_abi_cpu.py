@@ -1,0 +1,108 @@
+"""Host-side checks that need no GPU: the library loads, exports every declared symbol, validates
+its arguments before touching CUDA, and the module mirrors the reference's interface."""
+import ctypes as C
+import os
+import re
+
+import pytest
+import torch
+
+import mamba_tuckermoe_b200 as pkg
+from mamba_tuckermoe_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _layer(**kw):
+    base = dict(d_in=64, d_out=96, n_experts=8, top_k=2, r1=4, r2=64, r3=32, dtype=_lib.TMOE_F32, eps=1e-5)
+    base.update(kw)
+    return _lib.Layer(**base)
+
+
+def test_header_symbols_are_exported():
+    text = open(os.path.join(ROOT, "include", "tmoe_b200.h")).read()
+    declared = set(re.findall(r"\b(tmoe_[a-z_]+)\s*\(", text))
+    assert declared == set(_lib.EXPORTS)
+    lib = _lib.load()
+    for s in declared:
+        assert hasattr(lib, s), s
+    assert lib.tmoe_version() == 1
+
+
+def test_status_strings():
+    for code in range(0, -10, -1):
+        assert _lib.status_string(code) != "unknown status"
+    assert _lib.status_string(-99) == "unknown status"
+
+
+@pytest.mark.parametrize("kw,code", [
+    (dict(d_in=0), -2), (dict(top_k=9), -2), (dict(d_in=60), -2), (dict(dtype=7), -3),
+    (dict(top_k=17, n_experts=32), -2), (dict(r1=65), -2),
+])
+def test_invalid_layers_are_rejected(kw, code):
+    lib = _lib.load()
+    L = _layer(**kw)
+    assert lib.tmoe_workspace_bytes(C.byref(L), 16, 0) == code
+    assert lib.tmoe_prepared_bytes(C.byref(L)) == code
+    assert lib.tmoe_resolve_path(C.byref(L), 16, 0) == code
+
+
+def test_null_and_alignment_errors_before_any_cuda_call():
+    lib = _lib.load()
+    L = _layer()
+    F = _lib.Factors(*[4096] * 7)
+    assert lib.tmoe_forward(C.byref(L), None, None, 4096, 4, 4096, None, 4096, 1 << 20, 1, None) == -1
+    assert lib.tmoe_forward(C.byref(L), C.byref(F), None, None, 4, 4096, None, 4096, 1 << 20, 1, None) == -1
+    assert lib.tmoe_forward(C.byref(L), C.byref(F), None, 4100, 4, 4096, None, 4096, 1 << 20, 1, None) == -4
+    assert lib.tmoe_forward(C.byref(L), C.byref(F), None, 4096, 4, 4096, None, 4096, 16, 1, None) == -5
+    assert lib.tmoe_forward(C.byref(L), C.byref(F), None, 4096, -1, 4096, None, 4096, 1 << 20, 1, None) == -2
+    # the tensor-core path does not cover fp32 layers; T == 0 enqueues nothing
+    assert lib.tmoe_forward(C.byref(L), C.byref(F), None, 4096, 4, 4096, None, 4096, 1 << 20, 2, None) == -6
+    assert lib.tmoe_forward(C.byref(L), C.byref(F), None, 4096, 0, 4096, None, 4096, 1 << 20, 1, None) == 0
+    Fbad = _lib.Factors(4096, 4096, 4100, 4096, 4096, 4096, 4096)
+    assert lib.tmoe_forward(C.byref(L), C.byref(Fbad), None, 4096, 4, 4096, None, 4096, 1 << 20, 1, None) == -4
+    ex = _lib.Extras(residual=4096)
+    assert lib.tmoe_forward(C.byref(L), C.byref(F), None, 4096, 4, 4096, C.byref(ex), 4096, 1 << 20, 1, None) == -1
+
+
+def test_path_resolution_and_sizes():
+    lib = _lib.load()
+    cfg2 = _layer(d_in=1536, d_out=2304, n_experts=64, top_k=2, r1=4, r2=1024, r3=256, dtype=_lib.TMOE_BF16, eps=1e-6)
+    assert lib.tmoe_resolve_path(C.byref(cfg2), 32768, 0) == 2
+    assert lib.tmoe_resolve_path(C.byref(cfg2), 64, 0) == 1
+    assert lib.tmoe_resolve_path(C.byref(cfg2), 64, 2) == 2
+    f32 = _layer(d_in=1536, d_out=2304, r2=1024, r3=256)
+    assert lib.tmoe_resolve_path(C.byref(f32), 32768, 0) == 1
+    assert lib.tmoe_prepared_bytes(C.byref(f32)) == 0
+    n = lib.tmoe_prepared_bytes(C.byref(cfg2))
+    raw = 2 * (256 * 1536 + 64 * 1536 + 4 * 1024 * 256 + 2304 * 1024) + 4 * (256 + 2304 + 64 * 4)
+    assert raw <= n <= raw + 8 * 1024
+    ws = lib.tmoe_workspace_bytes(C.byref(cfg2), 32768, 0)
+    assert ws >= 32768 * 1024 * 2 + 256
+    shipped = _layer(d_in=768, d_out=768, r1=32, r2=512, r3=256, dtype=_lib.TMOE_BF16)
+    assert lib.tmoe_resolve_path(C.byref(shipped), 4096, 0) == 1      # r1=32 is served by the CUDA-core path
+    assert lib.tmoe_resolve_path(C.byref(shipped), 4096, 2) == -6
+
+
+def test_module_mirrors_reference_interface():
+    cfg = pkg.TuckerMoEConfig(kmoe_num_experts=8, kmoe_top_k=2, kmoe_r1=4, kmoe_r2=64, kmoe_r3=32, rms_norm_eps=1e-5)
+    m = pkg.TuckerMoE(64, 96, cfg)
+    assert list(m.state_dict().keys()) == ["U_in", "U_expert", "core", "U_out", "bias", "router.weight",
+                                           "inner_norm.weight"]
+    shapes = {k: tuple(v.shape) for k, v in m.state_dict().items()}
+    assert shapes == {"U_in": (64, 32), "U_expert": (8, 4), "core": (4, 32, 64), "U_out": (64, 96), "bias": (96,),
+                      "router.weight": (8, 64), "inner_norm.weight": (32,)}
+    assert m.top_k == 2 and m.inner_norm.eps == 1e-5
+    assert torch.equal(m.bias, torch.zeros(96)) and torch.equal(m.inner_norm.weight, torch.ones(32))
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        m(torch.randn(3, 64))
+
+
+def test_fake_kernel_gives_shapes_without_a_gpu():
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    with FakeTensorMode():
+        x = torch.empty(2, 5, 64)
+        y = torch.ops.tmoe_b200.forward(x, torch.empty(8, 64), torch.empty(64, 32), torch.empty(32), 1e-5,
+                                        torch.empty(8, 4), torch.empty(4, 32, 64), torch.empty(64, 96),
+                                        torch.empty(96), 2, 0, None, None)
+    assert y.shape == (2, 5, 96)

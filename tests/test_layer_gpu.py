@@ -1,0 +1,190 @@
+"""GPU parity of the drop-in layer against the golden outputs of the reference module and
+against the float64 oracle.  Everything goes through the C ABI (module -> custom op -> ctypes).
+
+Tolerances: fp32 -- relative Frobenius error and max-abs/max|y| <= 1e-4, expert indices equal
+except where the reference's own scores tie within 1e-6.  bf16 -- <= 2e-2 on tokens whose
+selection matches (index differences must be explained by scores within one bf16 ulp).
+"""
+import pytest
+import torch
+
+from golden_cases import ALL_CASES, BF16_CASES, F32_CASES, load_case
+from gpu_util import build_module
+from mamba_tuckermoe_b200 import PATH_AUTO, PATH_SIMT, PATH_TENSOR, read_device_status
+from oracle.tucker_moe_oracle import (LayerShape, classify_topk, layer_forward, layer_forward_f64, make_factors,
+                                      make_tokens, max_abs, rel_fro)
+
+pytestmark = pytest.mark.gpu
+
+F32_TOL = 1e-4
+BF16_TOL = 2e-2
+
+
+def bf16_ulp(scores):
+    """One unit in the last place of a bf16 number of the scores' magnitude (8 significand bits)."""
+    m = float(scores.abs().max()) if scores.numel() else 1.0
+    return 2.0 ** (torch.tensor(max(m, 1e-30)).log2().floor().item() - 7)
+
+
+def check_against(y, taps, y_ref, idx_ref, scores_ref, dtype, x, f, shape):
+    idx, gates, c = taps
+    gap = 1e-6 if dtype == torch.float32 else bf16_ulp(scores_ref)
+    rep = classify_topk(idx.cpu(), idx_ref, scores_ref, gap)
+    assert rep.unexplained == 0, f"unexplained top-k mismatches at tokens {rep.mismatch_tokens}"
+    keep = torch.ones(idx_ref.shape[0], dtype=torch.bool)
+    keep[rep.mismatch_tokens] = False
+    yk, rk = y.float().cpu().reshape(-1, shape.d_out)[keep], y_ref.float().reshape(-1, shape.d_out)[keep]
+    tol = F32_TOL if dtype == torch.float32 else BF16_TOL
+    scale = float(rk.abs().max()) if rk.numel() else 1.0
+    assert rel_fro(yk, rk) <= tol, f"rel-Fro {rel_fro(yk, rk):.3e} (max-abs {max_abs(yk, rk):.3e})"
+    assert max_abs(yk, rk) <= tol * max(scale, 1.0) * (1 if dtype == torch.float32 else 4), \
+        f"max-abs {max_abs(yk, rk):.3e} vs |y|max {scale:.3f}"
+    # tokens that broke a tie differently: compare with the float64 oracle under this run's own selection
+    if rep.mismatch_tokens:
+        t = torch.tensor(rep.mismatch_tokens)
+        y64, _ = layer_forward_f64(x.reshape(-1, shape.d_in)[t], f, shape.top_k, shape.eps, idx=idx.cpu()[t],
+                                   round_scores_to=None if dtype == torch.float32 else torch.bfloat16)
+        assert rel_fro(y.float().cpu().reshape(-1, shape.d_out)[t], y64) <= tol
+
+
+@pytest.mark.parametrize("name", ALL_CASES)
+def test_simt_path_matches_reference_golden(name):
+    shape, x, f, dtype, g = load_case(name)
+    m = build_module(shape, f, dtype, path=PATH_SIMT)
+    y, taps = m.forward_with_routing(x.cuda())
+    assert y.shape == g["y"].shape and y.dtype == dtype
+    assert read_device_status() == (0, 0, 0, 0)
+    if x.numel() == 0:
+        return
+    check_against(y, taps, g["y"], g["idx"], g["scores"], dtype, x, f, shape)
+    # plain forward (custom op) returns the same tensor as the tapped call
+    assert torch.equal(m(x.cuda()), y)
+
+
+@pytest.mark.parametrize("name", F32_CASES)
+def test_fp32_gates_and_coefficients(name):
+    shape, x, f, dtype, g = load_case(name)
+    if x.numel() == 0:
+        return
+    m = build_module(shape, f, dtype, path=PATH_SIMT)
+    _, (idx, gates, c) = m.forward_with_routing(x.cuda())
+    same = (idx.cpu().long() == g["idx"]).all(-1)
+    assert max_abs(gates.cpu()[same], g["gates"][same]) < 2e-6
+    c_ref = torch.einsum("tk,tkr->tr", g["gates"].double(), f["U_expert"].double()[g["idx"]])
+    assert max_abs(c.cpu()[same], c_ref[same]) < 1e-5
+
+
+def _tensor_case(shape, T, seed, router_std=0.02, bias_std=0.1, lead=None):
+    f = make_factors(shape, seed, torch.bfloat16, router_std, bias_std)
+    x = make_tokens(T, shape.d_in, seed, torch.bfloat16)
+    if lead:
+        x = x.reshape(*lead, shape.d_in)
+    return x, f
+
+
+TENSOR_SHAPES = [
+    # (shape, T) -- ragged token counts, several r1 / r3 / E, in-kernel and separate routing
+    (LayerShape(128, 64, 16, 2, 4, 64, 128, 1e-6), 300),
+    (LayerShape(256, 264, 8, 2, 2, 128, 256, 1e-5), 129),
+    (LayerShape(192, 320, 40, 8, 8, 192, 192, 1e-6), 77),
+    (LayerShape(1536, 2304, 8, 2, 4, 256, 1024, 1e-6), 64),
+    (LayerShape(1536, 2304, 64, 2, 4, 256, 1024, 1e-6), 1000),
+    (LayerShape(256, 128, 512, 8, 4, 64, 128, 1e-6), 200),   # E > 256: scores by the CUDA-core kernels
+]
+
+
+@pytest.mark.parametrize("shape,T", TENSOR_SHAPES)
+def test_tensor_path_matches_oracle(shape, T):
+    """tcgen05 path vs (a) the bf16 reference restatement and (b) float64 algebra on the run's own selection."""
+    x, f = _tensor_case(shape, T, seed=4000 + T, router_std=None if shape.E >= 40 else 0.02)
+    m = build_module(shape, f, torch.bfloat16, path=PATH_TENSOR)
+    y, taps = m.forward_with_routing(x.cuda())
+    torch.cuda.synchronize()
+    assert read_device_status() == (0, 0, 0, 0)
+    y_ref, rt = layer_forward(x, f, shape.top_k, shape.eps, return_taps=True)
+    check_against(y, taps, y_ref, rt["idx"], rt["scores"], torch.bfloat16, x, f, shape)
+    y64, _ = layer_forward_f64(x, f, shape.top_k, shape.eps, idx=taps[0].cpu(), round_scores_to=torch.bfloat16)
+    assert rel_fro(y.float().cpu(), y64) <= 1e-2, "tensor path vs float64 algebra with its own selection"
+    assert torch.equal(m(x.cuda()), y)
+
+
+@pytest.mark.parametrize("name", BF16_CASES)
+def test_tensor_path_matches_reference_golden(name):
+    shape, x, f, dtype, g = load_case(name)
+    if shape.r3 % 64:
+        pytest.skip("shape not covered by the tensor-core path")
+    m = build_module(shape, f, dtype, path=PATH_TENSOR)
+    y, taps = m.forward_with_routing(x.cuda())
+    assert read_device_status() == (0, 0, 0, 0)
+    check_against(y, taps, g["y"], g["idx"], g["scores"], dtype, x, f, shape)
+
+
+def test_tensor_and_simt_paths_agree():
+    shape = LayerShape(1536, 2304, 64, 2, 4, 256, 1024, 1e-6)
+    x, f = _tensor_case(shape, 515, seed=77, router_std=None)
+    a, ta = build_module(shape, f, torch.bfloat16, path=PATH_TENSOR).forward_with_routing(x.cuda())
+    b, tb = build_module(shape, f, torch.bfloat16, path=PATH_SIMT).forward_with_routing(x.cuda())
+    same = (ta[0] == tb[0]).all(-1).cpu()
+    assert same.float().mean() > 0.97
+    assert rel_fro(a.float().cpu()[same], b.float().cpu()[same]) < 1e-2
+
+
+@pytest.mark.parametrize("path", [PATH_SIMT, PATH_TENSOR])
+def test_fused_residual_epilogue(path):
+    """residual + layer_scale * layer(x) equals the callers' composition (model.py:259-260, 340-341)."""
+    shape = LayerShape(128, 64, 16, 2, 4, 64, 128, 1e-6)
+    x, f = _tensor_case(shape, 130, seed=5)
+    m = build_module(shape, f, torch.bfloat16, path=path)
+    g = torch.Generator().manual_seed(1)
+    res = torch.randn(130, shape.d_out, generator=g).bfloat16().cuda()
+    gamma = (1 + 0.1 * torch.randn(shape.d_out, generator=g)).bfloat16().cuda()
+    y = m(x.cuda()).float()
+    fused = m.forward_fused_residual(x.cuda(), res, gamma).float()
+    expect = res.float() + gamma.float() * y
+    assert rel_fro(fused.cpu(), expect.cpu()) < 1e-2
+
+
+def test_auto_path_and_leading_shapes():
+    shape = LayerShape(1536, 2304, 8, 2, 4, 256, 1024, 1e-6)
+    x, f = _tensor_case(shape, 96, seed=9, lead=(2, 48))
+    m = build_module(shape, f, torch.bfloat16, path=PATH_AUTO)
+    y = m(x.cuda())
+    assert y.shape == (2, 48, 2304)
+    y1 = m(x.cuda()[0, :1])     # T=1 -> CUDA-core path
+    assert y1.shape == (1, 2304)
+    y_ref = layer_forward(x, f, shape.top_k, shape.eps)
+    assert rel_fro(y.float().cpu(), y_ref.float()) < 3e-2
+
+
+def test_noncontiguous_input_and_worker_thread():
+    """The reference calls the layer from worker threads under no_grad (generate.py:107, server.py:125)."""
+    import threading
+    shape, x, f, dtype, g = load_case("tiny_f32")
+    m = build_module(shape, f, dtype)
+    xt = torch.cat([x, x], -1).cuda()[:, : shape.d_in]  # non-contiguous view
+    out = {}
+
+    def work():
+        with torch.no_grad():
+            out["y"] = m(xt)
+        torch.cuda.synchronize()
+
+    t = threading.Thread(target=work)
+    t.start(); t.join()
+    assert rel_fro(out["y"].cpu(), g["y"]) < F32_TOL
+
+
+def test_linearity_in_out_projection_and_bias():
+    """Size-independent property at a benchmark-sized T: y(x; bias) - y(x; 0) == bias for every token."""
+    shape = LayerShape(1536, 2304, 64, 2, 4, 256, 1024, 1e-6)
+    x, f = _tensor_case(shape, 8192, seed=21, router_std=None, bias_std=0.0)
+    m0 = build_module(shape, f, torch.bfloat16)
+    y0 = m0(x.cuda()).float()
+    f2 = dict(f); f2["bias"] = torch.full((shape.d_out,), 0.5).bfloat16()
+    y1 = build_module(shape, f2, torch.bfloat16)(x.cuda()).float()
+    assert read_device_status() == (0, 0, 0, 0)
+    d = (y1 - y0 - 0.5).abs()
+    assert float(d.max()) <= 0.07 and float(d.mean()) < 0.01   # one bf16 rounding of |y| <= 16
+    # token-wise independence: permuting tokens permutes outputs bit for bit
+    perm = torch.randperm(8192, generator=torch.Generator().manual_seed(3)).cuda()
+    assert torch.equal(m0(x.cuda()[perm]).float(), y0[perm])

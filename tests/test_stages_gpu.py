@@ -1,0 +1,94 @@
+"""The three C-ABI stages (router, in-projection + core, out-projection) one by one against the
+float64 oracle taps, on both paths."""
+import ctypes as C
+
+import pytest
+import torch
+
+from gpu_util import alloc_prepared, alloc_workspace, cuda_stream_ptr, factors_struct, layer_struct
+from mamba_tuckermoe_b200 import _lib
+from oracle.tucker_moe_oracle import LayerShape, classify_topk, layer_forward_f64, make_factors, make_tokens, max_abs, rel_fro
+
+pytestmark = pytest.mark.gpu
+
+CASES = [
+    (LayerShape(64, 96, 8, 2, 4, 32, 64, 1e-5), 37, torch.float32),
+    (LayerShape(256, 384, 64, 8, 8, 64, 128, 1e-6), 300, torch.float32),     # tiled scores + select kernel
+    (LayerShape(256, 384, 1024, 16, 3, 64, 128, 1e-6), 290, torch.float32),  # top-16 of 1024, odd r1
+    (LayerShape(1536, 2304, 8, 2, 4, 256, 1024, 1e-6), 8, torch.bfloat16),
+    (LayerShape(1536, 2304, 64, 2, 4, 256, 1024, 1e-6), 257, torch.bfloat16),
+]
+
+
+def _setup(shape, T, dtype, seed=31):
+    f = make_factors(shape, seed, dtype, None if shape.E >= 64 else 0.02, 0.1)
+    x = make_tokens(T, shape.d_in, seed, dtype)
+    fd = {k: v.cuda() for k, v in f.items()}
+    return x, f, fd
+
+
+@pytest.mark.parametrize("shape,T,dtype", CASES)
+def test_router_stage(shape, T, dtype):
+    lib = _lib.load()
+    x, f, fd = _setup(shape, T, dtype)
+    L, F = layer_struct(shape, dtype), factors_struct(fd)
+    ws = alloc_workspace(lib, L, T, 1)
+    idx = torch.empty(T, shape.top_k, dtype=torch.int32, device="cuda")
+    gates = torch.empty(T, shape.top_k, dtype=torch.float32, device="cuda")
+    c = torch.empty(T, shape.r1, dtype=torch.float32, device="cuda")
+    xd = x.cuda()
+    rc = lib.tmoe_router(C.byref(L), C.byref(F), xd.data_ptr(), T, idx.data_ptr(), gates.data_ptr(), c.data_ptr(),
+                         ws.data_ptr(), ws.numel(), cuda_stream_ptr())
+    assert rc == 0, _lib.status_string(rc)
+    torch.cuda.synchronize()
+    rnd = None if dtype == torch.float32 else torch.bfloat16
+    _, taps = layer_forward_f64(x, f, shape.top_k, shape.eps, round_scores_to=rnd)
+    gap = 1e-6 if dtype == torch.float32 else 2.0 ** -5
+    rep = classify_topk(idx.cpu(), taps["idx"], taps["scores"], gap)
+    assert rep.unexplained == 0
+    # with this run's own selection, gates and c agree with float64
+    _, own = layer_forward_f64(x, f, shape.top_k, shape.eps, idx=idx.cpu(), round_scores_to=rnd)
+    tol = 2e-6 if dtype == torch.float32 else 4e-3
+    assert max_abs(gates.cpu(), own["gates"]) < tol
+    assert max_abs(c.cpu(), own["c"]) < tol * 8
+    # descending order of the selected scores, indices distinct per token
+    s_sel = torch.gather(own["scores"], 1, idx.cpu().long())
+    assert bool((s_sel[:, :-1] >= s_sel[:, 1:]).all())
+    assert all(len(set(r.tolist())) == shape.top_k for r in idx.cpu())
+
+
+@pytest.mark.parametrize("shape,T,dtype", CASES)
+@pytest.mark.parametrize("path", [1, 2])
+def test_in_core_and_out_stages(shape, T, dtype, path):
+    lib = _lib.load()
+    L = layer_struct(shape, dtype)
+    if path == 2 and lib.tmoe_resolve_path(C.byref(L), T, 2) < 0:
+        pytest.skip("shape not covered by the tensor-core path")
+    x, f, fd = _setup(shape, T, dtype)
+    F = factors_struct(fd)
+    ws = alloc_workspace(lib, L, T, path)
+    prep = alloc_prepared(lib, L, F) if path == 2 else None
+    prep_ptr = prep.data_ptr() if prep is not None else None
+    rnd = None if dtype == torch.float32 else torch.bfloat16
+    y64, taps = layer_forward_f64(x, f, shape.top_k, shape.eps, round_scores_to=rnd)
+    c = taps["c"].float().cuda().contiguous()
+    zdtype = torch.float32 if path == 1 else torch.bfloat16
+    z = torch.empty(T, shape.r2, dtype=zdtype, device="cuda")
+    xd = x.cuda()
+    rc = lib.tmoe_in_core(C.byref(L), C.byref(F), prep_ptr, xd.data_ptr(), T, c.data_ptr(), z.data_ptr(),
+                          ws.data_ptr(), ws.numel(), path, cuda_stream_ptr())
+    assert rc == 0, _lib.status_string(rc)
+    torch.cuda.synchronize()
+    st = (C.c_int32 * 4)()
+    assert lib.tmoe_read_device_status(ws.data_ptr(), st, cuda_stream_ptr()) == 0 and list(st) == [0, 0, 0, 0]
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    assert rel_fro(z.float().cpu(), taps["z"]) < tol
+    # out stage on the oracle's z
+    z_in = taps["z"].to(zdtype).cuda().contiguous()
+    y = torch.empty(T, shape.d_out, dtype=dtype, device="cuda")
+    rc = lib.tmoe_out(C.byref(L), C.byref(F), prep_ptr, z_in.data_ptr(), T, y.data_ptr(), None, ws.data_ptr(),
+                      ws.numel(), path, cuda_stream_ptr())
+    assert rc == 0, _lib.status_string(rc)
+    torch.cuda.synchronize()
+    assert lib.tmoe_read_device_status(ws.data_ptr(), st, cuda_stream_ptr()) == 0 and list(st) == [0, 0, 0, 0]
+    assert rel_fro(y.float().cpu(), y64) < (1e-5 if dtype == torch.float32 else 1e-2)
