@@ -168,6 +168,8 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=8)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--path", type=int, default=0, help="0 auto, 1 CUDA-core, 2 tensor-core")
+    ap.add_argument("--profile", action="store_true",
+                    help="short run for use under ncu: device-resident steps only (no per-kernel, e2e or CPU legs)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
@@ -242,6 +244,14 @@ def main():
         ms_step = ms_total / args.steps
         value = world * T * args.steps / (ms_total * 1e-3)
 
+        if args.profile:
+            if rank == 0:
+                print(json.dumps({"profile_run": True, "ms_per_step": ms_step, "tokens_per_s": value,
+                                  "gpu_launches": int(launches)}), flush=True)
+            if world > 1:
+                dist.destroy_process_group()
+            return
+
         # ---------------- per-kernel timing of the two dominant kernels (stage API) ----------------
         kern = per_kernel_times(lib, _lib, layer, shape, dtype, x_dev[0], T, args.path)
 
@@ -312,6 +322,7 @@ def per_kernel_times(lib, _lib, layer, shape, dtype, x, T, path, reps=20):
           "U_expert": layer.U_expert, "core": layer.core, "U_out": layer.U_out, "bias": layer.bias}
     F = _lib.factors_struct(fd)
     ws = _lib.alloc_workspace(L, T, rpath)
+    ws_router = _lib.alloc_workspace(L, T, 1)  # the stand-alone router entry point uses the CUDA-core layout
     prep = _lib.alloc_prepared(L, F) if rpath == 2 else None
     pp = prep.data_ptr() if prep is not None else None
     zdt = torch.bfloat16 if rpath == 2 else torch.float32
@@ -336,7 +347,7 @@ def per_kernel_times(lib, _lib, layer, shape, dtype, x, T, path, reps=20):
         return statistics.mean(a.elapsed_time(b) for a, b in evs) * 1e3  # us
 
     us_router = t(lambda: lib.tmoe_router(C.byref(L), C.byref(F), x.data_ptr(), T, idx.data_ptr(), gates.data_ptr(),
-                                          c.data_ptr(), ws.data_ptr(), ws.numel(), st))
+                                          c.data_ptr(), ws_router.data_ptr(), ws_router.numel(), st))
     us_incore = t(lambda: lib.tmoe_in_core(C.byref(L), C.byref(F), pp, x.data_ptr(), T, c.data_ptr(), z.data_ptr(),
                                            ws.data_ptr(), ws.numel(), rpath, st))
     us_out = t(lambda: lib.tmoe_out(C.byref(L), C.byref(F), pp, z.data_ptr(), T, y.data_ptr(), None, ws.data_ptr(),

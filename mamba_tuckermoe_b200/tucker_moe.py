@@ -21,7 +21,7 @@ import torch.nn as nn
 from . import _lib
 from ._lib import PATH_AUTO, PATH_SIMT, PATH_TENSOR, Extras, Factors, Layer
 
-__all__ = ["TuckerMoE", "TuckerMoEConfig", "RMSNorm", "tucker_moe_forward", "tucker_moe_forward_taps",
+__all__ = ["TuckerMoE", "TuckerMoEConfig", "RMSNorm", "tucker_moe_forward", "tucker_moe_forward_taps", "prepare_factors",
            "PATH_AUTO", "PATH_SIMT", "PATH_TENSOR"]
 
 
@@ -55,11 +55,12 @@ class RMSNorm(nn.Module):
 _DTYPES = {torch.float32: _lib.TMOE_F32, torch.bfloat16: _lib.TMOE_BF16}
 
 # ------------------------------------------------------------------------------------------
-# per-(device, stream) scratch and per-parameter-set prepared factors
+# per-(device, stream) scratch.  Prepared factor sets are NOT cached globally: a key made of
+# addresses and versions can collide once a freed parameter's memory is reused, so the cache
+# lives on the module that owns the parameters (TuckerMoE._prepared_for).
 # ------------------------------------------------------------------------------------------
 _cache_lock = threading.Lock()
 _workspaces = {}   # (device index, stream handle) -> uint8 tensor
-_prepared = {}     # key of the seven parameter tensors -> uint8 tensor
 
 
 def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
@@ -78,11 +79,30 @@ def _param_key(tensors) -> tuple:
 
 
 def clear_caches() -> None:
-    """Drops cached workspaces and prepared factor sets (e.g. after in-place ``.data`` writes to
-    parameters, which do not bump tensor versions)."""
+    """Drops the cached per-stream workspaces."""
     with _cache_lock:
         _workspaces.clear()
-        _prepared.clear()
+
+
+def prepare_factors(router_w, U_in, inner_norm_w, eps, U_expert, core, U_out, bias, top_k) -> Optional[torch.Tensor]:
+    """Re-laid-out factor set for the tensor-core path (``tmoe_prepare_factors``), or None when
+    that path does not cover the layer.  Valid until any of the seven tensors changes."""
+    params = tuple(p if p.is_contiguous() else p.contiguous()
+                   for p in (router_w, U_in, inner_norm_w, U_expert, core, U_out, bias))
+    if not params[0].is_cuda or params[0].dtype not in _DTYPES:
+        return None
+    lib = _lib.load()
+    layer = _layer_struct(params[0], params[0], params[1], params[3], params[4], params[5], top_k, eps)
+    nbytes = _lib.check(lib.tmoe_prepared_bytes(C.byref(layer)), "tmoe_prepared_bytes")
+    if nbytes == 0:
+        return None
+    dev = params[0].device
+    with torch.cuda.device(dev):
+        prep = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        factors = Factors(*[p.data_ptr() for p in params])
+        _lib.check(lib.tmoe_prepare_factors(C.byref(layer), C.byref(factors), prep.data_ptr(), nbytes,
+                                            torch.cuda.current_stream(dev).cuda_stream), "tmoe_prepare_factors")
+    return prep
 
 
 def _layer_struct(x, router_w, U_in, U_expert, core, U_out, top_k, eps) -> Layer:
@@ -110,7 +130,7 @@ def _validate(x, params, top_k):
 
 
 def _run(x, router_w, U_in, inner_norm_w, eps, U_expert, core, U_out, bias, top_k, path,
-         residual=None, layer_scale=None, want_taps=False):
+         residual=None, layer_scale=None, want_taps=False, prepared=None):
     params = (router_w, U_in, inner_norm_w, U_expert, core, U_out, bias)
     _validate(x, params, top_k)
     lib = _lib.load()
@@ -139,19 +159,9 @@ def _run(x, router_w, U_in, inner_norm_w, eps, U_expert, core, U_out, bias, top_
         factors = Factors(*[p.data_ptr() for p in params])
         prepared_ptr = None
         if rpath == PATH_TENSOR:
-            key = _param_key(params)
-            with _cache_lock:
-                prep = _prepared.get(key)
-            if prep is None or os.environ.get("TMOE_ALWAYS_PREPARE") == "1":
-                nbytes = _lib.check(lib.tmoe_prepared_bytes(C.byref(layer)), "tmoe_prepared_bytes")
-                prep = torch.empty(nbytes, dtype=torch.uint8, device=dev)
-                _lib.check(lib.tmoe_prepare_factors(C.byref(layer), C.byref(factors), prep.data_ptr(), nbytes, stream),
-                           "tmoe_prepare_factors")
-                with _cache_lock:
-                    if len(_prepared) > 256:
-                        _prepared.clear()
-                    _prepared[key] = prep
-            prepared_ptr = prep.data_ptr()
+            if prepared is None:  # functional call without a cached set: prepare for this call
+                prepared = prepare_factors(router_w, U_in, inner_norm_w, eps, U_expert, core, U_out, bias, top_k)
+            prepared_ptr = prepared.data_ptr()
         ws_bytes = _lib.check(lib.tmoe_workspace_bytes(C.byref(layer), T, rpath), "tmoe_workspace_bytes")
         ws = _workspace(dev, ws_bytes)
         extras = Extras()
@@ -195,32 +205,36 @@ def read_device_status(device=None) -> Tuple[int, int, int, int]:
 @torch.library.custom_op("tmoe_b200::forward", mutates_args=())
 def _forward_op(x: torch.Tensor, router_w: torch.Tensor, U_in: torch.Tensor, inner_norm_w: torch.Tensor, eps: float,
                 U_expert: torch.Tensor, core: torch.Tensor, U_out: torch.Tensor, bias: torch.Tensor, top_k: int,
-                path: int, residual: Optional[torch.Tensor], layer_scale: Optional[torch.Tensor]) -> torch.Tensor:
-    y, _ = _run(x, router_w, U_in, inner_norm_w, eps, U_expert, core, U_out, bias, top_k, path, residual, layer_scale)
+                path: int, residual: Optional[torch.Tensor], layer_scale: Optional[torch.Tensor],
+                prepared: Optional[torch.Tensor]) -> torch.Tensor:
+    y, _ = _run(x, router_w, U_in, inner_norm_w, eps, U_expert, core, U_out, bias, top_k, path, residual, layer_scale,
+                prepared=prepared)
     return y
 
 
 @_forward_op.register_fake
-def _(x, router_w, U_in, inner_norm_w, eps, U_expert, core, U_out, bias, top_k, path, residual, layer_scale):
+def _(x, router_w, U_in, inner_norm_w, eps, U_expert, core, U_out, bias, top_k, path, residual, layer_scale, prepared):
     return x.new_empty((*x.shape[:-1], U_out.shape[1]))
 
 
 def tucker_moe_forward(x, router_w, U_in, inner_norm_w, eps, U_expert, core, U_out, bias, top_k, *, path=PATH_AUTO,
-                       residual=None, layer_scale=None):
+                       residual=None, layer_scale=None, prepared=None):
     """Functional form of the layer (parameter order of ``pure_torch_mlx/weights.py:74-81``).
     With ``residual``/``layer_scale`` it returns ``residual + layer_scale * layer(x)``
-    (the callers' epilogue, ``model.py:260, 341``)."""
+    (the callers' epilogue, ``model.py:260, 341``).  ``prepared`` is an optional result of
+    ``prepare_factors`` for the same seven tensors; without it the tensor-core path re-lays the
+    factors out on every call."""
     if (residual is None) != (layer_scale is None):
         raise RuntimeError("tmoe_b200: residual and layer_scale go together")
     return torch.ops.tmoe_b200.forward(x, router_w, U_in, inner_norm_w, float(eps), U_expert, core, U_out, bias,
-                                       int(top_k), int(path), residual, layer_scale)
+                                       int(top_k), int(path), residual, layer_scale, prepared)
 
 
 def tucker_moe_forward_taps(x, router_w, U_in, inner_norm_w, eps, U_expert, core, U_out, bias, top_k, *,
-                            path=PATH_AUTO):
+                            path=PATH_AUTO, prepared=None):
     """Forward that also returns the routing results (idx int32 [T,k], gates fp32 [T,k], c fp32 [T,r1])."""
     y, taps = _run(x, router_w, U_in, inner_norm_w, float(eps), U_expert, core, U_out, bias, int(top_k), int(path),
-                   want_taps=True)
+                   want_taps=True, prepared=prepared)
     return y, taps
 
 
@@ -245,6 +259,23 @@ class TuckerMoE(nn.Module):
         self.U_out = nn.Parameter(torch.empty(r2, d_out))
         self.bias = nn.Parameter(torch.zeros(d_out))
         self.path = PATH_AUTO
+        self._prep_key = None
+        self._prep = None
+
+    def _prepared_for(self, x: torch.Tensor) -> Optional[torch.Tensor]:
+        """Prepared factor set for the tensor-core path, rebuilt when a parameter's storage,
+        version, dtype or device changes; None when this call will not use that path."""
+        if not x.is_cuda or x.dtype != torch.bfloat16:
+            return None
+        T = x.numel() // max(x.shape[-1], 1)
+        if self.path == PATH_SIMT or (self.path == PATH_AUTO and T <= 64):
+            return None
+        ps = self._params()
+        key = _param_key(ps)
+        if key != self._prep_key or os.environ.get("TMOE_ALWAYS_PREPARE") == "1":
+            self._prep = prepare_factors(ps[0], ps[1], ps[2], self.inner_norm.eps, ps[3], ps[4], ps[5], ps[6], self.top_k)
+            self._prep_key = key
+        return self._prep
 
     def _params(self):
         return (self.router.weight, self.U_in, self.inner_norm.weight, self.U_expert, self.core, self.U_out, self.bias)
@@ -252,20 +283,22 @@ class TuckerMoE(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         """x: (..., d_in) -> (..., d_out)"""
         rw, ui, nw, ue, co, uo, b = self._params()
-        return tucker_moe_forward(x, rw, ui, nw, self.inner_norm.eps, ue, co, uo, b, self.top_k, path=self.path)
+        return tucker_moe_forward(x, rw, ui, nw, self.inner_norm.eps, ue, co, uo, b, self.top_k, path=self.path,
+                                  prepared=self._prepared_for(x))
 
     def forward_fused_residual(self, x: torch.Tensor, residual: torch.Tensor, layer_scale: torch.Tensor) -> torch.Tensor:
         """``residual + layer_scale * self(x)`` with the epilogue fused into the out-projection
         (what the callers compute at ``model.py:259-260`` and ``model.py:340-341``)."""
         rw, ui, nw, ue, co, uo, b = self._params()
         return tucker_moe_forward(x, rw, ui, nw, self.inner_norm.eps, ue, co, uo, b, self.top_k, path=self.path,
-                                  residual=residual, layer_scale=layer_scale)
+                                  residual=residual, layer_scale=layer_scale, prepared=self._prepared_for(x))
 
     def forward_with_routing(self, x: torch.Tensor):
         rw, ui, nw, ue, co, uo, b = self._params()
-        return tucker_moe_forward_taps(x, rw, ui, nw, self.inner_norm.eps, ue, co, uo, b, self.top_k, path=self.path)
+        return tucker_moe_forward_taps(x, rw, ui, nw, self.inner_norm.eps, ue, co, uo, b, self.top_k, path=self.path,
+                                       prepared=self._prepared_for(x))
 
     def invalidate_cache(self) -> None:
         """Call after writing parameters through ``.data`` once the layer has already run
         (such writes do not change tensor versions, which key the prepared-factor cache)."""
-        clear_caches()
+        self._prep_key, self._prep = None, None
