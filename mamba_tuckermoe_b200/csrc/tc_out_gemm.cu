@@ -55,7 +55,8 @@ constexpr int OM = 128, ON = 256, OKB = 64, OSTAGES = 4;
 constexpr int O_A_BYTES = OM * OKB * 2;   // 16 KB
 constexpr int O_B_BYTES = ON * OKB * 2;   // 32 KB
 constexpr int O_STAGE_BYTES = O_A_BYTES + O_B_BYTES;
-constexpr int O_SMEM_BYTES = OSTAGES * O_STAGE_BYTES + 1024;
+constexpr int O_Y_BYTES = OM * 64 * 2;  // 16 KB: 128 rows x 64 bf16 output columns
+constexpr int O_SMEM_BYTES = OSTAGES * O_STAGE_BYTES + 2 * O_Y_BYTES + 1024;
 constexpr int kKernelOut = 3;
 
 struct OutParams {
@@ -70,7 +71,8 @@ struct OutParams {
 };
 
 __global__ void __launch_bounds__(192, 1)
-tc_out_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, OutParams p) {
+tc_out_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+              const __grid_constant__ CUtensorMap tmY, OutParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[OSTAGES], bar_empty[OSTAGES], bar_tfull[2], bar_tempty[2];
   __shared__ uint32_t tmem_base_s;
@@ -84,6 +86,7 @@ tc_out_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
     fence_mbar_init();
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmB);
+    prefetch_tmap(&tmY);
   }
   if (warp == 1) { tmem_alloc(smem_u32(&tmem_base_s), 512); tmem_relinquish(); }
   tc_fence_before();
@@ -138,36 +141,43 @@ tc_out_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
   } else {
     const int quad = warp & 3;
     const int row_in_tile = quad * 32 + lane;
-    uint32_t tcount = 0;
+    const bool is_store_thread = (threadIdx.x == 64);
+    const uint32_t stage0 = ring + OSTAGES * O_STAGE_BYTES;  // two 16 KB output staging tiles
+    uint32_t tcount = 0, chunk_no = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
       const int m0 = (tile / p.num_n) * OM, n0 = (tile % p.num_n) * ON;
       const uint32_t slot = tcount & 1, aph = (tcount >> 1) & 1;
       ok = mbar_wait(smem_u32(&bar_tfull[slot]), aph, p.status, kKernelOut, 3);
-      ok = __all_sync(0xffffffffu, ok);  // the TMEM loads below are warp-collective
+      ok = named_bar_and(2, 128, ok);  // all four epilogue warps continue or leave together (they share barriers below)
       if (!ok) break;
       tc_fence_after();
       const int64_t row = (int64_t)m0 + row_in_tile;
       const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + slot * ON;
 #pragma unroll 1
-      for (int cc = 0; cc < ON / 32; ++cc) {
-        uint32_t r[32];
-        tmem_ld32(t_row + cc * 32, r);
-        tmem_ld_wait(r);
-        const int col0 = n0 + cc * 32;
-        if (row < p.T) {
+      for (int cc = 0; cc < ON / 64; ++cc, ++chunk_no) {
+        // 64 output columns per pass: TMEM -> registers -> bf16 -> swizzled staging tile -> TMA store
+        const uint32_t stage_buf = stage0 + (chunk_no & 1) * O_Y_BYTES;
+        if (is_store_thread) tma_store_wait_read<1>();  // the store that used this buffer two passes ago has read it
+        named_bar_sync(1, 128);
+        const int col0 = n0 + cc * 64;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t r[32];
+          tmem_ld32(t_row + cc * 64 + half * 32, r);
+          tmem_ld_wait(r);
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
-            const int col = col0 + g * 8;
-            if (col < p.N) {  // N % 8 == 0, so a group of 8 is entirely in or out
-              float v[8];
+            const int col = col0 + half * 32 + g * 8;
+            float v[8];
 #pragma unroll
-              for (int q = 0; q < 8; ++q) v[q] = __uint_as_float(r[g * 8 + q]);
+            for (int q = 0; q < 8; ++q) v[q] = __uint_as_float(r[g * 8 + q]);
+            if (col < p.N) {  // N % 8 == 0, so a group of 8 is entirely in or out; columns >= N are clipped by the store
               const float4 b0 = __ldg(reinterpret_cast<const float4 *>(p.bias + col));
               const float4 b1 = __ldg(reinterpret_cast<const float4 *>(p.bias + col + 4));
               v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
               v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
-              if (p.residual) {
+              if (p.residual && row < p.T) {
                 const uint4 rr = __ldg(reinterpret_cast<const uint4 *>(p.residual + row * p.N + col));
                 const uint4 gg = __ldg(reinterpret_cast<const uint4 *>(p.gamma + col));
                 const uint32_t rw[4] = {rr.x, rr.y, rr.z, rr.w}, gw[4] = {gg.x, gg.y, gg.z, gg.w};
@@ -177,18 +187,27 @@ tc_out_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                   v[2 * q + 1] = __uint_as_float(rw[q] & 0xffff0000u) + __uint_as_float(gw[q] & 0xffff0000u) * v[2 * q + 1];
                 }
               }
-              uint4 o;
-              o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
-              o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
-              *reinterpret_cast<uint4 *>(p.y + row * p.N + col) = o;
             }
+            // 16-byte chunk (half*4+g) of this thread's 128-byte row, XOR-swizzled like the TMA box expects
+            const uint32_t chunk = (uint32_t)(half * 4 + g) ^ (uint32_t)(row_in_tile & 7);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_buf + row_in_tile * 128 + chunk * 16),
+                         "r"(pack_bf16x2(v[0], v[1])), "r"(pack_bf16x2(v[2], v[3])), "r"(pack_bf16x2(v[4], v[5])),
+                         "r"(pack_bf16x2(v[6], v[7]))
+                         : "memory");
           }
+        }
+        fence_proxy_async_smem();
+        named_bar_sync(1, 128);
+        if (is_store_thread && col0 < p.N) {
+          tma_store_2d(&tmY, stage_buf, col0, m0);
+          tma_store_commit();
         }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[slot]));
     }
+    if (is_store_thread) tma_store_wait_all();
   }
   tc_fence_before();
   __syncthreads();
@@ -201,8 +220,10 @@ tc_out_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
 
 int launch_tc_out(const tmoe_layer_t &L, const void *z, const void *uout_t, const float *bias, const void *residual,
                   const void *layer_scale, int64_t T_, void *y, int32_t *status, cudaStream_t st) {
-  CUtensorMap tmA, tmB;
-  int rc = encode_tmap_bf16_2d(&tmA, z, (uint64_t)T_, (uint64_t)L.r2, OM);
+  CUtensorMap tmA, tmB, tmY;
+  int rc = encode_tmap_bf16_2d(&tmY, y, (uint64_t)T_, (uint64_t)L.d_out, OM);
+  if (rc) return rc;
+  rc = encode_tmap_bf16_2d(&tmA, z, (uint64_t)T_, (uint64_t)L.r2, OM);
   if (rc) return rc;
   rc = encode_tmap_bf16_2d(&tmB, uout_t, (uint64_t)L.d_out, (uint64_t)L.r2, ON);
   if (rc) return rc;
@@ -222,7 +243,7 @@ int launch_tc_out(const tmoe_layer_t &L, const void *z, const void *uout_t, cons
   p.status = status;
   const int tiles = p.num_m * p.num_n;
   const int grid = tiles < sms ? tiles : sms;
-  tc_out_kernel<<<grid, 192, O_SMEM_BYTES, st>>>(tmA, tmB, p);
+  tc_out_kernel<<<grid, 192, O_SMEM_BYTES, st>>>(tmA, tmB, tmY, p);
   count_launch();
   return launch_status();
 }
