@@ -11,14 +11,15 @@
 //             is applied to the r1 coefficients instead of the r3 values of h)
 //   phase B   for every r2 tile j (n2 = 256/r1 columns):
 //             P[128, r1*n2] = h[128, r3] @ G_j   with the r1 core slices of the tile side by side
-//   epilogue B z[t, j*n2 + s] = sum_a c[t,a] * P[t, a*n2 + s]  in registers -> bf16 -> HBM
+//   epilogue B z[t, j*n2 + s] = sum_a c[t,a] * P[t, a*n2 + s]  in registers -> bf16 -> smem -> TMA store
 //             (model.py:95-98 for all selected experts at once); P is double-buffered in TMEM so
 //             this runs under the next tile's MMAs and the [T, r1*r2] intermediate never leaves the SM.
 //
 // One CTA per 128-token tile, 6 warps: TMA producer, MMA issuer, 4 epilogue warps.
 // Shared memory: phase A uses a ring of {x tile, U_in^T tile, router tile} stages over the whole
 // 224 KB; after the last phase-A MMA has completed, the first 64 KB become h and the rest becomes a
-// 5-stage ring of 32 KB core tiles.  All mbarrier waits are bounded.
+// 4-stage ring of 32 KB core tiles plus two 16 KB staging tiles for the TMA stores of z.
+// All mbarrier waits are bounded.
 #include "common.cuh"
 #include "kernels.h"
 #include "ptx.cuh"
@@ -32,13 +33,14 @@ constexpr int X_TILE_BYTES = TM * 64 * 2;  // 16 KB
 constexpr int H_KBLOCK_BYTES = TM * 64 * 2;
 constexpr int H_REGION_BYTES = 4 * H_KBLOCK_BYTES;  // r3 <= 256
 constexpr int G_STAGE_BYTES = 256 * 64 * 2;         // 32 KB
-constexpr int G_STAGES = 5;
-constexpr int IC_RING_BYTES = H_REGION_BYTES + G_STAGES * G_STAGE_BYTES;  // 224 KB
+constexpr int G_STAGES = 4;
+constexpr int Z_STAGE_BYTES = TM * 64 * 2;  // 16 KB: 128 rows x 64 bf16 columns of z, staged for a TMA store
+constexpr int Z_STAGE_OFF = H_REGION_BYTES + G_STAGES * G_STAGE_BYTES;
+constexpr int IC_RING_BYTES = Z_STAGE_OFF + 2 * Z_STAGE_BYTES;  // 224 KB
 constexpr int IC_SMEM_BYTES = IC_RING_BYTES + 1024;
 constexpr int A_STAGES_MAX = 4;
 constexpr int SCORE_COL = 256;  // TMEM column of the router scores during phase A
 constexpr int kKernelInCore = 2;
-constexpr int RK = 8;  // capacity of the in-kernel top-k list
 
 struct InCoreParams {
   int64_t T;
@@ -55,10 +57,12 @@ struct InCoreParams {
   int32_t *status;
 };
 
-template <int R1>
+// R1: Tucker rank r1 (core slices per r2 tile); RK: capacity of the in-kernel top-k list (>= top_k)
+template <int R1, int RK>
 __global__ void __launch_bounds__(192, 1)
 tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmU,
-                  const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmG, InCoreParams p) {
+                  const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmG,
+                  const __grid_constant__ CUtensorMap tmZ, InCoreParams p) {
   constexpr int N2 = 256 / R1;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_fullA[A_STAGES_MAX], bar_emptyA[A_STAGES_MAX], bar_fullB[G_STAGES],
@@ -85,7 +89,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
     mbar_init(smem_u32(&bar_hready), 4);
     for (int s = 0; s < 2; ++s) { mbar_init(smem_u32(&bar_pfull[s]), 1); mbar_init(smem_u32(&bar_pempty[s]), 4); }
     fence_mbar_init();
-    prefetch_tmap(&tmX); prefetch_tmap(&tmU); prefetch_tmap(&tmG);
+    prefetch_tmap(&tmX); prefetch_tmap(&tmU); prefetch_tmap(&tmG); prefetch_tmap(&tmZ);
     if (p.e_pad) prefetch_tmap(&tmW);
   }
   if (warp == 1) { tmem_alloc(smem_u32(&tmem_base_s), 512); tmem_relinquish(); }
@@ -172,8 +176,10 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
     const bool live = grow < p.T;
     const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
     float c[R1];
+    const bool is_store_thread = (threadIdx.x == 64);
+    const uint32_t zstage0 = ring + Z_STAGE_OFF;
     bool ok = mbar_wait(smem_u32(&bar_accA), 0, p.status, kKernelInCore, 3);
-    ok = __all_sync(0xffffffffu, ok);
+    ok = named_bar_and(2, 128, ok);  // the four epilogue warps continue or leave together
     if (ok) {
       tc_fence_after();
       if (p.fuse_router) {
@@ -258,16 +264,23 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_hready));
 
-      // epilogue B
+      // epilogue B: z is staged in 64-column units (two 16 KB buffers) and written with TMA stores
       for (int j = 0; j < p.n_tiles2 && ok; ++j) {
         const uint32_t slot = j & 1, pph = (j >> 1) & 1;
         ok = mbar_wait(smem_u32(&bar_pfull[slot]), pph, p.status, kKernelInCore, 7);
-        ok = __all_sync(0xffffffffu, ok);
+        ok = named_bar_and(2, 128, ok);
         if (!ok) break;
         tc_fence_after();
         const uint32_t t_p = t_lane + slot * 256;
 #pragma unroll 1
         for (int sc = 0; sc < N2 / 16; ++sc) {
+          const int zc = j * N2 + sc * 16;        // first z column of this 16-column group
+          const int unit = zc >> 6, within = zc & 63;
+          const uint32_t zbuf = zstage0 + (unit & 1) * Z_STAGE_BYTES;
+          if (within == 0) {
+            if (is_store_thread) tma_store_wait_read<1>();  // the store that used this buffer two units ago has read it
+            named_bar_sync(1, 128);
+          }
           float acc[16];
 #pragma unroll
           for (int q = 0; q < 16; ++q) acc[q] = 0.f;
@@ -283,21 +296,28 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
               acc[q] = fmaf(c[a + 1], __uint_as_float(r1v[q]), acc[q]);
             }
           }
-          if (live) {
-            bf16 *dst = p.z + grow * p.r2 + (int64_t)j * N2 + sc * 16;
-            uint4 o0, o1;
-            o0.x = pack_bf16x2(acc[0], acc[1]); o0.y = pack_bf16x2(acc[2], acc[3]);
-            o0.z = pack_bf16x2(acc[4], acc[5]); o0.w = pack_bf16x2(acc[6], acc[7]);
-            o1.x = pack_bf16x2(acc[8], acc[9]); o1.y = pack_bf16x2(acc[10], acc[11]);
-            o1.z = pack_bf16x2(acc[12], acc[13]); o1.w = pack_bf16x2(acc[14], acc[15]);
-            *reinterpret_cast<uint4 *>(dst) = o0;
-            *reinterpret_cast<uint4 *>(dst + 8) = o1;
+#pragma unroll
+          for (int g = 0; g < 2; ++g) {
+            const uint32_t chunk = (uint32_t)((within >> 3) + g) ^ (uint32_t)(row & 7);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(zbuf + row * 128 + chunk * 16),
+                         "r"(pack_bf16x2(acc[8 * g + 0], acc[8 * g + 1])), "r"(pack_bf16x2(acc[8 * g + 2], acc[8 * g + 3])),
+                         "r"(pack_bf16x2(acc[8 * g + 4], acc[8 * g + 5])), "r"(pack_bf16x2(acc[8 * g + 6], acc[8 * g + 7]))
+                         : "memory");
+          }
+          if (within == 48) {
+            fence_proxy_async_smem();
+            named_bar_sync(1, 128);
+            if (is_store_thread) {
+              tma_store_2d(&tmZ, zbuf, unit * 64, m0);
+              tma_store_commit();
+            }
           }
         }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bar_pempty[slot]));
       }
+      if (is_store_thread) tma_store_wait_all();
     }
   }
   tc_fence_before();
@@ -313,9 +333,9 @@ int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared
                       int fuse_router, const float *c_in, int32_t *idx_out, float *gates_out, float *c_out, void *z,
                       int32_t *status, cudaStream_t st) {
   const char *base = reinterpret_cast<const char *>(prepared);
-  if (fuse_router && (P.e_pad > 256 || L.top_k > RK)) return TMOE_ERR_UNSUPPORTED;
+  if (fuse_router && (P.e_pad > 256 || L.top_k > 8)) return TMOE_ERR_UNSUPPORTED;
   if (!fuse_router && !c_in) return TMOE_ERR_NULL;
-  CUtensorMap tmX, tmU, tmW, tmG;
+  CUtensorMap tmX, tmU, tmW, tmG, tmZ;
   int rc = encode_tmap_bf16_2d(&tmX, x, (uint64_t)T_, (uint64_t)L.d_in, TM);
   if (rc) return rc;
   rc = encode_tmap_bf16_2d(&tmU, base + P.uin_t, (uint64_t)L.r3, (uint64_t)L.d_in, (uint32_t)L.r3);
@@ -325,6 +345,8 @@ int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared
                            fuse_router ? (uint32_t)P.e_pad : 16u);
   if (rc) return rc;
   rc = encode_tmap_bf16_2d(&tmG, base + P.g_t, (uint64_t)L.r1 * L.r2, (uint64_t)L.r3, 256);
+  if (rc) return rc;
+  rc = encode_tmap_bf16_2d(&tmZ, z, (uint64_t)T_, (uint64_t)L.r2, TM);
   if (rc) return rc;
 
   InCoreParams p{};
@@ -339,14 +361,15 @@ int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared
 
   const unsigned grid = (unsigned)((T_ + TM - 1) / TM);
   cudaError_t e = cudaSuccess;
-#define TMOE_IC(R)                                                                                              \
-  do {                                                                                                          \
-    e = cudaFuncSetAttribute(tc_in_core_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, IC_SMEM_BYTES); \
-    if (e == cudaSuccess) tc_in_core_kernel<R><<<grid, 192, IC_SMEM_BYTES, st>>>(tmX, tmU, tmW, tmG, p);         \
+#define TMOE_IC(R, K)                                                                                              \
+  do {                                                                                                             \
+    e = cudaFuncSetAttribute(tc_in_core_kernel<R, K>, cudaFuncAttributeMaxDynamicSharedMemorySize, IC_SMEM_BYTES); \
+    if (e == cudaSuccess) tc_in_core_kernel<R, K><<<grid, 192, IC_SMEM_BYTES, st>>>(tmX, tmU, tmW, tmG, tmZ, p);    \
   } while (0)
-  if (L.r1 == 2) TMOE_IC(2);
-  else if (L.r1 == 4) TMOE_IC(4);
-  else if (L.r1 == 8) TMOE_IC(8);
+  const bool small_k = L.top_k <= 2;
+  if (L.r1 == 2) { if (small_k) TMOE_IC(2, 2); else TMOE_IC(2, 8); }
+  else if (L.r1 == 4) { if (small_k) TMOE_IC(4, 2); else TMOE_IC(4, 8); }
+  else if (L.r1 == 8) { if (small_k) TMOE_IC(8, 2); else TMOE_IC(8, 8); }
   else return TMOE_ERR_UNSUPPORTED;
 #undef TMOE_IC
   if (e != cudaSuccess) return TMOE_ERR_CUDA;
