@@ -44,8 +44,16 @@ typedef enum tmoe_status {
 
 typedef enum tmoe_dtype { TMOE_F32 = 0, TMOE_BF16 = 1 } tmoe_dtype_t;
 
-/* Which kernels run.  AUTO: tensor-core path for bf16 shapes it covers when T > 64, else SIMT. */
-typedef enum tmoe_path { TMOE_PATH_AUTO = 0, TMOE_PATH_SIMT = 1, TMOE_PATH_TENSOR = 2 } tmoe_path_t;
+/* Which kernels run.
+ *  SIMT    CUDA-core fp32-FMA kernels: any shape, fp32 or bf16 (the accuracy path).
+ *  TENSOR  tcgen05 tensor-core kernels: bf16, r1 in {2,4,8}, r3 in {64,...,256} multiple of 64,
+ *          d_in and r2 multiples of 64.  Needs the prepared factor set.
+ *  DECODE  bandwidth-shaped kernels for T <= 64 tokens on the same shapes and prepared set
+ *          (tmoe_forward only).
+ *  AUTO    DECODE for T <= 64, TENSOR above, when the shape is covered; else SIMT. */
+typedef enum tmoe_path {
+  TMOE_PATH_AUTO = 0, TMOE_PATH_SIMT = 1, TMOE_PATH_TENSOR = 2, TMOE_PATH_DECODE = 3
+} tmoe_path_t;
 
 /* Sizes of one layer; mirrors the constructor arguments TuckerMoE(d_in, d_out, cfg) with
  * cfg.kmoe_num_experts, kmoe_top_k, kmoe_r1, kmoe_r2, kmoe_r3, rms_norm_eps
@@ -91,8 +99,8 @@ int tmoe_version(void);
 /* Static, human-readable text for a status code. */
 const char *tmoe_status_string(int status);
 
-/* Path that TMOE_PATH_AUTO resolves to for T tokens (TMOE_PATH_SIMT or TMOE_PATH_TENSOR),
- * or a negative status for an invalid layer. */
+/* Path that tmoe_forward would run for T tokens when asked for `path` (for TMOE_PATH_AUTO one of
+ * SIMT / TENSOR / DECODE), or a negative status for an invalid layer or an uncovered request. */
 int tmoe_resolve_path(const tmoe_layer_t *layer, int64_t T, int path);
 
 /* Bytes of the re-laid-out factor set used by the tensor-core path (0 when the layer's
@@ -138,6 +146,7 @@ int tmoe_out(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const voi
 
 /* The whole forward of TuckerMoE.forward (pure_torch_mlx/model.py:68-102) on one stream:
  * x [T, d_in] -> y [T, d_out].  `prepared` may be NULL when the resolved path is SIMT.
+ * The stage entry points above serve SIMT and TENSOR; for them AUTO means SIMT when T <= 64.
  * T == 0 is valid and enqueues nothing. */
 int tmoe_forward(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const void *prepared,
                  const void *x, int64_t T, void *y, const tmoe_extras_t *extras, void *workspace,

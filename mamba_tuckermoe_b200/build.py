@@ -46,6 +46,7 @@ def _stale(target: str, deps) -> bool:
 
 
 def build(verbose: bool = False, force: bool = False) -> str:
+    """Set TMOE_TRACE=1 in the environment to compile the per-CTA phase timestamps in (diagnostic builds)."""
     os.makedirs(LIBDIR, exist_ok=True)
     os.makedirs(OBJDIR, exist_ok=True)
     nvcc = _nvcc()
@@ -57,7 +58,8 @@ def build(verbose: bool = False, force: bool = False) -> str:
         obj = os.path.join(OBJDIR, os.path.basename(src)[:-3] + ".o")
         objs.append(obj)
         if force or _stale(obj, [src] + headers):
-            cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
+            trace = ["-DTMOE_TRACE"] if os.environ.get("TMOE_TRACE") == "1" else []
+            cmd = [nvcc] + NVCC_FLAGS + trace + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
             jobs.append(cmd)
 
     def run(cmd):

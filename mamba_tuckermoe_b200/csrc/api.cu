@@ -25,12 +25,17 @@ int check_layer(const tmoe_layer_t *L) {
   return TMOE_OK;
 }
 
-int resolve(const tmoe_layer_t &L, int64_t T, int path) {
+// allow_decode: tmoe_forward (and the sizing queries) may pick the decode kernels; the stage entry
+// points cannot, so for them AUTO with T <= 64 means the CUDA-core path.
+int resolve(const tmoe_layer_t &L, int64_t T, int path, bool allow_decode = true) {
   if (path == TMOE_PATH_SIMT) return TMOE_PATH_SIMT;
   const bool covered = tensor_path_covers(L);
   if (path == TMOE_PATH_TENSOR) return covered ? (int)TMOE_PATH_TENSOR : (int)TMOE_ERR_UNSUPPORTED;
+  if (path == TMOE_PATH_DECODE) return (covered && T <= 64 && allow_decode) ? (int)TMOE_PATH_DECODE : (int)TMOE_ERR_UNSUPPORTED;
   if (path != TMOE_PATH_AUTO) return TMOE_ERR_UNSUPPORTED;
-  return (covered && T > 64) ? TMOE_PATH_TENSOR : TMOE_PATH_SIMT;
+  if (!covered) return TMOE_PATH_SIMT;
+  if (T > 64) return TMOE_PATH_TENSOR;
+  return allow_decode ? TMOE_PATH_DECODE : TMOE_PATH_SIMT;
 }
 
 WsLayout ws_layout(const tmoe_layer_t &L, int64_t T, int rpath) {
@@ -46,6 +51,11 @@ WsLayout ws_layout(const tmoe_layer_t &L, int64_t T, int rpath) {
     W.scores = W.simt_router_fused ? 0 : take(T * L.n_experts * 4);
     W.h = take(T * L.r3 * 4);
     W.z = take(T * L.r2 * 4);
+  } else if (rpath == TMOE_PATH_DECODE) {
+    // h_raw and scores back to back (no padding in between): cleared together before the split-K atomics
+    W.h = take(T * (L.r3 + L.n_experts) * 4);
+    W.scores = W.h + T * L.r3 * 4;
+    W.z = take(T * L.r2 * 2);
   } else {
     W.scores = W.tc_router_fused ? 0 : take(T * L.n_experts * 4);
     W.h = 0;
@@ -160,7 +170,7 @@ int tmoe_in_core(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const
   if (T == 0) return TMOE_OK;
   if (!x || !c || !z || !workspace) return TMOE_ERR_NULL;
   if (misaligned(x) || misaligned(z) || misaligned(c) || (reinterpret_cast<uintptr_t>(workspace) & 255)) return TMOE_ERR_ALIGN;
-  int rp = resolve(*layer, T, path);
+  int rp = resolve(*layer, T, path, false);
   if (rp < 0) return rp;
   WsLayout W = ws_layout(*layer, T, rp);
   if (workspace_bytes < W.total) return TMOE_ERR_WORKSPACE;
@@ -190,7 +200,7 @@ int tmoe_out(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const voi
   const void *scale = extras ? extras->layer_scale : nullptr;
   if ((residual == nullptr) != (scale == nullptr)) return TMOE_ERR_NULL;
   if (residual && (misaligned(residual) || misaligned(scale))) return TMOE_ERR_ALIGN;
-  int rp = resolve(*layer, T, path);
+  int rp = resolve(*layer, T, path, false);
   if (rp < 0) return rp;
   cudaStream_t st = (cudaStream_t)stream;
   if (rp == TMOE_PATH_SIMT)
@@ -243,6 +253,12 @@ int tmoe_forward(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const
   const char *pb = reinterpret_cast<const char *>(prepared);
   void *z = ws + W.z;
   int32_t *status = reinterpret_cast<int32_t *>(ws);
+  if (rp == TMOE_PATH_DECODE) {
+    const bool taps = extras && (extras->idx_out || extras->gates_out || extras->c_out);
+    return launch_decode(L, x, prepared, P, T, reinterpret_cast<float *>(ws + W.h), scores, z,
+                         taps ? extras->idx_out : nullptr, taps ? extras->gates_out : nullptr,
+                         taps ? extras->c_out : nullptr, residual, scale, y, st);
+  }
   if (W.tc_router_fused) {
     const bool taps = extras && (extras->idx_out || extras->gates_out || extras->c_out);
     rc = launch_tc_in_core(L, x, prepared, P, T, 1, nullptr, taps ? extras->idx_out : nullptr,

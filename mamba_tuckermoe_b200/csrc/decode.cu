@@ -1,0 +1,288 @@
+// Decode-shaped path (T <= 64 tokens, bf16): three bandwidth-shaped kernels that stream the
+// K-major prepared factors once with 128-bit loads and keep the few token rows in shared memory.
+// The layer is memory/latency bound here (7.6 MB of factors against <= 64 token rows), so the
+// tensor cores are not used; every warp owns one output column and all T tokens.
+//
+//   decode_inproj_kernel   h_raw[T, r3] = x @ U_in, scores[T, E] = x @ router_w^T   (model.py:75, 80)
+//                          grid = column groups x K slices of 256; fp32 atomics combine the slices
+//   decode_core_kernel     per CTA prologue: inner RMSNorm statistics, top-k / softmax / c
+//                          (model.py:76-77, 81, 93); then z[t, s] = sum_a c'[t,a] * (hw[t] . core[a][:, s])
+//                          with one warp per z column reading the r1 interleaved core rows (model.py:95-98)
+//   decode_out_kernel      y[t, n] = z[t] . U_out[:, n] + bias (+ residual epilogue)      (model.py:101)
+#include "common.cuh"
+#include "kernels.h"
+#include "routing.cuh"
+
+namespace tmoe {
+
+namespace {
+
+constexpr int kDecWarps = 8;
+constexpr int kKSlice = 256;      // K elements per CTA in the in-projection (one 16-byte load per lane)
+constexpr int kInprojColsPerWarp = 4;
+constexpr int kOutWarps = 16;
+constexpr int kOutKChunk = 1024;  // z columns staged per pass in the out-projection
+
+__device__ __forceinline__ void unpack8(const uint4 &v, float (&o)[8]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    o[2 * q] = __uint_as_float(w[q] << 16);
+    o[2 * q + 1] = __uint_as_float(w[q] & 0xffff0000u);
+  }
+}
+__device__ __forceinline__ float dot8(const float (&a)[8], const float (&b)[8]) {
+  float s = 0.f;
+#pragma unroll
+  for (int q = 0; q < 8; ++q) s = fmaf(a[q], b[q], s);
+  return s;
+}
+
+// Sums N per-lane partial values over the warp.  On return v[0] of lane l holds the total of
+// value index (l % N) (N = 8 or 32): N + ... shuffles instead of 5 per value.
+template <int N>
+__device__ __forceinline__ void warp_reduce_many(float (&v)[N], int lane) {
+  int n = N;
+#pragma unroll
+  for (int m = 16; m >= 1; m >>= 1) {
+    if (m >= N) {  // more lanes than values: plain butterfly on every value
+#pragma unroll
+      for (int i = 0; i < N; ++i) v[i] += __shfl_xor_sync(0xffffffffu, v[i], m);
+    } else {       // halve the value set: lanes with bit m keep the upper half
+      n >>= 1;
+      const bool up = (lane & m) != 0;
+#pragma unroll
+      for (int i = 0; i < N / 2; ++i) {
+        if (i < n) {
+          const float keep = up ? v[i + n] : v[i];
+          const float send = up ? v[i] : v[i + n];
+          v[i] = keep + __shfl_xor_sync(0xffffffffu, send, m);
+        }
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+template <int TMAX>
+__global__ void __launch_bounds__(kDecWarps * 32)
+decode_inproj_kernel(const bf16 *__restrict__ x, const bf16 *__restrict__ uin_t, const bf16 *__restrict__ wr, int T,
+                     int d_in, int r3, int E, float *__restrict__ h_raw, float *__restrict__ scores) {
+  __shared__ __align__(16) bf16 xs[TMAX][kKSlice];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int k0 = blockIdx.y * kKSlice;
+  // stage the K slice of all token rows (zeros beyond T or d_in)
+  for (int i = threadIdx.x; i < TMAX * (kKSlice / 8); i += blockDim.x) {
+    const int t = i / (kKSlice / 8), kk = (i % (kKSlice / 8)) * 8;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (t < T && k0 + kk < d_in) v = __ldg(reinterpret_cast<const uint4 *>(x + (int64_t)t * d_in + k0 + kk));
+    *reinterpret_cast<uint4 *>(&xs[t][kk]) = v;
+  }
+  __syncthreads();
+  const int k = k0 + lane * 8;
+#pragma unroll 1
+  for (int ci = 0; ci < kInprojColsPerWarp; ++ci) {
+    const int n = (blockIdx.x * kDecWarps + warp) * kInprojColsPerWarp + ci;
+    if (n >= r3 + E) break;
+    const bf16 *row = (n < r3) ? uin_t + (int64_t)n * d_in : wr + (int64_t)(n - r3) * d_in;
+    float w8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (k < d_in) unpack8(__ldg(reinterpret_cast<const uint4 *>(row + k)), w8);
+    float *dst = (n < r3) ? h_raw + n : scores + (n - r3);
+    const int ld = (n < r3) ? r3 : E;
+#pragma unroll
+    for (int tb = 0; tb < TMAX; tb += 32) {
+      constexpr int NB = TMAX < 32 ? TMAX : 32;
+      float acc[NB];
+#pragma unroll
+      for (int t = 0; t < NB; ++t) {
+        float x8[8];
+        unpack8(*reinterpret_cast<const uint4 *>(&xs[tb + t][lane * 8]), x8);
+        acc[t] = dot8(x8, w8);
+      }
+      warp_reduce_many<NB>(acc, lane);
+      const int t = tb + (lane % NB);
+      if (lane < NB && t < T) atomicAdd(dst + (int64_t)t * ld, acc[0]);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+template <int TMAX, int R1, int KMAX>
+__global__ void __launch_bounds__(kDecWarps * 32)
+decode_core_kernel(const float *__restrict__ h_raw, const float *__restrict__ scores, const float *__restrict__ normw,
+                   const float *__restrict__ uexp, const bf16 *__restrict__ g_t, int T, int r3, int r2, int E, int top_k,
+                   float eps, bf16 *__restrict__ z, int32_t *__restrict__ idx_out, float *__restrict__ gates_out,
+                   float *__restrict__ c_out) {
+  constexpr int N2 = 256 / R1;
+  extern __shared__ __align__(16) uint8_t dsm[];
+  bf16 *hw = reinterpret_cast<bf16 *>(dsm);                                  // [TMAX][r3]
+  float *cs = reinterpret_cast<float *>(dsm + (size_t)TMAX * r3 * 2);       // [TMAX][R1]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+  // prologue (redundant per CTA, T is tiny): norm statistics, h*w -> bf16, routing, c' = c / rms
+  for (int t = warp; t < TMAX; t += kDecWarps) {
+    if (t < T) {
+      float ss = 0.f;
+      for (int i = lane; i < r3; i += 32) {
+        const float v = h_raw[(int64_t)t * r3 + i];
+        ss = fmaf(v, v, ss);
+        hw[t * r3 + i] = __float2bfloat16_rn(v * normw[i]);
+      }
+      ss = warp_sum(ss);
+      const float inv_rms = 1.f / sqrtf(ss / (float)r3 + eps);
+      TopList<KMAX> sel;
+      sel.init();
+      warp_select_topk<bf16, KMAX>(scores + (int64_t)t * E, E, top_k, lane, sel);
+      const bool tap = (blockIdx.x == 0);
+      emit_token<bf16, KMAX, float>(sel, top_k, E, R1, uexp, 0, lane, tap && idx_out ? idx_out + (int64_t)t * top_k : nullptr,
+                              tap && gates_out ? gates_out + (int64_t)t * top_k : nullptr, cs + t * R1);
+      __syncwarp();
+      if (lane < R1) {
+        const float cv = cs[t * R1 + lane];
+        if (tap && c_out) c_out[(int64_t)t * R1 + lane] = cv;
+        cs[t * R1 + lane] = cv * inv_rms;
+      }
+    } else {
+      for (int i = lane; i < r3; i += 32) hw[t * r3 + i] = __float2bfloat16_rn(0.f);
+      if (lane < R1) cs[t * R1 + lane] = 0.f;
+    }
+  }
+  __syncthreads();
+
+  const int s = blockIdx.x * kDecWarps + warp;  // z column of this warp
+  if (s >= r2) return;
+  const int j = s / N2, sl = s - j * N2;
+  const bf16 *rows = g_t + ((int64_t)j * 256 + sl) * r3;  // slice a is N2 rows further
+#pragma unroll
+  for (int tb = 0; tb < TMAX; tb += 32) {
+    constexpr int NB = TMAX < 32 ? TMAX : 32;
+    float acc[NB];
+#pragma unroll
+    for (int t = 0; t < NB; ++t) acc[t] = 0.f;
+    for (int k = lane * 8; k < r3; k += 256) {
+      float g8[R1][8];
+#pragma unroll
+      for (int a = 0; a < R1; ++a) unpack8(__ldg(reinterpret_cast<const uint4 *>(rows + (int64_t)a * N2 * r3 + k)), g8[a]);
+#pragma unroll
+      for (int t = 0; t < NB; ++t) {
+        float h8[8];
+        unpack8(*reinterpret_cast<const uint4 *>(&hw[(tb + t) * r3 + k]), h8);
+#pragma unroll
+        for (int a = 0; a < R1; ++a) acc[t] = fmaf(cs[(tb + t) * R1 + a], dot8(h8, g8[a]), acc[t]);
+      }
+    }
+    warp_reduce_many<NB>(acc, lane);
+    const int t = tb + (lane % NB);
+    if (lane < NB && t < T) z[(int64_t)t * r2 + s] = __float2bfloat16_rn(acc[0]);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+template <int TMAX>
+__global__ void __launch_bounds__(kOutWarps * 32)
+decode_out_kernel(const bf16 *__restrict__ z, const bf16 *__restrict__ uout_t, const float *__restrict__ bias,
+                  const bf16 *__restrict__ residual, const bf16 *__restrict__ gamma, int T, int r2, int d_out,
+                  bf16 *__restrict__ y) {
+  extern __shared__ __align__(16) uint8_t dsm[];
+  bf16 *zs = reinterpret_cast<bf16 *>(dsm);  // [TMAX][kc]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n = blockIdx.x * kOutWarps + warp;
+  constexpr int NB = TMAX < 32 ? TMAX : 32;
+  constexpr int NG = TMAX / NB;
+  float acc[NG][NB];
+#pragma unroll
+  for (int g = 0; g < NG; ++g)
+#pragma unroll
+    for (int t = 0; t < NB; ++t) acc[g][t] = 0.f;
+  for (int kc0 = 0; kc0 < r2; kc0 += kOutKChunk) {
+    const int kc = min(kOutKChunk, r2 - kc0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < TMAX * (kc / 8); i += blockDim.x) {
+      const int t = i / (kc / 8), kk = (i % (kc / 8)) * 8;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (t < T) v = __ldg(reinterpret_cast<const uint4 *>(z + (int64_t)t * r2 + kc0 + kk));
+      *reinterpret_cast<uint4 *>(&zs[t * kc + kk]) = v;
+    }
+    __syncthreads();
+    if (n < d_out) {
+      for (int k = lane * 8; k < kc; k += 256) {
+        float w8[8];
+        unpack8(__ldg(reinterpret_cast<const uint4 *>(uout_t + (int64_t)n * r2 + kc0 + k)), w8);
+#pragma unroll
+        for (int g = 0; g < NG; ++g)
+#pragma unroll
+          for (int t = 0; t < NB; ++t) {
+            float z8[8];
+            unpack8(*reinterpret_cast<const uint4 *>(&zs[(g * NB + t) * kc + k]), z8);
+            acc[g][t] += dot8(z8, w8);
+          }
+      }
+    }
+  }
+  if (n >= d_out) return;
+#pragma unroll
+  for (int g = 0; g < NG; ++g) {
+    warp_reduce_many<NB>(acc[g], lane);
+    const int t = g * NB + (lane % NB);
+    if (lane < NB && t < T) {
+      float v = acc[g][0] + bias[n];
+      if (residual) v = __bfloat162float(residual[(int64_t)t * d_out + n]) + __bfloat162float(gamma[n]) * v;
+      y[(int64_t)t * d_out + n] = __float2bfloat16_rn(v);
+    }
+  }
+}
+
+template <int TMAX>
+int launch_decode_t(const tmoe_layer_t &L, const void *x, const char *pb, const PreparedLayout &P, int T, float *h_raw,
+                    float *scores, void *z, int32_t *idx_out, float *gates_out, float *c_out, const void *residual,
+                    const void *layer_scale, void *y, cudaStream_t st) {
+  // h_raw and scores are adjacent in the workspace: one clear for the split-K atomics
+  const size_t clear_bytes = (size_t)((char *)(scores + (size_t)T * L.n_experts) - (char *)h_raw);
+  if (cudaMemsetAsync(h_raw, 0, clear_bytes, st) != cudaSuccess) return TMOE_ERR_CUDA;
+  const int ncols = L.r3 + L.n_experts;
+  dim3 g1((ncols + kDecWarps * kInprojColsPerWarp - 1) / (kDecWarps * kInprojColsPerWarp), (L.d_in + kKSlice - 1) / kKSlice);
+  decode_inproj_kernel<TMAX><<<g1, kDecWarps * 32, 0, st>>>((const bf16 *)x, (const bf16 *)(pb + P.uin_t),
+                                                           (const bf16 *)(pb + P.wr_b), T, L.d_in, L.r3, L.n_experts,
+                                                           h_raw, scores);
+  const size_t smem2 = (size_t)TMAX * L.r3 * 2 + (size_t)TMAX * L.r1 * 4;
+  const dim3 g2((L.r2 + kDecWarps - 1) / kDecWarps);
+  cudaError_t e = cudaSuccess;
+#define TMOE_DC(R, K)                                                                                              \
+  do {                                                                                                             \
+    e = cudaFuncSetAttribute(decode_core_kernel<TMAX, R, K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2); \
+    if (e == cudaSuccess)                                                                                          \
+      decode_core_kernel<TMAX, R, K><<<g2, kDecWarps * 32, smem2, st>>>(                                           \
+          h_raw, scores, (const float *)(pb + P.normw), (const float *)(pb + P.uexp), (const bf16 *)(pb + P.g_t), T, \
+          L.r3, L.r2, L.n_experts, L.top_k, L.eps, (bf16 *)z, idx_out, gates_out, c_out);                           \
+  } while (0)
+  const bool k2 = L.top_k <= 2, k8 = L.top_k <= 8;
+  if (L.r1 == 2) { if (k2) TMOE_DC(2, 2); else if (k8) TMOE_DC(2, 8); else TMOE_DC(2, 16); }
+  else if (L.r1 == 4) { if (k2) TMOE_DC(4, 2); else if (k8) TMOE_DC(4, 8); else TMOE_DC(4, 16); }
+  else if (L.r1 == 8) { if (k2) TMOE_DC(8, 2); else if (k8) TMOE_DC(8, 8); else TMOE_DC(8, 16); }
+  else return TMOE_ERR_UNSUPPORTED;
+#undef TMOE_DC
+  if (e != cudaSuccess) return TMOE_ERR_CUDA;
+  const int kc = L.r2 < kOutKChunk ? L.r2 : kOutKChunk;
+  const size_t smem3 = (size_t)TMAX * kc * 2;
+  e = cudaFuncSetAttribute(decode_out_kernel<TMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem3);
+  if (e != cudaSuccess) return TMOE_ERR_CUDA;
+  decode_out_kernel<TMAX><<<(L.d_out + kOutWarps - 1) / kOutWarps, kOutWarps * 32, smem3, st>>>(
+      (const bf16 *)z, (const bf16 *)(pb + P.uout_t), (const float *)(pb + P.bias), (const bf16 *)residual,
+      (const bf16 *)layer_scale, T, L.r2, L.d_out, (bf16 *)y);
+  count_launch(3);
+  return launch_status();
+}
+
+}  // namespace
+
+int launch_decode(const tmoe_layer_t &L, const void *x, const void *prepared, const PreparedLayout &P, int64_t T,
+                  float *h_raw, float *scores, void *z, int32_t *idx_out, float *gates_out, float *c_out,
+                  const void *residual, const void *layer_scale, void *y, cudaStream_t st) {
+  const char *pb = reinterpret_cast<const char *>(prepared);
+  if (T > 64) return TMOE_ERR_UNSUPPORTED;
+  if (T <= 8)
+    return launch_decode_t<8>(L, x, pb, P, (int)T, h_raw, scores, z, idx_out, gates_out, c_out, residual, layer_scale, y, st);
+  return launch_decode_t<64>(L, x, pb, P, (int)T, h_raw, scores, z, idx_out, gates_out, c_out, residual, layer_scale, y, st);
+}
+
+}  // namespace tmoe

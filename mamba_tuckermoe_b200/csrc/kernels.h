@@ -48,4 +48,11 @@ int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared
                       int fuse_router, const float *c_in, int32_t *idx_out, float *gates_out, float *c_out, void *z,
                       int32_t *status, cudaStream_t st);
 
+// ---- decode.cu ----
+// Whole forward for T <= 64 bf16 tokens on the prepared (K-major) factors: split-K in-projection with
+// fp32 atomics into h_raw/scores (adjacent in memory, cleared here), norm + routing + core, out-projection.
+int launch_decode(const tmoe_layer_t &L, const void *x, const void *prepared, const PreparedLayout &P, int64_t T,
+                  float *h_raw, float *scores, void *z, int32_t *idx_out, float *gates_out, float *c_out,
+                  const void *residual, const void *layer_scale, void *y, cudaStream_t st);
+
 }  // namespace tmoe

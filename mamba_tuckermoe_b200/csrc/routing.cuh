@@ -1,0 +1,113 @@
+// Device-side pieces of the routing rule shared by the router, select and decode kernels:
+// a sorted top-k list (higher score first, equal scores -> lower expert index first), the
+// softmax over the k winners and the coefficient vector c = sum_k gate_k * U_expert[idx_k]
+// (pure_torch_mlx/model.py:76-77, 93).
+#pragma once
+
+#include "common.cuh"
+
+namespace tmoe {
+
+template <int KMAX>
+struct TopList {
+  float v[KMAX];
+  int i[KMAX];
+  __device__ __forceinline__ void init() {
+#pragma unroll
+    for (int j = 0; j < KMAX; ++j) { v[j] = -INFINITY; i[j] = 0x7fffffff; }
+  }
+  // Insert (val, e) keeping the list sorted by ranks_before(); entries beyond k are ignored.
+  __device__ __forceinline__ void insert(float val, int e, int k) {
+    float cv = val; int ci = e;
+#pragma unroll
+    for (int j = 0; j < KMAX; ++j) {
+      if (j < k && ranks_before(cv, ci, v[j], i[j])) {
+        float tv = v[j]; int ti = i[j];
+        v[j] = cv; i[j] = ci; cv = tv; ci = ti;
+      }
+    }
+  }
+};
+
+// Writes idx / gates / c for one token from a finished selection list (all lanes hold it).
+// T: storage type the gates are rounded to; TU: element type of the U_expert table.
+template <typename T, int KMAX, typename TU = T>
+__device__ __forceinline__ void emit_token(const TopList<KMAX> &sel, int k, int E, int r1, const TU *__restrict__ uexp,
+                                           int64_t t, int lane, int32_t *__restrict__ idx,
+                                           float *__restrict__ gates, float *__restrict__ c) {
+  float gate[KMAX];
+  {
+    float m = sel.v[0], den = 0.f;
+#pragma unroll
+    for (int j = 0; j < KMAX; ++j) { gate[j] = (j < k) ? expf(sel.v[j] - m) : 0.f; den += gate[j]; }
+    float inv = 1.f / den;
+#pragma unroll
+    for (int j = 0; j < KMAX; ++j) gate[j] = round_to<T>(gate[j] * inv);
+  }
+#pragma unroll
+  for (int j = 0; j < KMAX; ++j) {
+    if (j < k && lane == (j & 31)) {
+      if (idx) idx[t * k + j] = sel.i[j];
+      if (gates) gates[t * k + j] = gate[j];
+    }
+  }
+  for (int a = lane; a < r1; a += 32) {
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < KMAX; ++j) {
+      if (j < k) {
+        int e = min(max(sel.i[j], 0), E - 1);
+        acc = fmaf(gate[j], to_f32(uexp[(int64_t)e * r1 + a]), acc);
+      }
+    }
+    c[t * r1 + a] = acc;
+  }
+}
+
+template <typename T> struct Vec16;
+template <> struct Vec16<float> {
+  static constexpr int N = 4;
+  __device__ static __forceinline__ void load(const float *p, float (&o)[4]) {
+    float4 v = __ldg(reinterpret_cast<const float4 *>(p));
+    o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+  }
+};
+template <> struct Vec16<bf16> {
+  static constexpr int N = 8;
+  __device__ static __forceinline__ void load(const bf16 *p, float (&o)[8]) {
+    uint4 v = __ldg(reinterpret_cast<const uint4 *>(p));
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      o[2 * q] = __uint_as_float(w[q] << 16);
+      o[2 * q + 1] = __uint_as_float(w[q] & 0xffff0000u);
+    }
+  }
+};
+
+
+// Top-k of one token's scores [E] by k passes over the row (all lanes end with the same list).
+// Scores are rounded to the storage type T before they are compared.
+template <typename T, int KMAX>
+__device__ __forceinline__ void warp_select_topk(const float *__restrict__ sr, int E, int k, int lane, TopList<KMAX> &sel) {
+  float pv = INFINITY; int pi = -1;
+#pragma unroll
+  for (int j = 0; j < KMAX; ++j) {
+    if (j < k) {
+      float bv = -INFINITY; int bi = 0x7fffffff;
+      for (int e = lane; e < E; e += 32) {
+        float v = round_to<T>(sr[e]);
+        if (ranks_before(pv, pi, v, e) && ranks_before(v, e, bv, bi)) { bv = v; bi = e; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ranks_before(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+      }
+      sel.v[j] = bv; sel.i[j] = bi; pv = bv; pi = bi;
+    }
+  }
+}
+
+}  // namespace tmoe

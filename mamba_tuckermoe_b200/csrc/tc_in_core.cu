@@ -28,6 +28,18 @@ namespace tmoe {
 
 using namespace ptx;
 
+// Optional per-CTA phase timestamps (build with -DTMOE_TRACE): clock64 deltas from kernel start are written to
+// status words [16 + 8*slot ...] by blocks 0 and gridDim.x-1.  Off in normal builds.
+#ifdef TMOE_TRACE
+#define TMOE_STAMP(i)                                                                       \
+  do {                                                                                      \
+    if (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)                                     \
+      p.status[16 + (blockIdx.x == 0 ? 0 : 8) + (i)] = (int32_t)(clock64() - trace_t0);     \
+  } while (0)
+#else
+#define TMOE_STAMP(i) do { } while (0)
+#endif
+
 constexpr int TM = 128;                    // tokens per CTA
 constexpr int X_TILE_BYTES = TM * 64 * 2;  // 16 KB
 constexpr int H_KBLOCK_BYTES = TM * 64 * 2;
@@ -98,6 +110,9 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_s;
   const uint32_t ringB = ring + H_REGION_BYTES;
+#ifdef TMOE_TRACE
+  const long long trace_t0 = clock64();
+#endif
 
   if (warp == 0) {
     // ------------------------------- TMA producer -------------------------------
@@ -146,8 +161,10 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         umma_commit(smem_u32(&bar_emptyA[s]));
       }
       if (ok) umma_commit(smem_u32(&bar_accA));
+      TMOE_STAMP(0);  // last phase-A MMA issued
       if (ok) ok = mbar_wait(smem_u32(&bar_hready), 0, p.status, kKernelInCore, 4);
       tc_fence_after();
+      TMOE_STAMP(1);  // MMA thread saw h ready
       const uint32_t idescP = umma_idesc_bf16(TM, 256);
       int it = 0;
       for (int j = 0; j < p.n_tiles2 && ok; ++j) {
@@ -182,11 +199,16 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
     ok = named_bar_and(2, 128, ok);  // the four epilogue warps continue or leave together
     if (ok) {
       tc_fence_after();
+      if (threadIdx.x == 64) TMOE_STAMP(2);  // phase A complete (accumulators readable)
       if (p.fuse_router) {
-        // running top-k over the score columns; scores are rounded to bf16 before comparison
-        float sv[RK]; int si[RK];
+        // Running top-k over the score columns, branch-free.  A score rounded to bf16 has 16 significant
+        // bits, so (order-preserving map of those bits) << 16 | (0xFFFF - expert) is a 32-bit key whose
+        // unsigned order is "higher score first, equal scores -> lower expert index first"; the sorted
+        // list is then maintained with integer max/min only (no data-dependent branches, independent
+        // scores pipeline through the levels).
+        uint32_t key[RK];
 #pragma unroll
-        for (int j = 0; j < RK; ++j) { sv[j] = -INFINITY; si[j] = 0x7fffffff; }
+        for (int j = 0; j < RK; ++j) key[j] = 0u;
         for (int cc = 0; cc < p.e_pad / 16; ++cc) {
           uint32_t r[16];
           tmem_ld16(t_lane + SCORE_COL + cc * 16, r);
@@ -194,18 +216,27 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
 #pragma unroll
           for (int q = 0; q < 16; ++q) {
             const int e = cc * 16 + q;
-            if (e < p.E) {
-              float cv = round_to<bf16>(__uint_as_float(r[q])); int ci = e;
+            uint32_t b = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(__uint_as_float(r[q])));
+            b = (b == 0x8000u) ? 0u : b;                                   // -0 and +0 compare equal
+            const uint32_t u = (b & 0x8000u) ? (~b & 0xffffu) : (b | 0x8000u);
+            uint32_t carry = (e < p.E) ? ((u << 16) | (0xffffu - (uint32_t)e)) : 0u;
 #pragma unroll
-              for (int j = 0; j < RK; ++j) {
-                if (j < p.top_k && ranks_before(cv, ci, sv[j], si[j])) {
-                  const float tv = sv[j]; const int ti = si[j];
-                  sv[j] = cv; si[j] = ci; cv = tv; ci = ti;
-                }
-              }
+            for (int j = 0; j < RK; ++j) {
+              const uint32_t hi = max(key[j], carry);
+              carry = min(key[j], carry);
+              key[j] = hi;
             }
           }
         }
+        float sv[RK]; int si[RK];
+#pragma unroll
+        for (int j = 0; j < RK; ++j) {
+          const uint32_t u = key[j] >> 16;
+          const uint32_t b = (u & 0x8000u) ? (u & 0x7fffu) : (~u & 0xffffu);
+          sv[j] = __uint_as_float(b << 16);
+          si[j] = (int)(0xffffu - (key[j] & 0xffffu));
+        }
+        if (threadIdx.x == 64) TMOE_STAMP(6);  // score scan done
         float gate[RK], den = 0.f;
 #pragma unroll
         for (int j = 0; j < RK; ++j) { gate[j] = (j < p.top_k) ? expf(sv[j] - sv[0]) : 0.f; den += gate[j]; }
@@ -225,6 +256,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
             }
           }
         }
+        if (threadIdx.x == 64) TMOE_STAMP(7);  // gates and c done
         if (live && p.c_out) {
 #pragma unroll
           for (int a = 0; a < R1; ++a) p.c_out[grow * R1 + a] = c[a];
@@ -233,6 +265,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
 #pragma unroll
         for (int a = 0; a < R1; ++a) c[a] = live ? __ldg(p.c_in + grow * R1 + a) : 0.f;
       }
+      if (threadIdx.x == 64) TMOE_STAMP(3);  // routing done
       // h row: statistics, weight, bf16, swizzled store (16-byte chunk index XOR row%8 inside 128-byte rows)
       float ss = 0.f;
       for (int cc = 0; cc < p.r3 / 32; ++cc) {
@@ -263,6 +296,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_hready));
+      if (threadIdx.x == 64) TMOE_STAMP(4);  // h written
 
       // epilogue B: z is staged in 64-column units (two 16 KB buffers) and written with TMA stores
       for (int j = 0; j < p.n_tiles2 && ok; ++j) {
@@ -318,6 +352,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         if (lane == 0) mbar_arrive(smem_u32(&bar_pempty[slot]));
       }
       if (is_store_thread) tma_store_wait_all();
+      if (threadIdx.x == 64) TMOE_STAMP(5);  // z stored
     }
   }
   tc_fence_before();
