@@ -41,6 +41,8 @@ WORKLOADS = {
     "cfg2": ("cfg2", 32768, "prefill bf16 T=32768 d_in=1536 d_out=2304 E=64 top2 r=(4,256,1024)"),
     "cfg0": ("cfg0", 512, "fp32 T=512 d_in=1536 d_out=2304 E=8 top2 r=(4,256,1024)"),
     "cfg1": ("cfg1", 64, "decode bf16 T=64 d_in=1536 d_out=2304 E=8 top2 r=(4,256,1024)"),
+    "cfg1_t8": ("cfg1", 8, "decode bf16 T=8 d_in=1536 d_out=2304 E=8 top2 r=(4,256,1024)"),
+    "cfg1_t1": ("cfg1", 1, "decode bf16 T=1 d_in=1536 d_out=2304 E=8 top2 r=(4,256,1024)"),
     "cfg3": ("cfg3", 16384, "bf16 T=16384 E=64 top2"),
 }
 N_INPUT_SETS = 4  # rotating x buffers so that no step re-reads the previous step's lines from L2
@@ -280,11 +282,20 @@ def main():
     flops_tok = shape.flops_per_token()
     dom = kern["dominant"]
     peak_tf = peaks["bf16_tflops"]
-    roofline = {
-        "bound": "tensor", "kernel": dom["name"], "achieved": dom["tflops"], "peak": peak_tf, "unit": "TFLOP/s",
-        "frac": dom["tflops"] / peak_tf, "traffic": None, "peak_source": f"{peaks['source']} (burst bf16)",
-        "flops_per_launch": dom["flops"], "us_per_launch": dom["us"],
-    }
+    if dom is None:  # decode-shaped call: bound by streaming the factor set
+        d = kern["decode"]
+        roofline = {
+            "bound": "hbm", "kernel": "decode forward (3 kernels + clear)", "achieved": d["gbs_cold"],
+            "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": d["gbs_cold"] / peaks["hbm_gbs"], "traffic": None,
+            "peak_source": f"{peaks['source']} (copy bandwidth)", "bytes_per_call": d["bytes"],
+            "us_per_call_cold_l2": d["us_cold"], "us_per_call_warm": d["us_warm"], "us_per_call_graph": d["us_graph"],
+        }
+    else:
+        roofline = {
+            "bound": "tensor", "kernel": dom["name"], "achieved": dom["tflops"], "peak": peak_tf, "unit": "TFLOP/s",
+            "frac": dom["tflops"] / peak_tf, "traffic": None, "peak_source": f"{peaks['source']} (burst bf16)",
+            "flops_per_launch": dom["flops"], "us_per_launch": dom["us"],
+        }
     line = {
         "metric": "tucker_moe_layer_tokens_per_sec", "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
@@ -314,16 +325,83 @@ def main():
         dist.destroy_process_group()
 
 
+def decode_times(lib, _lib, layer, shape, dtype, x, T, reps=30):
+    """Decode-shaped call (T <= 64): whole forward through tmoe_forward, CUDA events on the launching
+    stream.  'cold': L2 flushed before every call, so the factors come from HBM; 'warm': back-to-back
+    calls (factors L2-resident); 'graph': warm calls replayed from one CUDA graph of 20 forwards."""
+    L = _lib.layer_struct(shape, dtype)
+    fd = {"router_w": layer.router.weight, "U_in": layer.U_in, "inner_norm_w": layer.inner_norm.weight,
+          "U_expert": layer.U_expert, "core": layer.core, "U_out": layer.U_out, "bias": layer.bias}
+    F = _lib.factors_struct(fd)
+    ws = _lib.alloc_workspace(L, T, 3)
+    prep = _lib.alloc_prepared(L, F)
+    y = torch.empty(T, shape.d_out, dtype=dtype, device=x.device)
+    flush = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device=x.device)
+
+    def call():
+        rc = lib.tmoe_forward(C.byref(L), C.byref(F), prep.data_ptr(), x.data_ptr(), T, y.data_ptr(), None,
+                              ws.data_ptr(), ws.numel(), 3, _lib.current_stream_ptr())
+        assert rc == 0, _lib.status_string(rc)
+
+    for _ in range(3):
+        call()
+    torch.cuda.synchronize()
+    cold = []
+    for _ in range(reps):
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(); call(); b.record()
+        cold.append((a, b))
+    torch.cuda.synchronize()
+    us_cold = statistics.mean(a.elapsed_time(b) for a, b in cold) * 1e3
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        call()
+    b.record(); torch.cuda.synchronize()
+    us_warm = a.elapsed_time(b) * 1e3 / reps
+    us_graph = None
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            call()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                for _ in range(20):
+                    call()
+            g.replay(); side.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(side)
+            for _ in range(5):
+                g.replay()
+            b.record(side); side.synchronize()
+            us_graph = a.elapsed_time(b) * 1e3 / 100
+        torch.cuda.current_stream().wait_stream(side)
+    except Exception as e:  # graph capture is a convenience measurement, not the product path
+        us_graph = None
+    es = x.element_size()
+    factor_bytes = shape.factor_elems() * es
+    alg_bytes = factor_bytes + T * (shape.d_in + shape.d_out) * es
+    return {"us_cold": us_cold, "us_warm": us_warm, "us_graph": us_graph, "bytes": alg_bytes,
+            "gbs_cold": alg_bytes / us_cold / 1e3}
+
+
 def per_kernel_times(lib, _lib, layer, shape, dtype, x, T, path, reps=20):
     """CUDA-event time of each stage through the C-ABI stage entry points, on the current stream."""
     L = _lib.layer_struct(shape, dtype)
     rpath = lib.tmoe_resolve_path(C.byref(L), T, path)
+    if rpath == 3:
+        d = decode_times(lib, _lib, layer, shape, dtype, x, T)
+        return {"all": {"decode_forward": d, "path": "decode"}, "dominant": None, "decode": d}
     fd = {"router_w": layer.router.weight, "U_in": layer.U_in, "inner_norm_w": layer.inner_norm.weight,
           "U_expert": layer.U_expert, "core": layer.core, "U_out": layer.U_out, "bias": layer.bias}
     F = _lib.factors_struct(fd)
     ws = _lib.alloc_workspace(L, T, rpath)
     ws_router = _lib.alloc_workspace(L, T, 1)  # the stand-alone router entry point uses the CUDA-core layout
     prep = _lib.alloc_prepared(L, F) if rpath == 2 else None
+    if rpath == 1:
+        path = 1
     pp = prep.data_ptr() if prep is not None else None
     zdt = torch.bfloat16 if rpath == 2 else torch.float32
     z = torch.empty(T, shape.r2, dtype=zdt, device=x.device)

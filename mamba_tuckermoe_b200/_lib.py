@@ -9,7 +9,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG, "lib", "libtmoe_b200.so")
 
 TMOE_F32, TMOE_BF16 = 0, 1
-PATH_AUTO, PATH_SIMT, PATH_TENSOR = 0, 1, 2
+PATH_AUTO, PATH_SIMT, PATH_TENSOR, PATH_DECODE = 0, 1, 2, 3
 ERR_DEVICE_WAIT = -9
 
 # every symbol the header declares; checked when the library is loaded

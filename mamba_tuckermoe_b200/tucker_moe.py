@@ -19,10 +19,10 @@ import torch
 import torch.nn as nn
 
 from . import _lib
-from ._lib import PATH_AUTO, PATH_SIMT, PATH_TENSOR, Extras, Factors, Layer
+from ._lib import PATH_AUTO, PATH_DECODE, PATH_SIMT, PATH_TENSOR, Extras, Factors, Layer
 
 __all__ = ["TuckerMoE", "TuckerMoEConfig", "RMSNorm", "tucker_moe_forward", "tucker_moe_forward_taps", "prepare_factors",
-           "PATH_AUTO", "PATH_SIMT", "PATH_TENSOR"]
+           "PATH_AUTO", "PATH_SIMT", "PATH_TENSOR", "PATH_DECODE"]
 
 
 @dataclass
@@ -158,7 +158,7 @@ def _run(x, router_w, U_in, inner_norm_w, eps, U_expert, core, U_out, bias, top_
         rpath = _lib.check(lib.tmoe_resolve_path(C.byref(layer), T, path), "tmoe_resolve_path")
         factors = Factors(*[p.data_ptr() for p in params])
         prepared_ptr = None
-        if rpath == PATH_TENSOR:
+        if rpath in (PATH_TENSOR, PATH_DECODE):
             if prepared is None:  # functional call without a cached set: prepare for this call
                 prepared = prepare_factors(router_w, U_in, inner_norm_w, eps, U_expert, core, U_out, bias, top_k)
             prepared_ptr = prepared.data_ptr()
@@ -267,8 +267,7 @@ class TuckerMoE(nn.Module):
         version, dtype or device changes; None when this call will not use that path."""
         if not x.is_cuda or x.dtype != torch.bfloat16:
             return None
-        T = x.numel() // max(x.shape[-1], 1)
-        if self.path == PATH_SIMT or (self.path == PATH_AUTO and T <= 64):
+        if self.path == PATH_SIMT:
             return None
         ps = self._params()
         key = _param_key(ps)

@@ -69,10 +69,13 @@ def test_path_resolution_and_sizes():
     lib = _lib.load()
     cfg2 = _layer(d_in=1536, d_out=2304, n_experts=64, top_k=2, r1=4, r2=1024, r3=256, dtype=_lib.TMOE_BF16, eps=1e-6)
     assert lib.tmoe_resolve_path(C.byref(cfg2), 32768, 0) == 2
-    assert lib.tmoe_resolve_path(C.byref(cfg2), 64, 0) == 1
+    assert lib.tmoe_resolve_path(C.byref(cfg2), 64, 0) == 3     # decode-shaped kernels
+    assert lib.tmoe_resolve_path(C.byref(cfg2), 65, 3) == -6
+    assert lib.tmoe_resolve_path(C.byref(cfg2), 1, 3) == 3
     assert lib.tmoe_resolve_path(C.byref(cfg2), 64, 2) == 2
     f32 = _layer(d_in=1536, d_out=2304, r2=1024, r3=256)
     assert lib.tmoe_resolve_path(C.byref(f32), 32768, 0) == 1
+    assert lib.tmoe_resolve_path(C.byref(f32), 8, 3) == -6
     assert lib.tmoe_prepared_bytes(C.byref(f32)) == 0
     n = lib.tmoe_prepared_bytes(C.byref(cfg2))
     raw = 2 * (256 * 1536 + 64 * 1536 + 4 * 1024 * 256 + 2304 * 1024) + 4 * (256 + 2304 + 64 * 4)

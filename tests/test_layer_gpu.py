@@ -10,7 +10,7 @@ import torch
 
 from golden_cases import ALL_CASES, BF16_CASES, F32_CASES, load_case
 from gpu_util import build_module
-from mamba_tuckermoe_b200 import PATH_AUTO, PATH_SIMT, PATH_TENSOR, read_device_status
+from mamba_tuckermoe_b200 import PATH_AUTO, PATH_DECODE, PATH_SIMT, PATH_TENSOR, read_device_status
 from oracle.tucker_moe_oracle import (LayerShape, classify_topk, layer_forward, layer_forward_f64, make_factors,
                                       make_tokens, max_abs, rel_fro)
 
@@ -108,6 +108,43 @@ def test_tensor_path_matches_oracle(shape, T):
     assert torch.equal(m(x.cuda()), y)
 
 
+DECODE_SHAPES = [
+    (LayerShape(1536, 2304, 8, 2, 4, 256, 1024, 1e-6), 1),
+    (LayerShape(1536, 2304, 8, 2, 4, 256, 1024, 1e-6), 8),
+    (LayerShape(1536, 2304, 8, 2, 4, 256, 1024, 1e-6), 64),
+    (LayerShape(1536, 2304, 64, 2, 4, 256, 1024, 1e-6), 33),
+    (LayerShape(192, 320, 40, 8, 8, 192, 192, 1e-6), 5),
+    (LayerShape(256, 264, 24, 12, 2, 128, 256, 1e-5), 9),
+    (LayerShape(3072, 4608, 256, 8, 8, 256, 2048, 1e-6), 17),   # r2 > one staged chunk of z
+]
+
+
+@pytest.mark.parametrize("shape,T", DECODE_SHAPES)
+def test_decode_path_matches_oracle(shape, T):
+    """Bandwidth-shaped kernels for T <= 64 vs the bf16 reference restatement and float64 algebra."""
+    x, f = _tensor_case(shape, T, seed=6000 + T, router_std=None if shape.E >= 40 else 0.02)
+    m = build_module(shape, f, torch.bfloat16, path=PATH_DECODE)
+    y, taps = m.forward_with_routing(x.cuda())
+    torch.cuda.synchronize()
+    y_ref, rt = layer_forward(x, f, shape.top_k, shape.eps, return_taps=True)
+    check_against(y, taps, y_ref, rt["idx"], rt["scores"], torch.bfloat16, x, f, shape)
+    y64, _ = layer_forward_f64(x, f, shape.top_k, shape.eps, idx=taps[0].cpu(), round_scores_to=torch.bfloat16)
+    assert rel_fro(y.float().cpu(), y64) <= 1e-2
+    # AUTO picks the same kernels for these sizes; calling twice gives identical bits up to the atomics' order
+    m.path = PATH_AUTO
+    assert rel_fro(m(x.cuda()).float().cpu(), y.float().cpu()) < 5e-3
+
+
+@pytest.mark.parametrize("name", BF16_CASES)
+def test_decode_path_matches_reference_golden(name):
+    shape, x, f, dtype, g = load_case(name)
+    if shape.r3 % 64 or x.numel() // shape.d_in > 64:
+        pytest.skip("shape not covered by the decode path")
+    m = build_module(shape, f, dtype, path=PATH_DECODE)
+    y, taps = m.forward_with_routing(x.cuda())
+    check_against(y, taps, g["y"], g["idx"], g["scores"], dtype, x, f, shape)
+
+
 @pytest.mark.parametrize("name", BF16_CASES)
 def test_tensor_path_matches_reference_golden(name):
     shape, x, f, dtype, g = load_case(name)
@@ -129,14 +166,15 @@ def test_tensor_and_simt_paths_agree():
     assert rel_fro(a.float().cpu()[same], b.float().cpu()[same]) < 1e-2
 
 
-@pytest.mark.parametrize("path", [PATH_SIMT, PATH_TENSOR])
+@pytest.mark.parametrize("path", [PATH_SIMT, PATH_TENSOR, PATH_DECODE])
 def test_fused_residual_epilogue(path):
     """residual + layer_scale * layer(x) equals the callers' composition (model.py:259-260, 340-341)."""
     shape = LayerShape(128, 64, 16, 2, 4, 64, 128, 1e-6)
-    x, f = _tensor_case(shape, 130, seed=5)
+    n_tok = 40 if path == PATH_DECODE else 130
+    x, f = _tensor_case(shape, n_tok, seed=5)
     m = build_module(shape, f, torch.bfloat16, path=path)
     g = torch.Generator().manual_seed(1)
-    res = torch.randn(130, shape.d_out, generator=g).bfloat16().cuda()
+    res = torch.randn(n_tok, shape.d_out, generator=g).bfloat16().cuda()
     gamma = (1 + 0.1 * torch.randn(shape.d_out, generator=g)).bfloat16().cuda()
     y = m(x.cuda()).float()
     fused = m.forward_fused_residual(x.cuda(), res, gamma).float()
@@ -150,7 +188,7 @@ def test_auto_path_and_leading_shapes():
     m = build_module(shape, f, torch.bfloat16, path=PATH_AUTO)
     y = m(x.cuda())
     assert y.shape == (2, 48, 2304)
-    y1 = m(x.cuda()[0, :1])     # T=1 -> CUDA-core path
+    y1 = m(x.cuda()[0, :1])     # T=1 -> decode-shaped kernels
     assert y1.shape == (1, 2304)
     y_ref = layer_forward(x, f, shape.top_k, shape.eps)
     assert rel_fro(y.float().cpu(), y_ref.float()) < 3e-2
