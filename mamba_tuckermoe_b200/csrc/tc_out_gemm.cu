@@ -7,8 +7,9 @@
 //            128-byte swizzle) into a 4-stage shared-memory ring, mbarrier complete_tx.
 //   warp 1   one elected thread issues tcgen05.mma (128 x 256 x 16, bf16 -> fp32) into one of two
 //            256-column TMEM accumulators and commits stage-free / accumulator-full barriers.
-//   warps 2-5 epilogue: tcgen05.ld of the accumulator (thread = output row), bias / residual /
-//            layer-scale in fp32, bf16 pack, 16-byte global stores; runs under the next tile's MMAs.
+//   warps 2-9 epilogue: tcgen05.ld of the accumulator (thread = output row, two warps per row quadrant
+//            splitting the columns), bias / residual / layer-scale in fp32, bf16 pack into a swizzled
+//            4 KB staging tile per warp, TMA store; runs under the next tile's MMAs.
 // Every mbarrier wait is bounded and reports through the workspace status words.
 #include "common.cuh"
 #include "kernels.h"
@@ -55,8 +56,10 @@ constexpr int OM = 128, ON = 256, OKB = 64, OSTAGES = 4;
 constexpr int O_A_BYTES = OM * OKB * 2;   // 16 KB
 constexpr int O_B_BYTES = ON * OKB * 2;   // 32 KB
 constexpr int O_STAGE_BYTES = O_A_BYTES + O_B_BYTES;
-constexpr int O_Y_BYTES = OM * 64 * 2;  // 16 KB: 128 rows x 64 bf16 output columns
-constexpr int O_SMEM_BYTES = OSTAGES * O_STAGE_BYTES + 2 * O_Y_BYTES + 1024;
+constexpr int O_EPI_WARPS = 8;
+constexpr int O_THREADS = (2 + O_EPI_WARPS) * 32;
+constexpr int O_Y_BYTES = 32 * 64 * 2;  // 4 KB per epilogue warp: 32 rows x 64 bf16 output columns
+constexpr int O_SMEM_BYTES = OSTAGES * O_STAGE_BYTES + O_EPI_WARPS * O_Y_BYTES + 1024;
 constexpr int kKernelOut = 3;
 
 struct OutParams {
@@ -70,7 +73,7 @@ struct OutParams {
   int32_t *status;
 };
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(O_THREADS, 1)
 tc_out_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
               const __grid_constant__ CUtensorMap tmY, OutParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -82,7 +85,7 @@ tc_out_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < OSTAGES; ++s) { mbar_init(smem_u32(&bar_full[s]), 1); mbar_init(smem_u32(&bar_empty[s]), 1); }
-    for (int s = 0; s < 2; ++s) { mbar_init(smem_u32(&bar_tfull[s]), 1); mbar_init(smem_u32(&bar_tempty[s]), 4); }
+    for (int s = 0; s < 2; ++s) { mbar_init(smem_u32(&bar_tfull[s]), 1); mbar_init(smem_u32(&bar_tempty[s]), O_EPI_WARPS); }
     fence_mbar_init();
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmB);
@@ -139,40 +142,48 @@ tc_out_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
       }
     }
   } else {
+    // Eight epilogue warps: warp w may read TMEM lanes 32*(w%4)..+31, so two warps share each row
+    // quadrant and split the tile's 256 columns.  Each warp stages 32 rows x 64 columns (4 KB, swizzled)
+    // and issues its own TMA store, so the warps never wait for one another.
+    const int ew = warp - 2;
     const int quad = warp & 3;
+    const int half = ew >> 2;
     const int row_in_tile = quad * 32 + lane;
-    const bool is_store_thread = (threadIdx.x == 64);
-    const uint32_t stage0 = ring + OSTAGES * O_STAGE_BYTES;  // two 16 KB output staging tiles
-    uint32_t tcount = 0, chunk_no = 0;
+    const uint32_t stage_buf = ring + OSTAGES * O_STAGE_BYTES + ew * O_Y_BYTES;
+    uint32_t tcount = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
       const int m0 = (tile / p.num_n) * OM, n0 = (tile % p.num_n) * ON;
       const uint32_t slot = tcount & 1, aph = (tcount >> 1) & 1;
       ok = mbar_wait(smem_u32(&bar_tfull[slot]), aph, p.status, kKernelOut, 3);
-      ok = named_bar_and(2, 128, ok);  // all four epilogue warps continue or leave together (they share barriers below)
+      ok = __all_sync(0xffffffffu, ok);  // the TMEM loads below are warp-collective
       if (!ok) break;
       tc_fence_after();
       const int64_t row = (int64_t)m0 + row_in_tile;
-      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + slot * ON;
+      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + slot * ON + half * 128;
 #pragma unroll 1
-      for (int cc = 0; cc < ON / 64; ++cc, ++chunk_no) {
-        // 64 output columns per pass: TMEM -> registers -> bf16 -> swizzled staging tile -> TMA store
-        const uint32_t stage_buf = stage0 + (chunk_no & 1) * O_Y_BYTES;
-        if (is_store_thread) tma_store_wait_read<1>();  // the store that used this buffer two passes ago has read it
-        named_bar_sync(1, 128);
-        const int col0 = n0 + cc * 64;
+      for (int cc = 0; cc < 2; ++cc) {
+        const int col0 = n0 + half * 128 + cc * 64;
+        uint32_t r[2][32];
+        tmem_ld32(t_row + cc * 64, r[0]);
+        tmem_ld32(t_row + cc * 64 + 32, r[1]);
+        tmem_ld_wait(r[0], r[1]);
+        if (cc == 1) {  // this warp has read its whole share of the accumulator
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[slot]));
+        }
+        if (lane == 0) tma_store_wait_read<0>();  // the previous store has finished reading the staging tile
+        __syncwarp();
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t r[32];
-          tmem_ld32(t_row + cc * 64 + half * 32, r);
-          tmem_ld_wait(r);
+        for (int h2 = 0; h2 < 2; ++h2) {
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
-            const int col = col0 + half * 32 + g * 8;
+            const int col = col0 + h2 * 32 + g * 8;
             float v[8];
 #pragma unroll
-            for (int q = 0; q < 8; ++q) v[q] = __uint_as_float(r[g * 8 + q]);
-            if (col < p.N) {  // N % 8 == 0, so a group of 8 is entirely in or out; columns >= N are clipped by the store
+            for (int q = 0; q < 8; ++q) v[q] = __uint_as_float(r[h2][g * 8 + q]);
+            if (col < p.N) {  // N % 8 == 0: a group of 8 is entirely in or out; columns >= N are clipped by the store
               const float4 b0 = __ldg(reinterpret_cast<const float4 *>(p.bias + col));
               const float4 b1 = __ldg(reinterpret_cast<const float4 *>(p.bias + col + 4));
               v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
@@ -188,26 +199,23 @@ tc_out_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                 }
               }
             }
-            // 16-byte chunk (half*4+g) of this thread's 128-byte row, XOR-swizzled like the TMA box expects
-            const uint32_t chunk = (uint32_t)(half * 4 + g) ^ (uint32_t)(row_in_tile & 7);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_buf + row_in_tile * 128 + chunk * 16),
+            // 16-byte chunk (h2*4+g) of this lane's 128-byte row, XOR-swizzled as the TMA box expects
+            const uint32_t chunk = (uint32_t)(h2 * 4 + g) ^ (uint32_t)(lane & 7);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_buf + lane * 128 + chunk * 16),
                          "r"(pack_bf16x2(v[0], v[1])), "r"(pack_bf16x2(v[2], v[3])), "r"(pack_bf16x2(v[4], v[5])),
                          "r"(pack_bf16x2(v[6], v[7]))
                          : "memory");
           }
         }
         fence_proxy_async_smem();
-        named_bar_sync(1, 128);
-        if (is_store_thread && col0 < p.N) {
-          tma_store_2d(&tmY, stage_buf, col0, m0);
+        __syncwarp();
+        if (lane == 0 && col0 < p.N) {
+          tma_store_2d(&tmY, stage_buf, col0, m0 + quad * 32);
           tma_store_commit();
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[slot]));
     }
-    if (is_store_thread) tma_store_wait_all();
+    if (lane == 0) tma_store_wait_all();
   }
   tc_fence_before();
   __syncthreads();
@@ -221,7 +229,7 @@ tc_out_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
 int launch_tc_out(const tmoe_layer_t &L, const void *z, const void *uout_t, const float *bias, const void *residual,
                   const void *layer_scale, int64_t T_, void *y, int32_t *status, cudaStream_t st) {
   CUtensorMap tmA, tmB, tmY;
-  int rc = encode_tmap_bf16_2d(&tmY, y, (uint64_t)T_, (uint64_t)L.d_out, OM);
+  int rc = encode_tmap_bf16_2d(&tmY, y, (uint64_t)T_, (uint64_t)L.d_out, 32);
   if (rc) return rc;
   rc = encode_tmap_bf16_2d(&tmA, z, (uint64_t)T_, (uint64_t)L.r2, OM);
   if (rc) return rc;
@@ -243,7 +251,7 @@ int launch_tc_out(const tmoe_layer_t &L, const void *z, const void *uout_t, cons
   p.status = status;
   const int tiles = p.num_m * p.num_n;
   const int grid = tiles < sms ? tiles : sms;
-  tc_out_kernel<<<grid, 192, O_SMEM_BYTES, st>>>(tmA, tmB, tmY, p);
+  tc_out_kernel<<<grid, O_THREADS, O_SMEM_BYTES, st>>>(tmA, tmB, tmY, p);
   count_launch();
   return launch_status();
 }
