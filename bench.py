@@ -11,8 +11,9 @@ scaling) and `value` is tokens/s summed over all ranks, timed with CUDA events, 
 The JSON line also carries
   roofline      achieved TFLOP/s of the dominant kernel (algorithmic FLOPs / CUDA-event time)
                 against the measured bf16 peak in MEASURED_PEAKS.json
-  e2e           the same metric through the public module call with HOST buffers: pinned
-                host -> device copy of x and device -> host copy of y inside the timed region
+  e2e           the same metric through the public call for host-resident activations
+                (TuckerMoE.forward_host): pinned host -> device copy of x, the kernels and the
+                device -> host copy of y are all inside the timed region, chunk-pipelined on 3 streams
   cpu_baseline  the CPU restatement of the reference layer on this host (rank 0, N=1 only)
   clocks        SM clock / throttle reasons sampled with nvidia-smi during the timed region
 
@@ -260,13 +261,11 @@ def main():
         # ---------------- end to end with host buffers ----------------
         e2e_steps = max(2, min(args.e2e_steps, args.steps))
         for i in range(2):
-            xd = x_host[i % N_INPUT_SETS].to(dev, non_blocking=True)
-            y_host.copy_(layer(xd), non_blocking=True)
+            layer.forward_host(x_host[i % N_INPUT_SETS], out=y_host)
         barrier()
         ev0.record()
         for i in range(e2e_steps):
-            xd = x_host[i % N_INPUT_SETS].to(dev, non_blocking=True)
-            y_host.copy_(layer(xd), non_blocking=True)
+            layer.forward_host(x_host[i % N_INPUT_SETS], out=y_host)
         ev1.record()
         barrier()
         e_ms = torch.tensor([ev0.elapsed_time(ev1)], dtype=torch.float64, device=dev)

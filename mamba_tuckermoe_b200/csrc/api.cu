@@ -57,7 +57,7 @@ WsLayout ws_layout(const tmoe_layer_t &L, int64_t T, int rpath) {
     W.scores = W.h + T * L.r3 * 4;
     W.z = take(T * L.r2 * 2);
   } else {
-    W.scores = W.tc_router_fused ? 0 : take(T * L.n_experts * 4);
+    W.scores = W.tc_router_fused ? 0 : take(T * align_up(L.n_experts, 16) * 2);  // bf16 [T, e_pad], made by the GEMM kernel
     W.h = 0;
     W.z = take(T * L.r2 * 2);
   }
@@ -182,7 +182,8 @@ int tmoe_in_core(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const
     return launch_simt_core(*layer, h, c, factors->core, T, reinterpret_cast<float *>(z), st);
   }
   if (!prepared) return TMOE_ERR_NULL;
-  return launch_tc_in_core(*layer, x, prepared, prepared_layout(*layer), T, 0, c, nullptr, nullptr, nullptr, z,
+  return launch_tc_in_core(*layer, x, prepared, prepared_layout(*layer), T, 0, c,
+                           reinterpret_cast<float *>(ws + W.c), nullptr, nullptr, nullptr, z,
                            reinterpret_cast<int32_t *>(ws), st);
 }
 
@@ -261,11 +262,17 @@ int tmoe_forward(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const
   }
   if (W.tc_router_fused) {
     const bool taps = extras && (extras->idx_out || extras->gates_out || extras->c_out);
-    rc = launch_tc_in_core(L, x, prepared, P, T, 1, nullptr, taps ? extras->idx_out : nullptr,
+    rc = launch_tc_in_core(L, x, prepared, P, T, 1, nullptr, reinterpret_cast<float *>(ws + W.c),
+                           taps ? extras->idx_out : nullptr,
                            taps ? extras->gates_out : nullptr, taps ? extras->c_out : nullptr, z, status, st);
   } else {
-    if ((rc = router_simt(L, *factors, x, T, false, scores, idx, gates, c, st))) return rc;
-    rc = launch_tc_in_core(L, x, prepared, P, T, 0, c, nullptr, nullptr, nullptr, z, status, st);
+    // scores = x @ router_w^T on the tensor cores (bf16 out = the reference's rounding), then the select kernel
+    if ((rc = launch_tc_gemm_bf16(x, pb + P.wr_b, nullptr, nullptr, nullptr, T, P.e_pad, L.d_in, scores, status, st)))
+      return rc;
+    if ((rc = launch_select_bf16_scores(L, scores, P.e_pad, factors->U_expert, T, idx, gates, c, st))) return rc;
+    // c_work may alias c: every row is read by its own thread before that thread overwrites it
+    rc = launch_tc_in_core(L, x, prepared, P, T, 0, c, reinterpret_cast<float *>(ws + W.c), nullptr, nullptr, nullptr, z,
+                           status, st);
   }
   if (rc) return rc;
   return launch_tc_out(L, z, pb + P.uout_t, reinterpret_cast<const float *>(pb + P.bias), residual, scale, T, y, status,

@@ -12,6 +12,9 @@ int launch_router_fused(const tmoe_layer_t &L, const void *x, const void *wr, co
                         int32_t *idx, float *gates, float *c, cudaStream_t st);
 int launch_select(const tmoe_layer_t &L, const float *scores, const void *uexp, int64_t T, int32_t *idx,
                   float *gates, float *c, cudaStream_t st);
+// same selection from bf16 scores [T, ld] (ld >= E: row pitch), bf16 layer
+int launch_select_bf16_scores(const tmoe_layer_t &L, const void *scores, int ld, const void *uexp, int64_t T,
+                              int32_t *idx, float *gates, float *c, cudaStream_t st);
 
 // ---- simt_gemm.cu ----
 // scores[T, E] (fp32) = x @ router_w^T
@@ -40,13 +43,17 @@ int launch_prepare(const tmoe_layer_t &L, const tmoe_factors_t &F, void *prepare
 int launch_tc_out(const tmoe_layer_t &L, const void *z, const void *uout_t, const float *bias, const void *residual,
                   const void *layer_scale, int64_t T, void *y, int32_t *status, cudaStream_t st);
 
+// General form of the same kernel (used for the router scores when E is too large for the in-kernel router).
+int launch_tc_gemm_bf16(const void *A, const void *B_t, const float *bias, const void *residual, const void *gamma,
+                        int64_t M, int N, int K, void *y, int32_t *status, cudaStream_t st);
+
 // ---- tc_in_core.cu ----
 // Fused x@U_in (+ router scores) -> RMS statistics -> h@G tiles with c-weighted epilogue -> z bf16.
 // fuse_router != 0: scores/top-k/softmax/c are computed inside (c_in ignored, taps optional);
-// otherwise c_in [T, r1] is read.
+// otherwise c_in [T, r1] is read.  c_work [T, r1] is scratch in both cases.
 int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared, const PreparedLayout &P, int64_t T,
-                      int fuse_router, const float *c_in, int32_t *idx_out, float *gates_out, float *c_out, void *z,
-                      int32_t *status, cudaStream_t st);
+                      int fuse_router, const float *c_in, float *c_work, int32_t *idx_out, float *gates_out, float *c_out,
+                      void *z, int32_t *status, cudaStream_t st);
 
 // ---- decode.cu ----
 // Whole forward for T <= 64 bf16 tokens on the prepared (K-major) factors: split-K in-projection with

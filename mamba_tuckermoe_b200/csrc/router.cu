@@ -58,17 +58,17 @@ router_fused_kernel(const T *__restrict__ x, const T *__restrict__ wr, const T *
   emit_token<T, KMAX>(sel, k, E, r1, uexp, t, lane, idx, gates, c);
 }
 
-template <typename T, int KMAX>
+template <typename T, int KMAX, typename TS>
 __global__ void __launch_bounds__(kRouterWarps * 32)
-select_kernel(const float *__restrict__ scores, const T *__restrict__ uexp, int64_t Tn, int E, int k, int r1,
+select_kernel(const TS *__restrict__ scores, int ld, const T *__restrict__ uexp, int64_t Tn, int E, int k, int r1,
               int32_t *__restrict__ idx, float *__restrict__ gates, float *__restrict__ c) {
   const int lane = threadIdx.x & 31;
   const int64_t t = (int64_t)blockIdx.x * kRouterWarps + (threadIdx.x >> 5);
   if (t >= Tn) return;
-  const float *sr = scores + t * E;
+  const TS *sr = scores + t * ld;
   TopList<KMAX> sel;
   sel.init();
-  warp_select_topk<T, KMAX>(sr, E, k, lane, sel);
+  warp_select_topk<T, KMAX, TS>(sr, E, k, lane, sel);
   emit_token<T, KMAX>(sel, k, E, r1, uexp, t, lane, idx, gates, c);
 }
 
@@ -96,8 +96,8 @@ template <typename T>
 static int launch_select_t(const tmoe_layer_t &L, const float *scores, const void *uexp, int64_t T_, int32_t *idx,
                            float *gates, float *c, cudaStream_t st) {
   dim3 grid((unsigned)((T_ + kRouterWarps - 1) / kRouterWarps)), block(kRouterWarps * 32);
-#define TMOE_SEL(KM) select_kernel<T, KM><<<grid, block, 0, st>>>(scores, (const T *)uexp, T_, L.n_experts, L.top_k, \
-                       L.r1, idx, gates, c)
+#define TMOE_SEL(KM) select_kernel<T, KM, float><<<grid, block, 0, st>>>(scores, L.n_experts, (const T *)uexp, T_, \
+                       L.n_experts, L.top_k, L.r1, idx, gates, c)
   if (L.top_k <= 2) TMOE_SEL(2);
   else if (L.top_k <= 8) TMOE_SEL(8);
   else TMOE_SEL(16);
@@ -110,6 +110,19 @@ int launch_select(const tmoe_layer_t &L, const float *scores, const void *uexp, 
                   float *gates, float *c, cudaStream_t st) {
   if (L.dtype == TMOE_F32) return launch_select_t<float>(L, scores, uexp, T_, idx, gates, c, st);
   return launch_select_t<bf16>(L, scores, uexp, T_, idx, gates, c, st);
+}
+
+int launch_select_bf16_scores(const tmoe_layer_t &L, const void *scores, int ld, const void *uexp, int64_t T_,
+                              int32_t *idx, float *gates, float *c, cudaStream_t st) {
+  dim3 grid((unsigned)((T_ + kRouterWarps - 1) / kRouterWarps)), block(kRouterWarps * 32);
+#define TMOE_SELB(KM) select_kernel<bf16, KM, bf16><<<grid, block, 0, st>>>((const bf16 *)scores, ld, (const bf16 *)uexp, \
+                       T_, L.n_experts, L.top_k, L.r1, idx, gates, c)
+  if (L.top_k <= 2) TMOE_SELB(2);
+  else if (L.top_k <= 8) TMOE_SELB(8);
+  else TMOE_SELB(16);
+#undef TMOE_SELB
+  count_launch();
+  return launch_status();
 }
 
 }  // namespace tmoe

@@ -88,15 +88,15 @@ template <> struct Vec16<bf16> {
 
 // Top-k of one token's scores [E] by k passes over the row (all lanes end with the same list).
 // Scores are rounded to the storage type T before they are compared.
-template <typename T, int KMAX>
-__device__ __forceinline__ void warp_select_topk(const float *__restrict__ sr, int E, int k, int lane, TopList<KMAX> &sel) {
+template <typename T, int KMAX, typename TS = float>
+__device__ __forceinline__ void warp_select_topk(const TS *__restrict__ sr, int E, int k, int lane, TopList<KMAX> &sel) {
   float pv = INFINITY; int pi = -1;
 #pragma unroll
   for (int j = 0; j < KMAX; ++j) {
     if (j < k) {
       float bv = -INFINITY; int bi = 0x7fffffff;
       for (int e = lane; e < E; e += 32) {
-        float v = round_to<T>(sr[e]);
+        float v = round_to<T>(to_f32(sr[e]));
         if (ranks_before(pv, pi, v, e) && ranks_before(v, e, bv, bi)) { bv = v; bi = e; }
       }
 #pragma unroll

@@ -15,10 +15,10 @@
 //             (model.py:95-98 for all selected experts at once); P is double-buffered in TMEM so
 //             this runs under the next tile's MMAs and the [T, r1*r2] intermediate never leaves the SM.
 //
-// One CTA per 128-token tile, 6 warps: TMA producer, MMA issuer, 4 epilogue warps.
+// One CTA per 128-token tile, 10 warps: TMA producer, MMA issuer, 8 epilogue warps.
 // Shared memory: phase A uses a ring of {x tile, U_in^T tile, router tile} stages over the whole
 // 224 KB; after the last phase-A MMA has completed, the first 64 KB become h and the rest becomes a
-// 4-stage ring of 32 KB core tiles plus two 16 KB staging tiles for the TMA stores of z.
+// 4-stage ring of 32 KB core tiles plus one 4 KB staging tile per epilogue warp for the TMA stores of z.
 // All mbarrier waits are bounded.
 #include "common.cuh"
 #include "kernels.h"
@@ -46,9 +46,11 @@ constexpr int H_KBLOCK_BYTES = TM * 64 * 2;
 constexpr int H_REGION_BYTES = 4 * H_KBLOCK_BYTES;  // r3 <= 256
 constexpr int G_STAGE_BYTES = 256 * 64 * 2;         // 32 KB
 constexpr int G_STAGES = 4;
-constexpr int Z_STAGE_BYTES = TM * 64 * 2;  // 16 KB: 128 rows x 64 bf16 columns of z, staged for a TMA store
+constexpr int IC_EPI_WARPS = 8;
+constexpr int IC_THREADS = (2 + IC_EPI_WARPS) * 32;
+constexpr int Z_WARP_BYTES = 32 * 64 * 2;  // 4 KB per epilogue warp: 32 rows x 64 bf16 columns of z for one TMA store
 constexpr int Z_STAGE_OFF = H_REGION_BYTES + G_STAGES * G_STAGE_BYTES;
-constexpr int IC_RING_BYTES = Z_STAGE_OFF + 2 * Z_STAGE_BYTES;  // 224 KB
+constexpr int IC_RING_BYTES = Z_STAGE_OFF + IC_EPI_WARPS * Z_WARP_BYTES;  // 224 KB
 constexpr int IC_SMEM_BYTES = IC_RING_BYTES + 1024;
 constexpr int A_STAGES_MAX = 4;
 constexpr int SCORE_COL = 256;  // TMEM column of the router scores during phase A
@@ -62,6 +64,7 @@ struct InCoreParams {
   const float *normw;  // [r3]
   const float *uexp;   // [E, r1] fp32
   const float *c_in;   // [T, r1] when !fuse_router
+  float *c_work;       // [T, r1] scratch: c scaled by 1/rms, handed from the routing warps to their twins
   int32_t *idx_out;
   float *gates_out;
   float *c_out;
@@ -71,7 +74,7 @@ struct InCoreParams {
 
 // R1: Tucker rank r1 (core slices per r2 tile); RK: capacity of the in-kernel top-k list (>= top_k)
 template <int R1, int RK>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(IC_THREADS, 1)
 tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmU,
                   const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmG,
                   const __grid_constant__ CUtensorMap tmZ, InCoreParams p) {
@@ -81,6 +84,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       bar_emptyB[G_STAGES], bar_accA, bar_hready, bar_pfull[2], bar_pempty[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ float wnorm_s[256];
+  __shared__ float inv_rms_s[TM];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -98,7 +102,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
     for (int s = 0; s < A_STAGES_MAX; ++s) { mbar_init(smem_u32(&bar_fullA[s]), 1); mbar_init(smem_u32(&bar_emptyA[s]), 1); }
     for (int s = 0; s < G_STAGES; ++s) { mbar_init(smem_u32(&bar_fullB[s]), 1); mbar_init(smem_u32(&bar_emptyB[s]), 1); }
     mbar_init(smem_u32(&bar_accA), 1);
-    mbar_init(smem_u32(&bar_hready), 4);
+    mbar_init(smem_u32(&bar_hready), IC_EPI_WARPS);
     for (int s = 0; s < 2; ++s) { mbar_init(smem_u32(&bar_pfull[s]), 1); mbar_init(smem_u32(&bar_pempty[s]), 4); }
     fence_mbar_init();
     prefetch_tmap(&tmX); prefetch_tmap(&tmU); prefetch_tmap(&tmG); prefetch_tmap(&tmZ);
@@ -187,134 +191,154 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
     }
   } else {
     // ------------------------------- epilogue warps -------------------------------
+    // Eight warps: warp w may read TMEM lanes 32*(w%4)..+31, so each row quadrant has a "primary" warp
+    // (2-5) and a "secondary" warp (6-9); thread = token row in both.
+    //   epilogue A: primary = routing (scores -> top-k -> gates -> c), secondary = h row (sum of squares,
+    //               h*w -> bf16 -> shared memory); they meet at a named barrier, the primary scales c by the
+    //               row's 1/rms and publishes it through the workspace for its secondary twin.
+    //   epilogue B: the 64-column units of z alternate between the two groups, so each group has two MMA
+    //               tile times per unit; every warp stages its 32 rows x 64 columns and stores them by TMA.
     const int quad = warp & 3;
+    const int grp = (warp - 2) >> 2;  // 0 primary, 1 secondary
     const int row = quad * 32 + lane;
     const int64_t grow = (int64_t)m0 + row;
     const bool live = grow < p.T;
     const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const uint32_t zbuf = ring + Z_STAGE_OFF + (warp - 2) * Z_WARP_BYTES;
     float c[R1];
-    const bool is_store_thread = (threadIdx.x == 64);
-    const uint32_t zstage0 = ring + Z_STAGE_OFF;
     bool ok = mbar_wait(smem_u32(&bar_accA), 0, p.status, kKernelInCore, 3);
-    ok = named_bar_and(2, 128, ok);  // the four epilogue warps continue or leave together
+    ok = named_bar_and(2, 256, ok);  // the eight epilogue warps continue or leave together
     if (ok) {
       tc_fence_after();
       if (threadIdx.x == 64) TMOE_STAMP(2);  // phase A complete (accumulators readable)
-      if (p.fuse_router) {
-        // Running top-k over the score columns, branch-free.  A score rounded to bf16 has 16 significant
-        // bits, so (order-preserving map of those bits) << 16 | (0xFFFF - expert) is a 32-bit key whose
-        // unsigned order is "higher score first, equal scores -> lower expert index first"; the sorted
-        // list is then maintained with integer max/min only (no data-dependent branches, independent
-        // scores pipeline through the levels).
-        uint32_t key[RK];
+      if (grp == 0) {
+        if (p.fuse_router) {
+          // Running top-k over the score columns, branch-free.  A score rounded to bf16 has 16 significant
+          // bits, so (order-preserving map of those bits) << 16 | (0xFFFF - expert) is a 32-bit key whose
+          // unsigned order is "higher score first, equal scores -> lower expert index first"; the sorted
+          // list is then maintained with integer max/min only (no data-dependent branches, independent
+          // scores pipeline through the levels).
+          uint32_t key[RK];
 #pragma unroll
-        for (int j = 0; j < RK; ++j) key[j] = 0u;
-        for (int cc = 0; cc < p.e_pad / 16; ++cc) {
-          uint32_t r[16];
-          tmem_ld16(t_lane + SCORE_COL + cc * 16, r);
-          tmem_ld_wait(r);
+          for (int j = 0; j < RK; ++j) key[j] = 0u;
+          for (int cc = 0; cc < p.e_pad / 16; ++cc) {
+            uint32_t r[16];
+            tmem_ld16(t_lane + SCORE_COL + cc * 16, r);
+            tmem_ld_wait(r);
 #pragma unroll
-          for (int q = 0; q < 16; ++q) {
-            const int e = cc * 16 + q;
-            uint32_t b = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(__uint_as_float(r[q])));
-            b = (b == 0x8000u) ? 0u : b;                                   // -0 and +0 compare equal
-            const uint32_t u = (b & 0x8000u) ? (~b & 0xffffu) : (b | 0x8000u);
-            uint32_t carry = (e < p.E) ? ((u << 16) | (0xffffu - (uint32_t)e)) : 0u;
+            for (int q = 0; q < 16; ++q) {
+              const int e = cc * 16 + q;
+              uint32_t b = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(__uint_as_float(r[q])));
+              b = (b == 0x8000u) ? 0u : b;                                   // -0 and +0 compare equal
+              const uint32_t u = (b & 0x8000u) ? (~b & 0xffffu) : (b | 0x8000u);
+              uint32_t carry = (e < p.E) ? ((u << 16) | (0xffffu - (uint32_t)e)) : 0u;
 #pragma unroll
-            for (int j = 0; j < RK; ++j) {
-              const uint32_t hi = max(key[j], carry);
-              carry = min(key[j], carry);
-              key[j] = hi;
+              for (int j = 0; j < RK; ++j) {
+                const uint32_t hi = max(key[j], carry);
+                carry = min(key[j], carry);
+                key[j] = hi;
+              }
             }
           }
-        }
-        float sv[RK]; int si[RK];
+          float sv[RK]; int si[RK];
 #pragma unroll
-        for (int j = 0; j < RK; ++j) {
-          const uint32_t u = key[j] >> 16;
-          const uint32_t b = (u & 0x8000u) ? (u & 0x7fffu) : (~u & 0xffffu);
-          sv[j] = __uint_as_float(b << 16);
-          si[j] = (int)(0xffffu - (key[j] & 0xffffu));
-        }
-        if (threadIdx.x == 64) TMOE_STAMP(6);  // score scan done
-        float gate[RK], den = 0.f;
+          for (int j = 0; j < RK; ++j) {
+            const uint32_t u = key[j] >> 16;
+            const uint32_t b = (u & 0x8000u) ? (u & 0x7fffu) : (~u & 0xffffu);
+            sv[j] = __uint_as_float(b << 16);
+            si[j] = (int)(0xffffu - (key[j] & 0xffffu));
+          }
+          if (threadIdx.x == 64) TMOE_STAMP(6);  // score scan done
+          float gate[RK], den = 0.f;
 #pragma unroll
-        for (int j = 0; j < RK; ++j) { gate[j] = (j < p.top_k) ? expf(sv[j] - sv[0]) : 0.f; den += gate[j]; }
-        const float inv = 1.f / den;
+          for (int j = 0; j < RK; ++j) { gate[j] = (j < p.top_k) ? expf(sv[j] - sv[0]) : 0.f; den += gate[j]; }
+          const float inv = 1.f / den;
 #pragma unroll
-        for (int a = 0; a < R1; ++a) c[a] = 0.f;
+          for (int a = 0; a < R1; ++a) c[a] = 0.f;
 #pragma unroll
-        for (int j = 0; j < RK; ++j) {
-          if (j < p.top_k) {
-            gate[j] = round_to<bf16>(gate[j] * inv);
-            const int e = min(max(si[j], 0), p.E - 1);
+          for (int j = 0; j < RK; ++j) {
+            if (j < p.top_k) {
+              gate[j] = round_to<bf16>(gate[j] * inv);
+              const int e = min(max(si[j], 0), p.E - 1);
 #pragma unroll
-            for (int a = 0; a < R1; ++a) c[a] = fmaf(gate[j], __ldg(p.uexp + e * R1 + a), c[a]);
-            if (live) {
-              if (p.idx_out) p.idx_out[grow * p.top_k + j] = si[j];
-              if (p.gates_out) p.gates_out[grow * p.top_k + j] = gate[j];
+              for (int a = 0; a < R1; ++a) c[a] = fmaf(gate[j], __ldg(p.uexp + e * R1 + a), c[a]);
+              if (live) {
+                if (p.idx_out) p.idx_out[grow * p.top_k + j] = si[j];
+                if (p.gates_out) p.gates_out[grow * p.top_k + j] = gate[j];
+              }
             }
           }
-        }
-        if (threadIdx.x == 64) TMOE_STAMP(7);  // gates and c done
-        if (live && p.c_out) {
+          if (threadIdx.x == 64) TMOE_STAMP(7);  // gates and c done
+          if (live && p.c_out) {
 #pragma unroll
-          for (int a = 0; a < R1; ++a) p.c_out[grow * R1 + a] = c[a];
+            for (int a = 0; a < R1; ++a) p.c_out[grow * R1 + a] = c[a];
+          }
+        } else {
+#pragma unroll
+          for (int a = 0; a < R1; ++a) c[a] = live ? __ldg(p.c_in + grow * R1 + a) : 0.f;
+        }
+        if (threadIdx.x == 64) TMOE_STAMP(3);  // routing done
+        tc_fence_before();                      // score columns are free for the core-tile accumulators
+        named_bar_sync(3, 256);                 // the secondary warps have written inv_rms_s
+        const float inv_rms = inv_rms_s[row];
+#pragma unroll
+        for (int a = 0; a < R1; ++a) c[a] *= inv_rms;
+        if (live) {
+#pragma unroll
+          for (int a = 0; a < R1; ++a) p.c_work[grow * R1 + a] = c[a];
         }
       } else {
+        // h row: statistics, weight, bf16, swizzled store (16-byte chunk index XOR row%8 inside 128-byte rows)
+        float ss = 0.f;
+        for (int cc = 0; cc < p.r3 / 32; ++cc) {
+          uint32_t r[32];
+          tmem_ld32(t_lane + cc * 32, r);
+          tmem_ld_wait(r);
+          const uint32_t kblk_base = ring + (cc >> 1) * H_KBLOCK_BYTES + row * 128;
 #pragma unroll
-        for (int a = 0; a < R1; ++a) c[a] = live ? __ldg(p.c_in + grow * R1 + a) : 0.f;
-      }
-      if (threadIdx.x == 64) TMOE_STAMP(3);  // routing done
-      // h row: statistics, weight, bf16, swizzled store (16-byte chunk index XOR row%8 inside 128-byte rows)
-      float ss = 0.f;
-      for (int cc = 0; cc < p.r3 / 32; ++cc) {
-        uint32_t r[32];
-        tmem_ld32(t_lane + cc * 32, r);
-        tmem_ld_wait(r);
-        const uint32_t kblk_base = ring + (cc >> 1) * H_KBLOCK_BYTES + row * 128;
+          for (int g = 0; g < 4; ++g) {
+            float v[8];
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          float v[8];
-#pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            const float a = __uint_as_float(r[g * 8 + q]);
-            ss = fmaf(a, a, ss);
-            v[q] = a * wnorm_s[cc * 32 + g * 8 + q];
+            for (int q = 0; q < 8; ++q) {
+              const float a = __uint_as_float(r[g * 8 + q]);
+              ss = fmaf(a, a, ss);
+              v[q] = a * wnorm_s[cc * 32 + g * 8 + q];
+            }
+            const uint32_t chunk = (uint32_t)((cc & 1) * 4 + g) ^ (uint32_t)(row & 7);
+            const uint32_t addr = kblk_base + chunk * 16;
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pack_bf16x2(v[0], v[1])),
+                         "r"(pack_bf16x2(v[2], v[3])), "r"(pack_bf16x2(v[4], v[5])), "r"(pack_bf16x2(v[6], v[7]))
+                         : "memory");
           }
-          const uint32_t chunk = (uint32_t)((cc & 1) * 4 + g) ^ (uint32_t)(row & 7);
-          const uint32_t addr = kblk_base + chunk * 16;
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pack_bf16x2(v[0], v[1])),
-                       "r"(pack_bf16x2(v[2], v[3])), "r"(pack_bf16x2(v[4], v[5])), "r"(pack_bf16x2(v[6], v[7]))
-                       : "memory");
         }
+        inv_rms_s[row] = 1.f / sqrtf(ss / (float)p.r3 + p.eps);
+        fence_proxy_async_smem();
+        tc_fence_before();
+        named_bar_sync(3, 256);
       }
-      const float inv_rms = 1.f / sqrtf(ss / (float)p.r3 + p.eps);
-#pragma unroll
-      for (int a = 0; a < R1; ++a) c[a] *= inv_rms;
-      fence_proxy_async_smem();
-      tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bar_hready));
-      if (threadIdx.x == 64) TMOE_STAMP(4);  // h written
+      if (lane == 0) mbar_arrive(smem_u32(&bar_hready));  // 8 arrivals: h is in shared memory, TMEM columns are free
+      if (threadIdx.x == 64) TMOE_STAMP(4);  // epilogue A done
+      named_bar_sync(4, 256);                // c_work of every row is written
+      if (grp == 1) {
+#pragma unroll
+        for (int a = 0; a < R1; ++a) c[a] = live ? p.c_work[grow * R1 + a] : 0.f;
+      }
 
-      // epilogue B: z is staged in 64-column units (two 16 KB buffers) and written with TMA stores
+      // epilogue B: tile j belongs to group (j / JPU) & 1, JPU = tiles per 64-column unit of z
+      constexpr int JPU = (N2 >= 64) ? 1 : 64 / N2;
       for (int j = 0; j < p.n_tiles2 && ok; ++j) {
+        if (((j / JPU) & 1) != grp) continue;
         const uint32_t slot = j & 1, pph = (j >> 1) & 1;
         ok = mbar_wait(smem_u32(&bar_pfull[slot]), pph, p.status, kKernelInCore, 7);
-        ok = named_bar_and(2, 128, ok);
+        ok = __all_sync(0xffffffffu, ok);  // TMEM loads are warp-collective
         if (!ok) break;
         tc_fence_after();
         const uint32_t t_p = t_lane + slot * 256;
 #pragma unroll 1
         for (int sc = 0; sc < N2 / 16; ++sc) {
-          const int zc = j * N2 + sc * 16;        // first z column of this 16-column group
+          const int zc = j * N2 + sc * 16;  // first z column of this 16-column group
           const int unit = zc >> 6, within = zc & 63;
-          const uint32_t zbuf = zstage0 + (unit & 1) * Z_STAGE_BYTES;
-          if (within == 0) {
-            if (is_store_thread) tma_store_wait_read<1>();  // the store that used this buffer two units ago has read it
-            named_bar_sync(1, 128);
-          }
           float acc[16];
 #pragma unroll
           for (int q = 0; q < 16; ++q) acc[q] = 0.f;
@@ -330,28 +354,34 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
               acc[q] = fmaf(c[a + 1], __uint_as_float(r1v[q]), acc[q]);
             }
           }
+          if (sc == N2 / 16 - 1) {  // last TMEM read of this tile by this warp: hand the accumulator back
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_pempty[slot]));
+          }
+          if (within == 0) {
+            if (lane == 0) tma_store_wait_read<0>();  // the previous store has read the staging tile
+            __syncwarp();
+          }
 #pragma unroll
           for (int g = 0; g < 2; ++g) {
-            const uint32_t chunk = (uint32_t)((within >> 3) + g) ^ (uint32_t)(row & 7);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(zbuf + row * 128 + chunk * 16),
+            const uint32_t chunk = (uint32_t)((within >> 3) + g) ^ (uint32_t)(lane & 7);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(zbuf + lane * 128 + chunk * 16),
                          "r"(pack_bf16x2(acc[8 * g + 0], acc[8 * g + 1])), "r"(pack_bf16x2(acc[8 * g + 2], acc[8 * g + 3])),
                          "r"(pack_bf16x2(acc[8 * g + 4], acc[8 * g + 5])), "r"(pack_bf16x2(acc[8 * g + 6], acc[8 * g + 7]))
                          : "memory");
           }
           if (within == 48) {
             fence_proxy_async_smem();
-            named_bar_sync(1, 128);
-            if (is_store_thread) {
-              tma_store_2d(&tmZ, zbuf, unit * 64, m0);
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tmZ, zbuf, unit * 64, m0 + quad * 32);
               tma_store_commit();
             }
           }
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&bar_pempty[slot]));
       }
-      if (is_store_thread) tma_store_wait_all();
+      if (lane == 0) tma_store_wait_all();
       if (threadIdx.x == 64) TMOE_STAMP(5);  // z stored
     }
   }
@@ -365,11 +395,11 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
 }
 
 int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared, const PreparedLayout &P, int64_t T_,
-                      int fuse_router, const float *c_in, int32_t *idx_out, float *gates_out, float *c_out, void *z,
-                      int32_t *status, cudaStream_t st) {
+                      int fuse_router, const float *c_in, float *c_work, int32_t *idx_out, float *gates_out, float *c_out,
+                      void *z, int32_t *status, cudaStream_t st) {
   const char *base = reinterpret_cast<const char *>(prepared);
   if (fuse_router && (P.e_pad > 256 || L.top_k > 8)) return TMOE_ERR_UNSUPPORTED;
-  if (!fuse_router && !c_in) return TMOE_ERR_NULL;
+  if ((!fuse_router && !c_in) || !c_work) return TMOE_ERR_NULL;
   CUtensorMap tmX, tmU, tmW, tmG, tmZ;
   int rc = encode_tmap_bf16_2d(&tmX, x, (uint64_t)T_, (uint64_t)L.d_in, TM);
   if (rc) return rc;
@@ -381,7 +411,7 @@ int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared
   if (rc) return rc;
   rc = encode_tmap_bf16_2d(&tmG, base + P.g_t, (uint64_t)L.r1 * L.r2, (uint64_t)L.r3, 256);
   if (rc) return rc;
-  rc = encode_tmap_bf16_2d(&tmZ, z, (uint64_t)T_, (uint64_t)L.r2, TM);
+  rc = encode_tmap_bf16_2d(&tmZ, z, (uint64_t)T_, (uint64_t)L.r2, 32);
   if (rc) return rc;
 
   InCoreParams p{};
@@ -390,7 +420,7 @@ int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared
   p.n_tiles2 = P.n_tiles2; p.eps = L.eps; p.fuse_router = fuse_router;
   p.normw = reinterpret_cast<const float *>(base + P.normw);
   p.uexp = reinterpret_cast<const float *>(base + P.uexp);
-  p.c_in = c_in; p.idx_out = idx_out; p.gates_out = gates_out; p.c_out = c_out;
+  p.c_in = c_in; p.c_work = c_work; p.idx_out = idx_out; p.gates_out = gates_out; p.c_out = c_out;
   p.z = (bf16 *)z; p.status = status;
   if (X_TILE_BYTES + p.r3 * 128 + p.e_pad * 128 > IC_RING_BYTES) return TMOE_ERR_UNSUPPORTED;
 
@@ -399,7 +429,7 @@ int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared
 #define TMOE_IC(R, K)                                                                                              \
   do {                                                                                                             \
     e = cudaFuncSetAttribute(tc_in_core_kernel<R, K>, cudaFuncAttributeMaxDynamicSharedMemorySize, IC_SMEM_BYTES); \
-    if (e == cudaSuccess) tc_in_core_kernel<R, K><<<grid, 192, IC_SMEM_BYTES, st>>>(tmX, tmU, tmW, tmG, tmZ, p);    \
+    if (e == cudaSuccess) tc_in_core_kernel<R, K><<<grid, IC_THREADS, IC_SMEM_BYTES, st>>>(tmX, tmU, tmW, tmG, tmZ, p);    \
   } while (0)
   const bool small_k = L.top_k <= 2;
   if (L.r1 == 2) { if (small_k) TMOE_IC(2, 2); else TMOE_IC(2, 8); }

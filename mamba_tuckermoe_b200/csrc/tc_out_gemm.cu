@@ -184,10 +184,12 @@ tc_out_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
 #pragma unroll
             for (int q = 0; q < 8; ++q) v[q] = __uint_as_float(r[h2][g * 8 + q]);
             if (col < p.N) {  // N % 8 == 0: a group of 8 is entirely in or out; columns >= N are clipped by the store
-              const float4 b0 = __ldg(reinterpret_cast<const float4 *>(p.bias + col));
-              const float4 b1 = __ldg(reinterpret_cast<const float4 *>(p.bias + col + 4));
-              v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
-              v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+              if (p.bias) {
+                const float4 b0 = __ldg(reinterpret_cast<const float4 *>(p.bias + col));
+                const float4 b1 = __ldg(reinterpret_cast<const float4 *>(p.bias + col + 4));
+                v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+                v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+              }
               if (p.residual && row < p.T) {
                 const uint4 rr = __ldg(reinterpret_cast<const uint4 *>(p.residual + row * p.N + col));
                 const uint4 gg = __ldg(reinterpret_cast<const uint4 *>(p.gamma + col));
@@ -226,14 +228,16 @@ tc_out_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
   }
 }
 
-int launch_tc_out(const tmoe_layer_t &L, const void *z, const void *uout_t, const float *bias, const void *residual,
-                  const void *layer_scale, int64_t T_, void *y, int32_t *status, cudaStream_t st) {
+// y[M, N] (bf16) = A[M, K] (bf16, row-major) @ B_t[N, K]^T (bf16, K-major) + bias[N] (fp32, optional),
+// optionally residual + gamma * (...).  N and K multiples of 8.
+int launch_tc_gemm_bf16(const void *A, const void *B_t, const float *bias, const void *residual, const void *gamma,
+                        int64_t M, int N, int K, void *y, int32_t *status, cudaStream_t st) {
   CUtensorMap tmA, tmB, tmY;
-  int rc = encode_tmap_bf16_2d(&tmY, y, (uint64_t)T_, (uint64_t)L.d_out, 32);
+  int rc = encode_tmap_bf16_2d(&tmY, y, (uint64_t)M, (uint64_t)N, 32);
   if (rc) return rc;
-  rc = encode_tmap_bf16_2d(&tmA, z, (uint64_t)T_, (uint64_t)L.r2, OM);
+  rc = encode_tmap_bf16_2d(&tmA, A, (uint64_t)M, (uint64_t)K, OM);
   if (rc) return rc;
-  rc = encode_tmap_bf16_2d(&tmB, uout_t, (uint64_t)L.d_out, (uint64_t)L.r2, ON);
+  rc = encode_tmap_bf16_2d(&tmB, B_t, (uint64_t)N, (uint64_t)K, ON);
   if (rc) return rc;
   static bool attr_done[64] = {};
   int dev = 0, sms = 0;
@@ -245,15 +249,20 @@ int launch_tc_out(const tmoe_layer_t &L, const void *z, const void *uout_t, cons
     attr_done[dev] = true;
   }
   OutParams p{};
-  p.y = (bf16 *)y; p.bias = bias; p.residual = (const bf16 *)residual; p.gamma = (const bf16 *)layer_scale;
-  p.T = T_; p.N = L.d_out; p.K = L.r2;
-  p.num_m = (int)((T_ + OM - 1) / OM); p.num_n = (L.d_out + ON - 1) / ON;
+  p.y = (bf16 *)y; p.bias = bias; p.residual = (const bf16 *)residual; p.gamma = (const bf16 *)gamma;
+  p.T = M; p.N = N; p.K = K;
+  p.num_m = (int)((M + OM - 1) / OM); p.num_n = (N + ON - 1) / ON;
   p.status = status;
   const int tiles = p.num_m * p.num_n;
   const int grid = tiles < sms ? tiles : sms;
   tc_out_kernel<<<grid, O_THREADS, O_SMEM_BYTES, st>>>(tmA, tmB, tmY, p);
   count_launch();
   return launch_status();
+}
+
+int launch_tc_out(const tmoe_layer_t &L, const void *z, const void *uout_t, const float *bias, const void *residual,
+                  const void *layer_scale, int64_t T_, void *y, int32_t *status, cudaStream_t st) {
+  return launch_tc_gemm_bf16(z, uout_t, bias, residual, layer_scale, T_, L.d_out, L.r2, y, status, st);
 }
 
 }  // namespace tmoe

@@ -297,6 +297,60 @@ class TuckerMoE(nn.Module):
         return tucker_moe_forward_taps(x, rw, ui, nw, self.inner_norm.eps, ue, co, uo, b, self.top_k, path=self.path,
                                        prepared=self._prepared_for(x))
 
+    @torch.no_grad()
+    def forward_host(self, x_host: torch.Tensor, out: Optional[torch.Tensor] = None,
+                     chunk_tokens: int = 8192) -> torch.Tensor:
+        """Forward for activations that live in host memory: ``x_host`` (..., d_in) on the CPU (pinned
+        memory for full copy speed) -> CPU tensor (..., d_out).
+
+        The token range is cut into chunks; the host->device copy of chunk i+1, the kernels of chunk i
+        and the device->host copy of chunk i-1 run on three streams, so one call costs about the longer
+        of the two PCIe transfers instead of their sum plus the compute.  The result is complete when
+        the current stream has caught up (``torch.cuda.current_stream().synchronize()``)."""
+        dev = self.U_in.device
+        if dev.type != "cuda":
+            raise RuntimeError("tmoe_b200: move the layer to a CUDA device first (no CPU fallback)")
+        d_in, d_out = self.U_in.shape[0], self.U_out.shape[1]
+        lead = x_host.shape[:-1]
+        xh = x_host.reshape(-1, d_in)
+        T = xh.shape[0]
+        if out is None:
+            out = torch.empty((T, d_out), dtype=xh.dtype, pin_memory=True)
+        oh = out.reshape(-1, d_out)
+        if oh.shape[0] != T or oh.dtype != xh.dtype or oh.device.type != "cpu":
+            raise RuntimeError("tmoe_b200: `out` must be a CPU tensor (..., d_out) of x's dtype")
+        if T == 0:
+            return out.reshape(*lead, d_out)
+        with torch.cuda.device(dev):
+            cur = torch.cuda.current_stream(dev)
+            if getattr(self, "_host_streams", None) is None or self._host_streams[0].device != dev:
+                self._host_streams = (torch.cuda.Stream(dev), torch.cuda.Stream(dev))
+            h2d, d2h = self._host_streams
+            h2d.wait_stream(cur)
+            d2h.wait_stream(cur)
+            x_dev = torch.empty((T, d_in), dtype=xh.dtype, device=dev)
+            x_dev.record_stream(h2d)
+            step = max(1, int(chunk_tokens))
+            copied = []
+            for lo in range(0, T, step):
+                hi = min(T, lo + step)
+                with torch.cuda.stream(h2d):
+                    x_dev[lo:hi].copy_(xh[lo:hi], non_blocking=True)
+                    ev = torch.cuda.Event()
+                    ev.record(h2d)
+                copied.append((lo, hi, ev))
+            for lo, hi, ev in copied:
+                cur.wait_event(ev)
+                y = self.forward(x_dev[lo:hi])
+                done = torch.cuda.Event()
+                done.record(cur)
+                with torch.cuda.stream(d2h):
+                    d2h.wait_event(done)
+                    oh[lo:hi].copy_(y, non_blocking=True)
+                y.record_stream(d2h)
+            cur.wait_stream(d2h)
+        return out.reshape(*lead, d_out)
+
     def invalidate_cache(self) -> None:
         """Call after writing parameters through ``.data`` once the layer has already run
         (such writes do not change tensor versions, which key the prepared-factor cache)."""

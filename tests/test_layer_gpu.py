@@ -226,3 +226,24 @@ def test_linearity_in_out_projection_and_bias():
     # token-wise independence: permuting tokens permutes outputs bit for bit
     perm = torch.randperm(8192, generator=torch.Generator().manual_seed(3)).cuda()
     assert torch.equal(m0(x.cuda()[perm]).float(), y0[perm])
+
+
+@pytest.mark.parametrize("T,chunk", [(700, 256), (64, 8192), (3000, 1024)])
+def test_forward_host_equals_device_forward(T, chunk):
+    """Host-resident activations: the chunk-pipelined call returns what the device call returns."""
+    shape = LayerShape(256, 264, 8, 2, 4, 128, 256, 1e-5)
+    x, f = _tensor_case(shape, T, seed=99)
+    m = build_module(shape, f, torch.bfloat16)
+    xh = x.pin_memory()
+    out = torch.empty(T, shape.d_out, dtype=torch.bfloat16).pin_memory()
+    y_host = m.forward_host(xh, out=out, chunk_tokens=chunk)
+    torch.cuda.current_stream().synchronize()
+    assert y_host.data_ptr() == out.data_ptr()
+    y_ref = layer_forward(x, f, shape.top_k, shape.eps)
+    assert rel_fro(y_host.float(), y_ref.float()) < 3e-2
+    # each chunk is an independent forward on its tokens; chunks above 64 tokens use the tensor-core kernels
+    parts = [m(x[lo:lo + chunk].cuda()).cpu() for lo in range(0, T, chunk)]
+    assert torch.equal(torch.cat(parts), y_host) or rel_fro(torch.cat(parts).float(), y_host.float()) < 5e-3
+    y2 = m.forward_host(x.reshape(1, T, -1))   # unpinned input, allocated output, leading shape kept
+    torch.cuda.current_stream().synchronize()
+    assert y2.shape == (1, T, shape.d_out) and rel_fro(y2.float().reshape(T, -1), y_host.float()) < 5e-3
