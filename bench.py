@@ -45,7 +45,12 @@ WORKLOADS = {
     "cfg1_t8": ("cfg1", 8, "decode bf16 T=8 d_in=1536 d_out=2304 E=8 top2 r=(4,256,1024)"),
     "cfg1_t1": ("cfg1", 1, "decode bf16 T=1 d_in=1536 d_out=2304 E=8 top2 r=(4,256,1024)"),
     "cfg3": ("cfg3", 16384, "bf16 T=16384 E=64 top2"),
+    "cfg4": ("cfg4", 131072, "skewed bf16 T=131072 d_in=3072 d_out=4608 E=256 top8 r=(8,512,2048), Zipf(1.2) router bias"),
 }
+for _e in (8, 64, 256, 1024):
+    for _k in (2, 8):
+        WORKLOADS[f"cfg3_e{_e}_k{_k}"] = (f"cfg3_e{_e}_k{_k}", 16384,
+                                          f"sweep bf16 T=16384 d_in=1536 d_out=2304 E={_e} top{_k} r=(4,256,1024)")
 N_INPUT_SETS = 4  # rotating x buffers so that no step re-reads the previous step's lines from L2
 
 
@@ -189,7 +194,8 @@ def main():
 
     import mamba_tuckermoe_b200 as pkg
     from mamba_tuckermoe_b200 import _lib
-    from oracle.tucker_moe_oracle import BENCH_SHAPES, make_factors, make_tokens
+    from oracle.tucker_moe_oracle import (BENCH_SHAPES, ZIPF_SHAPES, apply_zipf_router_bias, make_factors,
+                                          make_tokens)
 
     shape_key, T, desc = WORKLOADS[args.workload]
     shape, _, dtype, seed, rstd = BENCH_SHAPES[shape_key]
@@ -199,6 +205,9 @@ def main():
     cfg = pkg.TuckerMoEConfig(shape.E, shape.top_k, shape.r1, shape.r2, shape.r3, shape.eps)
     layer = pkg.TuckerMoE(shape.d_in, shape.d_out, cfg)
     f = make_factors(shape, seed, torch.float32, rstd)
+    zipf = shape_key in ZIPF_SHAPES
+    if zipf:
+        _, f = apply_zipf_router_bias(torch.zeros(1, shape.d_in), f, seed)
     layer.load_state_dict({"router.weight": f["router_w"], "U_in": f["U_in"], "inner_norm.weight": f["inner_norm_w"],
                            "U_expert": f["U_expert"], "core": f["core"], "U_out": f["U_out"], "bias": f["bias"]})
     layer = layer.to(device=dev, dtype=dtype)
@@ -206,6 +215,9 @@ def main():
 
     # this rank's token shard: seeded per rank; host copies stay pinned for the end-to-end leg
     x_host = [make_tokens(T, shape.d_in, seed + 17 * rank + 1000 * i, dtype).pin_memory() for i in range(N_INPUT_SETS)]
+    if zipf:
+        for xh in x_host:
+            xh[:, 0] = 1.0  # the constant input channel that carries the per-expert bias
     x_dev = [x.to(dev) for x in x_host]
     y_host = torch.empty((T, shape.d_out), dtype=dtype).pin_memory()
 

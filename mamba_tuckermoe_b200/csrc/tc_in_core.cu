@@ -328,11 +328,13 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       // epilogue B: tile j belongs to group (j / JPU) & 1, JPU = tiles per 64-column unit of z
       constexpr int JPU = (N2 >= 64) ? 1 : 64 / N2;
       for (int j = 0; j < p.n_tiles2 && ok; ++j) {
-        if (((j / JPU) & 1) != grp) continue;
+        // every warp waits for every tile, also the ones its group does not own: a parity wait is only
+        // meaningful for a waiter that has seen the barrier's previous phase complete
         const uint32_t slot = j & 1, pph = (j >> 1) & 1;
         ok = mbar_wait(smem_u32(&bar_pfull[slot]), pph, p.status, kKernelInCore, 7);
         ok = __all_sync(0xffffffffu, ok);  // TMEM loads are warp-collective
         if (!ok) break;
+        if (((j / JPU) & 1) != grp) continue;
         tc_fence_after();
         const uint32_t t_p = t_lane + slot * 256;
 #pragma unroll 1
