@@ -156,6 +156,24 @@ int tmoe_forward(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const
  * (0, or TMOE_ERR_DEVICE_WAIT with details in the following words) and clears it. */
 int tmoe_read_device_status(void *workspace, int32_t *device_status, void *stream);
 
+/* Forward on the CUDA-core kernels with NO caller-provided workspace and no allocation of any kind.
+ * (This entry point has no counterpart in the reference; it exists for hosts that cannot allocate.)
+ * For callers that cannot call cudaMalloc when the layer runs -- a server whose arena already owns all
+ * device memory, or a decode loop that cannot afford the device-wide synchronisation an allocation
+ * implies -- the scratch lives in a fixed array of TMOE_STATIC_SCRATCH_BYTES inside the library, held by
+ * every GPU that loads it until the process exits.
+ *  - same arguments and results as tmoe_forward(..., path = TMOE_PATH_SIMT) minus workspace/prepared;
+ *  - returns TMOE_ERR_WORKSPACE when tmoe_workspace_bytes(layer, T, TMOE_PATH_SIMT) exceeds
+ *    TMOE_STATIC_SCRATCH_BYTES (T is then too large for the array: about 800 tokens for r3 = 256,
+ *    r2 = 1024; 64 tokens for r3 = 512, r2 = 2048);
+ *  - the first call on each device looks the array's device address up (a one-time host-side step);
+ *    make that first call outside of any stream capture;
+ *  - all calls on a device share the one array: two calls whose kernels overlap on the GPU (different
+ *    streams, or different host threads on different streams) race.  Serialise them on one stream. */
+#define TMOE_STATIC_SCRATCH_BYTES (4u << 20)
+int tmoe_forward_static_scratch(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const void *x,
+                                int64_t T, void *y, const tmoe_extras_t *extras, void *stream);
+
 /* Number of kernels the library has launched in this process (monotonic counter). */
 int64_t tmoe_launch_count(void);
 

@@ -16,8 +16,9 @@ ERR_DEVICE_WAIT = -9
 EXPORTS = (
     "tmoe_version", "tmoe_status_string", "tmoe_resolve_path", "tmoe_prepared_bytes",
     "tmoe_prepare_factors", "tmoe_workspace_bytes", "tmoe_router", "tmoe_in_core", "tmoe_out",
-    "tmoe_forward", "tmoe_read_device_status", "tmoe_launch_count",
+    "tmoe_forward", "tmoe_read_device_status", "tmoe_launch_count", "tmoe_forward_static_scratch",
 )
+STATIC_SCRATCH_BYTES = 4 << 20
 
 
 class Layer(C.Structure):
@@ -83,6 +84,8 @@ def load():
         lib.tmoe_out.argtypes = [LP, FP, vp, vp, i64, vp, EP, vp, i64, i32, vp]
         lib.tmoe_forward.restype = i32
         lib.tmoe_forward.argtypes = [LP, FP, vp, vp, i64, vp, EP, vp, i64, i32, vp]
+        lib.tmoe_forward_static_scratch.restype = i32
+        lib.tmoe_forward_static_scratch.argtypes = [LP, FP, vp, i64, vp, EP, vp]
         lib.tmoe_read_device_status.restype = i32
         lib.tmoe_read_device_status.argtypes = [vp, C.POINTER(C.c_int32), vp]
         lib.tmoe_launch_count.restype = i64
