@@ -23,7 +23,6 @@
 #include "common.cuh"
 #include "kernels.h"
 #include "ptx.cuh"
-#include <cstdlib>
 
 namespace tmoe {
 
@@ -62,7 +61,6 @@ struct InCoreParams {
   int d_in, r3, r2, E, e_pad, top_k, n_tiles2;
   float eps;
   int fuse_router;
-  int stagger;  // bit 0: rotate the k order of phase A per CTA, bit 1: rotate the r2-tile order of phase B per CTA
   const float *normw;  // [r3]
   const float *uexp;   // [E, r1] fp32
   const float *c_in;   // [T, r1] when !fuse_router
@@ -98,11 +96,6 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
   nA = nA > A_STAGES_MAX ? A_STAGES_MAX : nA;
   const int KA = p.d_in / 64;
   const int KH = p.r3 / 64;
-  // CTAs that start together would otherwise all ask L2 for the same weight lines at the same moment:
-  // each CTA walks the k blocks of phase A and the r2 tiles of phase B from its own starting point.
-  constexpr int JPU_ = (256 / R1 >= 64) ? 1 : 64 / (256 / R1);
-  const int rotA = (p.stagger & 1) ? (int)((blockIdx.x * 7u) % (unsigned)KA) : 0;
-  const int rotB = (p.stagger & 2) ? (int)((blockIdx.x * 5u) % (unsigned)(p.n_tiles2 / JPU_)) * JPU_ : 0;
 
   for (int i = threadIdx.x; i < p.r3; i += blockDim.x) wnorm_s[i] = p.normw[i];
   if (threadIdx.x == 0) {
@@ -135,10 +128,9 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         const uint32_t full = smem_u32(&bar_fullA[s]);
         mbar_arrive_expect_tx(full, stageA_bytes);
         const uint32_t sa = ring + s * stageA_bytes;
-        const int kk = (kb + rotA) % KA;
-        tma_load_2d(sa, &tmX, kk * 64, m0, full);
-        tma_load_2d(sa + X_TILE_BYTES, &tmU, kk * 64, 0, full);
-        if (p.e_pad) tma_load_2d(sa + X_TILE_BYTES + u_bytes, &tmW, kk * 64, 0, full);
+        tma_load_2d(sa, &tmX, kb * 64, m0, full);
+        tma_load_2d(sa + X_TILE_BYTES, &tmU, kb * 64, 0, full);
+        if (p.e_pad) tma_load_2d(sa + X_TILE_BYTES + u_bytes, &tmW, kb * 64, 0, full);
       }
       // ring A aliases h and the core-tile ring: wait until every phase-A MMA has retired
       if (ok) ok = mbar_wait(smem_u32(&bar_accA), 0, p.status, kKernelInCore, 3);
@@ -149,7 +141,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         if (!(ok = mbar_wait(smem_u32(&bar_emptyB[s]), ph ^ 1, p.status, kKernelInCore, 6))) break;
         const uint32_t full = smem_u32(&bar_fullB[s]);
         mbar_arrive_expect_tx(full, G_STAGE_BYTES);
-        tma_load_2d(ringB + s * G_STAGE_BYTES, &tmG, kb * 64, ((j + rotB) % p.n_tiles2) * 256, full);
+        tma_load_2d(ringB + s * G_STAGE_BYTES, &tmG, kb * 64, j * 256, full);
       }
     }
   } else if (warp == 1) {
@@ -347,7 +339,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         const uint32_t t_p = t_lane + slot * 256;
 #pragma unroll 1
         for (int sc = 0; sc < N2 / 16; ++sc) {
-          const int zc = ((j + rotB) % p.n_tiles2) * N2 + sc * 16;  // first z column of this 16-column group
+          const int zc = j * N2 + sc * 16;  // first z column of this 16-column group
           const int unit = zc >> 6, within = zc & 63;
           float acc[16];
 #pragma unroll
@@ -428,7 +420,6 @@ int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared
   p.T = T_; p.d_in = L.d_in; p.r3 = L.r3; p.r2 = L.r2; p.E = L.n_experts; p.top_k = L.top_k;
   p.e_pad = fuse_router ? P.e_pad : 0;
   p.n_tiles2 = P.n_tiles2; p.eps = L.eps; p.fuse_router = fuse_router;
-  { const char *e = getenv("TMOE_STAGGER"); p.stagger = e ? atoi(e) : 0; }
   p.normw = reinterpret_cast<const float *>(base + P.normw);
   p.uexp = reinterpret_cast<const float *>(base + P.uexp);
   p.c_in = c_in; p.c_work = c_work; p.idx_out = idx_out; p.gates_out = gates_out; p.c_out = c_out;
