@@ -11,14 +11,14 @@
 //             is applied to the r1 coefficients instead of the r3 values of h)
 //   phase B   for every r2 tile j (n2 = 256/r1 columns):
 //             P[128, r1*n2] = h[128, r3] @ G_j   with the r1 core slices of the tile side by side
-//   epilogue B z[t, j*n2 + s] = sum_a c[t,a] * P[t, a*n2 + s]  in registers -> bf16 -> smem -> TMA store
+//   epilogue B z[t, j*n2 + s] = sum_a c[t,a] * P[t, a*n2 + s]  in registers -> bf16 -> 16-byte stores
 //             (model.py:95-98 for all selected experts at once); P is double-buffered in TMEM so
 //             this runs under the next tile's MMAs and the [T, r1*r2] intermediate never leaves the SM.
 //
 // One CTA per 128-token tile, 10 warps: TMA producer, MMA issuer, 8 epilogue warps.
 // Shared memory: phase A uses a ring of {x tile, U_in^T tile, router tile} stages over the whole
 // 224 KB; after the last phase-A MMA has completed, the first 64 KB become h and the rest becomes a
-// 4-stage ring of 32 KB core tiles plus one 4 KB staging tile per epilogue warp for the TMA stores of z.
+// 5-stage ring of 32 KB core tiles (z leaves the SM as 16-byte stores straight from registers).
 // All mbarrier waits are bounded.
 #include "common.cuh"
 #include "kernels.h"
@@ -45,12 +45,10 @@ constexpr int X_TILE_BYTES = TM * 64 * 2;  // 16 KB
 constexpr int H_KBLOCK_BYTES = TM * 64 * 2;
 constexpr int H_REGION_BYTES = 4 * H_KBLOCK_BYTES;  // r3 <= 256
 constexpr int G_STAGE_BYTES = 256 * 64 * 2;         // 32 KB
-constexpr int G_STAGES = 4;
+constexpr int G_STAGES = 5;
 constexpr int IC_EPI_WARPS = 8;
 constexpr int IC_THREADS = (2 + IC_EPI_WARPS) * 32;
-constexpr int Z_WARP_BYTES = 32 * 64 * 2;  // 4 KB per epilogue warp: 32 rows x 64 bf16 columns of z for one TMA store
-constexpr int Z_STAGE_OFF = H_REGION_BYTES + G_STAGES * G_STAGE_BYTES;
-constexpr int IC_RING_BYTES = Z_STAGE_OFF + IC_EPI_WARPS * Z_WARP_BYTES;  // 224 KB
+constexpr int IC_RING_BYTES = H_REGION_BYTES + G_STAGES * G_STAGE_BYTES;  // 224 KB
 constexpr int IC_SMEM_BYTES = IC_RING_BYTES + 1024;
 constexpr int A_STAGES_MAX = 4;
 constexpr int SCORE_COL = 256;  // TMEM column of the router scores during phase A
@@ -76,8 +74,7 @@ struct InCoreParams {
 template <int R1, int RK>
 __global__ void __launch_bounds__(IC_THREADS, 1)
 tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmU,
-                  const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmG,
-                  const __grid_constant__ CUtensorMap tmZ, InCoreParams p) {
+                  const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmG, InCoreParams p) {
   constexpr int N2 = 256 / R1;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_fullA[A_STAGES_MAX], bar_emptyA[A_STAGES_MAX], bar_fullB[G_STAGES],
@@ -105,7 +102,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
     mbar_init(smem_u32(&bar_hready), IC_EPI_WARPS);
     for (int s = 0; s < 2; ++s) { mbar_init(smem_u32(&bar_pfull[s]), 1); mbar_init(smem_u32(&bar_pempty[s]), 4); }
     fence_mbar_init();
-    prefetch_tmap(&tmX); prefetch_tmap(&tmU); prefetch_tmap(&tmG); prefetch_tmap(&tmZ);
+    prefetch_tmap(&tmX); prefetch_tmap(&tmU); prefetch_tmap(&tmG);
     if (p.e_pad) prefetch_tmap(&tmW);
   }
   if (warp == 1) { tmem_alloc(smem_u32(&tmem_base_s), 512); tmem_relinquish(); }
@@ -197,14 +194,13 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
     //               h*w -> bf16 -> shared memory); they meet at a named barrier, the primary scales c by the
     //               row's 1/rms and publishes it through the workspace for its secondary twin.
     //   epilogue B: the 64-column units of z alternate between the two groups, so each group has two MMA
-    //               tile times per unit; every warp stages its 32 rows x 64 columns and stores them by TMA.
+    //               tile times per unit; each thread stores its row's columns as 16-byte pieces.
     const int quad = warp & 3;
     const int grp = (warp - 2) >> 2;  // 0 primary, 1 secondary
     const int row = quad * 32 + lane;
     const int64_t grow = (int64_t)m0 + row;
     const bool live = grow < p.T;
     const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
-    const uint32_t zbuf = ring + Z_STAGE_OFF + (warp - 2) * Z_WARP_BYTES;
     float c[R1];
     bool ok = mbar_wait(smem_u32(&bar_accA), 0, p.status, kKernelInCore, 3);
     ok = named_bar_and(2, 256, ok);  // the eight epilogue warps continue or leave together
@@ -340,7 +336,6 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
 #pragma unroll 1
         for (int sc = 0; sc < N2 / 16; ++sc) {
           const int zc = j * N2 + sc * 16;  // first z column of this 16-column group
-          const int unit = zc >> 6, within = zc & 63;
           float acc[16];
 #pragma unroll
           for (int q = 0; q < 16; ++q) acc[q] = 0.f;
@@ -361,29 +356,20 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bar_pempty[slot]));
           }
-          if (within == 0) {
-            if (lane == 0) tma_store_wait_read<0>();  // the previous store has read the staging tile
-            __syncwarp();
-          }
-#pragma unroll
-          for (int g = 0; g < 2; ++g) {
-            const uint32_t chunk = (uint32_t)((within >> 3) + g) ^ (uint32_t)(lane & 7);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(zbuf + lane * 128 + chunk * 16),
-                         "r"(pack_bf16x2(acc[8 * g + 0], acc[8 * g + 1])), "r"(pack_bf16x2(acc[8 * g + 2], acc[8 * g + 3])),
-                         "r"(pack_bf16x2(acc[8 * g + 4], acc[8 * g + 5])), "r"(pack_bf16x2(acc[8 * g + 6], acc[8 * g + 7]))
-                         : "memory");
-          }
-          if (within == 48) {
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              tma_store_2d(&tmZ, zbuf, unit * 64, m0 + quad * 32);
-              tma_store_commit();
-            }
+          // 32 bytes of this thread's z row straight from registers: the bytes in flight of the core-tile
+          // ring matter more to this kernel than coalesced stores (measured), so no staging tile is kept
+          if (live) {
+            bf16 *dst = p.z + grow * p.r2 + zc;
+            uint4 o0, o1;
+            o0.x = pack_bf16x2(acc[0], acc[1]); o0.y = pack_bf16x2(acc[2], acc[3]);
+            o0.z = pack_bf16x2(acc[4], acc[5]); o0.w = pack_bf16x2(acc[6], acc[7]);
+            o1.x = pack_bf16x2(acc[8], acc[9]); o1.y = pack_bf16x2(acc[10], acc[11]);
+            o1.z = pack_bf16x2(acc[12], acc[13]); o1.w = pack_bf16x2(acc[14], acc[15]);
+            *reinterpret_cast<uint4 *>(dst) = o0;
+            *reinterpret_cast<uint4 *>(dst + 8) = o1;
           }
         }
       }
-      if (lane == 0) tma_store_wait_all();
       if (threadIdx.x == 64) TMOE_STAMP(5);  // z stored
     }
   }
@@ -402,7 +388,7 @@ int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared
   const char *base = reinterpret_cast<const char *>(prepared);
   if (fuse_router && (P.e_pad > 256 || L.top_k > 8)) return TMOE_ERR_UNSUPPORTED;
   if ((!fuse_router && !c_in) || !c_work) return TMOE_ERR_NULL;
-  CUtensorMap tmX, tmU, tmW, tmG, tmZ;
+  CUtensorMap tmX, tmU, tmW, tmG;
   int rc = encode_tmap_bf16_2d(&tmX, x, (uint64_t)T_, (uint64_t)L.d_in, TM);
   if (rc) return rc;
   rc = encode_tmap_bf16_2d(&tmU, base + P.uin_t, (uint64_t)L.r3, (uint64_t)L.d_in, (uint32_t)L.r3);
@@ -412,8 +398,6 @@ int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared
                            fuse_router ? (uint32_t)P.e_pad : 16u);
   if (rc) return rc;
   rc = encode_tmap_bf16_2d(&tmG, base + P.g_t, (uint64_t)L.r1 * L.r2, (uint64_t)L.r3, 256);
-  if (rc) return rc;
-  rc = encode_tmap_bf16_2d(&tmZ, z, (uint64_t)T_, (uint64_t)L.r2, 32);
   if (rc) return rc;
 
   InCoreParams p{};
@@ -431,7 +415,7 @@ int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared
 #define TMOE_IC(R, K)                                                                                              \
   do {                                                                                                             \
     e = cudaFuncSetAttribute(tc_in_core_kernel<R, K>, cudaFuncAttributeMaxDynamicSharedMemorySize, IC_SMEM_BYTES); \
-    if (e == cudaSuccess) tc_in_core_kernel<R, K><<<grid, IC_THREADS, IC_SMEM_BYTES, st>>>(tmX, tmU, tmW, tmG, tmZ, p);    \
+    if (e == cudaSuccess) tc_in_core_kernel<R, K><<<grid, IC_THREADS, IC_SMEM_BYTES, st>>>(tmX, tmU, tmW, tmG, p);    \
   } while (0)
   const bool small_k = L.top_k <= 2;
   if (L.r1 == 2) { if (small_k) TMOE_IC(2, 2); else TMOE_IC(2, 8); }
