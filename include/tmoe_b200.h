@@ -91,6 +91,9 @@ typedef struct tmoe_extras {
   int32_t *idx_out;
   float *gates_out;
   float *c_out;
+  const void *silu_gate; /* [T, d_out], dtype of x: y = silu(silu_gate) * (acc @ U_out + bias), the FFN's
+                            silu(gate) * up (pure_torch_mlx/model.py:338-340) fused into the `up` layer;
+                            applied before the residual epilogue */
 } tmoe_extras_t;
 
 /* ABI version of the loaded library (== TMOE_ABI_VERSION of the header it was built from). */
@@ -151,6 +154,12 @@ int tmoe_out(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const voi
 int tmoe_forward(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const void *prepared,
                  const void *x, int64_t T, void *y, const tmoe_extras_t *extras, void *workspace,
                  int64_t workspace_bytes, int path, void *stream);
+
+/* RMSNorm of typed rows: y[t] = x[t] / sqrt(mean(x[t]^2) + eps) * weight (pure_torch_mlx/model.py:25-27),
+ * the callers' pre-norms in front of the layer (model.py:258, 337).  x, weight, y of `dtype`; d % 8 == 0;
+ * fp32 arithmetic with one rounding to the storage type.  y may equal x. */
+int tmoe_rms_norm(int dtype, const void *x, const void *weight, float eps, int64_t T, int32_t d, void *y,
+                  void *stream);
 
 /* Synchronises `stream`, reads the workspace's device status word into *device_status
  * (0, or TMOE_ERR_DEVICE_WAIT with details in the following words) and clears it. */

@@ -16,7 +16,7 @@ ERR_DEVICE_WAIT = -9
 EXPORTS = (
     "tmoe_version", "tmoe_status_string", "tmoe_resolve_path", "tmoe_prepared_bytes",
     "tmoe_prepare_factors", "tmoe_workspace_bytes", "tmoe_router", "tmoe_in_core", "tmoe_out",
-    "tmoe_forward", "tmoe_read_device_status", "tmoe_launch_count", "tmoe_forward_static_scratch",
+    "tmoe_forward", "tmoe_read_device_status", "tmoe_launch_count", "tmoe_forward_static_scratch", "tmoe_rms_norm",
 )
 STATIC_SCRATCH_BYTES = 4 << 20
 
@@ -34,7 +34,7 @@ class Factors(C.Structure):
 
 class Extras(C.Structure):
     _fields_ = [("residual", C.c_void_p), ("layer_scale", C.c_void_p), ("idx_out", C.c_void_p),
-                ("gates_out", C.c_void_p), ("c_out", C.c_void_p)]
+                ("gates_out", C.c_void_p), ("c_out", C.c_void_p), ("silu_gate", C.c_void_p)]
 
 
 class TmoeError(RuntimeError):
@@ -86,6 +86,8 @@ def load():
         lib.tmoe_forward.argtypes = [LP, FP, vp, vp, i64, vp, EP, vp, i64, i32, vp]
         lib.tmoe_forward_static_scratch.restype = i32
         lib.tmoe_forward_static_scratch.argtypes = [LP, FP, vp, i64, vp, EP, vp]
+        lib.tmoe_rms_norm.restype = i32
+        lib.tmoe_rms_norm.argtypes = [i32, vp, vp, C.c_float, i64, C.c_int32, vp, vp]
         lib.tmoe_read_device_status.restype = i32
         lib.tmoe_read_device_status.argtypes = [vp, C.POINTER(C.c_int32), vp]
         lib.tmoe_launch_count.restype = i64

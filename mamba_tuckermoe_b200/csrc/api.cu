@@ -77,6 +77,19 @@ int check_factors(const tmoe_factors_t *F) {
   return TMOE_OK;
 }
 
+// Validates the optional epilogue inputs of `extras` and copies them into an OutEpilogue.
+int epilogue_from(const tmoe_extras_t *extras, OutEpilogue *epi) {
+  if (!extras) return TMOE_OK;
+  if ((extras->residual == nullptr) != (extras->layer_scale == nullptr)) return TMOE_ERR_NULL;
+  const void *ps[3] = {extras->residual, extras->layer_scale, extras->silu_gate};
+  for (const void *q : ps)
+    if (q && misaligned(q)) return TMOE_ERR_ALIGN;
+  epi->residual = extras->residual;
+  epi->layer_scale = extras->layer_scale;
+  epi->silu_gate = extras->silu_gate;
+  return TMOE_OK;
+}
+
 int router_simt(const tmoe_layer_t &L, const tmoe_factors_t &F, const void *x, int64_t T, bool fused, float *scores,
                 int32_t *idx, float *gates, float *c, cudaStream_t st) {
   if (fused) return launch_router_fused(L, x, F.router_w, F.U_expert, T, idx, gates, c, st);
@@ -197,20 +210,17 @@ int tmoe_out(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const voi
   if (!z || !y || !workspace) return TMOE_ERR_NULL;
   if (misaligned(z) || misaligned(y) || (reinterpret_cast<uintptr_t>(workspace) & 255)) return TMOE_ERR_ALIGN;
   if (workspace_bytes < kStatusBytes) return TMOE_ERR_WORKSPACE;
-  const void *residual = extras ? extras->residual : nullptr;
-  const void *scale = extras ? extras->layer_scale : nullptr;
-  if ((residual == nullptr) != (scale == nullptr)) return TMOE_ERR_NULL;
-  if (residual && (misaligned(residual) || misaligned(scale))) return TMOE_ERR_ALIGN;
+  OutEpilogue epi;
+  if ((rc = epilogue_from(extras, &epi))) return rc;
   int rp = resolve(*layer, T, path, false);
   if (rp < 0) return rp;
   cudaStream_t st = (cudaStream_t)stream;
   if (rp == TMOE_PATH_SIMT)
-    return launch_simt_out(*layer, reinterpret_cast<const float *>(z), factors->U_out, factors->bias, residual, scale, T,
-                           y, st);
+    return launch_simt_out(*layer, reinterpret_cast<const float *>(z), factors->U_out, factors->bias, epi, T, y, st);
   if (!prepared) return TMOE_ERR_NULL;
   PreparedLayout P = prepared_layout(*layer);
   const char *pb = reinterpret_cast<const char *>(prepared);
-  return launch_tc_out(*layer, z, pb + P.uout_t, reinterpret_cast<const float *>(pb + P.bias), residual, scale, T, y,
+  return launch_tc_out(*layer, z, pb + P.uout_t, reinterpret_cast<const float *>(pb + P.bias), epi, T, y,
                        reinterpret_cast<int32_t *>(workspace), st);
 }
 
@@ -224,10 +234,8 @@ int tmoe_forward(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const
   if (T == 0) return TMOE_OK;
   if (!x || !y || !workspace) return TMOE_ERR_NULL;
   if (misaligned(x) || misaligned(y) || (reinterpret_cast<uintptr_t>(workspace) & 255)) return TMOE_ERR_ALIGN;
-  const void *residual = extras ? extras->residual : nullptr;
-  const void *scale = extras ? extras->layer_scale : nullptr;
-  if ((residual == nullptr) != (scale == nullptr)) return TMOE_ERR_NULL;
-  if (residual && (misaligned(residual) || misaligned(scale))) return TMOE_ERR_ALIGN;
+  OutEpilogue epi;
+  if ((rc = epilogue_from(extras, &epi))) return rc;
   int rp = resolve(*layer, T, path);
   if (rp < 0) return rp;
   const tmoe_layer_t &L = *layer;
@@ -246,7 +254,7 @@ int tmoe_forward(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const
     if ((rc = router_simt(L, *factors, x, T, W.simt_router_fused, scores, idx, gates, c, st))) return rc;
     if ((rc = launch_simt_inproj_norm(L, x, factors->U_in, factors->inner_norm_w, T, h, st))) return rc;
     if ((rc = launch_simt_core(L, h, c, factors->core, T, z, st))) return rc;
-    return launch_simt_out(L, z, factors->U_out, factors->bias, residual, scale, T, y, st);
+    return launch_simt_out(L, z, factors->U_out, factors->bias, epi, T, y, st);
   }
   if (!prepared) return TMOE_ERR_NULL;
   if (reinterpret_cast<uintptr_t>(prepared) & 255) return TMOE_ERR_ALIGN;
@@ -258,7 +266,7 @@ int tmoe_forward(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const
     const bool taps = extras && (extras->idx_out || extras->gates_out || extras->c_out);
     return launch_decode(L, x, prepared, P, T, reinterpret_cast<float *>(ws + W.h), scores, z,
                          taps ? extras->idx_out : nullptr, taps ? extras->gates_out : nullptr,
-                         taps ? extras->c_out : nullptr, residual, scale, y, st);
+                         taps ? extras->c_out : nullptr, epi, y, st);
   }
   if (W.tc_router_fused) {
     const bool taps = extras && (extras->idx_out || extras->gates_out || extras->c_out);
@@ -267,7 +275,7 @@ int tmoe_forward(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const
                            taps ? extras->gates_out : nullptr, taps ? extras->c_out : nullptr, z, status, st);
   } else {
     // scores = x @ router_w^T on the tensor cores (bf16 out = the reference's rounding), then the select kernel
-    if ((rc = launch_tc_gemm_bf16(x, pb + P.wr_b, nullptr, nullptr, nullptr, T, P.e_pad, L.d_in, scores, status, st)))
+    if ((rc = launch_tc_gemm_bf16(x, pb + P.wr_b, nullptr, OutEpilogue{}, T, P.e_pad, L.d_in, scores, status, st)))
       return rc;
     if ((rc = launch_select_bf16_scores(L, scores, P.e_pad, factors->U_expert, T, idx, gates, c, st))) return rc;
     // c_work may alias c: every row is read by its own thread before that thread overwrites it
@@ -275,8 +283,16 @@ int tmoe_forward(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const
                            status, st);
   }
   if (rc) return rc;
-  return launch_tc_out(L, z, pb + P.uout_t, reinterpret_cast<const float *>(pb + P.bias), residual, scale, T, y, status,
-                       st);
+  return launch_tc_out(L, z, pb + P.uout_t, reinterpret_cast<const float *>(pb + P.bias), epi, T, y, status, st);
+}
+
+int tmoe_rms_norm(int dtype, const void *x, const void *weight, float eps, int64_t T, int32_t d, void *y, void *stream) {
+  if (dtype != TMOE_F32 && dtype != TMOE_BF16) return TMOE_ERR_DTYPE;
+  if (T < 0 || d <= 0 || (d & 7)) return TMOE_ERR_SHAPE;
+  if (T == 0) return TMOE_OK;
+  if (!x || !weight || !y) return TMOE_ERR_NULL;
+  if (misaligned(x) || misaligned(weight) || misaligned(y)) return TMOE_ERR_ALIGN;
+  return launch_rms_norm(dtype, x, weight, eps, T, d, y, (cudaStream_t)stream);
 }
 
 int tmoe_read_device_status(void *workspace, int32_t *device_status, void *stream) {

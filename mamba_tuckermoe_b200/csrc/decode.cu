@@ -181,8 +181,8 @@ decode_core_kernel(const float *__restrict__ h_raw, const float *__restrict__ sc
 template <int TMAX>
 __global__ void __launch_bounds__(kOutWarps * 32)
 decode_out_kernel(const bf16 *__restrict__ z, const bf16 *__restrict__ uout_t, const float *__restrict__ bias,
-                  const bf16 *__restrict__ residual, const bf16 *__restrict__ gamma, int T, int r2, int d_out,
-                  bf16 *__restrict__ y) {
+                  const bf16 *__restrict__ residual, const bf16 *__restrict__ gamma, const bf16 *__restrict__ silu_gate,
+                  int T, int r2, int d_out, bf16 *__restrict__ y) {
   extern __shared__ __align__(16) uint8_t dsm[];
   bf16 *zs = reinterpret_cast<bf16 *>(dsm);  // [TMAX][kc]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -226,6 +226,10 @@ decode_out_kernel(const bf16 *__restrict__ z, const bf16 *__restrict__ uout_t, c
     const int t = g * NB + (lane % NB);
     if (lane < NB && t < T) {
       float v = acc[g][0] + bias[n];
+      if (silu_gate) {
+        const float gg = __bfloat162float(silu_gate[(int64_t)t * d_out + n]);
+        v *= gg / (1.f + expf(-gg));
+      }
       if (residual) v = __bfloat162float(residual[(int64_t)t * d_out + n]) + __bfloat162float(gamma[n]) * v;
       y[(int64_t)t * d_out + n] = __float2bfloat16_rn(v);
     }
@@ -234,8 +238,8 @@ decode_out_kernel(const bf16 *__restrict__ z, const bf16 *__restrict__ uout_t, c
 
 template <int TMAX>
 int launch_decode_t(const tmoe_layer_t &L, const void *x, const char *pb, const PreparedLayout &P, int T, float *h_raw,
-                    float *scores, void *z, int32_t *idx_out, float *gates_out, float *c_out, const void *residual,
-                    const void *layer_scale, void *y, cudaStream_t st) {
+                    float *scores, void *z, int32_t *idx_out, float *gates_out, float *c_out, const OutEpilogue &epi,
+                    void *y, cudaStream_t st) {
   // h_raw and scores are adjacent in the workspace: one clear for the split-K atomics
   const size_t clear_bytes = (size_t)((char *)(scores + (size_t)T * L.n_experts) - (char *)h_raw);
   if (cudaMemsetAsync(h_raw, 0, clear_bytes, st) != cudaSuccess) return TMOE_ERR_CUDA;
@@ -267,8 +271,8 @@ int launch_decode_t(const tmoe_layer_t &L, const void *x, const char *pb, const 
   e = cudaFuncSetAttribute(decode_out_kernel<TMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem3);
   if (e != cudaSuccess) return TMOE_ERR_CUDA;
   decode_out_kernel<TMAX><<<(L.d_out + kOutWarps - 1) / kOutWarps, kOutWarps * 32, smem3, st>>>(
-      (const bf16 *)z, (const bf16 *)(pb + P.uout_t), (const float *)(pb + P.bias), (const bf16 *)residual,
-      (const bf16 *)layer_scale, T, L.r2, L.d_out, (bf16 *)y);
+      (const bf16 *)z, (const bf16 *)(pb + P.uout_t), (const float *)(pb + P.bias), (const bf16 *)epi.residual,
+      (const bf16 *)epi.layer_scale, (const bf16 *)epi.silu_gate, T, L.r2, L.d_out, (bf16 *)y);
   count_launch(3);
   return launch_status();
 }
@@ -277,12 +281,12 @@ int launch_decode_t(const tmoe_layer_t &L, const void *x, const char *pb, const 
 
 int launch_decode(const tmoe_layer_t &L, const void *x, const void *prepared, const PreparedLayout &P, int64_t T,
                   float *h_raw, float *scores, void *z, int32_t *idx_out, float *gates_out, float *c_out,
-                  const void *residual, const void *layer_scale, void *y, cudaStream_t st) {
+                  const OutEpilogue &epi, void *y, cudaStream_t st) {
   const char *pb = reinterpret_cast<const char *>(prepared);
   if (T > 64) return TMOE_ERR_UNSUPPORTED;
   if (T <= 8)
-    return launch_decode_t<8>(L, x, pb, P, (int)T, h_raw, scores, z, idx_out, gates_out, c_out, residual, layer_scale, y, st);
-  return launch_decode_t<64>(L, x, pb, P, (int)T, h_raw, scores, z, idx_out, gates_out, c_out, residual, layer_scale, y, st);
+    return launch_decode_t<8>(L, x, pb, P, (int)T, h_raw, scores, z, idx_out, gates_out, c_out, epi, y, st);
+  return launch_decode_t<64>(L, x, pb, P, (int)T, h_raw, scores, z, idx_out, gates_out, c_out, epi, y, st);
 }
 
 }  // namespace tmoe

@@ -7,6 +7,16 @@
 
 namespace tmoe {
 
+// Optional element-wise tail of the out-projection, applied in fp32 to v = acc + bias, in this order:
+//   silu_gate   v = silu(g[t, n]) * v                      (the FFN's silu(gate) * up, model.py:340)
+//   residual    v = residual[t, n] + layer_scale[n] * v    (model.py:260, 341)
+// Pointers are in the layer dtype; nullptr = not applied.
+struct OutEpilogue {
+  const void *residual = nullptr;
+  const void *layer_scale = nullptr;
+  const void *silu_gate = nullptr;
+};
+
 // ---- router.cu ----
 int launch_router_fused(const tmoe_layer_t &L, const void *x, const void *wr, const void *uexp, int64_t T,
                         int32_t *idx, float *gates, float *c, cudaStream_t st);
@@ -26,8 +36,10 @@ int launch_simt_inproj_norm(const tmoe_layer_t &L, const void *x, const void *U_
 int launch_simt_core(const tmoe_layer_t &L, const float *h, const float *c, const void *core, int64_t T, float *z,
                      cudaStream_t st);
 // y[T, d_out] (layer dtype) = z @ U_out + bias, optionally residual + layer_scale * (...)
-int launch_simt_out(const tmoe_layer_t &L, const float *z, const void *U_out, const void *bias, const void *residual,
-                    const void *layer_scale, int64_t T, void *y, cudaStream_t st);
+int launch_simt_out(const tmoe_layer_t &L, const float *z, const void *U_out, const void *bias, const OutEpilogue &epi,
+                    int64_t T, void *y, cudaStream_t st);
+// y[T, d] = x / sqrt(mean(x^2) + eps) * w, fp32 arithmetic, one rounding to the storage type (model.py:25-27)
+int launch_rms_norm(int dtype, const void *x, const void *w, float eps, int64_t T, int d, void *y, cudaStream_t st);
 
 // ---- prepare.cu ----
 struct PreparedLayout {
@@ -40,12 +52,12 @@ int launch_prepare(const tmoe_layer_t &L, const tmoe_factors_t &F, void *prepare
 
 // ---- tc_out_gemm.cu ----
 // y[T, N] = z[T, K] (bf16) @ W_t[N, K]^T (bf16, K-major) + bias (fp32) on tcgen05 tensor cores.
-int launch_tc_out(const tmoe_layer_t &L, const void *z, const void *uout_t, const float *bias, const void *residual,
-                  const void *layer_scale, int64_t T, void *y, int32_t *status, cudaStream_t st);
+int launch_tc_out(const tmoe_layer_t &L, const void *z, const void *uout_t, const float *bias, const OutEpilogue &epi,
+                  int64_t T, void *y, int32_t *status, cudaStream_t st);
 
 // General form of the same kernel (used for the router scores when E is too large for the in-kernel router).
-int launch_tc_gemm_bf16(const void *A, const void *B_t, const float *bias, const void *residual, const void *gamma,
-                        int64_t M, int N, int K, void *y, int32_t *status, cudaStream_t st);
+int launch_tc_gemm_bf16(const void *A, const void *B_t, const float *bias, const OutEpilogue &epi, int64_t M, int N,
+                        int K, void *y, int32_t *status, cudaStream_t st);
 
 // ---- tc_in_core.cu ----
 // Fused x@U_in (+ router scores) -> RMS statistics -> h@G tiles with c-weighted epilogue -> z bf16.
@@ -60,6 +72,6 @@ int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared
 // fp32 atomics into h_raw/scores (adjacent in memory, cleared here), norm + routing + core, out-projection.
 int launch_decode(const tmoe_layer_t &L, const void *x, const void *prepared, const PreparedLayout &P, int64_t T,
                   float *h_raw, float *scores, void *z, int32_t *idx_out, float *gates_out, float *c_out,
-                  const void *residual, const void *layer_scale, void *y, cudaStream_t st);
+                  const OutEpilogue &epi, void *y, cudaStream_t st);
 
 }  // namespace tmoe

@@ -38,8 +38,13 @@ struct EpiOut {
   const T *bias;
   const T *residual;
   const T *gamma;
+  const T *silu_gate;
   __device__ __forceinline__ void operator()(int m, int n, float v) const {
     if (bias) v += to_f32(bias[n]);
+    if (silu_gate) {
+      const float g = to_f32(silu_gate[(int64_t)m * ldc + n]);
+      v *= g / (1.f + expf(-g));
+    }
     if (residual) v = to_f32(residual[(int64_t)m * ldc + n]) + to_f32(gamma[n]) * v;
     y[(int64_t)m * ldc + n] = from_f32<T>(v);
   }
@@ -188,18 +193,54 @@ int launch_simt_core(const tmoe_layer_t &L, const float *h, const float *c, cons
 }
 
 template <typename T>
-static int out_t(const tmoe_layer_t &L, const float *z, const void *U_out, const void *bias, const void *residual,
-                 const void *layer_scale, int64_t T_, void *y, cudaStream_t st) {
+static int out_t(const tmoe_layer_t &L, const float *z, const void *U_out, const void *bias, const OutEpilogue &epi,
+                 int64_t T_, void *y, cudaStream_t st) {
   GemmP p{z, U_out, (int)T_, L.d_out, L.r2, L.r2, L.d_out, nullptr, 0, 0};
-  EpiOut<T> e{(T *)y, L.d_out, (const T *)bias, (const T *)residual, (const T *)layer_scale};
+  EpiOut<T> e{(T *)y, L.d_out, (const T *)bias, (const T *)epi.residual, (const T *)epi.layer_scale,
+              (const T *)epi.silu_gate};
   simt_gemm_kernel<float, T, false, false, EpiOut<T>><<<gemm_grid(T_, L.d_out), 256, 0, st>>>(p, e);
   count_launch();
   return launch_status();
 }
-int launch_simt_out(const tmoe_layer_t &L, const float *z, const void *U_out, const void *bias, const void *residual,
-                    const void *layer_scale, int64_t T_, void *y, cudaStream_t st) {
-  return L.dtype == TMOE_F32 ? out_t<float>(L, z, U_out, bias, residual, layer_scale, T_, y, st)
-                             : out_t<bf16>(L, z, U_out, bias, residual, layer_scale, T_, y, st);
+int launch_simt_out(const tmoe_layer_t &L, const float *z, const void *U_out, const void *bias, const OutEpilogue &epi,
+                    int64_t T_, void *y, cudaStream_t st) {
+  return L.dtype == TMOE_F32 ? out_t<float>(L, z, U_out, bias, epi, T_, y, st) : out_t<bf16>(L, z, U_out, bias, epi, T_, y, st);
+}
+
+// Stand-alone RMSNorm of typed rows (the callers' pre-norms, model.py:258, 337): one warp per row,
+// 128-bit loads, the row stays in registers between the two passes when it fits.
+template <typename T>
+__global__ void __launch_bounds__(256) rms_norm_kernel(const T *__restrict__ x, const T *__restrict__ w, T *__restrict__ y,
+                                                       int64_t Tn, int d, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int64_t t = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (t >= Tn) return;
+  const T *xr = x + t * d;
+  T *yr = y + t * d;
+  float ss = 0.f;
+  for (int i = lane * 4; i < d; i += 128) {
+    float v[4];
+    load4<T>(xr + i, v);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) ss = fmaf(v[q], v[q], ss);
+  }
+  ss = warp_sum(ss);
+  const float den = sqrtf(ss / (float)d + eps);
+  for (int i = lane * 4; i < d; i += 128) {
+    float v[4], g[4];
+    load4<T>(xr + i, v);
+    load4<T>(w + i, g);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) yr[i + q] = from_f32<T>(v[q] / den * g[q]);
+  }
+}
+
+int launch_rms_norm(int dtype, const void *x, const void *w, float eps, int64_t T_, int d, void *y, cudaStream_t st) {
+  const unsigned grid = (unsigned)((T_ + 7) / 8);
+  if (dtype == TMOE_F32) rms_norm_kernel<float><<<grid, 256, 0, st>>>((const float *)x, (const float *)w, (float *)y, T_, d, eps);
+  else rms_norm_kernel<bf16><<<grid, 256, 0, st>>>((const bf16 *)x, (const bf16 *)w, (bf16 *)y, T_, d, eps);
+  count_launch();
+  return launch_status();
 }
 
 }  // namespace tmoe

@@ -113,6 +113,8 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
   const uint32_t ringB = ring + H_REGION_BYTES;
 #ifdef TMOE_TRACE
   const long long trace_t0 = clock64();
+  unsigned long long trace_ns0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(trace_ns0));
 #endif
 
   if (warp == 0) {
@@ -371,6 +373,13 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         }
       }
       if (threadIdx.x == 64) TMOE_STAMP(5);  // z stored
+#ifdef TMOE_TRACE
+      if (threadIdx.x == 64 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)) {
+        unsigned long long ns1;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns1));
+        p.status[32 + (blockIdx.x == 0 ? 0 : 1)] = (int32_t)(ns1 - trace_ns0);  // wall time of the same span in ns
+      }
+#endif
     }
   }
   tc_fence_before();

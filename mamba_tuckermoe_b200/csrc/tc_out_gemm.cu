@@ -67,6 +67,7 @@ struct OutParams {
   const float *bias;
   const bf16 *residual;
   const bf16 *gamma;
+  const bf16 *silu_gate;
   int64_t T;
   int N, K;
   int num_m, num_n;
@@ -190,6 +191,16 @@ tc_out_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                 v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
                 v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
               }
+              if (p.silu_gate && row < p.T) {
+                const uint4 gv = __ldg(reinterpret_cast<const uint4 *>(p.silu_gate + row * p.N + col));
+                const uint32_t gw2[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  const float g0 = __uint_as_float(gw2[q] << 16), g1 = __uint_as_float(gw2[q] & 0xffff0000u);
+                  v[2 * q] *= g0 / (1.f + __expf(-g0));
+                  v[2 * q + 1] *= g1 / (1.f + __expf(-g1));
+                }
+              }
               if (p.residual && row < p.T) {
                 const uint4 rr = __ldg(reinterpret_cast<const uint4 *>(p.residual + row * p.N + col));
                 const uint4 gg = __ldg(reinterpret_cast<const uint4 *>(p.gamma + col));
@@ -229,9 +240,9 @@ tc_out_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
 }
 
 // y[M, N] (bf16) = A[M, K] (bf16, row-major) @ B_t[N, K]^T (bf16, K-major) + bias[N] (fp32, optional),
-// optionally residual + gamma * (...).  N and K multiples of 8.
-int launch_tc_gemm_bf16(const void *A, const void *B_t, const float *bias, const void *residual, const void *gamma,
-                        int64_t M, int N, int K, void *y, int32_t *status, cudaStream_t st) {
+// then the optional OutEpilogue tail.  N and K multiples of 8.
+int launch_tc_gemm_bf16(const void *A, const void *B_t, const float *bias, const OutEpilogue &epi, int64_t M, int N,
+                        int K, void *y, int32_t *status, cudaStream_t st) {
   CUtensorMap tmA, tmB, tmY;
   int rc = encode_tmap_bf16_2d(&tmY, y, (uint64_t)M, (uint64_t)N, 32);
   if (rc) return rc;
@@ -249,7 +260,8 @@ int launch_tc_gemm_bf16(const void *A, const void *B_t, const float *bias, const
     attr_done[dev] = true;
   }
   OutParams p{};
-  p.y = (bf16 *)y; p.bias = bias; p.residual = (const bf16 *)residual; p.gamma = (const bf16 *)gamma;
+  p.y = (bf16 *)y; p.bias = bias; p.residual = (const bf16 *)epi.residual; p.gamma = (const bf16 *)epi.layer_scale;
+  p.silu_gate = (const bf16 *)epi.silu_gate;
   p.T = M; p.N = N; p.K = K;
   p.num_m = (int)((M + OM - 1) / OM); p.num_n = (N + ON - 1) / ON;
   p.status = status;
@@ -260,9 +272,9 @@ int launch_tc_gemm_bf16(const void *A, const void *B_t, const float *bias, const
   return launch_status();
 }
 
-int launch_tc_out(const tmoe_layer_t &L, const void *z, const void *uout_t, const float *bias, const void *residual,
-                  const void *layer_scale, int64_t T_, void *y, int32_t *status, cudaStream_t st) {
-  return launch_tc_gemm_bf16(z, uout_t, bias, residual, layer_scale, T_, L.d_out, L.r2, y, status, st);
+int launch_tc_out(const tmoe_layer_t &L, const void *z, const void *uout_t, const float *bias, const OutEpilogue &epi,
+                  int64_t T_, void *y, int32_t *status, cudaStream_t st) {
+  return launch_tc_gemm_bf16(z, uout_t, bias, epi, T_, L.d_out, L.r2, y, status, st);
 }
 
 }  // namespace tmoe

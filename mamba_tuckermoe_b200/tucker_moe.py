@@ -22,6 +22,7 @@ from . import _lib
 from ._lib import PATH_AUTO, PATH_DECODE, PATH_SIMT, PATH_TENSOR, Extras, Factors, Layer
 
 __all__ = ["TuckerMoE", "TuckerMoEConfig", "RMSNorm", "tucker_moe_forward", "tucker_moe_forward_taps", "prepare_factors",
+           "rms_norm", "fused_ffn", "fused_out_proj",
            "PATH_AUTO", "PATH_SIMT", "PATH_TENSOR", "PATH_DECODE"]
 
 
@@ -130,7 +131,7 @@ def _validate(x, params, top_k):
 
 
 def _run(x, router_w, U_in, inner_norm_w, eps, U_expert, core, U_out, bias, top_k, path,
-         residual=None, layer_scale=None, want_taps=False, prepared=None):
+         residual=None, layer_scale=None, want_taps=False, prepared=None, silu_gate=None):
     params = (router_w, U_in, inner_norm_w, U_expert, core, U_out, bias)
     _validate(x, params, top_k)
     lib = _lib.load()
@@ -173,6 +174,12 @@ def _run(x, router_w, U_in, inner_norm_w, eps, U_expert, core, U_out, bias, top_
                 raise RuntimeError("tmoe_b200: residual must be (..., d_out) and layer_scale (d_out,) in x's dtype")
             extras.residual, extras.layer_scale = res2.data_ptr(), ls.data_ptr()
             keep += [res2, ls]
+        if silu_gate is not None:
+            g2 = silu_gate.reshape(-1, d_out).contiguous()
+            if g2.shape[0] != T or g2.dtype != x.dtype or g2.device != dev:
+                raise RuntimeError("tmoe_b200: silu_gate must be (..., d_out) in x's dtype on x's device")
+            extras.silu_gate = g2.data_ptr()
+            keep.append(g2)
         if want_taps:
             taps = (torch.empty((T, top_k), dtype=torch.int32, device=dev),
                     torch.empty((T, top_k), dtype=torch.float32, device=dev),
@@ -206,28 +213,58 @@ def read_device_status(device=None) -> Tuple[int, int, int, int]:
 def _forward_op(x: torch.Tensor, router_w: torch.Tensor, U_in: torch.Tensor, inner_norm_w: torch.Tensor, eps: float,
                 U_expert: torch.Tensor, core: torch.Tensor, U_out: torch.Tensor, bias: torch.Tensor, top_k: int,
                 path: int, residual: Optional[torch.Tensor], layer_scale: Optional[torch.Tensor],
-                prepared: Optional[torch.Tensor]) -> torch.Tensor:
+                prepared: Optional[torch.Tensor], silu_gate: Optional[torch.Tensor]) -> torch.Tensor:
     y, _ = _run(x, router_w, U_in, inner_norm_w, eps, U_expert, core, U_out, bias, top_k, path, residual, layer_scale,
-                prepared=prepared)
+                prepared=prepared, silu_gate=silu_gate)
     return y
 
 
 @_forward_op.register_fake
-def _(x, router_w, U_in, inner_norm_w, eps, U_expert, core, U_out, bias, top_k, path, residual, layer_scale, prepared):
+def _(x, router_w, U_in, inner_norm_w, eps, U_expert, core, U_out, bias, top_k, path, residual, layer_scale, prepared,
+      silu_gate):
     return x.new_empty((*x.shape[:-1], U_out.shape[1]))
 
 
+@torch.library.custom_op("tmoe_b200::rms_norm", mutates_args=())
+def _rms_norm_op(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    if not x.is_cuda or x.dtype not in _DTYPES:
+        raise RuntimeError("tmoe_b200: rms_norm runs on float32 / bfloat16 CUDA tensors only (no CPU fallback)")
+    if weight.dtype != x.dtype or weight.device != x.device or weight.shape != (x.shape[-1],):
+        raise RuntimeError("tmoe_b200: rms_norm weight must be (d,) in x's dtype on x's device")
+    lib = _lib.load()
+    d = x.shape[-1]
+    x2 = x.reshape(-1, d)
+    x2 = x2 if x2.is_contiguous() else x2.contiguous()
+    w = weight if weight.is_contiguous() else weight.contiguous()
+    y = torch.empty_like(x2)
+    with torch.cuda.device(x.device):
+        _lib.check(lib.tmoe_rms_norm(_DTYPES[x.dtype], x2.data_ptr(), w.data_ptr(), float(eps), x2.shape[0], d,
+                                     y.data_ptr(), torch.cuda.current_stream(x.device).cuda_stream), "tmoe_rms_norm")
+    return y.reshape(x.shape)
+
+
+@_rms_norm_op.register_fake
+def _(x, weight, eps):
+    return torch.empty_like(x)
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """``x / sqrt(mean(x^2) + eps) * weight`` (the reference ``RMSNorm.forward``, ``model.py:25-27``)."""
+    return torch.ops.tmoe_b200.rms_norm(x, weight, float(eps))
+
+
 def tucker_moe_forward(x, router_w, U_in, inner_norm_w, eps, U_expert, core, U_out, bias, top_k, *, path=PATH_AUTO,
-                       residual=None, layer_scale=None, prepared=None):
+                       residual=None, layer_scale=None, prepared=None, silu_gate=None):
     """Functional form of the layer (parameter order of ``pure_torch_mlx/weights.py:74-81``).
     With ``residual``/``layer_scale`` it returns ``residual + layer_scale * layer(x)``
     (the callers' epilogue, ``model.py:260, 341``).  ``prepared`` is an optional result of
     ``prepare_factors`` for the same seven tensors; without it the tensor-core path re-lays the
-    factors out on every call."""
+    factors out on every call.  With ``silu_gate`` the result is ``silu(silu_gate) * layer(x)`` (the FFN's
+    ``silu(gate) * up``, ``model.py:338-340``), applied before the residual epilogue."""
     if (residual is None) != (layer_scale is None):
         raise RuntimeError("tmoe_b200: residual and layer_scale go together")
     return torch.ops.tmoe_b200.forward(x, router_w, U_in, inner_norm_w, float(eps), U_expert, core, U_out, bias,
-                                       int(top_k), int(path), residual, layer_scale, prepared)
+                                       int(top_k), int(path), residual, layer_scale, prepared, silu_gate)
 
 
 def tucker_moe_forward_taps(x, router_w, U_in, inner_norm_w, eps, U_expert, core, U_out, bias, top_k, *,
@@ -283,6 +320,23 @@ class TuckerMoE(nn.Module):
         """x: (..., d_in) -> (..., d_out)"""
         rw, ui, nw, ue, co, uo, b = self._params()
         return tucker_moe_forward(x, rw, ui, nw, self.inner_norm.eps, ue, co, uo, b, self.top_k, path=self.path,
+                                  prepared=self._prepared_for(x))
+
+    def forward_fused(self, x: torch.Tensor, *, pre_norm=None, residual: Optional[torch.Tensor] = None,
+                      layer_scale: Optional[torch.Tensor] = None, silu_gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """The layer with the callers' element-wise work attached:
+
+        ``pre_norm``  an RMSNorm module (anything with ``.weight`` and ``.eps``) or a ``(weight, eps)`` pair
+                      applied to ``x`` first (``norm_out_proj`` / ``norm_ffn``, ``model.py:258, 337``);
+        ``silu_gate`` ``silu(silu_gate) * layer(...)`` in the out-projection's epilogue (``model.py:340``);
+        ``residual``, ``layer_scale``  ``residual + layer_scale * (...)`` in the same epilogue (``model.py:260, 341``).
+        """
+        if pre_norm is not None:
+            w, e = (pre_norm.weight, pre_norm.eps) if hasattr(pre_norm, "weight") else pre_norm
+            x = rms_norm(x, w, e)
+        rw, ui, nw, ue, co, uo, b = self._params()
+        return tucker_moe_forward(x, rw, ui, nw, self.inner_norm.eps, ue, co, uo, b, self.top_k, path=self.path,
+                                  residual=residual, layer_scale=layer_scale, silu_gate=silu_gate,
                                   prepared=self._prepared_for(x))
 
     def forward_fused_residual(self, x: torch.Tensor, residual: torch.Tensor, layer_scale: torch.Tensor) -> torch.Tensor:
@@ -355,3 +409,22 @@ class TuckerMoE(nn.Module):
         """Call after writing parameters through ``.data`` once the layer has already run
         (such writes do not change tensor versions, which key the prepared-factor cache)."""
         self._prep_key, self._prep = None, None
+
+
+def fused_out_proj(out_proj: TuckerMoE, mid: torch.Tensor, norm, layer_scale: torch.Tensor) -> torch.Tensor:
+    """``mid + gamma * out_proj(norm(mid))`` -- the tail of the reference's Mamba block (``model.py:258-260``)
+    as one normalisation kernel and one layer call whose epilogue adds the scaled result to ``mid``."""
+    return out_proj.forward_fused(mid, pre_norm=norm, residual=mid, layer_scale=layer_scale)
+
+
+def fused_ffn(ffn_gate: TuckerMoE, ffn_up: TuckerMoE, ffn_down: TuckerMoE, x_res: torch.Tensor, norm,
+              layer_scale: torch.Tensor) -> torch.Tensor:
+    """``x_res + gamma * ffn_down(silu(ffn_gate(x_f)) * ffn_up(x_f))`` with ``x_f = norm(x_res)`` -- the FFN of the
+    reference's transformer block (``model.py:337-341``).  ``x_f`` is computed once and shared by the gate and up
+    layers, ``silu(gate) * up`` is the epilogue of the up layer and the residual add is the epilogue of the down
+    layer, so no element-wise pass over the 6x-wide activations remains."""
+    w, e = (norm.weight, norm.eps) if hasattr(norm, "weight") else norm
+    x_f = rms_norm(x_res, w, e)
+    gate = ffn_gate(x_f)
+    act = ffn_up.forward_fused(x_f, silu_gate=gate)
+    return ffn_down.forward_fused(act, residual=x_res, layer_scale=layer_scale)

@@ -107,5 +107,5 @@ def test_fake_kernel_gives_shapes_without_a_gpu():
         x = torch.empty(2, 5, 64)
         y = torch.ops.tmoe_b200.forward(x, torch.empty(8, 64), torch.empty(64, 32), torch.empty(32), 1e-5,
                                         torch.empty(8, 4), torch.empty(4, 32, 64), torch.empty(64, 96),
-                                        torch.empty(96), 2, 0, None, None, None)
+                                        torch.empty(96), 2, 0, None, None, None, None)
     assert y.shape == (2, 5, 96)

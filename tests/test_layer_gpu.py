@@ -247,3 +247,48 @@ def test_forward_host_equals_device_forward(T, chunk):
     y2 = m.forward_host(x.reshape(1, T, -1))   # unpinned input, allocated output, leading shape kept
     torch.cuda.current_stream().synchronize()
     assert y2.shape == (1, T, shape.d_out) and rel_fro(y2.float().reshape(T, -1), y_host.float()) < 5e-3
+
+
+@pytest.mark.parametrize("dtype,T", [(torch.float32, 50), (torch.bfloat16, 300), (torch.bfloat16, 7)])
+def test_rms_norm_matches_reference_formula(dtype, T):
+    g = torch.Generator().manual_seed(5)
+    x = (torch.randn(T, 768, generator=g) * 3).to(dtype)
+    w = (1 + 0.2 * torch.randn(768, generator=g)).to(dtype)
+    from mamba_tuckermoe_b200 import rms_norm
+    from oracle.tucker_moe_oracle import rms_norm as ref_norm
+    y = rms_norm(x.cuda(), w.cuda(), 1e-5).cpu()
+    ref = ref_norm(x, w, 1e-5)                         # the reference's formula in the tensor dtype (model.py:25-27)
+    tol = 2e-6 if dtype == torch.float32 else 1e-2     # bf16: the reference rounds after every step, the kernel once
+    assert rel_fro(y.float(), ref.float()) < tol
+    ref64 = x.double() / torch.sqrt(x.double().pow(2).mean(-1, keepdim=True) + 1e-5) * w.double()
+    assert rel_fro(y.float(), ref64) < (1e-6 if dtype == torch.float32 else 4e-3)
+
+
+@pytest.mark.parametrize("T", [5, 200])
+def test_fused_ffn_and_out_proj_match_callers_composition(T):
+    """fused_ffn / fused_out_proj against the literal composition of model.py:337-341 and 258-260 on the oracle."""
+    import torch.nn.functional as F
+    from mamba_tuckermoe_b200 import fused_ffn, fused_out_proj
+    from oracle.tucker_moe_oracle import rms_norm as ref_norm
+    d, dff = 256, 768
+    s_up = LayerShape(d, dff, 8, 2, 4, 128, 256, 1e-5)
+    s_dn = LayerShape(dff, d, 8, 2, 4, 128, 256, 1e-5)
+    fg, fu, fd = (make_factors(s, 70 + i, torch.bfloat16, 0.02, 0.05) for i, s in enumerate((s_up, s_up, s_dn)))
+    g = torch.Generator().manual_seed(8)
+    x = torch.randn(T, d, generator=g).bfloat16()
+    nw = (1 + 0.1 * torch.randn(d, generator=g)).bfloat16()
+    gamma = (0.5 + 0.1 * torch.randn(d, generator=g)).bfloat16()
+    mg, mu, md = build_module(s_up, fg, torch.bfloat16), build_module(s_up, fu, torch.bfloat16), build_module(s_dn, fd, torch.bfloat16)
+    out = fused_ffn(mg, mu, md, x.cuda(), (nw.cuda(), 1e-5), gamma.cuda()).float().cpu()
+    # float64 statement of the same composition (bf16 reference chains are too noisy to be a tight check)
+    xf = ref_norm(x.double(), nw.double(), 1e-5)
+    lay = lambda t, f, s: layer_forward_f64(t, f, s.top_k, s.eps, round_scores_to=torch.bfloat16)[0]
+    ref = x.double() + gamma.double() * lay(F.silu(lay(xf, fg, s_up)) * lay(xf, fu, s_up), fd, s_dn)
+    assert rel_fro(out, ref) < 3e-2
+    # out_proj tail: mid + gamma * layer(norm(mid))
+    s_o = LayerShape(d, d, 8, 2, 4, 128, 256, 1e-5)
+    fo = make_factors(s_o, 90, torch.bfloat16, 0.02, 0.05)
+    mo = build_module(s_o, fo, torch.bfloat16)
+    got = fused_out_proj(mo, x.cuda(), (nw.cuda(), 1e-5), gamma.cuda()).float().cpu()
+    want = x.double() + gamma.double() * lay(ref_norm(x.double(), nw.double(), 1e-5), fo, s_o)
+    assert rel_fro(got, want) < 2e-2
