@@ -14,6 +14,7 @@
 #include "common.cuh"
 #include "kernels.h"
 #include "ptx.cuh"
+#include <cstdlib>
 
 namespace tmoe {
 
@@ -62,6 +63,24 @@ constexpr int O_Y_BYTES = 32 * 64 * 2;  // 4 KB per epilogue warp: 32 rows x 64 
 constexpr int O_SMEM_BYTES = OSTAGES * O_STAGE_BYTES + O_EPI_WARPS * O_Y_BYTES + 1024;
 constexpr int kKernelOut = 3;
 
+// Diagnostic builds (-DTMOE_TRACE): block 0 accumulates the cycles its roles spend in each wait into
+// status words [40..47].
+#ifdef TMOE_TRACE
+#define TMOE_TIC() trace_tic = clock64()
+#define TMOE_TOC(i)                                                                             \
+  do {                                                                                          \
+    if (blockIdx.x == 0) {                                                                      \
+      const int dt_ = (int)(clock64() - trace_tic);                                             \
+      atomicAdd(&p.status[40 + (i)], dt_);                                                      \
+      if ((i) == 2) atomicAdd(&p.status[48 + (dt_ < 64 ? 0 : dt_ < 256 ? 1 : dt_ < 1024 ? 2 : 3)], 1); \
+      if ((i) == 2 && dt_ >= 1024) atomicAdd(&p.status[52], dt_);                               \
+    }                                                                                           \
+  } while (0)
+#else
+#define TMOE_TIC() do { } while (0)
+#define TMOE_TOC(i) do { } while (0)
+#endif
+
 struct OutParams {
   bf16 *y;
   const float *bias;
@@ -100,6 +119,10 @@ tc_out_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
 
   const int num_tiles = p.num_m * p.num_n;
   const int KB = (p.K + OKB - 1) / OKB;
+#ifdef TMOE_TRACE
+  const long long trace_t0 = clock64();
+  long long trace_tic = 0;
+#endif
 
   if (warp == 0) {
     if (lane == 0) {
@@ -109,7 +132,9 @@ tc_out_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
         const int m0 = (tile / p.num_n) * OM, n0 = (tile % p.num_n) * ON;
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const uint32_t s = it % OSTAGES, ph = (it / OSTAGES) & 1;
+          TMOE_TIC();
           if (!(ok = mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1, p.status, kKernelOut, 2))) break;
+          TMOE_TOC(0);  // producer waiting for a free stage
           const uint32_t full = smem_u32(&bar_full[s]);
           mbar_arrive_expect_tx(full, O_STAGE_BYTES);
           const uint32_t sa = ring + s * O_STAGE_BYTES;
@@ -125,12 +150,16 @@ tc_out_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
         const uint32_t slot = tcount & 1, aph = (tcount >> 1) & 1;
+        TMOE_TIC();
         if (!(ok = mbar_wait(smem_u32(&bar_tempty[slot]), aph ^ 1, p.status, kKernelOut, 4))) break;
+        TMOE_TOC(1);  // MMA thread waiting for the epilogue to release an accumulator
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + slot * ON;
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const uint32_t s = it % OSTAGES, ph = (it / OSTAGES) & 1;
+          TMOE_TIC();
           if (!(ok = mbar_wait(smem_u32(&bar_full[s]), ph, p.status, kKernelOut, 1))) break;
+          TMOE_TOC(2);  // MMA thread waiting for operand tiles
           tc_fence_after();
           const uint32_t sa = ring + s * O_STAGE_BYTES;
           const uint64_t da = umma_desc_k_sw128(sa), db = umma_desc_k_sw128(sa + O_A_BYTES);
@@ -156,7 +185,9 @@ tc_out_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
       const int m0 = (tile / p.num_n) * OM, n0 = (tile % p.num_n) * ON;
       const uint32_t slot = tcount & 1, aph = (tcount >> 1) & 1;
+      TMOE_TIC();
       ok = mbar_wait(smem_u32(&bar_tfull[slot]), aph, p.status, kKernelOut, 3);
+      if (threadIdx.x == 64) TMOE_TOC(3);  // epilogue warp 2 waiting for a finished accumulator
       ok = __all_sync(0xffffffffu, ok);  // the TMEM loads below are warp-collective
       if (!ok) break;
       tc_fence_after();
@@ -173,6 +204,203 @@ tc_out_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[slot]));
+        }
+        TMOE_TIC();
+        if (lane == 0) tma_store_wait_read<0>();  // the previous store has finished reading the staging tile
+        if (threadIdx.x == 64) TMOE_TOC(4);  // epilogue warp 2 waiting for its previous TMA store
+        __syncwarp();
+#pragma unroll
+        for (int h2 = 0; h2 < 2; ++h2) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int col = col0 + h2 * 32 + g * 8;
+            float v[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) v[q] = __uint_as_float(r[h2][g * 8 + q]);
+            if (col < p.N) {  // N % 8 == 0: a group of 8 is entirely in or out; columns >= N are clipped by the store
+              if (p.bias) {
+                const float4 b0 = __ldg(reinterpret_cast<const float4 *>(p.bias + col));
+                const float4 b1 = __ldg(reinterpret_cast<const float4 *>(p.bias + col + 4));
+                v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+                v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+              }
+              if (p.silu_gate && row < p.T) {
+                const uint4 gv = __ldg(reinterpret_cast<const uint4 *>(p.silu_gate + row * p.N + col));
+                const uint32_t gw2[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  const float g0 = __uint_as_float(gw2[q] << 16), g1 = __uint_as_float(gw2[q] & 0xffff0000u);
+                  v[2 * q] *= g0 / (1.f + __expf(-g0));
+                  v[2 * q + 1] *= g1 / (1.f + __expf(-g1));
+                }
+              }
+              if (p.residual && row < p.T) {
+                const uint4 rr = __ldg(reinterpret_cast<const uint4 *>(p.residual + row * p.N + col));
+                const uint4 gg = __ldg(reinterpret_cast<const uint4 *>(p.gamma + col));
+                const uint32_t rw[4] = {rr.x, rr.y, rr.z, rr.w}, gw[4] = {gg.x, gg.y, gg.z, gg.w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  v[2 * q] = __uint_as_float(rw[q] << 16) + __uint_as_float(gw[q] << 16) * v[2 * q];
+                  v[2 * q + 1] = __uint_as_float(rw[q] & 0xffff0000u) + __uint_as_float(gw[q] & 0xffff0000u) * v[2 * q + 1];
+                }
+              }
+            }
+            // 16-byte chunk (h2*4+g) of this lane's 128-byte row, XOR-swizzled as the TMA box expects
+            const uint32_t chunk = (uint32_t)(h2 * 4 + g) ^ (uint32_t)(lane & 7);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_buf + lane * 128 + chunk * 16),
+                         "r"(pack_bf16x2(v[0], v[1])), "r"(pack_bf16x2(v[2], v[3])), "r"(pack_bf16x2(v[4], v[5])),
+                         "r"(pack_bf16x2(v[6], v[7]))
+                         : "memory");
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0 && col0 < p.N) {
+          tma_store_2d(&tmY, stage_buf, col0, m0 + quad * 32);
+          tma_store_commit();
+        }
+      }
+    }
+    if (lane == 0) tma_store_wait_all();
+  }
+#ifdef TMOE_TRACE
+  if (blockIdx.x == 0 && threadIdx.x == 64) p.status[40 + 7] = (int32_t)(clock64() - trace_t0);  // kernel cycles
+#endif
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// The same GEMM on CTA pairs (cluster of 2, tcgen05 cta_group::2): a pair owns a 256 x 256 output tile,
+// each CTA its own 128 rows.  Per k block a CTA loads its 128 x 64 piece of A and HALF of the B tile
+// (128 of the 256 rows); the MMA issued by CTA 0 reads both halves.  Shared-memory traffic per SM drops
+// from 48 KB written + 48 KB read per k block to 32 KB + 32 KB, which is what bounds the single-CTA kernel
+// (128 B/clk of shared-memory bandwidth against 96 B/clk of operand reads plus the TMA fills).
+// Barriers: full[s] lives in CTA 0 and counts the bytes of both CTAs' loads; empty[s] and tfull[slot] are
+// signalled in both CTAs by multicast commits; tempty[slot] lives in CTA 0 and collects 16 warp arrivals.
+constexpr int P_STAGES = 6;
+constexpr int P_STAGE_BYTES = O_A_BYTES + O_A_BYTES;  // 16 KB of A + 16 KB (half) of B
+constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + O_EPI_WARPS * O_Y_BYTES + 1024;
+constexpr int kKernelOutPair = 4;
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(O_THREADS, 1)
+tc_out_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                   const __grid_constant__ CUtensorMap tmY, OutParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[P_STAGES], bar_empty[P_STAGES], bar_tfull[2], bar_tempty[2];
+  __shared__ uint32_t tmem_base_s;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t rank = cluster_ctarank();
+  const int pair_id = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P_STAGES; ++s) { mbar_init(smem_u32(&bar_full[s]), 1); mbar_init(smem_u32(&bar_empty[s]), 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(smem_u32(&bar_tfull[s]), 1); mbar_init(smem_u32(&bar_tempty[s]), 2 * O_EPI_WARPS); }
+    fence_mbar_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+    prefetch_tmap(&tmY);
+  }
+  if (warp == 1) { tmem_alloc_pair(smem_u32(&tmem_base_s), 512); tmem_relinquish_pair(); }
+  tc_fence_before();
+  __syncthreads();
+  cluster_arrive();   // both CTAs' barriers are initialised before anyone signals across the pair
+  cluster_wait();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+
+  const int num_tiles = p.num_m * p.num_n;  // num_m counts 256-row tiles here
+  const int KB = (p.K + OKB - 1) / OKB;
+#ifdef TMOE_TRACE
+  const long long trace_t0 = clock64();
+  long long trace_tic = 0;
+#endif
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+        const int m0 = (tile / p.num_n) * (2 * OM) + (int)rank * OM;
+        const int n0 = (tile % p.num_n) * ON + (int)rank * (ON / 2);
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const uint32_t s = it % P_STAGES, ph = (it / P_STAGES) & 1;
+          TMOE_TIC();
+          if (!(ok = mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1, p.status, kKernelOutPair, 2))) break;
+          TMOE_TOC(0);
+          const uint32_t full0 = mapa_u32(smem_u32(&bar_full[s]), 0);
+          if (rank == 0) mbar_arrive_expect_tx(smem_u32(&bar_full[s]), 2 * P_STAGE_BYTES);  // both CTAs' bytes
+          const uint32_t sa = ring + s * P_STAGE_BYTES;
+          tma_load_2d_pair(sa, &tmA, kb * OKB, m0, full0);
+          tma_load_2d_pair(sa + O_A_BYTES, &tmB, kb * OKB, n0, full0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = umma_idesc_bf16(2 * OM, ON);
+      uint32_t it = 0, tcount = 0;
+      bool ok = true;
+      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++tcount) {
+        const uint32_t slot = tcount & 1, aph = (tcount >> 1) & 1;
+        TMOE_TIC();
+        if (!(ok = mbar_wait(smem_u32(&bar_tempty[slot]), aph ^ 1, p.status, kKernelOutPair, 4))) break;
+        TMOE_TOC(1);
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + slot * ON;
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const uint32_t s = it % P_STAGES, ph = (it / P_STAGES) & 1;
+          TMOE_TIC();
+          if (!(ok = mbar_wait(smem_u32(&bar_full[s]), ph, p.status, kKernelOutPair, 1))) break;
+          TMOE_TOC(2);
+          tc_fence_after();
+          const uint32_t sa = ring + s * P_STAGE_BYTES;
+          const uint64_t da = umma_desc_k_sw128(sa), db = umma_desc_k_sw128(sa + O_A_BYTES);
+#pragma unroll
+          for (int k = 0; k < OKB / 16; ++k) umma_bf16_pair(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+          umma_commit_pair(smem_u32(&bar_empty[s]), 3);
+        }
+        if (ok) umma_commit_pair(smem_u32(&bar_tfull[slot]), 3);
+      }
+    }
+  } else {
+    // Eight epilogue warps: warp w may read TMEM lanes 32*(w%4)..+31, so two warps share each row
+    // quadrant and split the tile's 256 columns.  Each warp stages 32 rows x 64 columns (4 KB, swizzled)
+    // and issues its own TMA store, so the warps never wait for one another.
+    const int ew = warp - 2;
+    const int quad = warp & 3;
+    const int half = ew >> 2;
+    const int row_in_tile = quad * 32 + lane;
+    const uint32_t stage_buf = ring + P_STAGES * P_STAGE_BYTES + ew * O_Y_BYTES;
+    uint32_t tcount = 0;
+    bool ok = true;
+    for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++tcount) {
+      const int m0 = (tile / p.num_n) * (2 * OM) + (int)rank * OM, n0 = (tile % p.num_n) * ON;
+      const uint32_t slot = tcount & 1, aph = (tcount >> 1) & 1;
+      ok = mbar_wait(smem_u32(&bar_tfull[slot]), aph, p.status, kKernelOutPair, 3);
+      ok = __all_sync(0xffffffffu, ok);  // the TMEM loads below are warp-collective
+      if (!ok) break;
+      tc_fence_after();
+      const int64_t row = (int64_t)m0 + row_in_tile;
+      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + slot * ON + half * 128;
+#pragma unroll 1
+      for (int cc = 0; cc < 2; ++cc) {
+        const int col0 = n0 + half * 128 + cc * 64;
+        uint32_t r[2][32];
+        tmem_ld32(t_row + cc * 64, r[0]);
+        tmem_ld32(t_row + cc * 64 + 32, r[1]);
+        tmem_ld_wait(r[0], r[1]);
+        if (cc == 1) {  // this warp has read its whole share of the accumulator
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&bar_tempty[slot]), 0));  // the MMA thread lives in CTA 0
         }
         if (lane == 0) tma_store_wait_read<0>();  // the previous store has finished reading the staging tile
         __syncwarp();
@@ -230,12 +458,17 @@ tc_out_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
     }
     if (lane == 0) tma_store_wait_all();
   }
+#ifdef TMOE_TRACE
+  if (blockIdx.x == 0 && threadIdx.x == 64) p.status[40 + 7] = (int32_t)(clock64() - trace_t0);
+#endif
   tc_fence_before();
   __syncthreads();
+  cluster_arrive();   // the other CTA may still be reading this CTA's shared memory or signalling its barriers
+  cluster_wait();
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    tmem_dealloc_pair(tmem_base, 512);
   }
 }
 
@@ -258,6 +491,46 @@ int launch_tc_gemm_bf16(const void *A, const void *B_t, const float *bias, const
     if (cudaFuncSetAttribute(tc_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, O_SMEM_BYTES) != cudaSuccess)
       return TMOE_ERR_CUDA;
     attr_done[dev] = true;
+  }
+  // Opt-in (environment TMOE_OUT_PAIRS=1): measured 120.5 us against 124.7 us for the single-CTA kernel on the
+  // prefill configuration; wait-cycle traces show both kernels' MMA threads waiting for operand tiles about a
+  // quarter of the time, so halving the operand traffic is not what this GEMM is short of.
+  static const bool use_pairs = []() { const char *e = getenv("TMOE_OUT_PAIRS"); return e && atoi(e) != 0; }();
+  if (use_pairs) {
+    static bool attr2_done[64] = {};
+    if (dev < 64 && !attr2_done[dev]) {
+      if (cudaFuncSetAttribute(tc_out_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES) != cudaSuccess)
+        return TMOE_ERR_CUDA;
+      attr2_done[dev] = true;
+    }
+    CUtensorMap tmBh;
+    rc = encode_tmap_bf16_2d(&tmBh, B_t, (uint64_t)N, (uint64_t)K, ON / 2);
+    if (rc) return rc;
+    OutParams q{};
+    q.y = (bf16 *)y; q.bias = bias; q.residual = (const bf16 *)epi.residual; q.gamma = (const bf16 *)epi.layer_scale;
+    q.silu_gate = (const bf16 *)epi.silu_gate;
+    q.T = M; q.N = N; q.K = K;
+    q.num_m = (int)((M + 2 * OM - 1) / (2 * OM)); q.num_n = (N + ON - 1) / ON;
+    q.status = status;
+    const int tiles2 = q.num_m * q.num_n;
+    // a persistent grid must be fully co-resident: ask how many 2-CTA clusters the device can hold at once
+    static int max_pairs[64] = {};
+    if (dev < 64 && max_pairs[dev] == 0) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(2 * (sms / 2)); cfg.blockDim = dim3(O_THREADS); cfg.dynamicSmemBytes = P_SMEM_BYTES;
+      cudaLaunchAttribute at[1];
+      at[0].id = cudaLaunchAttributeClusterDimension;
+      at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+      cfg.attrs = at; cfg.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, tc_out_pair_kernel, &cfg) != cudaSuccess || n <= 0) return TMOE_ERR_CUDA;
+      max_pairs[dev] = n;
+    }
+    int pairs = dev < 64 ? max_pairs[dev] : sms / 2;
+    if (tiles2 < pairs) pairs = tiles2;
+    tc_out_pair_kernel<<<2 * pairs, O_THREADS, P_SMEM_BYTES, st>>>(tmA, tmBh, tmY, q);
+    count_launch();
+    return launch_status();
   }
   OutParams p{};
   p.y = (bf16 *)y; p.bias = bias; p.residual = (const bf16 *)epi.residual; p.gamma = (const bf16 *)epi.layer_scale;
