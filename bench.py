@@ -51,6 +51,9 @@ for _e in (8, 64, 256, 1024):
     for _k in (2, 8):
         WORKLOADS[f"cfg3_e{_e}_k{_k}"] = (f"cfg3_e{_e}_k{_k}", 16384,
                                           f"sweep bf16 T=16384 d_in=1536 d_out=2304 E={_e} top{_k} r=(4,256,1024)")
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised in
+# profiles/ncu_full_tc_kernels_prefill_cfg2.txt (same workload, same kernels); None where no capture exists.
+NCU_TRAFFIC_BYTES = {("cfg2", "tc_out_gemm"): 71_862_272 + 97_605_120, ("cfg2", "tc_in_core"): 105_422_848 + 25_484_544}
 N_INPUT_SETS = 4  # rotating x buffers so that no step re-reads the previous step's lines from L2
 
 
@@ -304,7 +307,9 @@ def main():
     else:
         roofline = {
             "bound": "tensor", "kernel": dom["name"], "achieved": dom["tflops"], "peak": peak_tf, "unit": "TFLOP/s",
-            "frac": dom["tflops"] / peak_tf, "traffic": None, "peak_source": f"{peaks['source']} (burst bf16)",
+            "frac": dom["tflops"] / peak_tf, "traffic": NCU_TRAFFIC_BYTES.get((args.workload, dom["name"])),
+            "traffic_unit": "bytes per launch (ncu dram read+write, see profiles/)",
+            "peak_source": f"{peaks['source']} (burst bf16)",
             "flops_per_launch": dom["flops"], "us_per_launch": dom["us"],
         }
     line = {

@@ -95,4 +95,5 @@ def load_prepared_sidecar(layer: TuckerMoE, path: str) -> bool:
     dev = layer.U_in.device
     layer._prep = torch.from_numpy(z["prepared"]).to(dev)
     layer._prep_key = _param_key(layer._params())
+    layer._plan = None
     return True

@@ -46,7 +46,7 @@ WsLayout ws_layout(const tmoe_layer_t &L, int64_t T, int rpath) {
   W.gates = take(T * L.top_k * 4);
   W.c = take(T * L.r1 * 4);
   W.simt_router_fused = (L.n_experts <= 32) || (T <= 256);
-  W.tc_router_fused = (align_up(L.n_experts, 16) <= 256) && (L.top_k <= 8);
+  W.tc_router_fused = (align_up(L.n_experts, 16) <= 256) && (L.top_k <= 8) && (L.r3 <= 256);
   if (rpath == TMOE_PATH_SIMT) {
     W.scores = W.simt_router_fused ? 0 : take(T * L.n_experts * 4);
     W.h = take(T * L.r3 * 4);

@@ -19,7 +19,7 @@ namespace tmoe {
 bool tensor_path_covers(const tmoe_layer_t &L) {
   if (L.dtype != TMOE_BF16) return false;
   if (!(L.r1 == 2 || L.r1 == 4 || L.r1 == 8)) return false;
-  if (L.r3 % 64 != 0 || L.r3 > 256) return false;
+  if (L.r3 % 64 != 0 || L.r3 > 512 || (L.r3 > 256 && L.r3 % 256 != 0)) return false;
   if (L.d_in % 64 != 0 || L.r2 % 64 != 0) return false;
   if (L.r2 % (256 / L.r1) != 0) return false;
   if (L.d_out % 8 != 0) return false;

@@ -17,8 +17,10 @@
 //
 // One CTA per 128-token tile, 10 warps: TMA producer, MMA issuer, 8 epilogue warps.
 // Shared memory: phase A uses a ring of {x tile, U_in^T tile, router tile} stages over the whole
-// 224 KB; after the last phase-A MMA has completed, the first 64 KB become h and the rest becomes a
-// 5-stage ring of 32 KB core tiles (z leaves the SM as 16-byte stores straight from registers).
+// 224 KB; after the last phase-A MMA has completed, the first r3/64 * 16 KB become h and the rest becomes a
+// ring of 32 KB core tiles (5 stages for r3 <= 256, 3 for r3 = 512; z leaves the SM as 16-byte stores
+// straight from registers).  r3 = 512 fills all 512 TMEM columns with h, so the router scores then come
+// from a separate GEMM launch.
 // All mbarrier waits are bounded.
 #include "common.cuh"
 #include "kernels.h"
@@ -43,12 +45,11 @@ using namespace ptx;
 constexpr int TM = 128;                    // tokens per CTA
 constexpr int X_TILE_BYTES = TM * 64 * 2;  // 16 KB
 constexpr int H_KBLOCK_BYTES = TM * 64 * 2;
-constexpr int H_REGION_BYTES = 4 * H_KBLOCK_BYTES;  // r3 <= 256
 constexpr int G_STAGE_BYTES = 256 * 64 * 2;         // 32 KB
-constexpr int G_STAGES = 5;
+constexpr int G_STAGES_MAX = 5;  // core-tile stages: (224 KB - h) / 32 KB -> 5 for r3 <= 256, 3 for r3 = 512
 constexpr int IC_EPI_WARPS = 8;
 constexpr int IC_THREADS = (2 + IC_EPI_WARPS) * 32;
-constexpr int IC_RING_BYTES = H_REGION_BYTES + G_STAGES * G_STAGE_BYTES;  // 224 KB
+constexpr int IC_RING_BYTES = 224 * 1024;
 constexpr int IC_SMEM_BYTES = IC_RING_BYTES + 1024;
 constexpr int A_STAGES_MAX = 4;
 constexpr int SCORE_COL = 256;  // TMEM column of the router scores during phase A
@@ -77,11 +78,11 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                   const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmG, InCoreParams p) {
   constexpr int N2 = 256 / R1;
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bar_fullA[A_STAGES_MAX], bar_emptyA[A_STAGES_MAX], bar_fullB[G_STAGES],
-      bar_emptyB[G_STAGES], bar_accA, bar_hready, bar_pfull[2], bar_pempty[2];
+  __shared__ __align__(8) uint64_t bar_fullA[A_STAGES_MAX], bar_emptyA[A_STAGES_MAX], bar_fullB[G_STAGES_MAX],
+      bar_emptyB[G_STAGES_MAX], bar_accA, bar_hready, bar_pfull[2], bar_pempty[2];
   __shared__ uint32_t tmem_base_s;
-  __shared__ float wnorm_s[256];
   __shared__ float inv_rms_s[TM];
+  __shared__ bf16 wnorm_s[512];  // inner_norm weight; the layer is bf16, so this copy is exact
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -92,12 +93,17 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
   int nA = IC_RING_BYTES / stageA_bytes;
   nA = nA > A_STAGES_MAX ? A_STAGES_MAX : nA;
   const int KA = p.d_in / 64;
-  const int KH = p.r3 / 64;
+  const int KH = p.r3 / 64;                       // 64-wide k blocks of h
+  const int h_bytes = KH * H_KBLOCK_BYTES;        // 64 KB for r3 = 256, 128 KB for r3 = 512
+  int nG = (IC_RING_BYTES - h_bytes) / G_STAGE_BYTES;
+  nG = nG > G_STAGES_MAX ? G_STAGES_MAX : nG;
+  const int u_boxes = (p.r3 + 255) / 256;         // U_in^T rows are loaded (and multiplied) in pieces of <= 256
+  const int u_box_rows = p.r3 / u_boxes;
 
-  for (int i = threadIdx.x; i < p.r3; i += blockDim.x) wnorm_s[i] = p.normw[i];
+  for (int i = threadIdx.x; i < p.r3; i += blockDim.x) wnorm_s[i] = __float2bfloat16_rn(p.normw[i]);
   if (threadIdx.x == 0) {
     for (int s = 0; s < A_STAGES_MAX; ++s) { mbar_init(smem_u32(&bar_fullA[s]), 1); mbar_init(smem_u32(&bar_emptyA[s]), 1); }
-    for (int s = 0; s < G_STAGES; ++s) { mbar_init(smem_u32(&bar_fullB[s]), 1); mbar_init(smem_u32(&bar_emptyB[s]), 1); }
+    for (int s = 0; s < G_STAGES_MAX; ++s) { mbar_init(smem_u32(&bar_fullB[s]), 1); mbar_init(smem_u32(&bar_emptyB[s]), 1); }
     mbar_init(smem_u32(&bar_accA), 1);
     mbar_init(smem_u32(&bar_hready), IC_EPI_WARPS);
     for (int s = 0; s < 2; ++s) { mbar_init(smem_u32(&bar_pfull[s]), 1); mbar_init(smem_u32(&bar_pempty[s]), 4); }
@@ -110,7 +116,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_s;
-  const uint32_t ringB = ring + H_REGION_BYTES;
+  const uint32_t ringB = ring + h_bytes;
 #ifdef TMOE_TRACE
   const long long trace_t0 = clock64();
   unsigned long long trace_ns0;
@@ -128,14 +134,15 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         mbar_arrive_expect_tx(full, stageA_bytes);
         const uint32_t sa = ring + s * stageA_bytes;
         tma_load_2d(sa, &tmX, kb * 64, m0, full);
-        tma_load_2d(sa + X_TILE_BYTES, &tmU, kb * 64, 0, full);
+        for (int ub = 0; ub < u_boxes; ++ub)
+          tma_load_2d(sa + X_TILE_BYTES + ub * u_box_rows * 128, &tmU, kb * 64, ub * u_box_rows, full);
         if (p.e_pad) tma_load_2d(sa + X_TILE_BYTES + u_bytes, &tmW, kb * 64, 0, full);
       }
       // ring A aliases h and the core-tile ring: wait until every phase-A MMA has retired
       if (ok) ok = mbar_wait(smem_u32(&bar_accA), 0, p.status, kKernelInCore, 3);
       const int total = p.n_tiles2 * KH;
       for (int it = 0; it < total && ok; ++it) {
-        const uint32_t s = it % G_STAGES, ph = (it / G_STAGES) & 1;
+        const uint32_t s = it % nG, ph = (it / nG) & 1;
         const int j = it / KH, kb = it - j * KH;
         if (!(ok = mbar_wait(smem_u32(&bar_emptyB[s]), ph ^ 1, p.status, kKernelInCore, 6))) break;
         const uint32_t full = smem_u32(&bar_fullB[s]);
@@ -147,7 +154,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
     // ------------------------------- MMA issuer -------------------------------
     if (lane == 0) {
       bool ok = true;
-      const uint32_t idescH = umma_idesc_bf16(TM, p.r3);
+      const uint32_t idescH = umma_idesc_bf16(TM, u_box_rows);
       const uint32_t idescS = umma_idesc_bf16(TM, p.e_pad ? p.e_pad : 16);
       for (int kb = 0; kb < KA && ok; ++kb) {
         const uint32_t s = kb % nA, ph = (kb / nA) & 1;
@@ -158,7 +165,9 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                        dw = umma_desc_k_sw128(sa + X_TILE_BYTES + u_bytes);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          umma_bf16(tmem_base, dx + 2 * k, du + 2 * k, idescH, (kb | k) != 0);
+          for (int ub = 0; ub < u_boxes; ++ub)  // one MMA per <= 256 columns of h; the piece's rows are 128 B apart
+            umma_bf16(tmem_base + ub * u_box_rows, dx + 2 * k, du + (uint64_t)(ub * u_box_rows * 8) + 2 * k, idescH,
+                      (kb | k) != 0);
           if (p.e_pad) umma_bf16(tmem_base + SCORE_COL, dx + 2 * k, dw + 2 * k, idescS, (kb | k) != 0);
         }
         umma_commit(smem_u32(&bar_emptyA[s]));
@@ -176,7 +185,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + slot * 256;
         for (int kb = 0; kb < KH; ++kb, ++it) {
-          const uint32_t s = it % G_STAGES, ph = (it / G_STAGES) & 1;
+          const uint32_t s = it % nG, ph = (it / nG) & 1;
           if (!(ok = mbar_wait(smem_u32(&bar_fullB[s]), ph, p.status, kKernelInCore, 5))) break;
           tc_fence_after();
           const uint64_t dh = umma_desc_k_sw128(ring + kb * H_KBLOCK_BYTES);
@@ -300,7 +309,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
             for (int q = 0; q < 8; ++q) {
               const float a = __uint_as_float(r[g * 8 + q]);
               ss = fmaf(a, a, ss);
-              v[q] = a * wnorm_s[cc * 32 + g * 8 + q];
+              v[q] = a * __bfloat162float(wnorm_s[cc * 32 + g * 8 + q]);
             }
             const uint32_t chunk = (uint32_t)((cc & 1) * 4 + g) ^ (uint32_t)(row & 7);
             const uint32_t addr = kblk_base + chunk * 16;
@@ -395,12 +404,13 @@ int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared
                       int fuse_router, const float *c_in, float *c_work, int32_t *idx_out, float *gates_out, float *c_out,
                       void *z, int32_t *status, cudaStream_t st) {
   const char *base = reinterpret_cast<const char *>(prepared);
-  if (fuse_router && (P.e_pad > 256 || L.top_k > 8)) return TMOE_ERR_UNSUPPORTED;
+  if (fuse_router && (P.e_pad > 256 || L.top_k > 8 || L.r3 > 256)) return TMOE_ERR_UNSUPPORTED;
   if ((!fuse_router && !c_in) || !c_work) return TMOE_ERR_NULL;
   CUtensorMap tmX, tmU, tmW, tmG;
   int rc = encode_tmap_bf16_2d(&tmX, x, (uint64_t)T_, (uint64_t)L.d_in, TM);
   if (rc) return rc;
-  rc = encode_tmap_bf16_2d(&tmU, base + P.uin_t, (uint64_t)L.r3, (uint64_t)L.d_in, (uint32_t)L.r3);
+  rc = encode_tmap_bf16_2d(&tmU, base + P.uin_t, (uint64_t)L.r3, (uint64_t)L.d_in,
+                           (uint32_t)(L.r3 / ((L.r3 + 255) / 256)));
   if (rc) return rc;
   // the router tile is only loaded when the scores are computed in-kernel (e_pad <= 256 checked above)
   rc = encode_tmap_bf16_2d(&tmW, base + P.wr_b, (uint64_t)P.e_pad, (uint64_t)L.d_in,

@@ -64,8 +64,8 @@ _cache_lock = threading.Lock()
 _workspaces = {}   # (device index, stream handle) -> uint8 tensor
 
 
-def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
-    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+def _workspace(device: torch.device, nbytes: int, stream: Optional[int] = None) -> torch.Tensor:
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream if stream is None else stream)
     with _cache_lock:
         ws = _workspaces.get(key)
         if ws is None or ws.numel() < nbytes:
@@ -275,6 +275,14 @@ def tucker_moe_forward_taps(x, router_w, U_in, inner_norm_w, eps, U_expert, core
     return y, taps
 
 
+class _Plan:
+    """Everything about a (module, dtype, device, path) combination that does not change from call to call:
+    validated contiguous parameters, the C structs, the prepared factor set and, per token count, the resolved
+    kernel path and workspace size.  Rebuilt when a parameter's storage or version changes."""
+    __slots__ = ("key", "params", "layer", "factors", "layer_ref", "factors_ref", "prepared", "prepared_ptr", "per_T",
+                 "dev", "d_in", "d_out", "lib")
+
+
 class TuckerMoE(nn.Module):
     """Low-rank Tucker-decomposed Mixture-of-Experts, B200 forward.
 
@@ -298,6 +306,7 @@ class TuckerMoE(nn.Module):
         self.path = PATH_AUTO
         self._prep_key = None
         self._prep = None
+        self._plan = None
 
     def _prepared_for(self, x: torch.Tensor) -> Optional[torch.Tensor]:
         """Prepared factor set for the tensor-core path, rebuilt when a parameter's storage,
@@ -316,8 +325,67 @@ class TuckerMoE(nn.Module):
     def _params(self):
         return (self.router.weight, self.U_in, self.inner_norm.weight, self.U_expert, self.core, self.U_out, self.bias)
 
+    def _plan_for(self, x: torch.Tensor) -> _Plan:
+        ps = self._params()
+        key = (x.dtype, x.device, self.path, self.top_k, self.inner_norm.eps) + tuple((p.data_ptr(), p._version) for p in ps)
+        plan = self._plan
+        if plan is not None and plan.key == key:
+            return plan
+        _validate(x, ps, self.top_k)
+        plan = _Plan()
+        plan.key = key
+        plan.lib = _lib.load()
+        plan.params = tuple(p if p.is_contiguous() else p.contiguous() for p in ps)
+        rw, ui, nw, ue, co, uo, b = plan.params
+        plan.layer = _layer_struct(x, rw, ui, ue, co, uo, self.top_k, self.inner_norm.eps)
+        plan.factors = Factors(*[p.data_ptr() for p in plan.params])
+        plan.layer_ref, plan.factors_ref = C.byref(plan.layer), C.byref(plan.factors)
+        plan.prepared = self._prepared_for(x)
+        plan.prepared_ptr = plan.prepared.data_ptr() if plan.prepared is not None else None
+        plan.per_T = {}
+        plan.dev, plan.d_in, plan.d_out = x.device, ui.shape[0], uo.shape[1]
+        self._plan = plan
+        return plan
+
+    def _fast_forward(self, x: torch.Tensor) -> torch.Tensor:
+        """Eager call without the dispatcher: the same C entry point as the custom op, with the per-call
+        Python work cut to a cache lookup (decode-sized calls cost more in Python than on the GPU)."""
+        plan = self._plan_for(x)
+        if x.shape[-1] != plan.d_in:
+            raise RuntimeError(f"tmoe_b200: x has {x.shape[-1]} features, the layer expects {plan.d_in}")
+        x2 = x.reshape(-1, plan.d_in)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        T = x2.shape[0]
+        y = torch.empty((T, plan.d_out), dtype=x.dtype, device=x.device)
+        if T:
+            lib, dev = plan.lib, plan.dev
+            info = plan.per_T.get(T)
+            if info is None:
+                rpath = _lib.check(lib.tmoe_resolve_path(plan.layer_ref, T, self.path), "tmoe_resolve_path")
+                info = (rpath, _lib.check(lib.tmoe_workspace_bytes(plan.layer_ref, T, rpath), "tmoe_workspace_bytes"))
+                if len(plan.per_T) < 4096:
+                    plan.per_T[T] = info
+            rpath, ws_bytes = info
+            if torch.cuda.current_device() == dev.index:
+                stream = torch.cuda.current_stream().cuda_stream
+                ws = _workspace(dev, ws_bytes, stream)
+                rc = lib.tmoe_forward(plan.layer_ref, plan.factors_ref, plan.prepared_ptr, x2.data_ptr(), T, y.data_ptr(),
+                                      None, ws.data_ptr(), ws.numel(), rpath, stream)
+            else:
+                with torch.cuda.device(dev):
+                    stream = torch.cuda.current_stream(dev).cuda_stream
+                    ws = _workspace(dev, ws_bytes, stream)
+                    rc = lib.tmoe_forward(plan.layer_ref, plan.factors_ref, plan.prepared_ptr, x2.data_ptr(), T,
+                                          y.data_ptr(), None, ws.data_ptr(), ws.numel(), rpath, stream)
+            if rc < 0:
+                _lib.check(rc, "tmoe_forward")
+        return y.reshape(*x.shape[:-1], plan.d_out)
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         """x: (..., d_in) -> (..., d_out)"""
+        if x.is_cuda and not torch.compiler.is_compiling():
+            return self._fast_forward(x)
         rw, ui, nw, ue, co, uo, b = self._params()
         return tucker_moe_forward(x, rw, ui, nw, self.inner_norm.eps, ue, co, uo, b, self.top_k, path=self.path,
                                   prepared=self._prepared_for(x))
@@ -408,7 +476,7 @@ class TuckerMoE(nn.Module):
     def invalidate_cache(self) -> None:
         """Call after writing parameters through ``.data`` once the layer has already run
         (such writes do not change tensor versions, which key the prepared-factor cache)."""
-        self._prep_key, self._prep = None, None
+        self._prep_key, self._prep, self._plan = None, None, None
 
 
 def fused_out_proj(out_proj: TuckerMoE, mid: torch.Tensor, norm, layer_scale: torch.Tensor) -> torch.Tensor:

@@ -89,7 +89,9 @@ TENSOR_SHAPES = [
     (LayerShape(192, 320, 40, 8, 8, 192, 192, 1e-6), 77),
     (LayerShape(1536, 2304, 8, 2, 4, 256, 1024, 1e-6), 64),
     (LayerShape(1536, 2304, 64, 2, 4, 256, 1024, 1e-6), 1000),
-    (LayerShape(256, 128, 512, 8, 4, 64, 128, 1e-6), 200),   # E > 256: scores by the CUDA-core kernels
+    (LayerShape(256, 128, 512, 8, 4, 64, 128, 1e-6), 200),   # E > 256: scores by the GEMM kernel + select kernel
+    (LayerShape(512, 384, 256, 8, 8, 512, 256, 1e-6), 200),  # r3 = 512: h fills all of TMEM, scores by a separate GEMM
+    (LayerShape(3072, 4608, 256, 8, 8, 512, 2048, 1e-6), 130),  # the large skewed configuration's shapes
 ]
 
 
@@ -116,6 +118,7 @@ DECODE_SHAPES = [
     (LayerShape(192, 320, 40, 8, 8, 192, 192, 1e-6), 5),
     (LayerShape(256, 264, 24, 12, 2, 128, 256, 1e-5), 9),
     (LayerShape(3072, 4608, 256, 8, 8, 256, 2048, 1e-6), 17),   # r2 > one staged chunk of z
+    (LayerShape(3072, 4608, 256, 8, 8, 512, 2048, 1e-6), 9),    # r3 = 512
 ]
 
 
