@@ -55,6 +55,13 @@ typedef enum tmoe_path {
   TMOE_PATH_AUTO = 0, TMOE_PATH_SIMT = 1, TMOE_PATH_TENSOR = 2, TMOE_PATH_DECODE = 3
 } tmoe_path_t;
 
+/* Gate rule.
+ *  TOPK_SOFTMAX    top-k of the raw scores, softmax over the k winners (pure_torch_mlx/model.py:75-77).
+ *  CAPPED_SOFTMAX  the trained checkpoints' rule (sft_cot_bundle/scripts/model.py:318-329,
+ *                  mamba3_mlx/mlx_model/tucker_moe.py:107-114): l = cap * tanh(score / cap) / temperature,
+ *                  p = softmax(l) over all experts, top-k of l, gate_k = p_k / (sum of the k selected p + 1e-6). */
+typedef enum tmoe_router_mode { TMOE_ROUTER_TOPK_SOFTMAX = 0, TMOE_ROUTER_CAPPED_SOFTMAX = 1 } tmoe_router_mode_t;
+
 /* Sizes of one layer; mirrors the constructor arguments TuckerMoE(d_in, d_out, cfg) with
  * cfg.kmoe_num_experts, kmoe_top_k, kmoe_r1, kmoe_r2, kmoe_r3, rms_norm_eps
  * (pure_torch_mlx/model.py:54-62). */
@@ -64,6 +71,9 @@ typedef struct tmoe_layer {
   int32_t r1, r2, r3;
   int32_t dtype;  /* tmoe_dtype_t */
   float eps;      /* inner_norm epsilon */
+  int32_t router_mode;      /* tmoe_router_mode_t; 0 = the pure-PyTorch module's rule */
+  float router_cap;         /* TMOE_ROUTER_CAPPED_SOFTMAX: soft cap of the scores (reference: 10) */
+  float router_temperature; /* TMOE_ROUTER_CAPPED_SOFTMAX: softmax temperature (reference at inference: 0.5) */
 } tmoe_layer_t;
 
 /* The seven parameters in the reference's own layouts (pure_torch_mlx/model.py:60-66,

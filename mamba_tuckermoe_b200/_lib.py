@@ -10,6 +10,7 @@ LIB_PATH = os.path.join(PKG, "lib", "libtmoe_b200.so")
 
 TMOE_F32, TMOE_BF16 = 0, 1
 PATH_AUTO, PATH_SIMT, PATH_TENSOR, PATH_DECODE = 0, 1, 2, 3
+ROUTER_TOPK_SOFTMAX, ROUTER_CAPPED_SOFTMAX = 0, 1
 ERR_DEVICE_WAIT = -9
 
 # every symbol the header declares; checked when the library is loaded
@@ -24,7 +25,8 @@ STATIC_SCRATCH_BYTES = 4 << 20
 class Layer(C.Structure):
     _fields_ = [("d_in", C.c_int32), ("d_out", C.c_int32), ("n_experts", C.c_int32), ("top_k", C.c_int32),
                 ("r1", C.c_int32), ("r2", C.c_int32), ("r3", C.c_int32), ("dtype", C.c_int32),
-                ("eps", C.c_float)]
+                ("eps", C.c_float), ("router_mode", C.c_int32), ("router_cap", C.c_float),
+                ("router_temperature", C.c_float)]
 
 
 class Factors(C.Structure):
@@ -113,11 +115,12 @@ def check(status: int, where: str) -> int:
 FACTOR_ORDER = ("router_w", "U_in", "inner_norm_w", "U_expert", "core", "U_out", "bias")
 
 
-def layer_struct(shape, dtype) -> Layer:
+def layer_struct(shape, dtype, router_mode: int = 0, router_cap: float = 10.0, router_temperature: float = 0.5) -> Layer:
     """``shape`` has d_in, d_out, E, top_k, r1, r2, r3, eps; ``dtype`` is a torch dtype."""
     import torch
     return Layer(shape.d_in, shape.d_out, shape.E, shape.top_k, shape.r1, shape.r2, shape.r3,
-                 TMOE_BF16 if dtype == torch.bfloat16 else TMOE_F32, shape.eps)
+                 TMOE_BF16 if dtype == torch.bfloat16 else TMOE_F32, shape.eps, router_mode, router_cap,
+                 router_temperature)
 
 
 def factors_struct(dev_factors) -> Factors:

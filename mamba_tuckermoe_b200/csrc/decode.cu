@@ -112,7 +112,7 @@ __global__ void __launch_bounds__(kDecWarps * 32)
 decode_core_kernel(const float *__restrict__ h_raw, const float *__restrict__ scores, const float *__restrict__ normw,
                    const float *__restrict__ uexp, const bf16 *__restrict__ g_t, int T, int r3, int r2, int E, int top_k,
                    float eps, bf16 *__restrict__ z, int32_t *__restrict__ idx_out, float *__restrict__ gates_out,
-                   float *__restrict__ c_out) {
+                   float *__restrict__ c_out, RouterCfg rc) {
   constexpr int N2 = 256 / R1;
   extern __shared__ __align__(16) uint8_t dsm[];
   bf16 *hw = reinterpret_cast<bf16 *>(dsm);                                  // [TMAX][r3]
@@ -134,8 +134,9 @@ decode_core_kernel(const float *__restrict__ h_raw, const float *__restrict__ sc
       sel.init();
       warp_select_topk<bf16, KMAX>(scores + (int64_t)t * E, E, top_k, lane, sel);
       const bool tap = (blockIdx.x == 0);
+      const float z_all = rc.mode == 1 ? warp_softmax_denominator<bf16, float>(scores + (int64_t)t * E, E, lane, rc, sel.v[0]) : 1.f;
       emit_token<bf16, KMAX, float>(sel, top_k, E, R1, uexp, 0, lane, tap && idx_out ? idx_out + (int64_t)t * top_k : nullptr,
-                              tap && gates_out ? gates_out + (int64_t)t * top_k : nullptr, cs + t * R1);
+                                    tap && gates_out ? gates_out + (int64_t)t * top_k : nullptr, cs + t * R1, rc, z_all);
       __syncwarp();
       if (lane < R1) {
         const float cv = cs[t * R1 + lane];
@@ -257,7 +258,7 @@ int launch_decode_t(const tmoe_layer_t &L, const void *x, const char *pb, const 
     if (e == cudaSuccess)                                                                                          \
       decode_core_kernel<TMAX, R, K><<<g2, kDecWarps * 32, smem2, st>>>(                                           \
           h_raw, scores, (const float *)(pb + P.normw), (const float *)(pb + P.uexp), (const bf16 *)(pb + P.g_t), T, \
-          L.r3, L.r2, L.n_experts, L.top_k, L.eps, (bf16 *)z, idx_out, gates_out, c_out);                           \
+          L.r3, L.r2, L.n_experts, L.top_k, L.eps, (bf16 *)z, idx_out, gates_out, c_out, router_cfg(L));                           \
   } while (0)
   const bool k2 = L.top_k <= 2, k8 = L.top_k <= 8;
   if (L.r1 == 2) { if (k2) TMOE_DC(2, 2); else if (k8) TMOE_DC(2, 8); else TMOE_DC(2, 16); }

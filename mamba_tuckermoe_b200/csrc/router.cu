@@ -24,7 +24,7 @@ template <typename T, int KMAX, int EG>
 __global__ void __launch_bounds__(kRouterWarps * 32)
 router_fused_kernel(const T *__restrict__ x, const T *__restrict__ wr, const T *__restrict__ uexp, int64_t Tn,
                     int d_in, int E, int k, int r1, int32_t *__restrict__ idx, float *__restrict__ gates,
-                    float *__restrict__ c) {
+                    float *__restrict__ c, RouterCfg rc) {
   const int lane = threadIdx.x & 31;
   const int64_t t = (int64_t)blockIdx.x * kRouterWarps + (threadIdx.x >> 5);
   if (t >= Tn) return;
@@ -32,6 +32,7 @@ router_fused_kernel(const T *__restrict__ x, const T *__restrict__ wr, const T *
   const T *xr = x + t * d_in;
   TopList<KMAX> sel;
   sel.init();
+  float run_max = -INFINITY, run_sum = 0.f;  // online softmax over all experts' logits (mode 1)
   for (int e0 = 0; e0 < E; e0 += EG) {
     float acc[EG];
 #pragma unroll
@@ -52,16 +53,24 @@ router_fused_kernel(const T *__restrict__ x, const T *__restrict__ wr, const T *
 #pragma unroll
     for (int g = 0; g < EG; ++g) {
       float s = warp_sum(acc[g]);
-      if (e0 + g < E) sel.insert(round_to<T>(s), e0 + g, k);
+      if (e0 + g < E) {
+        const float sr = round_to<T>(s);
+        sel.insert(sr, e0 + g, k);
+        if (rc.mode == 1) {
+          const float l = rc.logit(sr);
+          if (l > run_max) { run_sum = run_sum * expf(run_max - l) + 1.f; run_max = l; }
+          else run_sum += expf(l - run_max);
+        }
+      }
     }
   }
-  emit_token<T, KMAX>(sel, k, E, r1, uexp, t, lane, idx, gates, c);
+  emit_token<T, KMAX>(sel, k, E, r1, uexp, t, lane, idx, gates, c, rc, run_sum);
 }
 
 template <typename T, int KMAX, typename TS>
 __global__ void __launch_bounds__(kRouterWarps * 32)
 select_kernel(const TS *__restrict__ scores, int ld, const T *__restrict__ uexp, int64_t Tn, int E, int k, int r1,
-              int32_t *__restrict__ idx, float *__restrict__ gates, float *__restrict__ c) {
+              int32_t *__restrict__ idx, float *__restrict__ gates, float *__restrict__ c, RouterCfg rc) {
   const int lane = threadIdx.x & 31;
   const int64_t t = (int64_t)blockIdx.x * kRouterWarps + (threadIdx.x >> 5);
   if (t >= Tn) return;
@@ -69,7 +78,8 @@ select_kernel(const TS *__restrict__ scores, int ld, const T *__restrict__ uexp,
   TopList<KMAX> sel;
   sel.init();
   warp_select_topk<T, KMAX, TS>(sr, E, k, lane, sel);
-  emit_token<T, KMAX>(sel, k, E, r1, uexp, t, lane, idx, gates, c);
+  const float z_all = rc.mode == 1 ? warp_softmax_denominator<T, TS>(sr, E, lane, rc, sel.v[0]) : 1.f;
+  emit_token<T, KMAX>(sel, k, E, r1, uexp, t, lane, idx, gates, c, rc, z_all);
 }
 
 template <typename T>
@@ -77,7 +87,7 @@ static int launch_router_fused_t(const tmoe_layer_t &L, const void *x, const voi
                                  int32_t *idx, float *gates, float *c, cudaStream_t st) {
   dim3 grid((unsigned)((T_ + kRouterWarps - 1) / kRouterWarps)), block(kRouterWarps * 32);
 #define TMOE_RF(KM) router_fused_kernel<T, KM, 8><<<grid, block, 0, st>>>((const T *)x, (const T *)wr, (const T *)uexp, \
-                       T_, L.d_in, L.n_experts, L.top_k, L.r1, idx, gates, c)
+                       T_, L.d_in, L.n_experts, L.top_k, L.r1, idx, gates, c, router_cfg(L))
   if (L.top_k <= 2) TMOE_RF(2);
   else if (L.top_k <= 8) TMOE_RF(8);
   else TMOE_RF(16);
@@ -97,7 +107,7 @@ static int launch_select_t(const tmoe_layer_t &L, const float *scores, const voi
                            float *gates, float *c, cudaStream_t st) {
   dim3 grid((unsigned)((T_ + kRouterWarps - 1) / kRouterWarps)), block(kRouterWarps * 32);
 #define TMOE_SEL(KM) select_kernel<T, KM, float><<<grid, block, 0, st>>>(scores, L.n_experts, (const T *)uexp, T_, \
-                       L.n_experts, L.top_k, L.r1, idx, gates, c)
+                       L.n_experts, L.top_k, L.r1, idx, gates, c, router_cfg(L))
   if (L.top_k <= 2) TMOE_SEL(2);
   else if (L.top_k <= 8) TMOE_SEL(8);
   else TMOE_SEL(16);
@@ -116,7 +126,7 @@ int launch_select_bf16_scores(const tmoe_layer_t &L, const void *scores, int ld,
                               int32_t *idx, float *gates, float *c, cudaStream_t st) {
   dim3 grid((unsigned)((T_ + kRouterWarps - 1) / kRouterWarps)), block(kRouterWarps * 32);
 #define TMOE_SELB(KM) select_kernel<bf16, KM, bf16><<<grid, block, 0, st>>>((const bf16 *)scores, ld, (const bf16 *)uexp, \
-                       T_, L.n_experts, L.top_k, L.r1, idx, gates, c)
+                       T_, L.n_experts, L.top_k, L.r1, idx, gates, c, router_cfg(L))
   if (L.top_k <= 2) TMOE_SELB(2);
   else if (L.top_k <= 8) TMOE_SELB(8);
   else TMOE_SELB(16);

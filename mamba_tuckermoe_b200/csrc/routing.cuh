@@ -8,6 +8,21 @@
 
 namespace tmoe {
 
+// Gate rule parameters (tmoe_layer_t::router_mode / router_cap / router_temperature).
+struct RouterCfg {
+  int mode;        // 0: softmax over the k winners' raw scores; 1: capped / tempered softmax over all experts
+  float cap;
+  float inv_temp;
+  __device__ __forceinline__ float logit(float score) const { return cap * tanhf(score / cap) * inv_temp; }
+};
+inline RouterCfg router_cfg(const tmoe_layer_t &L) {
+  RouterCfg rc;
+  rc.mode = L.router_mode;
+  rc.cap = L.router_cap > 0.f ? L.router_cap : 10.f;
+  rc.inv_temp = 1.f / (L.router_temperature > 0.f ? L.router_temperature : 0.5f);
+  return rc;
+}
+
 template <int KMAX>
 struct TopList {
   float v[KMAX];
@@ -31,19 +46,38 @@ struct TopList {
 
 // Writes idx / gates / c for one token from a finished selection list (all lanes hold it).
 // T: storage type the gates are rounded to; TU: element type of the U_expert table.
-template <typename T, int KMAX, typename TU = T>
-__device__ __forceinline__ void emit_token(const TopList<KMAX> &sel, int k, int E, int r1, const TU *__restrict__ uexp,
-                                           int64_t t, int lane, int32_t *__restrict__ idx,
-                                           float *__restrict__ gates, float *__restrict__ c) {
-  float gate[KMAX];
-  {
-    float m = sel.v[0], den = 0.f;
+// Gate weights of the k selected experts (sel_v sorted descending), rounded to the storage type T.
+// mode 0: softmax over the k raw scores.  mode 1: p_j = exp(l_j - l_0) / z_all with l = rc.logit(score) and
+// z_all = sum over ALL experts of exp(l_e - l_0); gate_j = p_j / (sum_j p_j + 1e-6).
+template <typename T, int KMAX>
+__device__ __forceinline__ void gates_of(const float (&sel_v)[KMAX], int k, const RouterCfg &rc, float z_all,
+                                         float (&gate)[KMAX]) {
+  if (rc.mode == 0) {
+    const float m = sel_v[0];
+    float den = 0.f;
 #pragma unroll
-    for (int j = 0; j < KMAX; ++j) { gate[j] = (j < k) ? expf(sel.v[j] - m) : 0.f; den += gate[j]; }
-    float inv = 1.f / den;
+    for (int j = 0; j < KMAX; ++j) { gate[j] = (j < k) ? expf(sel_v[j] - m) : 0.f; den += gate[j]; }
+    const float inv = 1.f / den;
+#pragma unroll
+    for (int j = 0; j < KMAX; ++j) gate[j] = round_to<T>(gate[j] * inv);
+  } else {
+    const float l0 = rc.logit(sel_v[0]);
+    float den = 0.f;
+#pragma unroll
+    for (int j = 0; j < KMAX; ++j) { gate[j] = (j < k) ? expf(rc.logit(sel_v[j]) - l0) / z_all : 0.f; den += gate[j]; }
+    const float inv = 1.f / (den + 1e-6f);
 #pragma unroll
     for (int j = 0; j < KMAX; ++j) gate[j] = round_to<T>(gate[j] * inv);
   }
+}
+
+template <typename T, int KMAX, typename TU = T>
+__device__ __forceinline__ void emit_token(const TopList<KMAX> &sel, int k, int E, int r1, const TU *__restrict__ uexp,
+                                           int64_t t, int lane, int32_t *__restrict__ idx,
+                                           float *__restrict__ gates, float *__restrict__ c,
+                                           const RouterCfg &rc = RouterCfg{0, 10.f, 2.f}, float z_all = 1.f) {
+  float gate[KMAX];
+  gates_of<T, KMAX>(sel.v, k, rc, z_all, gate);
 #pragma unroll
   for (int j = 0; j < KMAX; ++j) {
     if (j < k && lane == (j & 31)) {
@@ -108,6 +142,16 @@ __device__ __forceinline__ void warp_select_topk(const TS *__restrict__ sr, int 
       sel.v[j] = bv; sel.i[j] = bi; pv = bv; pi = bi;
     }
   }
+}
+
+// sum over all experts of exp(logit(score_e) - logit(top score)) for one token's score row (mode 1 only)
+template <typename T, typename TS>
+__device__ __forceinline__ float warp_softmax_denominator(const TS *__restrict__ sr, int E, int lane, const RouterCfg &rc,
+                                                          float top_score) {
+  const float l0 = rc.logit(top_score);
+  float z = 0.f;
+  for (int e = lane; e < E; e += 32) z += expf(rc.logit(round_to<T>(to_f32(sr[e]))) - l0);
+  return warp_sum(z);
 }
 
 }  // namespace tmoe

@@ -25,6 +25,7 @@
 #include "common.cuh"
 #include "kernels.h"
 #include "ptx.cuh"
+#include "routing.cuh"
 
 namespace tmoe {
 
@@ -60,6 +61,7 @@ struct InCoreParams {
   int d_in, r3, r2, E, e_pad, top_k, n_tiles2;
   float eps;
   int fuse_router;
+  RouterCfg rc;  // gate rule (tmoe_layer_t::router_mode)
   const float *normw;  // [r3]
   const float *uexp;   // [E, r1] fp32
   const float *c_in;   // [T, r1] when !fuse_router
@@ -228,6 +230,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
           uint32_t key[RK];
 #pragma unroll
           for (int j = 0; j < RK; ++j) key[j] = 0u;
+          float run_max = -INFINITY, run_sum = 0.f;  // online softmax over all experts' logits (capped-softmax rule)
           for (int cc = 0; cc < p.e_pad / 16; ++cc) {
             uint32_t r[16];
             tmem_ld16(t_lane + SCORE_COL + cc * 16, r);
@@ -245,6 +248,11 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                 carry = min(key[j], carry);
                 key[j] = hi;
               }
+              if (p.rc.mode == 1 && e < p.E) {
+                const float l = p.rc.logit(__uint_as_float(b << 16));
+                if (l > run_max) { run_sum = run_sum * expf(run_max - l) + 1.f; run_max = l; }
+                else run_sum += expf(l - run_max);
+              }
             }
           }
           float sv[RK]; int si[RK];
@@ -256,16 +264,13 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
             si[j] = (int)(0xffffu - (key[j] & 0xffffu));
           }
           if (threadIdx.x == 64) TMOE_STAMP(6);  // score scan done
-          float gate[RK], den = 0.f;
-#pragma unroll
-          for (int j = 0; j < RK; ++j) { gate[j] = (j < p.top_k) ? expf(sv[j] - sv[0]) : 0.f; den += gate[j]; }
-          const float inv = 1.f / den;
+          float gate[RK];
+          gates_of<bf16, RK>(sv, p.top_k, p.rc, run_sum, gate);
 #pragma unroll
           for (int a = 0; a < R1; ++a) c[a] = 0.f;
 #pragma unroll
           for (int j = 0; j < RK; ++j) {
             if (j < p.top_k) {
-              gate[j] = round_to<bf16>(gate[j] * inv);
               const int e = min(max(si[j], 0), p.E - 1);
 #pragma unroll
               for (int a = 0; a < R1; ++a) c[a] = fmaf(gate[j], __ldg(p.uexp + e * R1 + a), c[a]);
@@ -422,7 +427,7 @@ int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared
   InCoreParams p{};
   p.T = T_; p.d_in = L.d_in; p.r3 = L.r3; p.r2 = L.r2; p.E = L.n_experts; p.top_k = L.top_k;
   p.e_pad = fuse_router ? P.e_pad : 0;
-  p.n_tiles2 = P.n_tiles2; p.eps = L.eps; p.fuse_router = fuse_router;
+  p.n_tiles2 = P.n_tiles2; p.eps = L.eps; p.fuse_router = fuse_router; p.rc = router_cfg(L);
   p.normw = reinterpret_cast<const float *>(base + P.normw);
   p.uexp = reinterpret_cast<const float *>(base + P.uexp);
   p.c_in = c_in; p.c_work = c_work; p.idx_out = idx_out; p.gates_out = gates_out; p.c_out = c_out;

@@ -106,10 +106,13 @@ def prepare_factors(router_w, U_in, inner_norm_w, eps, U_expert, core, U_out, bi
     return prep
 
 
-def _layer_struct(x, router_w, U_in, U_expert, core, U_out, top_k, eps) -> Layer:
+_DEFAULT_ROUTER = (0, 10.0, 0.5)  # (mode, soft cap, temperature); mode 0 ignores the other two
+
+
+def _layer_struct(x, router_w, U_in, U_expert, core, U_out, top_k, eps, router=_DEFAULT_ROUTER) -> Layer:
     r1, r3, r2 = core.shape
     return Layer(int(U_in.shape[0]), int(U_out.shape[1]), int(router_w.shape[0]), int(top_k), int(r1), int(r2),
-                 int(r3), _DTYPES[x.dtype], float(eps))
+                 int(r3), _DTYPES[x.dtype], float(eps), int(router[0]), float(router[1]), float(router[2]))
 
 
 def _validate(x, params, top_k):
@@ -131,7 +134,7 @@ def _validate(x, params, top_k):
 
 
 def _run(x, router_w, U_in, inner_norm_w, eps, U_expert, core, U_out, bias, top_k, path,
-         residual=None, layer_scale=None, want_taps=False, prepared=None, silu_gate=None):
+         residual=None, layer_scale=None, want_taps=False, prepared=None, silu_gate=None, router=_DEFAULT_ROUTER):
     params = (router_w, U_in, inner_norm_w, U_expert, core, U_out, bias)
     _validate(x, params, top_k)
     lib = _lib.load()
@@ -153,7 +156,7 @@ def _run(x, router_w, U_in, inner_norm_w, eps, U_expert, core, U_out, bias, top_
         return y.reshape(*lead, d_out), taps
     params = tuple(p if p.is_contiguous() else p.contiguous() for p in params)
     router_w, U_in, inner_norm_w, U_expert, core, U_out, bias = params
-    layer = _layer_struct(x, router_w, U_in, U_expert, core, U_out, top_k, eps)
+    layer = _layer_struct(x, router_w, U_in, U_expert, core, U_out, top_k, eps, router)
     with torch.cuda.device(dev):
         stream = torch.cuda.current_stream(dev).cuda_stream
         rpath = _lib.check(lib.tmoe_resolve_path(C.byref(layer), T, path), "tmoe_resolve_path")
@@ -213,15 +216,16 @@ def read_device_status(device=None) -> Tuple[int, int, int, int]:
 def _forward_op(x: torch.Tensor, router_w: torch.Tensor, U_in: torch.Tensor, inner_norm_w: torch.Tensor, eps: float,
                 U_expert: torch.Tensor, core: torch.Tensor, U_out: torch.Tensor, bias: torch.Tensor, top_k: int,
                 path: int, residual: Optional[torch.Tensor], layer_scale: Optional[torch.Tensor],
-                prepared: Optional[torch.Tensor], silu_gate: Optional[torch.Tensor]) -> torch.Tensor:
+                prepared: Optional[torch.Tensor], silu_gate: Optional[torch.Tensor], router_mode: int,
+                router_cap: float, router_temperature: float) -> torch.Tensor:
     y, _ = _run(x, router_w, U_in, inner_norm_w, eps, U_expert, core, U_out, bias, top_k, path, residual, layer_scale,
-                prepared=prepared, silu_gate=silu_gate)
+                prepared=prepared, silu_gate=silu_gate, router=(router_mode, router_cap, router_temperature))
     return y
 
 
 @_forward_op.register_fake
 def _(x, router_w, U_in, inner_norm_w, eps, U_expert, core, U_out, bias, top_k, path, residual, layer_scale, prepared,
-      silu_gate):
+      silu_gate, router_mode, router_cap, router_temperature):
     return x.new_empty((*x.shape[:-1], U_out.shape[1]))
 
 
@@ -254,24 +258,27 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
 
 
 def tucker_moe_forward(x, router_w, U_in, inner_norm_w, eps, U_expert, core, U_out, bias, top_k, *, path=PATH_AUTO,
-                       residual=None, layer_scale=None, prepared=None, silu_gate=None):
+                       residual=None, layer_scale=None, prepared=None, silu_gate=None, router=_DEFAULT_ROUTER):
     """Functional form of the layer (parameter order of ``pure_torch_mlx/weights.py:74-81``).
     With ``residual``/``layer_scale`` it returns ``residual + layer_scale * layer(x)``
     (the callers' epilogue, ``model.py:260, 341``).  ``prepared`` is an optional result of
     ``prepare_factors`` for the same seven tensors; without it the tensor-core path re-lays the
     factors out on every call.  With ``silu_gate`` the result is ``silu(silu_gate) * layer(x)`` (the FFN's
-    ``silu(gate) * up``, ``model.py:338-340``), applied before the residual epilogue."""
+    ``silu(gate) * up``, ``model.py:338-340``), applied before the residual epilogue.  ``router`` is
+    ``(mode, cap, temperature)``: mode 0 is the pure-PyTorch rule (top-k of the raw scores, softmax over the
+    winners), mode 1 the trained checkpoints' rule (``sft_cot_bundle/scripts/model.py:318-329``)."""
     if (residual is None) != (layer_scale is None):
         raise RuntimeError("tmoe_b200: residual and layer_scale go together")
     return torch.ops.tmoe_b200.forward(x, router_w, U_in, inner_norm_w, float(eps), U_expert, core, U_out, bias,
-                                       int(top_k), int(path), residual, layer_scale, prepared, silu_gate)
+                                       int(top_k), int(path), residual, layer_scale, prepared, silu_gate, int(router[0]),
+                                       float(router[1]), float(router[2]))
 
 
 def tucker_moe_forward_taps(x, router_w, U_in, inner_norm_w, eps, U_expert, core, U_out, bias, top_k, *,
-                            path=PATH_AUTO, prepared=None):
+                            path=PATH_AUTO, prepared=None, router=_DEFAULT_ROUTER):
     """Forward that also returns the routing results (idx int32 [T,k], gates fp32 [T,k], c fp32 [T,r1])."""
     y, taps = _run(x, router_w, U_in, inner_norm_w, float(eps), U_expert, core, U_out, bias, int(top_k), int(path),
-                   want_taps=True, prepared=prepared)
+                   want_taps=True, prepared=prepared, router=router)
     return y, taps
 
 
@@ -304,6 +311,11 @@ class TuckerMoE(nn.Module):
         self.U_out = nn.Parameter(torch.empty(r2, d_out))
         self.bias = nn.Parameter(torch.zeros(d_out))
         self.path = PATH_AUTO
+        # gate rule: 0 = this module's reference (model.py:75-77); 1 = capped / tempered softmax over all experts,
+        # the rule the trained checkpoints were produced with (sft_cot_bundle/scripts/model.py:318-329)
+        self.router_mode = int(getattr(cfg, "kmoe_router_mode", 0))
+        self.router_cap = float(getattr(cfg, "kmoe_router_cap", 10.0))
+        self.router_temperature = float(getattr(cfg, "kmoe_router_temperature", 0.5))
         self._prep_key = None
         self._prep = None
         self._plan = None
@@ -325,9 +337,12 @@ class TuckerMoE(nn.Module):
     def _params(self):
         return (self.router.weight, self.U_in, self.inner_norm.weight, self.U_expert, self.core, self.U_out, self.bias)
 
+    def _router(self):
+        return (self.router_mode, self.router_cap, self.router_temperature)
+
     def _plan_for(self, x: torch.Tensor) -> _Plan:
         ps = self._params()
-        key = (x.dtype, x.device, self.path, self.top_k, self.inner_norm.eps) + tuple((p.data_ptr(), p._version) for p in ps)
+        key = (x.dtype, x.device, self.path, self.top_k, self.inner_norm.eps) + self._router() + tuple((p.data_ptr(), p._version) for p in ps)
         plan = self._plan
         if plan is not None and plan.key == key:
             return plan
@@ -337,7 +352,7 @@ class TuckerMoE(nn.Module):
         plan.lib = _lib.load()
         plan.params = tuple(p if p.is_contiguous() else p.contiguous() for p in ps)
         rw, ui, nw, ue, co, uo, b = plan.params
-        plan.layer = _layer_struct(x, rw, ui, ue, co, uo, self.top_k, self.inner_norm.eps)
+        plan.layer = _layer_struct(x, rw, ui, ue, co, uo, self.top_k, self.inner_norm.eps, self._router())
         plan.factors = Factors(*[p.data_ptr() for p in plan.params])
         plan.layer_ref, plan.factors_ref = C.byref(plan.layer), C.byref(plan.factors)
         plan.prepared = self._prepared_for(x)
@@ -388,7 +403,7 @@ class TuckerMoE(nn.Module):
             return self._fast_forward(x)
         rw, ui, nw, ue, co, uo, b = self._params()
         return tucker_moe_forward(x, rw, ui, nw, self.inner_norm.eps, ue, co, uo, b, self.top_k, path=self.path,
-                                  prepared=self._prepared_for(x))
+                                  prepared=self._prepared_for(x), router=self._router())
 
     def forward_fused(self, x: torch.Tensor, *, pre_norm=None, residual: Optional[torch.Tensor] = None,
                       layer_scale: Optional[torch.Tensor] = None, silu_gate: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -405,19 +420,20 @@ class TuckerMoE(nn.Module):
         rw, ui, nw, ue, co, uo, b = self._params()
         return tucker_moe_forward(x, rw, ui, nw, self.inner_norm.eps, ue, co, uo, b, self.top_k, path=self.path,
                                   residual=residual, layer_scale=layer_scale, silu_gate=silu_gate,
-                                  prepared=self._prepared_for(x))
+                                  prepared=self._prepared_for(x), router=self._router())
 
     def forward_fused_residual(self, x: torch.Tensor, residual: torch.Tensor, layer_scale: torch.Tensor) -> torch.Tensor:
         """``residual + layer_scale * self(x)`` with the epilogue fused into the out-projection
         (what the callers compute at ``model.py:259-260`` and ``model.py:340-341``)."""
         rw, ui, nw, ue, co, uo, b = self._params()
         return tucker_moe_forward(x, rw, ui, nw, self.inner_norm.eps, ue, co, uo, b, self.top_k, path=self.path,
-                                  residual=residual, layer_scale=layer_scale, prepared=self._prepared_for(x))
+                                  residual=residual, layer_scale=layer_scale, prepared=self._prepared_for(x),
+                                  router=self._router())
 
     def forward_with_routing(self, x: torch.Tensor):
         rw, ui, nw, ue, co, uo, b = self._params()
         return tucker_moe_forward_taps(x, rw, ui, nw, self.inner_norm.eps, ue, co, uo, b, self.top_k, path=self.path,
-                                       prepared=self._prepared_for(x))
+                                       prepared=self._prepared_for(x), router=self._router())
 
     @torch.no_grad()
     def forward_host(self, x_host: torch.Tensor, out: Optional[torch.Tensor] = None,

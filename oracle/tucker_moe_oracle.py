@@ -67,12 +67,29 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     return (x / denom) * weight
 
 
+def capped_softmax_gates(scores: torch.Tensor, top_k: int, cap: float, temperature: float):
+    """The trained checkpoints' gate rule, restated from ``sft_cot_bundle/scripts/model.py:318-329`` (same math in
+    ``mamba3_mlx/mlx_model/tucker_moe.py:107-114``): soft cap ``cap*tanh(s/cap)``, temperature, softmax over ALL
+    experts, top-k of the tempered logits, renormalise the k selected probabilities with ``+1e-6``.
+    PARITY UNPINNED for this rule: that file needs a Triton GPU driver to import and its fused kernels to run, so no
+    golden vectors could be produced from the reference itself; this restatement is the only oracle for it."""
+    capped = cap * torch.tanh(scores / cap)
+    logits = capped / temperature
+    probs = torch.softmax(logits, dim=-1)
+    _, idx = torch.topk(logits, top_k, dim=-1)
+    raw = probs.gather(-1, idx)
+    return idx, raw / (raw.sum(-1, keepdim=True) + 1e-6)
+
+
 def _forward_chunk(x_flat: torch.Tensor, f: Dict[str, torch.Tensor], top_k: int, eps: float,
-                   taps: Optional[dict]) -> torch.Tensor:
-    # model.py:75-77 -- raw scores, top-k on the raw scores, softmax over the k winners only
+                   taps: Optional[dict], router=(0, 10.0, 0.5)) -> torch.Tensor:
     scores = F.linear(x_flat, f["router_w"])
-    sel_val, sel_idx = torch.topk(scores, top_k, dim=-1)
-    gates = F.softmax(sel_val, dim=-1)
+    if router[0] == 0:
+        # model.py:75-77 -- raw scores, top-k on the raw scores, softmax over the k winners only
+        sel_val, sel_idx = torch.topk(scores, top_k, dim=-1)
+        gates = F.softmax(sel_val, dim=-1)
+    else:
+        sel_idx, gates = capped_softmax_gates(scores, top_k, router[1], router[2])
     # model.py:80-81 -- shared in-projection, then the inner RMSNorm
     h = rms_norm(x_flat @ f["U_in"], f["inner_norm_w"], eps)
     # model.py:87-98 -- per selected expert: mix the core slices, contract, weight, accumulate
@@ -94,7 +111,7 @@ def _forward_chunk(x_flat: torch.Tensor, f: Dict[str, torch.Tensor], top_k: int,
 
 @torch.no_grad()
 def layer_forward(x: torch.Tensor, factors: Dict[str, torch.Tensor], top_k: int, eps: float,
-                  chunk_tokens: int = 256, return_taps: bool = False):
+                  chunk_tokens: int = 256, return_taps: bool = False, router=(0, 10.0, 0.5)):
     """Reference-order forward on CPU.  ``x``: (..., d_in) -> (..., d_out).
 
     Tokens are processed in chunks because the reference materialises a ``[T, r3, r2]``
@@ -108,7 +125,7 @@ def layer_forward(x: torch.Tensor, factors: Dict[str, torch.Tensor], top_k: int,
     taps: Optional[dict] = {} if return_taps else None
     outs = []
     for t0 in range(0, T, chunk_tokens):
-        outs.append(_forward_chunk(x_flat[t0:t0 + chunk_tokens], factors, top_k, eps, taps))
+        outs.append(_forward_chunk(x_flat[t0:t0 + chunk_tokens], factors, top_k, eps, taps, router))
     y = torch.cat(outs, 0) if outs else x_flat.new_zeros(0, d_out)
     y = y.reshape(*batch, d_out)
     if return_taps:
@@ -120,7 +137,7 @@ def layer_forward(x: torch.Tensor, factors: Dict[str, torch.Tensor], top_k: int,
 @torch.no_grad()
 def layer_forward_f64(x: torch.Tensor, factors: Dict[str, torch.Tensor], top_k: int, eps: float,
                       idx: Optional[torch.Tensor] = None, round_scores_to: Optional[torch.dtype] = None,
-                      chunk_tokens: int = 2048):
+                      chunk_tokens: int = 2048, router=(0, 10.0, 0.5)):
     """float64 forward in the coefficient-vector algebra.
 
     ``idx`` (optional, [T, k]) forces the selected experts so that outputs can be compared
@@ -146,7 +163,12 @@ def layer_forward_f64(x: torch.Tensor, factors: Dict[str, torch.Tensor], top_k: 
         else:
             sel_idx = idx[t0:t0 + chunk_tokens].long()
             sel_val = torch.gather(scores, 1, sel_idx)
-        gates = torch.softmax(sel_val, -1)
+        if router[0] == 0:
+            gates = torch.softmax(sel_val, -1)
+        else:  # capped / tempered softmax over all experts, renormalised over the selection (+1e-6)
+            logits = router[1] * torch.tanh(scores / router[1]) / router[2]
+            raw = torch.softmax(logits, -1).gather(-1, sel_idx)
+            gates = raw / (raw.sum(-1, keepdim=True) + 1e-6)
         c = torch.einsum("tk,tkr->tr", gates, f["U_expert"][sel_idx])         # [t, r1]
         h = xc @ f["U_in"]
         h = h / torch.sqrt(h.pow(2).mean(-1, keepdim=True) + eps) * f["inner_norm_w"]

@@ -14,7 +14,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def _layer(**kw):
-    base = dict(d_in=64, d_out=96, n_experts=8, top_k=2, r1=4, r2=64, r3=32, dtype=_lib.TMOE_F32, eps=1e-5)
+    base = dict(d_in=64, d_out=96, n_experts=8, top_k=2, r1=4, r2=64, r3=32, dtype=_lib.TMOE_F32, eps=1e-5,
+                router_mode=0, router_cap=10.0, router_temperature=0.5)
     base.update(kw)
     return _lib.Layer(**base)
 
@@ -107,5 +108,5 @@ def test_fake_kernel_gives_shapes_without_a_gpu():
         x = torch.empty(2, 5, 64)
         y = torch.ops.tmoe_b200.forward(x, torch.empty(8, 64), torch.empty(64, 32), torch.empty(32), 1e-5,
                                         torch.empty(8, 4), torch.empty(4, 32, 64), torch.empty(64, 96),
-                                        torch.empty(96), 2, 0, None, None, None, None)
+                                        torch.empty(96), 2, 0, None, None, None, None, 0, 10.0, 0.5)
     assert y.shape == (2, 5, 96)

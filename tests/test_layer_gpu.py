@@ -304,3 +304,37 @@ def test_fused_ffn_and_out_proj_match_callers_composition(T):
     got = fused_out_proj(mo, x.cuda(), (nw.cuda(), 1e-5), gamma.cuda()).float().cpu()
     want = x.double() + gamma.double() * lay(ref_norm(x.double(), nw.double(), 1e-5), fo, s_o)
     close_tokens(got, want, 2e-2)
+
+
+@pytest.mark.parametrize("dtype,path,T", [
+    (torch.float32, PATH_SIMT, 33), (torch.float32, PATH_SIMT, 300), (torch.bfloat16, PATH_SIMT, 40),
+    (torch.bfloat16, PATH_TENSOR, 300), (torch.bfloat16, PATH_DECODE, 9), (torch.bfloat16, PATH_DECODE, 64)])
+def test_capped_softmax_router_rule(dtype, path, T):
+    """router_mode = 1 (tanh cap, temperature, softmax over all experts, renormalised top-k) on every kernel path,
+    against the oracle's restatement of sft_cot_bundle/scripts/model.py:318-329 (no reference goldens exist)."""
+    small = T != 300 or dtype == torch.float32
+    shape = LayerShape(256, 384, 64, 8, 8, 64, 128, 1e-6) if small else LayerShape(1536, 2304, 64, 2, 4, 256, 1024, 1e-6)
+    f = make_factors(shape, 123, dtype, None, 0.1)
+    f["router_w"] = (f["router_w"].float() * 4).to(dtype)          # scores of a few units so that the cap matters
+    x = make_tokens(T, shape.d_in, 123, dtype)
+    m = build_module(shape, f, dtype, path=path)
+    m.router_mode, m.router_cap, m.router_temperature = 1, 10.0, 0.5
+    router = (1, 10.0, 0.5)
+    y, taps = m.forward_with_routing(x.cuda())
+    torch.cuda.synchronize()
+    rnd = None if dtype == torch.float32 else torch.bfloat16
+    y_ref, rt = layer_forward(x, f, shape.top_k, shape.eps, return_taps=True, router=router)
+    # scores here are a few units large; two competing bf16 scores may each round one ulp differently in the two
+    # implementations, so an order flip is explained by a gap of up to two ulps
+    gap = 1e-6 if dtype == torch.float32 else 2 * bf16_ulp(rt["scores"])
+    rep = classify_topk(taps[0].cpu(), rt["idx"], rt["scores"], gap)
+    assert rep.unexplained == 0
+    y64, own = layer_forward_f64(x, f, shape.top_k, shape.eps, idx=taps[0].cpu(), round_scores_to=rnd, router=router)
+    tol = F32_TOL if dtype == torch.float32 else 1e-2
+    assert rel_fro(y.float().cpu(), y64) <= tol
+    # tempered logits reach ~20, so fp32 exp/tanh round-off of 1e-7 relative becomes a few 1e-6 in a gate
+    assert max_abs(taps[1].cpu(), own["gates"]) < (1e-5 if dtype == torch.float32 else 4e-3)
+    assert torch.equal(m(x.cuda()), y)                              # eager fast path uses the same rule
+    # rule 0 on the same module gives a different answer
+    m.router_mode = 0
+    assert rel_fro(m(x.cuda()).float().cpu(), y64) > 3 * tol

@@ -57,3 +57,21 @@ def test_classify_topk_flags_real_mismatch():
     assert classify_topk(torch.tensor([[3, 1]]), ref, s, 1e-6).unexplained == 1
     s2 = torch.tensor([[0.0, 2.0, 2.0, 3.0]])
     assert classify_topk(torch.tensor([[3, 1]]), ref, s2, 1e-6).tie_explained == 1
+
+
+def test_capped_softmax_rule_properties():
+    """The second gate rule has no golden vectors (its reference file cannot run here); check the restatement's
+    defining properties: same selection as the raw scores, gates proportional to the full-softmax probabilities,
+    sum = S / (S + 1e-6), and agreement between the dtype-faithful and the float64 statements."""
+    shape, x, f, _, g = load_case("ragged_e64_k8_f32")
+    router = (1, 10.0, 0.5)
+    y, taps = layer_forward(x, f, shape.top_k, shape.eps, return_taps=True, router=router)
+    assert torch.equal(taps["idx"], g["idx"])          # tanh and 1/T are monotone: same experts, same order
+    logits = 10.0 * torch.tanh(taps["scores"] / 10.0) / 0.5
+    p = torch.softmax(logits, -1).gather(-1, taps["idx"])
+    s = p.sum(-1, keepdim=True)
+    assert torch.allclose(taps["gates"], p / (s + 1e-6), atol=1e-7)
+    assert torch.allclose(taps["gates"].sum(-1, keepdim=True), s / (s + 1e-6), atol=1e-6)
+    y64, t64 = layer_forward_f64(x, f, shape.top_k, shape.eps, router=router)
+    assert rel_fro(y64, y) < 1e-5
+    assert not torch.allclose(y, g["y"], atol=1e-3)    # and it is a different function from rule 0
