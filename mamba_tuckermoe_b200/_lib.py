@@ -6,7 +6,8 @@ import os
 import threading
 
 PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(PKG, "lib", "libtmoe_b200.so")
+# TMOE_LIB_PATH lets a developer point the binding at another build of the same ABI (A/B timing of kernels)
+LIB_PATH = os.environ.get("TMOE_LIB_PATH") or os.path.join(PKG, "lib", "libtmoe_b200.so")
 
 TMOE_F32, TMOE_BF16 = 0, 1
 PATH_AUTO, PATH_SIMT, PATH_TENSOR, PATH_DECODE = 0, 1, 2, 3

@@ -83,6 +83,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap
       : "memory");
 }
 
+// Ask L2 to fetch the box at (c0, c1) of a tiled tensor; no shared-memory destination, no completion signal.
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap *m, int c0, int c1) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(m)),
+               "r"(c0), "r"(c1)
+               : "memory");
+}
+
 // 2-D tiled store shared (this CTA) -> global, tracked by the thread's bulk async-group.
 // Elements of the box that fall outside the tensor are not written.
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap *m, uint32_t src_smem, int c0, int c1) {

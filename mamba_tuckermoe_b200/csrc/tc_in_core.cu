@@ -129,48 +129,62 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
     // ------------------------------- TMA producer -------------------------------
     if (lane == 0) {
       bool ok = true;
+      uint32_t sA = 0, phA = 0, sB = 0, phB = 0;
       for (int kb = 0; kb < KA && ok; ++kb) {
-        const uint32_t s = kb % nA, ph = (kb / nA) & 1;
+        const uint32_t s = sA, ph = phA;
+        if (++sA == (uint32_t)nA) { sA = 0; phA ^= 1; }  // ring position kept incrementally: no division in this loop
         if (!(ok = mbar_wait(smem_u32(&bar_emptyA[s]), ph ^ 1, p.status, kKernelInCore, 2))) break;
         const uint32_t full = smem_u32(&bar_fullA[s]);
         mbar_arrive_expect_tx(full, stageA_bytes);
         const uint32_t sa = ring + s * stageA_bytes;
         tma_load_2d(sa, &tmX, kb * 64, m0, full);
-        for (int ub = 0; ub < u_boxes; ++ub)
-          tma_load_2d(sa + X_TILE_BYTES + ub * u_box_rows * 128, &tmU, kb * 64, ub * u_box_rows, full);
+        tma_load_2d(sa + X_TILE_BYTES, &tmU, kb * 64, 0, full);
+        if (u_boxes == 2) tma_load_2d(sa + X_TILE_BYTES + 256 * 128, &tmU, kb * 64, 256, full);
         if (p.e_pad) tma_load_2d(sa + X_TILE_BYTES + u_bytes, &tmW, kb * 64, 0, full);
       }
       // ring A aliases h and the core-tile ring: wait until every phase-A MMA has retired
       if (ok) ok = mbar_wait(smem_u32(&bar_accA), 0, p.status, kKernelInCore, 3);
       const int total = p.n_tiles2 * KH;
+      int j = 0, kbB = 0;
       for (int it = 0; it < total && ok; ++it) {
-        const uint32_t s = it % nG, ph = (it / nG) & 1;
-        const int j = it / KH, kb = it - j * KH;
+        const uint32_t s = sB, ph = phB;
+        if (++sB == (uint32_t)nG) { sB = 0; phB ^= 1; }
+        const int kb = kbB;
+        const int row0 = j * 256;
+        if (++kbB == KH) { kbB = 0; ++j; }
         if (!(ok = mbar_wait(smem_u32(&bar_emptyB[s]), ph ^ 1, p.status, kKernelInCore, 6))) break;
         const uint32_t full = smem_u32(&bar_fullB[s]);
         mbar_arrive_expect_tx(full, G_STAGE_BYTES);
-        tma_load_2d(ringB + s * G_STAGE_BYTES, &tmG, kb * 64, j * 256, full);
+        tma_load_2d(ringB + s * G_STAGE_BYTES, &tmG, kb * 64, row0, full);
       }
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -------------------------------
     if (lane == 0) {
       bool ok = true;
+      uint32_t sA = 0, phA = 0, sB = 0, phB = 0;
       const uint32_t idescH = umma_idesc_bf16(TM, u_box_rows);
       const uint32_t idescS = umma_idesc_bf16(TM, p.e_pad ? p.e_pad : 16);
+      // This thread is the serial path of the kernel: the tensor pipe idles whenever it is not ahead, so the
+      // loop bodies below are kept to a barrier wait, a few adds on precomputed descriptors, the MMAs and a
+      // commit.  (No tcgen05 fence after a "tiles landed" wait: the mbarrier completion orders the TMA writes
+      // before the MMA reads; the fence is only needed where another thread's tcgen05.ld preceded, i.e. after
+      // the accumulator / h hand-offs.)
+      const uint64_t desc0 = umma_desc_k_sw128(ring);          // descriptor of the ring base; tiles add (bytes >> 4)
+      const uint32_t stageA16 = (uint32_t)stageA_bytes >> 4, xtile16 = X_TILE_BYTES >> 4, u16 = (uint32_t)u_bytes >> 4;
       for (int kb = 0; kb < KA && ok; ++kb) {
-        const uint32_t s = kb % nA, ph = (kb / nA) & 1;
+        const uint32_t s = sA, ph = phA;
+        if (++sA == (uint32_t)nA) { sA = 0; phA ^= 1; }
         if (!(ok = mbar_wait(smem_u32(&bar_fullA[s]), ph, p.status, kKernelInCore, 1))) break;
-        tc_fence_after();
-        const uint32_t sa = ring + s * stageA_bytes;
-        const uint64_t dx = umma_desc_k_sw128(sa), du = umma_desc_k_sw128(sa + X_TILE_BYTES),
-                       dw = umma_desc_k_sw128(sa + X_TILE_BYTES + u_bytes);
+        const uint64_t dx = desc0 + s * stageA16, du = dx + xtile16, dw = du + u16;
+        const uint32_t acc0 = kb != 0;
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          for (int ub = 0; ub < u_boxes; ++ub)  // one MMA per <= 256 columns of h; the piece's rows are 128 B apart
-            umma_bf16(tmem_base + ub * u_box_rows, dx + 2 * k, du + (uint64_t)(ub * u_box_rows * 8) + 2 * k, idescH,
-                      (kb | k) != 0);
-          if (p.e_pad) umma_bf16(tmem_base + SCORE_COL, dx + 2 * k, dw + 2 * k, idescS, (kb | k) != 0);
+          const uint32_t acc = acc0 | (uint32_t)(k != 0);
+          // one MMA per <= 256 columns of h (two when r3 = 512: the second piece starts 256 rows = 32 KB further)
+          umma_bf16(tmem_base, dx + 2 * k, du + 2 * k, idescH, acc);
+          if (u_boxes == 2) umma_bf16(tmem_base + 256, dx + 2 * k, du + 2048 + 2 * k, idescH, acc);
+          if (p.e_pad) umma_bf16(tmem_base + SCORE_COL, dx + 2 * k, dw + 2 * k, idescS, acc);
         }
         umma_commit(smem_u32(&bar_emptyA[s]));
       }
@@ -180,20 +194,21 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       tc_fence_after();
       TMOE_STAMP(1);  // MMA thread saw h ready
       const uint32_t idescP = umma_idesc_bf16(TM, 256);
-      int it = 0;
+      const uint64_t descB0 = desc0 + ((uint32_t)h_bytes >> 4);
       for (int j = 0; j < p.n_tiles2 && ok; ++j) {
         const uint32_t slot = j & 1, pph = (j >> 1) & 1;
         if (!(ok = mbar_wait(smem_u32(&bar_pempty[slot]), pph ^ 1, p.status, kKernelInCore, 8))) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + slot * 256;
-        for (int kb = 0; kb < KH; ++kb, ++it) {
-          const uint32_t s = it % nG, ph = (it / nG) & 1;
+        for (int kb = 0; kb < KH; ++kb) {
+          const uint32_t s = sB, ph = phB;
+          if (++sB == (uint32_t)nG) { sB = 0; phB ^= 1; }
           if (!(ok = mbar_wait(smem_u32(&bar_fullB[s]), ph, p.status, kKernelInCore, 5))) break;
-          tc_fence_after();
-          const uint64_t dh = umma_desc_k_sw128(ring + kb * H_KBLOCK_BYTES);
-          const uint64_t dg = umma_desc_k_sw128(ringB + s * G_STAGE_BYTES);
+          const uint64_t dh = desc0 + kb * (H_KBLOCK_BYTES >> 4);
+          const uint64_t dg = descB0 + s * (G_STAGE_BYTES >> 4);
+          const uint32_t acc0 = kb != 0;
 #pragma unroll
-          for (int k = 0; k < 4; ++k) umma_bf16(d_tmem, dh + 2 * k, dg + 2 * k, idescP, (kb | k) != 0);
+          for (int k = 0; k < 4; ++k) umma_bf16(d_tmem, dh + 2 * k, dg + 2 * k, idescP, acc0 | (uint32_t)(k != 0));
           umma_commit(smem_u32(&bar_emptyB[s]));
         }
         if (ok) umma_commit(smem_u32(&bar_pfull[slot]));
