@@ -245,7 +245,6 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
           uint32_t key[RK];
 #pragma unroll
           for (int j = 0; j < RK; ++j) key[j] = 0u;
-          float run_max = -INFINITY, run_sum = 0.f;  // online softmax over all experts' logits (capped-softmax rule)
           for (int cc = 0; cc < p.e_pad / 16; ++cc) {
             uint32_t r[16];
             tmem_ld16(t_lane + SCORE_COL + cc * 16, r);
@@ -263,11 +262,6 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                 carry = min(key[j], carry);
                 key[j] = hi;
               }
-              if (p.rc.mode == 1 && e < p.E) {
-                const float l = p.rc.logit(__uint_as_float(b << 16));
-                if (l > run_max) { run_sum = run_sum * expf(run_max - l) + 1.f; run_max = l; }
-                else run_sum += expf(l - run_max);
-              }
             }
           }
           float sv[RK]; int si[RK];
@@ -279,8 +273,25 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
             si[j] = (int)(0xffffu - (key[j] & 0xffffu));
           }
           if (threadIdx.x == 64) TMOE_STAMP(6);  // score scan done
+          // capped-softmax rule only: denominator over ALL experts, relative to the top logit.  Kept out of the
+          // scan above (a second pass over the score columns) so that the default rule's loop stays branch-free.
+          float z_all = 1.f;
+          if (p.rc.mode == 1) {
+            const float l0 = p.rc.logit(sv[0]);
+            z_all = 0.f;
+            for (int cc = 0; cc < p.e_pad / 16; ++cc) {
+              uint32_t r[16];
+              tmem_ld16(t_lane + SCORE_COL + cc * 16, r);
+              tmem_ld_wait(r);
+#pragma unroll
+              for (int q = 0; q < 16; ++q) {
+                const float sc = round_to<bf16>(__uint_as_float(r[q]));
+                if (cc * 16 + q < p.E) z_all += expf(p.rc.logit(sc) - l0);
+              }
+            }
+          }
           float gate[RK];
-          gates_of<bf16, RK>(sv, p.top_k, p.rc, run_sum, gate);
+          gates_of<bf16, RK>(sv, p.top_k, p.rc, z_all, gate);
 #pragma unroll
           for (int a = 0; a < R1; ++a) c[a] = 0.f;
 #pragma unroll
