@@ -179,6 +179,8 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=8)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--path", type=int, default=0, help="0 auto, 1 CUDA-core, 2 tensor-core")
+    ap.add_argument("--allgather", action="store_true",
+                    help="also time the forward followed by the optional NCCL all-gather of y (N > 1), chunk-overlapped")
     ap.add_argument("--profile", action="store_true",
                     help="short run for use under ncu: device-resident steps only (no per-kernel, e2e or CPU legs)")
     args = ap.parse_args()
@@ -288,6 +290,27 @@ def main():
             dist.all_reduce(e_ms, op=dist.ReduceOp.MAX)
         e2e_value = world * T * e2e_steps / (float(e_ms.item()) * 1e-3)
 
+    gather_info = None
+    if args.allgather and world > 1:
+        from mamba_tuckermoe_b200.sharding import sharded_forward
+        with torch.no_grad():
+            for chunks in (1, 4):
+                for _ in range(2):
+                    sharded_forward(layer, x_dev[0], n_tokens=T * world, gather=True, chunks=chunks)
+                barrier()
+                ev0.record()
+                for i in range(5):
+                    y_all = sharded_forward(layer, x_dev[i % N_INPUT_SETS], n_tokens=T * world, gather=True, chunks=chunks)
+                ev1.record()
+                barrier()
+                g_ms = torch.tensor([ev0.elapsed_time(ev1) / 5], dtype=torch.float64, device=dev)
+                dist.all_reduce(g_ms, op=dist.ReduceOp.MAX)
+                gather_info = gather_info or {}
+                gather_info[f"chunks{chunks}"] = {"ms_per_step": float(g_ms.item()),
+                                                  "tokens_per_s": world * T / (float(g_ms.item()) * 1e-3)}
+            gather_info["bytes_received_per_gpu"] = (world - 1) * T * shape.d_out * y_all.element_size()
+            gather_info["note"] = "forward + all_gather_into_tensor of y on a side stream per token chunk (sharding.py)"
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -332,6 +355,8 @@ def main():
         "gpu_launches": int(launches),
         "clocks": clocks,
     }
+    if gather_info:
+        line["allgather"] = gather_info
     if world == 1 and not args.no_cpu_baseline:
         rate, threads, dt = cpu_reference_rate(args.workload, min(T, 8192), 2)
         line["cpu_baseline"] = {"value": rate, "unit": "tokens/s", "cores": threads, "kind": "port",

@@ -104,6 +104,12 @@ typedef struct tmoe_extras {
   const void *silu_gate; /* [T, d_out], dtype of x: y = silu(silu_gate) * (acc @ U_out + bias), the FFN's
                             silu(gate) * up (pure_torch_mlx/model.py:338-340) fused into the `up` layer;
                             applied before the residual epilogue */
+  int32_t pre_norm;      /* 1: the callers' RMSNorm of x (norm_out_proj / norm_ffn, model.py:258, 337) is applied
+                            inside the in-projection kernel.  `prepared` must then come from
+                            tmoe_prepare_factors_prenorm (the norm weight is folded into it).  Tensor-core path with
+                            the in-kernel router only (n_experts <= 256, top_k <= 8, r3 <= 256); other
+                            combinations return TMOE_ERR_UNSUPPORTED -- use tmoe_rms_norm in front instead. */
+  float pre_norm_eps;    /* epsilon of that RMSNorm */
 } tmoe_extras_t;
 
 /* ABI version of the loaded library (== TMOE_ABI_VERSION of the header it was built from). */
@@ -127,6 +133,12 @@ int64_t tmoe_prepared_bytes(const tmoe_layer_t *layer);
  * must be 256-byte aligned and tmoe_prepared_bytes() large. */
 int tmoe_prepare_factors(const tmoe_layer_t *layer, const tmoe_factors_t *factors, void *prepared,
                          int64_t prepared_bytes, void *stream);
+
+/* Same re-layout with the callers' pre-norm weight ([d_in], layer dtype) folded into the U_in and router copies:
+ * RMSNorm(x) @ W = (x @ (diag(w) W)) / rms(x), so a forward with tmoe_extras_t.pre_norm = 1 only has to find
+ * 1/rms(x) per row, which it does from the x tiles on their way through shared memory. */
+int tmoe_prepare_factors_prenorm(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const void *pre_norm_w,
+                                 void *prepared, int64_t prepared_bytes, void *stream);
 
 /* Bytes of scratch that tmoe_forward / tmoe_router / tmoe_in_core / tmoe_out need for T
  * tokens on `path`, or a negative status.  The workspace must be 256-byte aligned.  Its

@@ -19,6 +19,7 @@ EXPORTS = (
     "tmoe_version", "tmoe_status_string", "tmoe_resolve_path", "tmoe_prepared_bytes",
     "tmoe_prepare_factors", "tmoe_workspace_bytes", "tmoe_router", "tmoe_in_core", "tmoe_out",
     "tmoe_forward", "tmoe_read_device_status", "tmoe_launch_count", "tmoe_forward_static_scratch", "tmoe_rms_norm",
+    "tmoe_prepare_factors_prenorm",
 )
 STATIC_SCRATCH_BYTES = 4 << 20
 
@@ -37,7 +38,8 @@ class Factors(C.Structure):
 
 class Extras(C.Structure):
     _fields_ = [("residual", C.c_void_p), ("layer_scale", C.c_void_p), ("idx_out", C.c_void_p),
-                ("gates_out", C.c_void_p), ("c_out", C.c_void_p), ("silu_gate", C.c_void_p)]
+                ("gates_out", C.c_void_p), ("c_out", C.c_void_p), ("silu_gate", C.c_void_p),
+                ("pre_norm", C.c_int32), ("pre_norm_eps", C.c_float)]
 
 
 class TmoeError(RuntimeError):
@@ -77,6 +79,8 @@ def load():
         lib.tmoe_prepared_bytes.argtypes = [LP]
         lib.tmoe_prepare_factors.restype = i32
         lib.tmoe_prepare_factors.argtypes = [LP, FP, vp, i64, vp]
+        lib.tmoe_prepare_factors_prenorm.restype = i32
+        lib.tmoe_prepare_factors_prenorm.argtypes = [LP, FP, vp, vp, i64, vp]
         lib.tmoe_workspace_bytes.restype = i64
         lib.tmoe_workspace_bytes.argtypes = [LP, i64, i32]
         lib.tmoe_router.restype = i32

@@ -146,7 +146,19 @@ int tmoe_prepare_factors(const tmoe_layer_t *layer, const tmoe_factors_t *factor
   if (!tensor_path_covers(*layer)) return TMOE_ERR_UNSUPPORTED;
   if (reinterpret_cast<uintptr_t>(prepared) & 255) return TMOE_ERR_ALIGN;
   if (prepared_bytes < prepared_layout(*layer).total) return TMOE_ERR_WORKSPACE;
-  return launch_prepare(*layer, *factors, prepared, (cudaStream_t)stream);
+  return launch_prepare(*layer, *factors, nullptr, prepared, (cudaStream_t)stream);
+}
+
+int tmoe_prepare_factors_prenorm(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const void *pre_norm_w,
+                                 void *prepared, int64_t prepared_bytes, void *stream) {
+  int rc = check_layer(layer);
+  if (rc) return rc;
+  if ((rc = check_factors(factors))) return rc;
+  if (!prepared || !pre_norm_w) return TMOE_ERR_NULL;
+  if (!tensor_path_covers(*layer)) return TMOE_ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(prepared) & 255) || misaligned(pre_norm_w)) return TMOE_ERR_ALIGN;
+  if (prepared_bytes < prepared_layout(*layer).total) return TMOE_ERR_WORKSPACE;
+  return launch_prepare(*layer, *factors, pre_norm_w, prepared, (cudaStream_t)stream);
 }
 
 int64_t tmoe_workspace_bytes(const tmoe_layer_t *layer, int64_t T, int path) {
@@ -195,7 +207,7 @@ int tmoe_in_core(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const
     return launch_simt_core(*layer, h, c, factors->core, T, reinterpret_cast<float *>(z), st);
   }
   if (!prepared) return TMOE_ERR_NULL;
-  return launch_tc_in_core(*layer, x, prepared, prepared_layout(*layer), T, 0, c,
+  return launch_tc_in_core(*layer, x, prepared, prepared_layout(*layer), T, 0, 0.f, 0, c,
                            reinterpret_cast<float *>(ws + W.c), nullptr, nullptr, nullptr, z,
                            reinterpret_cast<int32_t *>(ws), st);
 }
@@ -236,11 +248,14 @@ int tmoe_forward(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const
   if (misaligned(x) || misaligned(y) || (reinterpret_cast<uintptr_t>(workspace) & 255)) return TMOE_ERR_ALIGN;
   OutEpilogue epi;
   if ((rc = epilogue_from(extras, &epi))) return rc;
+  const int pre_norm = (extras && extras->pre_norm) ? 1 : 0;
   int rp = resolve(*layer, T, path);
   if (rp < 0) return rp;
   const tmoe_layer_t &L = *layer;
   WsLayout W = ws_layout(L, T, rp);
   if (workspace_bytes < W.total) return TMOE_ERR_WORKSPACE;
+  // the in-kernel pre-norm exists on the tensor-core path with the in-kernel router only
+  if (pre_norm && !(rp == TMOE_PATH_TENSOR && W.tc_router_fused)) return TMOE_ERR_UNSUPPORTED;
   char *ws = reinterpret_cast<char *>(workspace);
   cudaStream_t st = (cudaStream_t)stream;
   int32_t *idx = (extras && extras->idx_out) ? extras->idx_out : reinterpret_cast<int32_t *>(ws + W.idx);
@@ -270,7 +285,8 @@ int tmoe_forward(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const
   }
   if (W.tc_router_fused) {
     const bool taps = extras && (extras->idx_out || extras->gates_out || extras->c_out);
-    rc = launch_tc_in_core(L, x, prepared, P, T, 1, nullptr, reinterpret_cast<float *>(ws + W.c),
+    rc = launch_tc_in_core(L, x, prepared, P, T, pre_norm, pre_norm ? extras->pre_norm_eps : 0.f, 1, nullptr,
+                           reinterpret_cast<float *>(ws + W.c),
                            taps ? extras->idx_out : nullptr,
                            taps ? extras->gates_out : nullptr, taps ? extras->c_out : nullptr, z, status, st);
   } else {
@@ -279,7 +295,7 @@ int tmoe_forward(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const
       return rc;
     if ((rc = launch_select_bf16_scores(L, scores, P.e_pad, factors->U_expert, T, idx, gates, c, st))) return rc;
     // c_work may alias c: every row is read by its own thread before that thread overwrites it
-    rc = launch_tc_in_core(L, x, prepared, P, T, 0, c, reinterpret_cast<float *>(ws + W.c), nullptr, nullptr, nullptr, z,
+    rc = launch_tc_in_core(L, x, prepared, P, T, 0, 0.f, 0, c, reinterpret_cast<float *>(ws + W.c), nullptr, nullptr, nullptr, z,
                            status, st);
   }
   if (rc) return rc;

@@ -48,7 +48,8 @@ struct PreparedLayout {
 };
 bool tensor_path_covers(const tmoe_layer_t &L);
 PreparedLayout prepared_layout(const tmoe_layer_t &L);
-int launch_prepare(const tmoe_layer_t &L, const tmoe_factors_t &F, void *prepared, cudaStream_t st);
+// pre_norm_w (optional, [d_in], layer dtype): folded into the U_in and router copies (see prepare.cu)
+int launch_prepare(const tmoe_layer_t &L, const tmoe_factors_t &F, const void *pre_norm_w, void *prepared, cudaStream_t st);
 
 // ---- tc_out_gemm.cu ----
 // y[T, N] = z[T, K] (bf16) @ W_t[N, K]^T (bf16, K-major) + bias (fp32) on tcgen05 tensor cores.
@@ -63,8 +64,10 @@ int launch_tc_gemm_bf16(const void *A, const void *B_t, const float *bias, const
 // Fused x@U_in (+ router scores) -> RMS statistics -> h@G tiles with c-weighted epilogue -> z bf16.
 // fuse_router != 0: scores/top-k/softmax/c are computed inside (c_in ignored, taps optional);
 // otherwise c_in [T, r1] is read.  c_work [T, r1] is scratch in both cases.
+// pre_norm != 0: `prepared` carries the pre-norm weight folded into U_in / router rows; the kernel then computes every
+// row's 1/rms(x) from the x tiles passing through shared memory and applies it to the scores and to the RMS statistics.
 int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared, const PreparedLayout &P, int64_t T,
-                      int fuse_router, const float *c_in, float *c_work, int32_t *idx_out, float *gates_out, float *c_out,
+                      int pre_norm, float pre_norm_eps, int fuse_router, const float *c_in, float *c_work, int32_t *idx_out, float *gates_out, float *c_out,
                       void *z, int32_t *status, cudaStream_t st);
 
 // ---- decode.cu ----

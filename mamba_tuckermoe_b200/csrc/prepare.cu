@@ -44,14 +44,17 @@ PreparedLayout prepared_layout(const tmoe_layer_t &L) {
   return P;
 }
 
+// `kscale` (optional, [K]): a weight per contraction index folded into the copy -- the callers' pre-norm weight,
+// so that RMSNorm(x) @ W becomes (x @ (diag(w_pre) W)) / rms(x) and only the per-row 1/rms is left for the kernel.
 template <typename T>
-__global__ void transpose_to_bf16_kernel(const T *__restrict__ src, bf16 *__restrict__ dst, int K, int N) {
+__global__ void transpose_to_bf16_kernel(const T *__restrict__ src, bf16 *__restrict__ dst, int K, int N,
+                                         const T *__restrict__ kscale) {
   // src [K, N] -> dst [N, K]; 32x32 tiles through shared memory
   __shared__ float tile[32][33];
   const int k0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
   for (int i = threadIdx.y; i < 32; i += blockDim.y) {
     int k = k0 + i, n = n0 + threadIdx.x;
-    tile[i][threadIdx.x] = (k < K && n < N) ? to_f32(src[(int64_t)k * N + n]) : 0.f;
+    tile[i][threadIdx.x] = (k < K && n < N) ? to_f32(src[(int64_t)k * N + n]) * (kscale ? to_f32(kscale[k]) : 1.f) : 0.f;
   }
   __syncthreads();
   for (int i = threadIdx.y; i < 32; i += blockDim.y) {
@@ -61,12 +64,14 @@ __global__ void transpose_to_bf16_kernel(const T *__restrict__ src, bf16 *__rest
 }
 
 template <typename T>
-__global__ void router_rows_kernel(const T *__restrict__ wr, bf16 *__restrict__ dst, int E, int e_pad, int d_in) {
+__global__ void router_rows_kernel(const T *__restrict__ wr, bf16 *__restrict__ dst, int E, int e_pad, int d_in,
+                                   const T *__restrict__ kscale) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   int64_t total = (int64_t)e_pad * d_in;
   if (i >= total) return;
   int e = (int)(i / d_in);
-  dst[i] = (e < E) ? __float2bfloat16_rn(to_f32(wr[i])) : __float2bfloat16_rn(0.f);
+  const float sc = kscale ? to_f32(kscale[i - (int64_t)e * d_in]) : 1.f;
+  dst[i] = (e < E) ? __float2bfloat16_rn(to_f32(wr[i]) * sc) : __float2bfloat16_rn(0.f);
 }
 
 template <typename T>
@@ -93,18 +98,18 @@ __global__ void to_f32_kernel(const T *__restrict__ src, float *__restrict__ dst
 }
 
 template <typename T>
-static int prepare_t(const tmoe_layer_t &L, const tmoe_factors_t &F, void *prepared, cudaStream_t st) {
+static int prepare_t(const tmoe_layer_t &L, const tmoe_factors_t &F, const void *pre_w, void *prepared, cudaStream_t st) {
   PreparedLayout P = prepared_layout(L);
   char *base = reinterpret_cast<char *>(prepared);
   dim3 tb(32, 8);
   transpose_to_bf16_kernel<T><<<dim3((L.r3 + 31) / 32, (L.d_in + 31) / 32), tb, 0, st>>>(
-      (const T *)F.U_in, (bf16 *)(base + P.uin_t), L.d_in, L.r3);
+      (const T *)F.U_in, (bf16 *)(base + P.uin_t), L.d_in, L.r3, (const T *)pre_w);
   transpose_to_bf16_kernel<T><<<dim3((L.d_out + 31) / 32, (L.r2 + 31) / 32), tb, 0, st>>>(
-      (const T *)F.U_out, (bf16 *)(base + P.uout_t), L.r2, L.d_out);
+      (const T *)F.U_out, (bf16 *)(base + P.uout_t), L.r2, L.d_out, (const T *)nullptr);
   {
     int64_t n = (int64_t)P.e_pad * L.d_in;
     router_rows_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, st>>>((const T *)F.router_w, (bf16 *)(base + P.wr_b),
-                                                                      L.n_experts, P.e_pad, L.d_in);
+                                                                      L.n_experts, P.e_pad, L.d_in, (const T *)pre_w);
   }
   {
     int64_t n = (int64_t)L.r1 * L.r2 * L.r3;
@@ -121,8 +126,8 @@ static int prepare_t(const tmoe_layer_t &L, const tmoe_factors_t &F, void *prepa
   return launch_status();
 }
 
-int launch_prepare(const tmoe_layer_t &L, const tmoe_factors_t &F, void *prepared, cudaStream_t st) {
-  return L.dtype == TMOE_F32 ? prepare_t<float>(L, F, prepared, st) : prepare_t<bf16>(L, F, prepared, st);
+int launch_prepare(const tmoe_layer_t &L, const tmoe_factors_t &F, const void *pre_norm_w, void *prepared, cudaStream_t st) {
+  return L.dtype == TMOE_F32 ? prepare_t<float>(L, F, pre_norm_w, prepared, st) : prepare_t<bf16>(L, F, pre_norm_w, prepared, st);
 }
 
 }  // namespace tmoe

@@ -61,6 +61,8 @@ struct InCoreParams {
   int d_in, r3, r2, E, e_pad, top_k, n_tiles2;
   float eps;
   int fuse_router;
+  int pre_norm;        // 1: apply the callers' RMSNorm to x in-kernel (its weight is folded into the prepared U_in / router rows)
+  float pre_norm_eps;
   RouterCfg rc;  // gate rule (tmoe_layer_t::router_mode)
   const float *normw;  // [r3]
   const float *uexp;   // [E, r1] fp32
@@ -104,7 +106,9 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
 
   for (int i = threadIdx.x; i < p.r3; i += blockDim.x) wnorm_s[i] = __float2bfloat16_rn(p.normw[i]);
   if (threadIdx.x == 0) {
-    for (int s = 0; s < A_STAGES_MAX; ++s) { mbar_init(smem_u32(&bar_fullA[s]), 1); mbar_init(smem_u32(&bar_emptyA[s]), 1); }
+    // a phase-A stage is free once its MMAs have retired and, with the in-kernel pre-norm, the four secondary
+    // warps have read its x tile for the row statistics
+    for (int s = 0; s < A_STAGES_MAX; ++s) { mbar_init(smem_u32(&bar_fullA[s]), 1); mbar_init(smem_u32(&bar_emptyA[s]), p.pre_norm ? 5 : 1); }
     for (int s = 0; s < G_STAGES_MAX; ++s) { mbar_init(smem_u32(&bar_fullB[s]), 1); mbar_init(smem_u32(&bar_emptyB[s]), 1); }
     mbar_init(smem_u32(&bar_accA), 1);
     mbar_init(smem_u32(&bar_hready), IC_EPI_WARPS);
@@ -230,11 +234,48 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
     const bool live = grow < p.T;
     const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
     float c[R1];
-    bool ok = mbar_wait(smem_u32(&bar_accA), 0, p.status, kKernelInCore, 3);
+    bool ok = true;
+    float inv_x = 1.f;  // 1 / rms(x row) when the callers' pre-norm is applied here
+    if (p.pre_norm && grp == 1) {
+      // The secondary warps are idle during phase A: they follow the x tiles through the ring and accumulate
+      // each row's sum of squares (the swizzle permutes 16-byte chunks inside a row, which a sum does not see).
+      float ssx = 0.f;
+      uint32_t sA = 0, phA = 0;
+      for (int kb = 0; kb < KA && ok; ++kb) {
+        const uint32_t s = sA, ph = phA;
+        if (++sA == (uint32_t)nA) { sA = 0; phA ^= 1; }
+        ok = mbar_wait(smem_u32(&bar_fullA[s]), ph, p.status, kKernelInCore, 9);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const uint32_t xrow = ring + s * stageA_bytes + row * 128;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          uint32_t w0, w1, w2, w3;
+          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3)
+                       : "r"(xrow + (uint32_t)((i ^ (row & 7)) * 16)));
+          const uint32_t w[4] = {w0, w1, w2, w3};
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float lo = __uint_as_float(w[q] << 16), hi = __uint_as_float(w[q] & 0xffff0000u);
+            ssx = fmaf(lo, lo, ssx);
+            ssx = fmaf(hi, hi, ssx);
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_emptyA[s]));
+      }
+      inv_x = 1.f / sqrtf(ssx / (float)p.d_in + p.pre_norm_eps);
+    }
+    if (ok) ok = mbar_wait(smem_u32(&bar_accA), 0, p.status, kKernelInCore, 3);
     ok = named_bar_and(2, 256, ok);  // the eight epilogue warps continue or leave together
     if (ok) {
       tc_fence_after();
       if (threadIdx.x == 64) TMOE_STAMP(2);  // phase A complete (accumulators readable)
+      if (p.pre_norm) {  // hand 1/rms(x) from the secondary warp of each row to its primary twin (through the workspace)
+        if (grp == 1 && live) p.c_work[grow * R1] = inv_x;
+        named_bar_sync(5, 256);
+        if (grp == 0) inv_x = live ? p.c_work[grow * R1] : 1.f;
+      }
       if (grp == 0) {
         if (p.fuse_router) {
           // Running top-k over the score columns, branch-free.  A score rounded to bf16 has 16 significant
@@ -252,7 +293,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
 #pragma unroll
             for (int q = 0; q < 16; ++q) {
               const int e = cc * 16 + q;
-              uint32_t b = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(__uint_as_float(r[q])));
+              uint32_t b = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(__uint_as_float(r[q]) * inv_x));
               b = (b == 0x8000u) ? 0u : b;                                   // -0 and +0 compare equal
               const uint32_t u = (b & 0x8000u) ? (~b & 0xffffu) : (b | 0x8000u);
               uint32_t carry = (e < p.E) ? ((u << 16) | (0xffffu - (uint32_t)e)) : 0u;
@@ -285,7 +326,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
               tmem_ld_wait(r);
 #pragma unroll
               for (int q = 0; q < 16; ++q) {
-                const float sc = round_to<bf16>(__uint_as_float(r[q]));
+                const float sc = round_to<bf16>(__uint_as_float(r[q]) * inv_x);
                 if (cc * 16 + q < p.E) z_all += expf(p.rc.logit(sc) - l0);
               }
             }
@@ -349,7 +390,8 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                          : "memory");
           }
         }
-        inv_rms_s[row] = 1.f / sqrtf(ss / (float)p.r3 + p.eps);
+        // h = inv_x * h_raw: RMSNorm(h) = h_raw * inv_x / sqrt(inv_x^2 * mean(h_raw^2) + eps)
+        inv_rms_s[row] = inv_x / sqrtf(inv_x * inv_x * ss / (float)p.r3 + p.eps);
         fence_proxy_async_smem();
         tc_fence_before();
         named_bar_sync(3, 256);
@@ -432,7 +474,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
 }
 
 int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared, const PreparedLayout &P, int64_t T_,
-                      int fuse_router, const float *c_in, float *c_work, int32_t *idx_out, float *gates_out, float *c_out,
+                      int pre_norm, float pre_norm_eps, int fuse_router, const float *c_in, float *c_work, int32_t *idx_out, float *gates_out, float *c_out,
                       void *z, int32_t *status, cudaStream_t st) {
   const char *base = reinterpret_cast<const char *>(prepared);
   if (fuse_router && (P.e_pad > 256 || L.top_k > 8 || L.r3 > 256)) return TMOE_ERR_UNSUPPORTED;
@@ -454,6 +496,8 @@ int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared
   p.T = T_; p.d_in = L.d_in; p.r3 = L.r3; p.r2 = L.r2; p.E = L.n_experts; p.top_k = L.top_k;
   p.e_pad = fuse_router ? P.e_pad : 0;
   p.n_tiles2 = P.n_tiles2; p.eps = L.eps; p.fuse_router = fuse_router; p.rc = router_cfg(L);
+  p.pre_norm = pre_norm; p.pre_norm_eps = pre_norm_eps;
+  if (pre_norm && !fuse_router) return TMOE_ERR_UNSUPPORTED;
   p.normw = reinterpret_cast<const float *>(base + P.normw);
   p.uexp = reinterpret_cast<const float *>(base + P.uexp);
   p.c_in = c_in; p.c_work = c_work; p.idx_out = idx_out; p.gates_out = gates_out; p.c_out = c_out;

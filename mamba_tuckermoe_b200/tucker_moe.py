@@ -85,9 +85,12 @@ def clear_caches() -> None:
         _workspaces.clear()
 
 
-def prepare_factors(router_w, U_in, inner_norm_w, eps, U_expert, core, U_out, bias, top_k) -> Optional[torch.Tensor]:
+def prepare_factors(router_w, U_in, inner_norm_w, eps, U_expert, core, U_out, bias, top_k,
+                    pre_norm_weight: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
     """Re-laid-out factor set for the tensor-core path (``tmoe_prepare_factors``), or None when
-    that path does not cover the layer.  Valid until any of the seven tensors changes."""
+    that path does not cover the layer.  Valid until any of the seven tensors changes.
+    With ``pre_norm_weight`` ([d_in]) the callers' RMSNorm weight is folded into the U_in / router copies
+    (``tmoe_prepare_factors_prenorm``); such a set is only for forwards that apply the pre-norm in-kernel."""
     params = tuple(p if p.is_contiguous() else p.contiguous()
                    for p in (router_w, U_in, inner_norm_w, U_expert, core, U_out, bias))
     if not params[0].is_cuda or params[0].dtype not in _DTYPES:
@@ -101,8 +104,16 @@ def prepare_factors(router_w, U_in, inner_norm_w, eps, U_expert, core, U_out, bi
     with torch.cuda.device(dev):
         prep = torch.empty(nbytes, dtype=torch.uint8, device=dev)
         factors = Factors(*[p.data_ptr() for p in params])
-        _lib.check(lib.tmoe_prepare_factors(C.byref(layer), C.byref(factors), prep.data_ptr(), nbytes,
-                                            torch.cuda.current_stream(dev).cuda_stream), "tmoe_prepare_factors")
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        if pre_norm_weight is None:
+            _lib.check(lib.tmoe_prepare_factors(C.byref(layer), C.byref(factors), prep.data_ptr(), nbytes, stream),
+                       "tmoe_prepare_factors")
+        else:
+            w = pre_norm_weight.contiguous()
+            if w.dtype != params[0].dtype or w.device != dev or w.shape != (params[1].shape[0],):
+                raise RuntimeError("tmoe_b200: pre-norm weight must be (d_in,) in the layer's dtype on its device")
+            _lib.check(lib.tmoe_prepare_factors_prenorm(C.byref(layer), C.byref(factors), w.data_ptr(), prep.data_ptr(),
+                                                        nbytes, stream), "tmoe_prepare_factors_prenorm")
     return prep
 
 
@@ -134,7 +145,8 @@ def _validate(x, params, top_k):
 
 
 def _run(x, router_w, U_in, inner_norm_w, eps, U_expert, core, U_out, bias, top_k, path,
-         residual=None, layer_scale=None, want_taps=False, prepared=None, silu_gate=None, router=_DEFAULT_ROUTER):
+         residual=None, layer_scale=None, want_taps=False, prepared=None, silu_gate=None, router=_DEFAULT_ROUTER,
+         pre_norm_eps=None):
     params = (router_w, U_in, inner_norm_w, U_expert, core, U_out, bias)
     _validate(x, params, top_k)
     lib = _lib.load()
@@ -183,6 +195,8 @@ def _run(x, router_w, U_in, inner_norm_w, eps, U_expert, core, U_out, bias, top_
                 raise RuntimeError("tmoe_b200: silu_gate must be (..., d_out) in x's dtype on x's device")
             extras.silu_gate = g2.data_ptr()
             keep.append(g2)
+        if pre_norm_eps is not None:  # `prepared` carries the folded norm weight (prepare_factors(pre_norm_weight=...))
+            extras.pre_norm, extras.pre_norm_eps = 1, float(pre_norm_eps)
         if want_taps:
             taps = (torch.empty((T, top_k), dtype=torch.int32, device=dev),
                     torch.empty((T, top_k), dtype=torch.float32, device=dev),
@@ -318,6 +332,8 @@ class TuckerMoE(nn.Module):
         self.router_temperature = float(getattr(cfg, "kmoe_router_temperature", 0.5))
         self._prep_key = None
         self._prep = None
+        self._prep_pn_key = None
+        self._prep_pn = None
         self._plan = None
 
     def _prepared_for(self, x: torch.Tensor) -> Optional[torch.Tensor]:
@@ -333,6 +349,24 @@ class TuckerMoE(nn.Module):
             self._prep = prepare_factors(ps[0], ps[1], ps[2], self.inner_norm.eps, ps[3], ps[4], ps[5], ps[6], self.top_k)
             self._prep_key = key
         return self._prep
+
+    def _prepared_prenorm_for(self, x: torch.Tensor, norm_weight: torch.Tensor) -> Optional[torch.Tensor]:
+        """Prepared factors with `norm_weight` folded in, when this call can run the pre-norm inside the tensor-core
+        kernels (bf16, more than 64 tokens, in-kernel router: E <= 256, top_k <= 8, r3 <= 256); else None."""
+        if not x.is_cuda or x.dtype != torch.bfloat16 or self.path not in (PATH_AUTO, PATH_TENSOR):
+            return None
+        T = x.numel() // max(x.shape[-1], 1)
+        r1, r3, _ = self.core.shape
+        E = self.router.weight.shape[0]
+        if T <= 64 or r3 > 256 or (E + 15) // 16 * 16 > 256 or self.top_k > 8:
+            return None
+        ps = self._params()
+        key = _param_key(ps) + _param_key((norm_weight,))
+        if key != self._prep_pn_key:
+            self._prep_pn = prepare_factors(ps[0], ps[1], ps[2], self.inner_norm.eps, ps[3], ps[4], ps[5], ps[6], self.top_k,
+                                            pre_norm_weight=norm_weight)
+            self._prep_pn_key = key
+        return self._prep_pn
 
     def _params(self):
         return (self.router.weight, self.U_in, self.inner_norm.weight, self.U_expert, self.core, self.U_out, self.bias)
@@ -414,10 +448,17 @@ class TuckerMoE(nn.Module):
         ``silu_gate`` ``silu(silu_gate) * layer(...)`` in the out-projection's epilogue (``model.py:340``);
         ``residual``, ``layer_scale``  ``residual + layer_scale * (...)`` in the same epilogue (``model.py:260, 341``).
         """
+        rw, ui, nw, ue, co, uo, b = self._params()
         if pre_norm is not None:
             w, e = (pre_norm.weight, pre_norm.eps) if hasattr(pre_norm, "weight") else pre_norm
+            prep_pn = self._prepared_prenorm_for(x, w)
+            if prep_pn is not None:
+                # norm weight folded into the prepared factors, 1/rms(x) found inside the in-projection kernel
+                y, _ = _run(x, rw, ui, nw, self.inner_norm.eps, ue, co, uo, b, self.top_k, PATH_TENSOR, residual,
+                            layer_scale, prepared=prep_pn, silu_gate=silu_gate, router=self._router(),
+                            pre_norm_eps=float(e))
+                return y
             x = rms_norm(x, w, e)
-        rw, ui, nw, ue, co, uo, b = self._params()
         return tucker_moe_forward(x, rw, ui, nw, self.inner_norm.eps, ue, co, uo, b, self.top_k, path=self.path,
                                   residual=residual, layer_scale=layer_scale, silu_gate=silu_gate,
                                   prepared=self._prepared_for(x), router=self._router())
@@ -493,6 +534,7 @@ class TuckerMoE(nn.Module):
         """Call after writing parameters through ``.data`` once the layer has already run
         (such writes do not change tensor versions, which key the prepared-factor cache)."""
         self._prep_key, self._prep, self._plan = None, None, None
+        self._prep_pn_key, self._prep_pn = None, None
 
 
 def fused_out_proj(out_proj: TuckerMoE, mid: torch.Tensor, norm, layer_scale: torch.Tensor) -> torch.Tensor:

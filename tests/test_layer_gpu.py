@@ -338,3 +338,54 @@ def test_capped_softmax_router_rule(dtype, path, T):
     # rule 0 on the same module gives a different answer
     m.router_mode = 0
     assert rel_fro(m(x.cuda()).float().cpu(), y64) > 3 * tol
+
+
+@pytest.mark.parametrize("T", [65, 700])
+def test_in_kernel_pre_norm_matches_separate_norm(T):
+    """forward_fused(pre_norm=...) on the tensor-core path folds the norm weight into the prepared factors and finds
+    1/rms(x) in-kernel; it must agree with RMSNorm-then-layer (model.py:258-259, 337-339) in float64 and with the
+    two-kernel composition of this library."""
+    from oracle.tucker_moe_oracle import rms_norm as ref_norm
+    shape = LayerShape(1536, 2304, 64, 2, 4, 256, 1024, 1e-6)
+    x, f = _tensor_case(shape, T, seed=31, router_std=None)
+    x = (x.float() * 2.5 + 0.3).bfloat16()                       # rms(x) clearly different from 1
+    g = torch.Generator().manual_seed(2)
+    nw = (1 + 0.3 * torch.randn(shape.d_in, generator=g)).bfloat16()
+    m = build_module(shape, f, torch.bfloat16)
+    y_fused, = (m.forward_fused(x.cuda(), pre_norm=(nw.cuda(), 1e-5)),)
+    torch.cuda.synchronize()
+    assert read_device_status() == (0, 0, 0, 0)
+    assert m._prep_pn is not None                                  # the in-kernel route was taken
+    from mamba_tuckermoe_b200 import rms_norm
+    y_two = m(rms_norm(x.cuda(), nw.cuda(), 1e-5))
+    xn64 = ref_norm(x.double(), nw.double(), 1e-5)
+    y64, _ = layer_forward_f64(xn64, f, shape.top_k, shape.eps, round_scores_to=torch.bfloat16)
+    err = (y_fused.float().cpu().double() - y64).norm(dim=-1) / y64.norm(dim=-1)
+    assert float((err < 2e-2).float().mean()) >= 0.95              # a few tokens flip a near-tie of bf16 scores
+    good = err < 2e-2
+    assert rel_fro(y_fused.float().cpu()[good], y64[good]) < 1e-2
+    err2 = (y_fused.float() - y_two.float()).norm(dim=-1) / y_two.float().norm(dim=-1)
+    assert float((err2 < 2e-2).float().mean()) >= 0.95
+    # residual + silu epilogues ride along unchanged
+    res = torch.randn(T, shape.d_out, generator=g).bfloat16().cuda()
+    gam = torch.ones(shape.d_out).bfloat16().cuda()
+    y_r = m.forward_fused(x.cuda(), pre_norm=(nw.cuda(), 1e-5), residual=res, layer_scale=gam)
+    assert rel_fro((y_r.float() - res.float()).cpu(), y_fused.float().cpu()) < 1e-2
+
+
+def test_prepared_sidecar_round_trip(tmp_path):
+    """The prepared-factor sidecar installs only on a layer whose parameters match its fingerprint."""
+    from mamba_tuckermoe_b200.checkpoint import load_prepared_sidecar, save_prepared_sidecar
+    shape = LayerShape(256, 264, 8, 2, 4, 128, 256, 1e-5)
+    x, f = _tensor_case(shape, 200, seed=3)
+    a = build_module(shape, f, torch.bfloat16)
+    y = a(x.cuda())
+    path = str(tmp_path / "layer0.prepared.npz")
+    save_prepared_sidecar(a, path)
+    b = build_module(shape, f, torch.bfloat16)
+    assert load_prepared_sidecar(b, path) and b._prep is not None
+    assert torch.equal(b(x.cuda()), y)
+    f2 = dict(f); f2["bias"] = (f["bias"].float() + 1).bfloat16()
+    c = build_module(shape, f2, torch.bfloat16)
+    assert not load_prepared_sidecar(c, path)          # different parameters: refused, layer untouched
+    assert c._prep is None
