@@ -29,13 +29,12 @@ int check_layer(const tmoe_layer_t *L) {
 // points cannot, so for them AUTO with T <= 64 means the CUDA-core path.
 int resolve(const tmoe_layer_t &L, int64_t T, int path, bool allow_decode = true) {
   if (path == TMOE_PATH_SIMT) return TMOE_PATH_SIMT;
-  const bool covered = tensor_path_covers(L);
-  if (path == TMOE_PATH_TENSOR) return covered ? (int)TMOE_PATH_TENSOR : (int)TMOE_ERR_UNSUPPORTED;
-  if (path == TMOE_PATH_DECODE) return (covered && T <= 64 && allow_decode) ? (int)TMOE_PATH_DECODE : (int)TMOE_ERR_UNSUPPORTED;
+  const bool tensor_ok = tensor_path_covers(L), decode_ok = prepared_covers(L) && allow_decode && T <= 64;
+  if (path == TMOE_PATH_TENSOR) return tensor_ok ? (int)TMOE_PATH_TENSOR : (int)TMOE_ERR_UNSUPPORTED;
+  if (path == TMOE_PATH_DECODE) return decode_ok ? (int)TMOE_PATH_DECODE : (int)TMOE_ERR_UNSUPPORTED;
   if (path != TMOE_PATH_AUTO) return TMOE_ERR_UNSUPPORTED;
-  if (!covered) return TMOE_PATH_SIMT;
-  if (T > 64) return TMOE_PATH_TENSOR;
-  return allow_decode ? TMOE_PATH_DECODE : TMOE_PATH_SIMT;
+  if (T > 64) return tensor_ok ? TMOE_PATH_TENSOR : TMOE_PATH_SIMT;
+  return decode_ok ? TMOE_PATH_DECODE : TMOE_PATH_SIMT;
 }
 
 WsLayout ws_layout(const tmoe_layer_t &L, int64_t T, int rpath) {
@@ -133,7 +132,7 @@ int tmoe_resolve_path(const tmoe_layer_t *layer, int64_t T, int path) {
 int64_t tmoe_prepared_bytes(const tmoe_layer_t *layer) {
   int rc = check_layer(layer);
   if (rc) return rc;
-  if (!tensor_path_covers(*layer)) return 0;
+  if (!prepared_covers(*layer)) return 0;
   return prepared_layout(*layer).total;
 }
 
@@ -143,7 +142,7 @@ int tmoe_prepare_factors(const tmoe_layer_t *layer, const tmoe_factors_t *factor
   if (rc) return rc;
   if ((rc = check_factors(factors))) return rc;
   if (!prepared) return TMOE_ERR_NULL;
-  if (!tensor_path_covers(*layer)) return TMOE_ERR_UNSUPPORTED;
+  if (!prepared_covers(*layer)) return TMOE_ERR_UNSUPPORTED;
   if (reinterpret_cast<uintptr_t>(prepared) & 255) return TMOE_ERR_ALIGN;
   if (prepared_bytes < prepared_layout(*layer).total) return TMOE_ERR_WORKSPACE;
   return launch_prepare(*layer, *factors, nullptr, prepared, (cudaStream_t)stream);
@@ -155,7 +154,7 @@ int tmoe_prepare_factors_prenorm(const tmoe_layer_t *layer, const tmoe_factors_t
   if (rc) return rc;
   if ((rc = check_factors(factors))) return rc;
   if (!prepared || !pre_norm_w) return TMOE_ERR_NULL;
-  if (!tensor_path_covers(*layer)) return TMOE_ERR_UNSUPPORTED;
+  if (!prepared_covers(*layer)) return TMOE_ERR_UNSUPPORTED;
   if ((reinterpret_cast<uintptr_t>(prepared) & 255) || misaligned(pre_norm_w)) return TMOE_ERR_ALIGN;
   if (prepared_bytes < prepared_layout(*layer).total) return TMOE_ERR_WORKSPACE;
   return launch_prepare(*layer, *factors, pre_norm_w, prepared, (cudaStream_t)stream);

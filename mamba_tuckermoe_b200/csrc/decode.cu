@@ -160,16 +160,21 @@ decode_core_kernel(const float *__restrict__ h_raw, const float *__restrict__ sc
     float acc[NB];
 #pragma unroll
     for (int t = 0; t < NB; ++t) acc[t] = 0.f;
+    constexpr int AC = R1 < 8 ? R1 : 8;  // core slices held in registers at a time
     for (int k = lane * 8; k < r3; k += 256) {
-      float g8[R1][8];
+#pragma unroll 1
+      for (int a0 = 0; a0 < R1; a0 += AC) {
+        float g8[AC][8];
 #pragma unroll
-      for (int a = 0; a < R1; ++a) unpack8(__ldg(reinterpret_cast<const uint4 *>(rows + (int64_t)a * N2 * r3 + k)), g8[a]);
+        for (int a = 0; a < AC; ++a)
+          unpack8(__ldg(reinterpret_cast<const uint4 *>(rows + (int64_t)(a0 + a) * N2 * r3 + k)), g8[a]);
 #pragma unroll
-      for (int t = 0; t < NB; ++t) {
-        float h8[8];
-        unpack8(*reinterpret_cast<const uint4 *>(&hw[(tb + t) * r3 + k]), h8);
+        for (int t = 0; t < NB; ++t) {
+          float h8[8];
+          unpack8(*reinterpret_cast<const uint4 *>(&hw[(tb + t) * r3 + k]), h8);
 #pragma unroll
-        for (int a = 0; a < R1; ++a) acc[t] = fmaf(cs[(tb + t) * R1 + a], dot8(h8, g8[a]), acc[t]);
+          for (int a = 0; a < AC; ++a) acc[t] = fmaf(cs[(tb + t) * R1 + a0 + a], dot8(h8, g8[a]), acc[t]);
+        }
       }
     }
     warp_reduce_many<NB>(acc, lane);
@@ -264,6 +269,8 @@ int launch_decode_t(const tmoe_layer_t &L, const void *x, const char *pb, const 
   if (L.r1 == 2) { if (k2) TMOE_DC(2, 2); else if (k8) TMOE_DC(2, 8); else TMOE_DC(2, 16); }
   else if (L.r1 == 4) { if (k2) TMOE_DC(4, 2); else if (k8) TMOE_DC(4, 8); else TMOE_DC(4, 16); }
   else if (L.r1 == 8) { if (k2) TMOE_DC(8, 2); else if (k8) TMOE_DC(8, 8); else TMOE_DC(8, 16); }
+  else if (L.r1 == 16) { if (k2) TMOE_DC(16, 2); else if (k8) TMOE_DC(16, 8); else TMOE_DC(16, 16); }
+  else if (L.r1 == 32) { if (k2) TMOE_DC(32, 2); else if (k8) TMOE_DC(32, 8); else TMOE_DC(32, 16); }
   else return TMOE_ERR_UNSUPPORTED;
 #undef TMOE_DC
   if (e != cudaSuccess) return TMOE_ERR_CUDA;

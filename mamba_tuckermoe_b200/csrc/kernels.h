@@ -46,7 +46,8 @@ struct PreparedLayout {
   int64_t uin_t, wr_b, g_t, uout_t, normw, bias, uexp, total;  // byte offsets
   int e_pad, n2, n_tiles2;
 };
-bool tensor_path_covers(const tmoe_layer_t &L);
+bool prepared_covers(const tmoe_layer_t &L);     // prepared layout + decode kernels (r1 in {2,...,32})
+bool tensor_path_covers(const tmoe_layer_t &L);  // tcgen05 kernels (r1 <= 16)
 PreparedLayout prepared_layout(const tmoe_layer_t &L);
 // pre_norm_w (optional, [d_in], layer dtype): folded into the U_in and router copies (see prepare.cu)
 int launch_prepare(const tmoe_layer_t &L, const tmoe_factors_t &F, const void *pre_norm_w, void *prepared, cudaStream_t st);

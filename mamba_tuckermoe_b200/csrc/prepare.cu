@@ -16,15 +16,20 @@
 
 namespace tmoe {
 
-bool tensor_path_covers(const tmoe_layer_t &L) {
+// Shapes the prepared (K-major bf16) factor layout and the decode kernels handle.
+bool prepared_covers(const tmoe_layer_t &L) {
   if (L.dtype != TMOE_BF16) return false;
-  if (!(L.r1 == 2 || L.r1 == 4 || L.r1 == 8)) return false;
+  if (!(L.r1 == 2 || L.r1 == 4 || L.r1 == 8 || L.r1 == 16 || L.r1 == 32)) return false;
   if (L.r3 % 64 != 0 || L.r3 > 512 || (L.r3 > 256 && L.r3 % 256 != 0)) return false;
   if (L.d_in % 64 != 0 || L.r2 % 64 != 0) return false;
   if (L.r2 % (256 / L.r1) != 0) return false;
   if (L.d_out % 8 != 0) return false;
   return true;
 }
+
+// Shapes the tcgen05 kernels handle: the epilogue reads the r1 slices of a tile in 16-column groups, so a
+// slice needs at least 16 columns of the 256-column accumulator (r1 <= 16).
+bool tensor_path_covers(const tmoe_layer_t &L) { return prepared_covers(L) && L.r1 <= 16; }
 
 PreparedLayout prepared_layout(const tmoe_layer_t &L) {
   PreparedLayout P{};

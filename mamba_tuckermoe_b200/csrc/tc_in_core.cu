@@ -515,6 +515,7 @@ int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared
   if (L.r1 == 2) { if (small_k) TMOE_IC(2, 2); else TMOE_IC(2, 8); }
   else if (L.r1 == 4) { if (small_k) TMOE_IC(4, 2); else TMOE_IC(4, 8); }
   else if (L.r1 == 8) { if (small_k) TMOE_IC(8, 2); else TMOE_IC(8, 8); }
+  else if (L.r1 == 16) { if (small_k) TMOE_IC(16, 2); else TMOE_IC(16, 8); }
   else return TMOE_ERR_UNSUPPORTED;
 #undef TMOE_IC
   if (e != cudaSuccess) return TMOE_ERR_CUDA;

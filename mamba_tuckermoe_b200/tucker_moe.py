@@ -358,7 +358,7 @@ class TuckerMoE(nn.Module):
         T = x.numel() // max(x.shape[-1], 1)
         r1, r3, _ = self.core.shape
         E = self.router.weight.shape[0]
-        if T <= 64 or r3 > 256 or (E + 15) // 16 * 16 > 256 or self.top_k > 8:
+        if T <= 64 or r3 > 256 or r1 > 16 or (E + 15) // 16 * 16 > 256 or self.top_k > 8:
             return None
         ps = self._params()
         key = _param_key(ps) + _param_key((norm_weight,))

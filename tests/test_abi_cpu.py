@@ -86,6 +86,8 @@ def test_path_resolution_and_sizes():
     shipped = _layer(d_in=768, d_out=768, r1=32, r2=512, r3=256, dtype=_lib.TMOE_BF16)
     assert lib.tmoe_resolve_path(C.byref(shipped), 4096, 0) == 1      # r1=32 is served by the CUDA-core path
     assert lib.tmoe_resolve_path(C.byref(shipped), 4096, 2) == -6
+    assert lib.tmoe_resolve_path(C.byref(shipped), 1, 0) == 3          # ... and by the decode kernels for T <= 64
+    assert lib.tmoe_prepared_bytes(C.byref(shipped)) > 0
 
 
 def test_module_mirrors_reference_interface():

@@ -92,6 +92,7 @@ TENSOR_SHAPES = [
     (LayerShape(256, 128, 512, 8, 4, 64, 128, 1e-6), 200),   # E > 256: scores by the GEMM kernel + select kernel
     (LayerShape(512, 384, 256, 8, 8, 512, 256, 1e-6), 200),  # r3 = 512: h fills all of TMEM, scores by a separate GEMM
     (LayerShape(3072, 4608, 256, 8, 8, 512, 2048, 1e-6), 130),  # the large skewed configuration's shapes
+    (LayerShape(768, 1536, 8, 2, 16, 256, 512, 1e-5), 300),     # r1 = 16: sixteen 16-column slices per accumulator
 ]
 
 
@@ -119,6 +120,9 @@ DECODE_SHAPES = [
     (LayerShape(256, 264, 24, 12, 2, 128, 256, 1e-5), 9),
     (LayerShape(3072, 4608, 256, 8, 8, 256, 2048, 1e-6), 17),   # r2 > one staged chunk of z
     (LayerShape(3072, 4608, 256, 8, 8, 512, 2048, 1e-6), 9),    # r3 = 512
+    (LayerShape(768, 768, 8, 2, 32, 256, 512, 1e-5), 1),        # the shipped model configuration (r1 = 32), one token
+    (LayerShape(768, 4608, 8, 2, 32, 256, 512, 1e-5), 7),
+    (LayerShape(4608, 768, 8, 2, 16, 256, 512, 1e-5), 33),
 ]
 
 
