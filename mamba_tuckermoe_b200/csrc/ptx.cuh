@@ -65,6 +65,37 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int32_t
   return mbar_wait_slow(bar, parity, status, kernel_id, tag);
 }
 
+// Wait for the thread that issues the MMAs.  That thread is the serial path of a tensor-core kernel: it spends
+// ~50 cycles per tcgen05.mma, ~100 per tcgen05.commit and ~55 per satisfied wait, against 128 cycles of tensor-pipe
+// time per 128x256x16 MMA, and a loop with a side exit (a `break` on a failed wait) was measured ~100 cycles per
+// k-block slower than one without.  So this wait has no failure return: when the limit expires (or another waiter of
+// the launch has reported) it records the failure and retires the calling THREAD.  The other roles then find the
+// status word set at their own waits and leave; __syncthreads counts only threads that have not exited, and the TMEM
+// columns are released by a warp that never exits early.
+static __device__ __noinline__ void mbar_wait_slow_or_exit(uint32_t bar, uint32_t parity, int32_t *status, int kernel_id, int tag) {
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  for (;;) {
+    if (mbar_try_wait(bar, parity)) return;
+    if ((++spins & 0xffu) == 0) {
+      if (*reinterpret_cast<volatile int32_t *>(status) != 0) break;
+      if (clock64() - t0 > kWaitLimitCycles) {
+        if (atomicCAS(status, 0, (int32_t)TMOE_ERR_DEVICE_WAIT) == 0) {
+          status[1] = kernel_id;
+          status[2] = tag;
+          status[3] = (int32_t)blockIdx.x;
+          __threadfence();
+        }
+        break;
+      }
+    }
+  }
+  asm volatile("exit;");
+}
+__device__ __forceinline__ void mbar_wait_or_exit(uint32_t bar, uint32_t parity, int32_t *status, int kernel_id, int tag) {
+  if (!mbar_try_wait(bar, parity)) mbar_wait_slow_or_exit(bar, parity, status, kernel_id, tag);
+}
+
 // ---------------- fences ----------------
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }

@@ -75,6 +75,32 @@ struct InCoreParams {
   int32_t *status;
 };
 
+// Phase-A issue loop of the MMA thread.  TWO_BOX: r3 = 512, h takes two 256-column MMAs per k step (the second piece of
+// U_in^T starts 256 rows = 32 KB further).  SCORES: the router tile follows U_in^T in the stage and a third, N = e_pad MMA
+// accumulates the scores at TMEM column SCORE_COL.
+template <bool TWO_BOX, bool SCORES>
+__device__ __forceinline__ void issue_phase_a(uint32_t tmem_base, uint64_t desc0, uint32_t stage16, uint32_t u16, int KA, int nA,
+                                              int u_box_rows, int e_pad, uint64_t *bar_full, uint64_t *bar_empty, int32_t *status) {
+  const uint32_t idescH = umma_idesc_bf16(TM, u_box_rows);
+  const uint32_t idescS = umma_idesc_bf16(TM, e_pad);
+  constexpr uint32_t xtile16 = X_TILE_BYTES >> 4;
+  uint32_t sA = 0, phA = 0;
+  for (int kb = 0; kb < KA; ++kb) {
+    mbar_wait_or_exit(smem_u32(&bar_full[sA]), phA, status, kKernelInCore, 1);
+    const uint64_t dx = desc0 + sA * stage16, du = dx + xtile16, dw = du + u16;
+    const uint32_t acc0 = kb != 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const uint32_t acc = acc0 | (uint32_t)(k != 0);
+      umma_bf16(tmem_base, dx + 2 * k, du + 2 * k, idescH, acc);
+      if (TWO_BOX) umma_bf16(tmem_base + 256, dx + 2 * k, du + 2048 + 2 * k, idescH, acc);
+      if (SCORES) umma_bf16(tmem_base + SCORE_COL, dx + 2 * k, dw + 2 * k, idescS, acc);
+    }
+    umma_commit(smem_u32(&bar_empty[sA]));
+    if (++sA == (uint32_t)nA) { sA = 0; phA ^= 1; }
+  }
+}
+
 // R1: Tucker rank r1 (core slices per r2 tile); RK: capacity of the in-kernel top-k list (>= top_k)
 template <int R1, int RK>
 __global__ void __launch_bounds__(IC_THREADS, 1)
@@ -117,7 +143,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
     prefetch_tmap(&tmX); prefetch_tmap(&tmU); prefetch_tmap(&tmG);
     if (p.e_pad) prefetch_tmap(&tmW);
   }
-  if (warp == 1) { tmem_alloc(smem_u32(&tmem_base_s), 512); tmem_relinquish(); }
+  if (warp == 2) { tmem_alloc(smem_u32(&tmem_base_s), 512); tmem_relinquish(); }  // an epilogue warp: its lanes never retire early
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -165,57 +191,44 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -------------------------------
     if (lane == 0) {
-      bool ok = true;
-      uint32_t sA = 0, phA = 0, sB = 0, phB = 0;
-      const uint32_t idescH = umma_idesc_bf16(TM, u_box_rows);
-      const uint32_t idescS = umma_idesc_bf16(TM, p.e_pad ? p.e_pad : 16);
-      // This thread is the serial path of the kernel: the tensor pipe idles whenever it is not ahead, so the
-      // loop bodies below are kept to a barrier wait, a few adds on precomputed descriptors, the MMAs and a
-      // commit.  (No tcgen05 fence after a "tiles landed" wait: the mbarrier completion orders the TMA writes
-      // before the MMA reads; the fence is only needed where another thread's tcgen05.ld preceded, i.e. after
-      // the accumulator / h hand-offs.)
+      // This thread is the serial path of the kernel (see mbar_wait_or_exit): the loops below have fixed trip
+      // counts and no side exits, ring positions and descriptors are kept incrementally, and the shape variants of
+      // phase A are separate loops so that no MMA sits behind a run-time condition (each of those was measured in a
+      // replica of this loop: a conditional MMA costs ~43 cycles even when skipped, a `break` ~100 per k block).
+      // No tcgen05 fence after a "tiles landed" wait: the mbarrier completion orders the TMA writes before the MMA
+      // reads; the fence is only needed where another thread's tcgen05.ld preceded (accumulator / h hand-offs).
       const uint64_t desc0 = umma_desc_k_sw128(ring);          // descriptor of the ring base; tiles add (bytes >> 4)
-      const uint32_t stageA16 = (uint32_t)stageA_bytes >> 4, xtile16 = X_TILE_BYTES >> 4, u16 = (uint32_t)u_bytes >> 4;
-      for (int kb = 0; kb < KA && ok; ++kb) {
-        const uint32_t s = sA, ph = phA;
-        if (++sA == (uint32_t)nA) { sA = 0; phA ^= 1; }
-        if (!(ok = mbar_wait(smem_u32(&bar_fullA[s]), ph, p.status, kKernelInCore, 1))) break;
-        const uint64_t dx = desc0 + s * stageA16, du = dx + xtile16, dw = du + u16;
-        const uint32_t acc0 = kb != 0;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const uint32_t acc = acc0 | (uint32_t)(k != 0);
-          // one MMA per <= 256 columns of h (two when r3 = 512: the second piece starts 256 rows = 32 KB further)
-          umma_bf16(tmem_base, dx + 2 * k, du + 2 * k, idescH, acc);
-          if (u_boxes == 2) umma_bf16(tmem_base + 256, dx + 2 * k, du + 2048 + 2 * k, idescH, acc);
-          if (p.e_pad) umma_bf16(tmem_base + SCORE_COL, dx + 2 * k, dw + 2 * k, idescS, acc);
-        }
-        umma_commit(smem_u32(&bar_emptyA[s]));
-      }
-      if (ok) umma_commit(smem_u32(&bar_accA));
+      const uint32_t stageA16 = (uint32_t)stageA_bytes >> 4;
+      if (p.e_pad)
+        issue_phase_a<false, true>(tmem_base, desc0, stageA16, (uint32_t)u_bytes >> 4, KA, nA, u_box_rows, p.e_pad, bar_fullA, bar_emptyA, p.status);
+      else if (u_boxes == 2)
+        issue_phase_a<true, false>(tmem_base, desc0, stageA16, (uint32_t)u_bytes >> 4, KA, nA, u_box_rows, 16, bar_fullA, bar_emptyA, p.status);
+      else
+        issue_phase_a<false, false>(tmem_base, desc0, stageA16, (uint32_t)u_bytes >> 4, KA, nA, u_box_rows, 16, bar_fullA, bar_emptyA, p.status);
+      umma_commit(smem_u32(&bar_accA));
       TMOE_STAMP(0);  // last phase-A MMA issued
-      if (ok) ok = mbar_wait(smem_u32(&bar_hready), 0, p.status, kKernelInCore, 4);
+      mbar_wait_or_exit(smem_u32(&bar_hready), 0, p.status, kKernelInCore, 4);
       tc_fence_after();
       TMOE_STAMP(1);  // MMA thread saw h ready
       const uint32_t idescP = umma_idesc_bf16(TM, 256);
       const uint64_t descB0 = desc0 + ((uint32_t)h_bytes >> 4);
-      for (int j = 0; j < p.n_tiles2 && ok; ++j) {
+      uint32_t sB = 0, phB = 0;
+      for (int j = 0; j < p.n_tiles2; ++j) {
         const uint32_t slot = j & 1, pph = (j >> 1) & 1;
-        if (!(ok = mbar_wait(smem_u32(&bar_pempty[slot]), pph ^ 1, p.status, kKernelInCore, 8))) break;
+        mbar_wait_or_exit(smem_u32(&bar_pempty[slot]), pph ^ 1, p.status, kKernelInCore, 8);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + slot * 256;
         for (int kb = 0; kb < KH; ++kb) {
-          const uint32_t s = sB, ph = phB;
-          if (++sB == (uint32_t)nG) { sB = 0; phB ^= 1; }
-          if (!(ok = mbar_wait(smem_u32(&bar_fullB[s]), ph, p.status, kKernelInCore, 5))) break;
+          mbar_wait_or_exit(smem_u32(&bar_fullB[sB]), phB, p.status, kKernelInCore, 5);
           const uint64_t dh = desc0 + kb * (H_KBLOCK_BYTES >> 4);
-          const uint64_t dg = descB0 + s * (G_STAGE_BYTES >> 4);
+          const uint64_t dg = descB0 + sB * (G_STAGE_BYTES >> 4);
           const uint32_t acc0 = kb != 0;
 #pragma unroll
           for (int k = 0; k < 4; ++k) umma_bf16(d_tmem, dh + 2 * k, dg + 2 * k, idescP, acc0 | (uint32_t)(k != 0));
-          umma_commit(smem_u32(&bar_emptyB[s]));
+          umma_commit(smem_u32(&bar_emptyB[sB]));
+          if (++sB == (uint32_t)nG) { sB = 0; phB ^= 1; }
         }
-        if (ok) umma_commit(smem_u32(&bar_pfull[slot]));
+        umma_commit(smem_u32(&bar_pfull[slot]));
       }
     }
   } else {
@@ -466,7 +479,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == 2) {
     __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);

@@ -111,7 +111,7 @@ tc_out_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
     prefetch_tmap(&tmB);
     prefetch_tmap(&tmY);
   }
-  if (warp == 1) { tmem_alloc(smem_u32(&tmem_base_s), 512); tmem_relinquish(); }
+  if (warp == 2) { tmem_alloc(smem_u32(&tmem_base_s), 512); tmem_relinquish(); }  // an epilogue warp: its lanes never retire early
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -145,30 +145,31 @@ tc_out_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
     }
   } else if (warp == 1) {
     if (lane == 0) {
+      // The issuing thread's loop is the serial path (see mbar_wait_or_exit): fixed trip counts, no side exits,
+      // ring position and descriptors kept incrementally.
       const uint32_t idesc = umma_idesc_bf16(OM, ON);
-      uint32_t it = 0, tcount = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+      const uint64_t desc0 = umma_desc_k_sw128(ring);
+      uint32_t s = 0, ph = 0, tcount = 0;
+      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcount) {
         const uint32_t slot = tcount & 1, aph = (tcount >> 1) & 1;
         TMOE_TIC();
-        if (!(ok = mbar_wait(smem_u32(&bar_tempty[slot]), aph ^ 1, p.status, kKernelOut, 4))) break;
+        mbar_wait_or_exit(smem_u32(&bar_tempty[slot]), aph ^ 1, p.status, kKernelOut, 4);
         TMOE_TOC(1);  // MMA thread waiting for the epilogue to release an accumulator
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + slot * ON;
-        for (int kb = 0; kb < KB; ++kb, ++it) {
-          const uint32_t s = it % OSTAGES, ph = (it / OSTAGES) & 1;
+        for (int kb = 0; kb < KB; ++kb) {
           TMOE_TIC();
-          if (!(ok = mbar_wait(smem_u32(&bar_full[s]), ph, p.status, kKernelOut, 1))) break;
+          mbar_wait_or_exit(smem_u32(&bar_full[s]), ph, p.status, kKernelOut, 1);
           TMOE_TOC(2);  // MMA thread waiting for operand tiles
-          tc_fence_after();
-          const uint32_t sa = ring + s * O_STAGE_BYTES;
-          const uint64_t da = umma_desc_k_sw128(sa), db = umma_desc_k_sw128(sa + O_A_BYTES);
+          const uint64_t da = desc0 + s * (uint32_t)(O_STAGE_BYTES >> 4), db = da + (O_A_BYTES >> 4);
+          const uint32_t acc0 = kb != 0;
 #pragma unroll
           for (int k = 0; k < OKB / 16; ++k)  // +32 bytes (= 2 in >>4 units) per 16-element K step
-            umma_bf16(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+            umma_bf16(d_tmem, da + 2 * k, db + 2 * k, idesc, acc0 | (uint32_t)(k != 0));
           umma_commit(smem_u32(&bar_empty[s]));
+          if (++s == OSTAGES) { s = 0; ph ^= 1; }
         }
-        if (ok) umma_commit(smem_u32(&bar_tfull[slot]));
+        umma_commit(smem_u32(&bar_tfull[slot]));
       }
     }
   } else {
@@ -268,7 +269,7 @@ tc_out_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
 #endif
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == 2) {
     __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
@@ -308,7 +309,7 @@ tc_out_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     prefetch_tmap(&tmB);
     prefetch_tmap(&tmY);
   }
-  if (warp == 1) { tmem_alloc_pair(smem_u32(&tmem_base_s), 512); tmem_relinquish_pair(); }
+  if (warp == 2) { tmem_alloc_pair(smem_u32(&tmem_base_s), 512); tmem_relinquish_pair(); }
   tc_fence_before();
   __syncthreads();
   cluster_arrive();   // both CTAs' barriers are initialised before anyone signals across the pair
@@ -346,28 +347,27 @@ tc_out_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   } else if (warp == 1) {
     if (lane == 0 && rank == 0) {
       const uint32_t idesc = umma_idesc_bf16(2 * OM, ON);
-      uint32_t it = 0, tcount = 0;
-      bool ok = true;
-      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++tcount) {
+      const uint64_t desc0 = umma_desc_k_sw128(ring);
+      uint32_t s = 0, ph = 0, tcount = 0;
+      for (int tile = pair_id; tile < num_tiles; tile += num_pairs, ++tcount) {
         const uint32_t slot = tcount & 1, aph = (tcount >> 1) & 1;
         TMOE_TIC();
-        if (!(ok = mbar_wait(smem_u32(&bar_tempty[slot]), aph ^ 1, p.status, kKernelOutPair, 4))) break;
+        mbar_wait_or_exit(smem_u32(&bar_tempty[slot]), aph ^ 1, p.status, kKernelOutPair, 4);
         TMOE_TOC(1);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + slot * ON;
-        for (int kb = 0; kb < KB; ++kb, ++it) {
-          const uint32_t s = it % P_STAGES, ph = (it / P_STAGES) & 1;
+        for (int kb = 0; kb < KB; ++kb) {
           TMOE_TIC();
-          if (!(ok = mbar_wait(smem_u32(&bar_full[s]), ph, p.status, kKernelOutPair, 1))) break;
+          mbar_wait_or_exit(smem_u32(&bar_full[s]), ph, p.status, kKernelOutPair, 1);
           TMOE_TOC(2);
-          tc_fence_after();
-          const uint32_t sa = ring + s * P_STAGE_BYTES;
-          const uint64_t da = umma_desc_k_sw128(sa), db = umma_desc_k_sw128(sa + O_A_BYTES);
+          const uint64_t da = desc0 + s * (uint32_t)(P_STAGE_BYTES >> 4), db = da + (O_A_BYTES >> 4);
+          const uint32_t acc0 = kb != 0;
 #pragma unroll
-          for (int k = 0; k < OKB / 16; ++k) umma_bf16_pair(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+          for (int k = 0; k < OKB / 16; ++k) umma_bf16_pair(d_tmem, da + 2 * k, db + 2 * k, idesc, acc0 | (uint32_t)(k != 0));
           umma_commit_pair(smem_u32(&bar_empty[s]), 3);
+          if (++s == P_STAGES) { s = 0; ph ^= 1; }
         }
-        if (ok) umma_commit_pair(smem_u32(&bar_tfull[slot]), 3);
+        umma_commit_pair(smem_u32(&bar_tfull[slot]), 3);
       }
     }
   } else {
@@ -465,7 +465,7 @@ tc_out_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   __syncthreads();
   cluster_arrive();   // the other CTA may still be reading this CTA's shared memory or signalling its barriers
   cluster_wait();
-  if (warp == 1) {
+  if (warp == 2) {
     __syncwarp();
     tc_fence_after();
     tmem_dealloc_pair(tmem_base, 512);
