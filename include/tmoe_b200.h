@@ -208,6 +208,12 @@ int tmoe_forward_static_scratch(const tmoe_layer_t *layer, const tmoe_factors_t 
 /* Number of kernels the library has launched in this process (monotonic counter). */
 int64_t tmoe_launch_count(void);
 
+/* Scheduling detail of tmoe_forward on the tensor-core path, for diagnostics.  When the 128-token tiles of a call do not
+ * fill whole waves of CTAs on the current device, the in/core kernel's grid is padded with "helper" CTAs that compute
+ * the out-projection of token tiles finished in the first wave while the last wave runs.  Writes the number of helper
+ * CTAs (0: none for this shape) and of 128-token tiles whose out-projection they take.  No reference counterpart. */
+int tmoe_handoff_plan(const tmoe_layer_t *layer, int64_t T, int32_t *n_helper_ctas, int32_t *n_token_tiles);
+
 #ifdef __cplusplus
 }
 #endif

@@ -2,6 +2,7 @@
 // dispatch between the CUDA-core path and the tcgen05 tensor-core path.
 #include "common.cuh"
 #include "kernels.h"
+#include <atomic>
 
 namespace tmoe {
 
@@ -39,7 +40,7 @@ int resolve(const tmoe_layer_t &L, int64_t T, int path, bool allow_decode = true
 
 WsLayout ws_layout(const tmoe_layer_t &L, int64_t T, int rpath) {
   WsLayout W{};
-  int64_t off = kStatusBytes;
+  int64_t off = kStatusBytes + kHandoffBytes;
   auto take = [&](int64_t bytes) { int64_t o = off; off = align_up(off + bytes, 256); return o; };
   W.idx = take(T * L.top_k * 4);
   W.gates = take(T * L.top_k * 4);
@@ -282,12 +283,32 @@ int tmoe_forward(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const
                          taps ? extras->idx_out : nullptr, taps ? extras->gates_out : nullptr,
                          taps ? extras->c_out : nullptr, epi, y, st);
   }
+  // token tiles that do not fill whole waves of CTAs: pad the in/core grid with helper CTAs that run out-projection tiles
+  OutHelperArgs helper{};
+  {
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return TMOE_ERR_CUDA;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return TMOE_ERR_CUDA;
+    plan_out_handoff(L, T, sms, &helper.ho);
+    if (helper.ho.n_helpers > 0) {
+      static std::atomic<uint32_t> epoch_counter{1};
+      uint32_t e = epoch_counter.fetch_add(1, std::memory_order_relaxed);
+      if (e == 0) e = epoch_counter.fetch_add(1, std::memory_order_relaxed);   // 0 is what a cleared word holds
+      helper.ho.epoch = e;
+      helper.ho.ready = reinterpret_cast<uint32_t *>(ws + kStatusBytes);
+      helper.uout_t = pb + P.uout_t;
+      helper.bias = reinterpret_cast<const float *>(pb + P.bias);
+      helper.epi = epi;
+      helper.y = y;
+    }
+  }
+  const OutHelperArgs *hp = helper.ho.n_helpers > 0 ? &helper : nullptr;
   if (W.tc_router_fused) {
     const bool taps = extras && (extras->idx_out || extras->gates_out || extras->c_out);
     rc = launch_tc_in_core(L, x, prepared, P, T, pre_norm, pre_norm ? extras->pre_norm_eps : 0.f, 1, nullptr,
                            reinterpret_cast<float *>(ws + W.c),
                            taps ? extras->idx_out : nullptr,
-                           taps ? extras->gates_out : nullptr, taps ? extras->c_out : nullptr, z, status, st);
+                           taps ? extras->gates_out : nullptr, taps ? extras->c_out : nullptr, z, status, st, hp);
   } else {
     // scores = x @ router_w^T on the tensor cores (bf16 out = the reference's rounding), then the select kernel
     if ((rc = launch_tc_gemm_bf16(x, pb + P.wr_b, nullptr, OutEpilogue{}, T, P.e_pad, L.d_in, scores, status, st)))
@@ -295,10 +316,11 @@ int tmoe_forward(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const
     if ((rc = launch_select_bf16_scores(L, scores, P.e_pad, factors->U_expert, T, idx, gates, c, st))) return rc;
     // c_work may alias c: every row is read by its own thread before that thread overwrites it
     rc = launch_tc_in_core(L, x, prepared, P, T, 0, 0.f, 0, c, reinterpret_cast<float *>(ws + W.c), nullptr, nullptr, nullptr, z,
-                           status, st);
+                           status, st, hp);
   }
   if (rc) return rc;
-  return launch_tc_out(L, z, pb + P.uout_t, reinterpret_cast<const float *>(pb + P.bias), epi, T, y, status, st);
+  return launch_tc_out(L, z, pb + P.uout_t, reinterpret_cast<const float *>(pb + P.bias), epi, T, y, status, st,
+                       hp ? &helper.ho : nullptr);
 }
 
 int tmoe_rms_norm(int dtype, const void *x, const void *weight, float eps, int64_t T, int32_t d, void *y, void *stream) {
@@ -317,6 +339,21 @@ int tmoe_read_device_status(void *workspace, int32_t *device_status, void *strea
   if (cudaMemcpy(words, workspace, sizeof(words), cudaMemcpyDeviceToHost) != cudaSuccess) return TMOE_ERR_CUDA;
   for (int i = 0; i < 4; ++i) device_status[i] = words[i];
   if (words[0] != 0 && cudaMemset(workspace, 0, kStatusBytes) != cudaSuccess) return TMOE_ERR_CUDA;
+  return TMOE_OK;
+}
+
+int tmoe_handoff_plan(const tmoe_layer_t *layer, int64_t T, int32_t *n_helper_ctas, int32_t *n_token_tiles) {
+  int rc = check_layer(layer);
+  if (rc) return rc;
+  if (!n_helper_ctas || !n_token_tiles) return TMOE_ERR_NULL;
+  *n_helper_ctas = 0; *n_token_tiles = 0;
+  if (T <= 0 || resolve(*layer, T, TMOE_PATH_AUTO) != TMOE_PATH_TENSOR) return TMOE_OK;
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return TMOE_ERR_CUDA;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return TMOE_ERR_CUDA;
+  OutHandoff h;
+  plan_out_handoff(*layer, T, sms, &h);
+  *n_helper_ctas = h.n_helpers; *n_token_tiles = h.m_tiles;
   return TMOE_OK;
 }
 

@@ -14,6 +14,8 @@ using bf16 = __nv_bfloat16;
 // ---- workspace status words (first 256 bytes of every workspace) -------------------------
 // word 0: 0 or TMOE_ERR_DEVICE_WAIT; word 1: kernel id; word 2: barrier tag; word 3: block id.
 constexpr int kStatusBytes = 256;
+// hand-off words between the in/core kernel's helper CTAs and the out-projection: 8 per 128-token tile, after the status words
+constexpr int kHandoffBytes = 128 * 8 * 4;
 
 // Counts kernel launches made by this library (read through tmoe_launch_count()).
 extern unsigned long long g_launch_count;

@@ -53,15 +53,37 @@ PreparedLayout prepared_layout(const tmoe_layer_t &L);
 int launch_prepare(const tmoe_layer_t &L, const tmoe_factors_t &F, const void *pre_norm_w, void *prepared, cudaStream_t st);
 
 // ---- tc_out_gemm.cu ----
+// Hand-off between the in/core kernel and the out-projection when the token tiles do not fill whole waves of CTAs: the
+// in/core grid is padded with `n_helpers` CTAs that compute the out-projection of the first `m_tiles` 128-token tiles
+// (finished in the first wave) while the last wave runs, and the out kernel starts behind them.  ready: 8 words per
+// 128-token tile in the workspace, set to `epoch` by the CTA that wrote the tile's z rows, cleared by the out kernel.
+struct OutHandoff {
+  int m_tiles = 0;    // even, <= kMaxHandoffTiles
+  int n_helpers = 0;
+  uint32_t *ready = nullptr;
+  uint32_t epoch = 0;
+};
+constexpr int kMaxHandoffTiles = 128;
+// Fills `h` for a forward of T tokens on a device with `sms` SMs (n_helpers = 0: no hand-off for this shape).
+void plan_out_handoff(const tmoe_layer_t &L, int64_t T, int sms, OutHandoff *h);
+
 // y[T, N] = z[T, K] (bf16) @ W_t[N, K]^T (bf16, K-major) + bias (fp32) on tcgen05 tensor cores.
 int launch_tc_out(const tmoe_layer_t &L, const void *z, const void *uout_t, const float *bias, const OutEpilogue &epi,
-                  int64_t T, void *y, int32_t *status, cudaStream_t st);
+                  int64_t T, void *y, int32_t *status, cudaStream_t st, const OutHandoff *ho = nullptr);
 
 // General form of the same kernel (used for the router scores when E is too large for the in-kernel router).
 int launch_tc_gemm_bf16(const void *A, const void *B_t, const float *bias, const OutEpilogue &epi, int64_t M, int N,
-                        int K, void *y, int32_t *status, cudaStream_t st);
+                        int K, void *y, int32_t *status, cudaStream_t st, const OutHandoff *ho = nullptr);
 
 // ---- tc_in_core.cu ----
+// Arguments of the out-projection that the in/core kernel's helper CTAs run (see OutHandoff).
+struct OutHelperArgs {
+  const void *uout_t;
+  const float *bias;
+  OutEpilogue epi;
+  void *y;
+  OutHandoff ho;
+};
 // Fused x@U_in (+ router scores) -> RMS statistics -> h@G tiles with c-weighted epilogue -> z bf16.
 // fuse_router != 0: scores/top-k/softmax/c are computed inside (c_in ignored, taps optional);
 // otherwise c_in [T, r1] is read.  c_work [T, r1] is scratch in both cases.
@@ -69,7 +91,7 @@ int launch_tc_gemm_bf16(const void *A, const void *B_t, const float *bias, const
 // row's 1/rms(x) from the x tiles passing through shared memory and applies it to the scores and to the RMS statistics.
 int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared, const PreparedLayout &P, int64_t T,
                       int pre_norm, float pre_norm_eps, int fuse_router, const float *c_in, float *c_work, int32_t *idx_out, float *gates_out, float *c_out,
-                      void *z, int32_t *status, cudaStream_t st);
+                      void *z, int32_t *status, cudaStream_t st, const OutHelperArgs *helper = nullptr);
 
 // ---- decode.cu ----
 // Whole forward for T <= 64 bf16 tokens on the prepared (K-major) factors: split-K in-projection with

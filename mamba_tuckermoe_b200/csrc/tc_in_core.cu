@@ -26,6 +26,7 @@
 #include "kernels.h"
 #include "ptx.cuh"
 #include "routing.cuh"
+#include "tc_out_body.cuh"
 
 namespace tmoe {
 
@@ -55,6 +56,7 @@ constexpr int IC_SMEM_BYTES = IC_RING_BYTES + 1024;
 constexpr int A_STAGES_MAX = 4;
 constexpr int SCORE_COL = 256;  // TMEM column of the router scores during phase A
 constexpr int kKernelInCore = 2;
+static_assert(IC_THREADS == O_THREADS && IC_SMEM_BYTES >= O_SMEM_BYTES, "helper CTAs run the out-projection body inside this kernel's CTA shape");
 
 struct InCoreParams {
   int64_t T;
@@ -73,6 +75,11 @@ struct InCoreParams {
   float *c_out;
   bf16 *z;  // [T, r2]
   int32_t *status;
+  // CTAs [0, n_token_ctas) own token tiles; the rest are helper CTAs that run out-projection tiles (OutHelperCfg).
+  // A token CTA with blockIdx.x < n_ready_m publishes `epoch` in ready[8 * blockIdx.x + epilogue warp] once its z rows are stored.
+  int n_token_ctas, n_ready_m;
+  uint32_t *ready;
+  uint32_t epoch;
 };
 
 // Phase-A issue loop of the MMA thread.  TWO_BOX: r3 = 512, h takes two 256-column MMAs per k step (the second piece of
@@ -105,9 +112,15 @@ __device__ __forceinline__ void issue_phase_a(uint32_t tmem_base, uint64_t desc0
 template <int R1, int RK>
 __global__ void __launch_bounds__(IC_THREADS, 1)
 tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmU,
-                  const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmG, InCoreParams p) {
+                  const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmG, InCoreParams p,
+                  const __grid_constant__ OutHelperCfg hc) {
   constexpr int N2 = 256 / R1;
   extern __shared__ uint8_t smem_raw[];
+  if ((int)blockIdx.x >= p.n_token_ctas) {
+    // grid padding: this CTA would idle during the last wave; it computes out-projection tiles of finished token tiles
+    tc_out_body(&hc.tmA, &hc.tmB, &hc.tmY, hc.p, (int)blockIdx.x - p.n_token_ctas, hc.n_helpers, hc.n_tiles, smem_raw);
+    return;
+  }
   __shared__ __align__(8) uint64_t bar_fullA[A_STAGES_MAX], bar_emptyA[A_STAGES_MAX], bar_fullB[G_STAGES_MAX],
       bar_emptyB[G_STAGES_MAX], bar_accA, bar_hready, bar_pfull[2], bar_pempty[2];
   __shared__ uint32_t tmem_base_s;
@@ -467,6 +480,12 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
           }
         }
       }
+      if (p.ready && (int)blockIdx.x < p.n_ready_m && ok) {
+        // this warp's z rows are written: make them visible device-wide, then raise the warp's hand-off word
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) *reinterpret_cast<volatile uint32_t *>(p.ready + blockIdx.x * 8 + (warp - 2)) = p.epoch;
+      }
       if (threadIdx.x == 64) TMOE_STAMP(5);  // z stored
 #ifdef TMOE_TRACE
       if (threadIdx.x == 64 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)) {
@@ -488,7 +507,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
 
 int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared, const PreparedLayout &P, int64_t T_,
                       int pre_norm, float pre_norm_eps, int fuse_router, const float *c_in, float *c_work, int32_t *idx_out, float *gates_out, float *c_out,
-                      void *z, int32_t *status, cudaStream_t st) {
+                      void *z, int32_t *status, cudaStream_t st, const OutHelperArgs *helper) {
   const char *base = reinterpret_cast<const char *>(prepared);
   if (fuse_router && (P.e_pad > 256 || L.top_k > 8 || L.r3 > 256)) return TMOE_ERR_UNSUPPORTED;
   if ((!fuse_router && !c_in) || !c_work) return TMOE_ERR_NULL;
@@ -517,12 +536,34 @@ int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared
   p.z = (bf16 *)z; p.status = status;
   if (X_TILE_BYTES + p.r3 * 128 + p.e_pad * 128 > IC_RING_BYTES) return TMOE_ERR_UNSUPPORTED;
 
-  const unsigned grid = (unsigned)((T_ + TM - 1) / TM);
+  unsigned grid = (unsigned)((T_ + TM - 1) / TM);
+  p.n_token_ctas = (int)grid;
+  static OutHelperCfg hc_none;   // zero-initialised: no helper CTAs
+  OutHelperCfg hc_local;
+  const OutHelperCfg *hc = &hc_none;
+  if (helper && helper->ho.n_helpers > 0) {
+    OutHelperCfg &h = hc_local;
+    h = OutHelperCfg{};
+    if ((rc = encode_tmap_bf16_2d(&h.tmY, helper->y, (uint64_t)T_, (uint64_t)L.d_out, 32))) return rc;
+    if ((rc = encode_tmap_bf16_2d(&h.tmA, z, (uint64_t)T_, (uint64_t)L.r2, OM))) return rc;
+    if ((rc = encode_tmap_bf16_2d(&h.tmB, helper->uout_t, (uint64_t)L.d_out, (uint64_t)L.r2, ON))) return rc;
+    h.p.y = (bf16 *)helper->y; h.p.bias = helper->bias; h.p.residual = (const bf16 *)helper->epi.residual;
+    h.p.gamma = (const bf16 *)helper->epi.layer_scale; h.p.silu_gate = (const bf16 *)helper->epi.silu_gate;
+    h.p.T = T_; h.p.N = L.d_out; h.p.K = L.r2;
+    h.p.num_m = (int)((T_ + OM - 1) / OM); h.p.num_n = (L.d_out + ON - 1) / ON;
+    h.p.status = status;
+    h.p.ready = helper->ho.ready; h.p.epoch = helper->ho.epoch;
+    h.n_helpers = helper->ho.n_helpers;
+    h.n_tiles = helper->ho.m_tiles * h.p.num_n;
+    p.n_ready_m = helper->ho.m_tiles; p.ready = helper->ho.ready; p.epoch = helper->ho.epoch;
+    grid += (unsigned)h.n_helpers;
+    hc = &hc_local;
+  }
   cudaError_t e = cudaSuccess;
 #define TMOE_IC(R, K)                                                                                              \
   do {                                                                                                             \
     e = cudaFuncSetAttribute(tc_in_core_kernel<R, K>, cudaFuncAttributeMaxDynamicSharedMemorySize, IC_SMEM_BYTES); \
-    if (e == cudaSuccess) tc_in_core_kernel<R, K><<<grid, IC_THREADS, IC_SMEM_BYTES, st>>>(tmX, tmU, tmW, tmG, p);    \
+    if (e == cudaSuccess) tc_in_core_kernel<R, K><<<grid, IC_THREADS, IC_SMEM_BYTES, st>>>(tmX, tmU, tmW, tmG, p, *hc);    \
   } while (0)
   const bool small_k = L.top_k <= 2;
   if (L.r1 == 2) { if (small_k) TMOE_IC(2, 2); else TMOE_IC(2, 8); }

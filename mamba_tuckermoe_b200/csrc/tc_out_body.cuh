@@ -1,0 +1,287 @@
+// Body of the out-projection GEMM kernel (see tc_out_gemm.cu for the description), as a device function so that
+// two kernels can run it: tc_out_kernel itself, and the in/core kernel, whose grid is padded to whole waves with
+// "helper" CTAs that compute out-projection tiles of token tiles finished in the first wave instead of idling.
+#pragma once
+#include "common.cuh"
+#include "kernels.h"
+#include "ptx.cuh"
+
+namespace tmoe {
+
+using namespace ptx;
+
+// ------------------------------------------------------------------------------------------
+constexpr int OM = 128, ON = 256, OKB = 64, OSTAGES = 4;
+constexpr int O_A_BYTES = OM * OKB * 2;   // 16 KB
+constexpr int O_B_BYTES = ON * OKB * 2;   // 32 KB
+constexpr int O_STAGE_BYTES = O_A_BYTES + O_B_BYTES;
+constexpr int O_EPI_WARPS = 8;
+constexpr int O_THREADS = (2 + O_EPI_WARPS) * 32;
+constexpr int O_Y_BYTES = 32 * 64 * 2;  // 4 KB per epilogue warp: 32 rows x 64 bf16 output columns
+constexpr int O_SMEM_BYTES = OSTAGES * O_STAGE_BYTES + O_EPI_WARPS * O_Y_BYTES + 1024;
+constexpr int kKernelOut = 3;
+
+// Diagnostic builds (-DTMOE_TRACE): block 0 accumulates the cycles its roles spend in each wait into
+// status words [40..47].
+#ifdef TMOE_TRACE
+#define TMOE_TIC() trace_tic = clock64()
+#define TMOE_TOC(i)                                                                             \
+  do {                                                                                          \
+    if (blockIdx.x == 0) {                                                                      \
+      const int dt_ = (int)(clock64() - trace_tic);                                             \
+      atomicAdd(&p.status[40 + (i)], dt_);                                                      \
+      if ((i) == 2) atomicAdd(&p.status[48 + (dt_ < 64 ? 0 : dt_ < 256 ? 1 : dt_ < 1024 ? 2 : 3)], 1); \
+      if ((i) == 2 && dt_ >= 1024) atomicAdd(&p.status[52], dt_);                               \
+    }                                                                                           \
+  } while (0)
+#else
+#define TMOE_TIC() do { } while (0)
+#define TMOE_TOC(i) do { } while (0)
+#endif
+
+struct OutParams {
+  bf16 *y;
+  const float *bias;
+  const bf16 *residual;
+  const bf16 *gamma;
+  const bf16 *silu_gate;
+  int64_t T;
+  int N, K;
+  int num_m, num_n;
+  int32_t *status;
+  // Tiles [0, tile_begin) of this GEMM were computed by helper CTAs of the kernel that produced A; this launch starts
+  // at tile_begin (in its own tile units) and clears the hand-off flags.
+  int tile_begin;
+  uint32_t *ready_clear;
+  int ready_words;
+  // Helper CTAs only: rows [128 m, 128 m + 128) of A may be read once ready[8 m .. 8 m + 7] all equal `epoch` (one word
+  // per epilogue warp of the producing CTA).
+  const uint32_t *ready;
+  uint32_t epoch;
+};
+
+
+// What a helper CTA of the in/core kernel needs to run out-projection tiles: the three tensor maps and parameters of the
+// GEMM, the number of helper CTAs and the number of tiles they share (tile t goes to helper t mod n_helpers).
+struct alignas(64) OutHelperCfg {
+  CUtensorMap tmA, tmB, tmY;
+  OutParams p;
+  int n_helpers;
+  int n_tiles;
+};
+
+// Bounded wait for the eight hand-off words of one 128-row tile of A (written with st.global after a __threadfence by the
+// producing CTA's epilogue warps).  The TMA loads that follow read through the async proxy, hence the proxy fence.
+__device__ __forceinline__ bool rows_ready_wait(const uint32_t *flags, uint32_t epoch, int32_t *status) {
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  for (;;) {
+    int n = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      uint32_t v;
+      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + i) : "memory");
+      n += (v == epoch);
+    }
+    if (n == 8) break;
+    if ((++spins & 0x3fu) == 0) {
+      if (*reinterpret_cast<volatile int32_t *>(status) != 0) return false;
+      if (clock64() - t0 > kWaitLimitCycles) {
+        if (atomicCAS(status, 0, (int32_t)TMOE_ERR_DEVICE_WAIT) == 0) {
+          status[1] = 3; status[2] = 11; status[3] = (int32_t)blockIdx.x;
+          __threadfence();
+        }
+        return false;
+      }
+    }
+    __nanosleep(100);
+  }
+  asm volatile("fence.proxy.async;" ::: "memory");
+  return true;
+}
+
+// Processes tiles tile_first, tile_first + tile_step, ... < tile_end (tile = m * num_n + n, 128 x 256 outputs each).
+// Must be entered by all O_THREADS threads of a CTA that holds O_SMEM_BYTES of dynamic shared memory and no TMEM.
+__device__ __forceinline__ void tc_out_body(const CUtensorMap *tmA, const CUtensorMap *tmB, const CUtensorMap *tmY,
+                                            const OutParams &p, int tile_first, int tile_step, int tile_end,
+                                            uint8_t *smem_raw) {
+  __shared__ __align__(8) uint64_t bar_full[OSTAGES], bar_empty[OSTAGES], bar_tfull[2], bar_tempty[2];
+  __shared__ uint32_t tmem_base_s;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < OSTAGES; ++s) { mbar_init(smem_u32(&bar_full[s]), 1); mbar_init(smem_u32(&bar_empty[s]), 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(smem_u32(&bar_tfull[s]), 1); mbar_init(smem_u32(&bar_tempty[s]), O_EPI_WARPS); }
+    fence_mbar_init();
+    prefetch_tmap(tmA);
+    prefetch_tmap(tmB);
+    prefetch_tmap(tmY);
+  }
+  if (warp == 2) { tmem_alloc(smem_u32(&tmem_base_s), 512); tmem_relinquish(); }  // an epilogue warp: its lanes never retire early
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+
+  const int KB = (p.K + OKB - 1) / OKB;
+#ifdef TMOE_TRACE
+  const long long trace_t0 = clock64();
+  long long trace_tic = 0;
+#endif
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = tile_first; tile < tile_end && ok; tile += tile_step) {
+        const int m0 = (tile / p.num_n) * OM, n0 = (tile % p.num_n) * ON;
+        if (p.ready && !(ok = rows_ready_wait(p.ready + (tile / p.num_n) * 8, p.epoch, p.status))) break;
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const uint32_t s = it % OSTAGES, ph = (it / OSTAGES) & 1;
+          TMOE_TIC();
+          if (!(ok = mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1, p.status, kKernelOut, 2))) break;
+          TMOE_TOC(0);  // producer waiting for a free stage
+          const uint32_t full = smem_u32(&bar_full[s]);
+          mbar_arrive_expect_tx(full, O_STAGE_BYTES);
+          const uint32_t sa = ring + s * O_STAGE_BYTES;
+          tma_load_2d(sa, tmA, kb * OKB, m0, full);
+          tma_load_2d(sa + O_A_BYTES, tmB, kb * OKB, n0, full);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // The issuing thread's loop is the serial path (see mbar_wait_or_exit): fixed trip counts, no side exits,
+      // ring position and descriptors kept incrementally.
+      const uint32_t idesc = umma_idesc_bf16(OM, ON);
+      const uint64_t desc0 = umma_desc_k_sw128(ring);
+      uint32_t s = 0, ph = 0, tcount = 0;
+      for (int tile = tile_first; tile < tile_end; tile += tile_step, ++tcount) {
+        const uint32_t slot = tcount & 1, aph = (tcount >> 1) & 1;
+        TMOE_TIC();
+        mbar_wait_or_exit(smem_u32(&bar_tempty[slot]), aph ^ 1, p.status, kKernelOut, 4);
+        TMOE_TOC(1);  // MMA thread waiting for the epilogue to release an accumulator
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + slot * ON;
+        for (int kb = 0; kb < KB; ++kb) {
+          TMOE_TIC();
+          mbar_wait_or_exit(smem_u32(&bar_full[s]), ph, p.status, kKernelOut, 1);
+          TMOE_TOC(2);  // MMA thread waiting for operand tiles
+          const uint64_t da = desc0 + s * (uint32_t)(O_STAGE_BYTES >> 4), db = da + (O_A_BYTES >> 4);
+          const uint32_t acc0 = kb != 0;
+#pragma unroll
+          for (int k = 0; k < OKB / 16; ++k)  // +32 bytes (= 2 in >>4 units) per 16-element K step
+            umma_bf16(d_tmem, da + 2 * k, db + 2 * k, idesc, acc0 | (uint32_t)(k != 0));
+          umma_commit(smem_u32(&bar_empty[s]));
+          if (++s == OSTAGES) { s = 0; ph ^= 1; }
+        }
+        umma_commit(smem_u32(&bar_tfull[slot]));
+      }
+    }
+  } else {
+    // Eight epilogue warps: warp w may read TMEM lanes 32*(w%4)..+31, so two warps share each row
+    // quadrant and split the tile's 256 columns.  Each warp stages 32 rows x 64 columns (4 KB, swizzled)
+    // and issues its own TMA store, so the warps never wait for one another.
+    const int ew = warp - 2;
+    const int quad = warp & 3;
+    const int half = ew >> 2;
+    const int row_in_tile = quad * 32 + lane;
+    const uint32_t stage_buf = ring + OSTAGES * O_STAGE_BYTES + ew * O_Y_BYTES;
+    uint32_t tcount = 0;
+    bool ok = true;
+    for (int tile = tile_first; tile < tile_end && ok; tile += tile_step, ++tcount) {
+      const int m0 = (tile / p.num_n) * OM, n0 = (tile % p.num_n) * ON;
+      const uint32_t slot = tcount & 1, aph = (tcount >> 1) & 1;
+      TMOE_TIC();
+      ok = mbar_wait(smem_u32(&bar_tfull[slot]), aph, p.status, kKernelOut, 3);
+      if (threadIdx.x == 64) TMOE_TOC(3);  // epilogue warp 2 waiting for a finished accumulator
+      ok = __all_sync(0xffffffffu, ok);  // the TMEM loads below are warp-collective
+      if (!ok) break;
+      tc_fence_after();
+      const int64_t row = (int64_t)m0 + row_in_tile;
+      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + slot * ON + half * 128;
+#pragma unroll 1
+      for (int cc = 0; cc < 2; ++cc) {
+        const int col0 = n0 + half * 128 + cc * 64;
+        uint32_t r[2][32];
+        tmem_ld32(t_row + cc * 64, r[0]);
+        tmem_ld32(t_row + cc * 64 + 32, r[1]);
+        tmem_ld_wait(r[0], r[1]);
+        if (cc == 1) {  // this warp has read its whole share of the accumulator
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[slot]));
+        }
+        TMOE_TIC();
+        if (lane == 0) tma_store_wait_read<0>();  // the previous store has finished reading the staging tile
+        if (threadIdx.x == 64) TMOE_TOC(4);  // epilogue warp 2 waiting for its previous TMA store
+        __syncwarp();
+#pragma unroll
+        for (int h2 = 0; h2 < 2; ++h2) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int col = col0 + h2 * 32 + g * 8;
+            float v[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) v[q] = __uint_as_float(r[h2][g * 8 + q]);
+            if (col < p.N) {  // N % 8 == 0: a group of 8 is entirely in or out; columns >= N are clipped by the store
+              if (p.bias) {
+                const float4 b0 = __ldg(reinterpret_cast<const float4 *>(p.bias + col));
+                const float4 b1 = __ldg(reinterpret_cast<const float4 *>(p.bias + col + 4));
+                v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+                v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+              }
+              if (p.silu_gate && row < p.T) {
+                const uint4 gv = __ldg(reinterpret_cast<const uint4 *>(p.silu_gate + row * p.N + col));
+                const uint32_t gw2[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  const float g0 = __uint_as_float(gw2[q] << 16), g1 = __uint_as_float(gw2[q] & 0xffff0000u);
+                  v[2 * q] *= g0 / (1.f + __expf(-g0));
+                  v[2 * q + 1] *= g1 / (1.f + __expf(-g1));
+                }
+              }
+              if (p.residual && row < p.T) {
+                const uint4 rr = __ldg(reinterpret_cast<const uint4 *>(p.residual + row * p.N + col));
+                const uint4 gg = __ldg(reinterpret_cast<const uint4 *>(p.gamma + col));
+                const uint32_t rw[4] = {rr.x, rr.y, rr.z, rr.w}, gw[4] = {gg.x, gg.y, gg.z, gg.w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  v[2 * q] = __uint_as_float(rw[q] << 16) + __uint_as_float(gw[q] << 16) * v[2 * q];
+                  v[2 * q + 1] = __uint_as_float(rw[q] & 0xffff0000u) + __uint_as_float(gw[q] & 0xffff0000u) * v[2 * q + 1];
+                }
+              }
+            }
+            // 16-byte chunk (h2*4+g) of this lane's 128-byte row, XOR-swizzled as the TMA box expects
+            const uint32_t chunk = (uint32_t)(h2 * 4 + g) ^ (uint32_t)(lane & 7);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_buf + lane * 128 + chunk * 16),
+                         "r"(pack_bf16x2(v[0], v[1])), "r"(pack_bf16x2(v[2], v[3])), "r"(pack_bf16x2(v[4], v[5])),
+                         "r"(pack_bf16x2(v[6], v[7]))
+                         : "memory");
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0 && col0 < p.N) {
+          tma_store_2d(tmY, stage_buf, col0, m0 + quad * 32);
+          tma_store_commit();
+        }
+      }
+    }
+    if (lane == 0) tma_store_wait_all();
+  }
+#ifdef TMOE_TRACE
+  if (blockIdx.x == 0 && threadIdx.x == 64) p.status[40 + 7] = (int32_t)(clock64() - trace_t0);  // kernel cycles
+#endif
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace tmoe

@@ -14,6 +14,7 @@
 #include "common.cuh"
 #include "kernels.h"
 #include "ptx.cuh"
+#include "tc_out_body.cuh"
 #include <cstdlib>
 
 namespace tmoe {
@@ -52,228 +53,13 @@ int encode_tmap_bf16_2d(CUtensorMap *out, const void *base, uint64_t rows, uint6
   return r == CUDA_SUCCESS ? TMOE_OK : TMOE_ERR_DRIVER;
 }
 
-// ------------------------------------------------------------------------------------------
-constexpr int OM = 128, ON = 256, OKB = 64, OSTAGES = 4;
-constexpr int O_A_BYTES = OM * OKB * 2;   // 16 KB
-constexpr int O_B_BYTES = ON * OKB * 2;   // 32 KB
-constexpr int O_STAGE_BYTES = O_A_BYTES + O_B_BYTES;
-constexpr int O_EPI_WARPS = 8;
-constexpr int O_THREADS = (2 + O_EPI_WARPS) * 32;
-constexpr int O_Y_BYTES = 32 * 64 * 2;  // 4 KB per epilogue warp: 32 rows x 64 bf16 output columns
-constexpr int O_SMEM_BYTES = OSTAGES * O_STAGE_BYTES + O_EPI_WARPS * O_Y_BYTES + 1024;
-constexpr int kKernelOut = 3;
-
-// Diagnostic builds (-DTMOE_TRACE): block 0 accumulates the cycles its roles spend in each wait into
-// status words [40..47].
-#ifdef TMOE_TRACE
-#define TMOE_TIC() trace_tic = clock64()
-#define TMOE_TOC(i)                                                                             \
-  do {                                                                                          \
-    if (blockIdx.x == 0) {                                                                      \
-      const int dt_ = (int)(clock64() - trace_tic);                                             \
-      atomicAdd(&p.status[40 + (i)], dt_);                                                      \
-      if ((i) == 2) atomicAdd(&p.status[48 + (dt_ < 64 ? 0 : dt_ < 256 ? 1 : dt_ < 1024 ? 2 : 3)], 1); \
-      if ((i) == 2 && dt_ >= 1024) atomicAdd(&p.status[52], dt_);                               \
-    }                                                                                           \
-  } while (0)
-#else
-#define TMOE_TIC() do { } while (0)
-#define TMOE_TOC(i) do { } while (0)
-#endif
-
-struct OutParams {
-  bf16 *y;
-  const float *bias;
-  const bf16 *residual;
-  const bf16 *gamma;
-  const bf16 *silu_gate;
-  int64_t T;
-  int N, K;
-  int num_m, num_n;
-  int32_t *status;
-};
-
 __global__ void __launch_bounds__(O_THREADS, 1)
 tc_out_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
               const __grid_constant__ CUtensorMap tmY, OutParams p) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bar_full[OSTAGES], bar_empty[OSTAGES], bar_tfull[2], bar_tempty[2];
-  __shared__ uint32_t tmem_base_s;
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < OSTAGES; ++s) { mbar_init(smem_u32(&bar_full[s]), 1); mbar_init(smem_u32(&bar_empty[s]), 1); }
-    for (int s = 0; s < 2; ++s) { mbar_init(smem_u32(&bar_tfull[s]), 1); mbar_init(smem_u32(&bar_tempty[s]), O_EPI_WARPS); }
-    fence_mbar_init();
-    prefetch_tmap(&tmA);
-    prefetch_tmap(&tmB);
-    prefetch_tmap(&tmY);
-  }
-  if (warp == 2) { tmem_alloc(smem_u32(&tmem_base_s), 512); tmem_relinquish(); }  // an epilogue warp: its lanes never retire early
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = tmem_base_s;
-
-  const int num_tiles = p.num_m * p.num_n;
-  const int KB = (p.K + OKB - 1) / OKB;
-#ifdef TMOE_TRACE
-  const long long trace_t0 = clock64();
-  long long trace_tic = 0;
-#endif
-
-  if (warp == 0) {
-    if (lane == 0) {
-      uint32_t it = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile / p.num_n) * OM, n0 = (tile % p.num_n) * ON;
-        for (int kb = 0; kb < KB; ++kb, ++it) {
-          const uint32_t s = it % OSTAGES, ph = (it / OSTAGES) & 1;
-          TMOE_TIC();
-          if (!(ok = mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1, p.status, kKernelOut, 2))) break;
-          TMOE_TOC(0);  // producer waiting for a free stage
-          const uint32_t full = smem_u32(&bar_full[s]);
-          mbar_arrive_expect_tx(full, O_STAGE_BYTES);
-          const uint32_t sa = ring + s * O_STAGE_BYTES;
-          tma_load_2d(sa, &tmA, kb * OKB, m0, full);
-          tma_load_2d(sa + O_A_BYTES, &tmB, kb * OKB, n0, full);
-        }
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      // The issuing thread's loop is the serial path (see mbar_wait_or_exit): fixed trip counts, no side exits,
-      // ring position and descriptors kept incrementally.
-      const uint32_t idesc = umma_idesc_bf16(OM, ON);
-      const uint64_t desc0 = umma_desc_k_sw128(ring);
-      uint32_t s = 0, ph = 0, tcount = 0;
-      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcount) {
-        const uint32_t slot = tcount & 1, aph = (tcount >> 1) & 1;
-        TMOE_TIC();
-        mbar_wait_or_exit(smem_u32(&bar_tempty[slot]), aph ^ 1, p.status, kKernelOut, 4);
-        TMOE_TOC(1);  // MMA thread waiting for the epilogue to release an accumulator
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + slot * ON;
-        for (int kb = 0; kb < KB; ++kb) {
-          TMOE_TIC();
-          mbar_wait_or_exit(smem_u32(&bar_full[s]), ph, p.status, kKernelOut, 1);
-          TMOE_TOC(2);  // MMA thread waiting for operand tiles
-          const uint64_t da = desc0 + s * (uint32_t)(O_STAGE_BYTES >> 4), db = da + (O_A_BYTES >> 4);
-          const uint32_t acc0 = kb != 0;
-#pragma unroll
-          for (int k = 0; k < OKB / 16; ++k)  // +32 bytes (= 2 in >>4 units) per 16-element K step
-            umma_bf16(d_tmem, da + 2 * k, db + 2 * k, idesc, acc0 | (uint32_t)(k != 0));
-          umma_commit(smem_u32(&bar_empty[s]));
-          if (++s == OSTAGES) { s = 0; ph ^= 1; }
-        }
-        umma_commit(smem_u32(&bar_tfull[slot]));
-      }
-    }
-  } else {
-    // Eight epilogue warps: warp w may read TMEM lanes 32*(w%4)..+31, so two warps share each row
-    // quadrant and split the tile's 256 columns.  Each warp stages 32 rows x 64 columns (4 KB, swizzled)
-    // and issues its own TMA store, so the warps never wait for one another.
-    const int ew = warp - 2;
-    const int quad = warp & 3;
-    const int half = ew >> 2;
-    const int row_in_tile = quad * 32 + lane;
-    const uint32_t stage_buf = ring + OSTAGES * O_STAGE_BYTES + ew * O_Y_BYTES;
-    uint32_t tcount = 0;
-    bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
-      const int m0 = (tile / p.num_n) * OM, n0 = (tile % p.num_n) * ON;
-      const uint32_t slot = tcount & 1, aph = (tcount >> 1) & 1;
-      TMOE_TIC();
-      ok = mbar_wait(smem_u32(&bar_tfull[slot]), aph, p.status, kKernelOut, 3);
-      if (threadIdx.x == 64) TMOE_TOC(3);  // epilogue warp 2 waiting for a finished accumulator
-      ok = __all_sync(0xffffffffu, ok);  // the TMEM loads below are warp-collective
-      if (!ok) break;
-      tc_fence_after();
-      const int64_t row = (int64_t)m0 + row_in_tile;
-      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + slot * ON + half * 128;
-#pragma unroll 1
-      for (int cc = 0; cc < 2; ++cc) {
-        const int col0 = n0 + half * 128 + cc * 64;
-        uint32_t r[2][32];
-        tmem_ld32(t_row + cc * 64, r[0]);
-        tmem_ld32(t_row + cc * 64 + 32, r[1]);
-        tmem_ld_wait(r[0], r[1]);
-        if (cc == 1) {  // this warp has read its whole share of the accumulator
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[slot]));
-        }
-        TMOE_TIC();
-        if (lane == 0) tma_store_wait_read<0>();  // the previous store has finished reading the staging tile
-        if (threadIdx.x == 64) TMOE_TOC(4);  // epilogue warp 2 waiting for its previous TMA store
-        __syncwarp();
-#pragma unroll
-        for (int h2 = 0; h2 < 2; ++h2) {
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const int col = col0 + h2 * 32 + g * 8;
-            float v[8];
-#pragma unroll
-            for (int q = 0; q < 8; ++q) v[q] = __uint_as_float(r[h2][g * 8 + q]);
-            if (col < p.N) {  // N % 8 == 0: a group of 8 is entirely in or out; columns >= N are clipped by the store
-              if (p.bias) {
-                const float4 b0 = __ldg(reinterpret_cast<const float4 *>(p.bias + col));
-                const float4 b1 = __ldg(reinterpret_cast<const float4 *>(p.bias + col + 4));
-                v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
-                v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
-              }
-              if (p.silu_gate && row < p.T) {
-                const uint4 gv = __ldg(reinterpret_cast<const uint4 *>(p.silu_gate + row * p.N + col));
-                const uint32_t gw2[4] = {gv.x, gv.y, gv.z, gv.w};
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                  const float g0 = __uint_as_float(gw2[q] << 16), g1 = __uint_as_float(gw2[q] & 0xffff0000u);
-                  v[2 * q] *= g0 / (1.f + __expf(-g0));
-                  v[2 * q + 1] *= g1 / (1.f + __expf(-g1));
-                }
-              }
-              if (p.residual && row < p.T) {
-                const uint4 rr = __ldg(reinterpret_cast<const uint4 *>(p.residual + row * p.N + col));
-                const uint4 gg = __ldg(reinterpret_cast<const uint4 *>(p.gamma + col));
-                const uint32_t rw[4] = {rr.x, rr.y, rr.z, rr.w}, gw[4] = {gg.x, gg.y, gg.z, gg.w};
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                  v[2 * q] = __uint_as_float(rw[q] << 16) + __uint_as_float(gw[q] << 16) * v[2 * q];
-                  v[2 * q + 1] = __uint_as_float(rw[q] & 0xffff0000u) + __uint_as_float(gw[q] & 0xffff0000u) * v[2 * q + 1];
-                }
-              }
-            }
-            // 16-byte chunk (h2*4+g) of this lane's 128-byte row, XOR-swizzled as the TMA box expects
-            const uint32_t chunk = (uint32_t)(h2 * 4 + g) ^ (uint32_t)(lane & 7);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_buf + lane * 128 + chunk * 16),
-                         "r"(pack_bf16x2(v[0], v[1])), "r"(pack_bf16x2(v[2], v[3])), "r"(pack_bf16x2(v[4], v[5])),
-                         "r"(pack_bf16x2(v[6], v[7]))
-                         : "memory");
-          }
-        }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0 && col0 < p.N) {
-          tma_store_2d(&tmY, stage_buf, col0, m0 + quad * 32);
-          tma_store_commit();
-        }
-      }
-    }
-    if (lane == 0) tma_store_wait_all();
-  }
-#ifdef TMOE_TRACE
-  if (blockIdx.x == 0 && threadIdx.x == 64) p.status[40 + 7] = (int32_t)(clock64() - trace_t0);  // kernel cycles
-#endif
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 2) {
-    __syncwarp();
-    tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
-  }
+  if (p.ready_clear && blockIdx.x == 0)   // the hand-off flags of this forward have served (the kernel that set them is complete)
+    for (int i = threadIdx.x; i < p.ready_words; i += blockDim.x) p.ready_clear[i] = 0u;
+  tc_out_body(&tmA, &tmB, &tmY, p, p.tile_begin + (int)blockIdx.x, (int)gridDim.x, p.num_m * p.num_n, smem_raw);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -300,6 +86,8 @@ tc_out_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t rank = cluster_ctarank();
   const int pair_id = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  if (p.ready_clear && blockIdx.x == 0)
+    for (int i = threadIdx.x; i < p.ready_words; i += blockDim.x) p.ready_clear[i] = 0u;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < P_STAGES; ++s) { mbar_init(smem_u32(&bar_full[s]), 1); mbar_init(smem_u32(&bar_empty[s]), 1); }
@@ -328,7 +116,7 @@ tc_out_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+      for (int tile = p.tile_begin + pair_id; tile < num_tiles && ok; tile += num_pairs) {
         const int m0 = (tile / p.num_n) * (2 * OM) + (int)rank * OM;
         const int n0 = (tile % p.num_n) * ON + (int)rank * (ON / 2);
         for (int kb = 0; kb < KB; ++kb, ++it) {
@@ -349,7 +137,7 @@ tc_out_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       const uint32_t idesc = umma_idesc_bf16(2 * OM, ON);
       const uint64_t desc0 = umma_desc_k_sw128(ring);
       uint32_t s = 0, ph = 0, tcount = 0;
-      for (int tile = pair_id; tile < num_tiles; tile += num_pairs, ++tcount) {
+      for (int tile = p.tile_begin + pair_id; tile < num_tiles; tile += num_pairs, ++tcount) {
         const uint32_t slot = tcount & 1, aph = (tcount >> 1) & 1;
         TMOE_TIC();
         mbar_wait_or_exit(smem_u32(&bar_tempty[slot]), aph ^ 1, p.status, kKernelOutPair, 4);
@@ -381,7 +169,7 @@ tc_out_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     const uint32_t stage_buf = ring + P_STAGES * P_STAGE_BYTES + ew * O_Y_BYTES;
     uint32_t tcount = 0;
     bool ok = true;
-    for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++tcount) {
+    for (int tile = p.tile_begin + pair_id; tile < num_tiles && ok; tile += num_pairs, ++tcount) {
       const int m0 = (tile / p.num_n) * (2 * OM) + (int)rank * OM, n0 = (tile % p.num_n) * ON;
       const uint32_t slot = tcount & 1, aph = (tcount >> 1) & 1;
       ok = mbar_wait(smem_u32(&bar_tfull[slot]), aph, p.status, kKernelOutPair, 3);
@@ -475,7 +263,7 @@ tc_out_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 // y[M, N] (bf16) = A[M, K] (bf16, row-major) @ B_t[N, K]^T (bf16, K-major) + bias[N] (fp32, optional),
 // then the optional OutEpilogue tail.  N and K multiples of 8.
 int launch_tc_gemm_bf16(const void *A, const void *B_t, const float *bias, const OutEpilogue &epi, int64_t M, int N,
-                        int K, void *y, int32_t *status, cudaStream_t st) {
+                        int K, void *y, int32_t *status, cudaStream_t st, const OutHandoff *ho) {
   CUtensorMap tmA, tmB, tmY;
   int rc = encode_tmap_bf16_2d(&tmY, y, (uint64_t)M, (uint64_t)N, 32);
   if (rc) return rc;
@@ -492,10 +280,12 @@ int launch_tc_gemm_bf16(const void *A, const void *B_t, const float *bias, const
       return TMOE_ERR_CUDA;
     attr_done[dev] = true;
   }
-  // Opt-in (environment TMOE_OUT_PAIRS=1): measured 120.5 us against 124.7 us for the single-CTA kernel on the
-  // prefill configuration; wait-cycle traces show both kernels' MMA threads waiting for operand tiles about a
-  // quarter of the time, so halving the operand traffic is not what this GEMM is short of.
-  static const bool use_pairs = []() { const char *e = getenv("TMOE_OUT_PAIRS"); return e && atoi(e) != 0; }();
+  // CTA pairs for GEMMs with at least two 256x256 tiles per pair of SMs (each CTA then streams 32 KB instead of 48 KB per
+  // k block and the ring is six stages deep: 112 us against 119 us on the prefill configuration); smaller GEMMs keep the
+  // single-CTA kernel, whose 128-row tiles cover more SMs.  TMOE_OUT_PAIRS=0 / 1 forces the choice.
+  static const int pairs_env = []() { const char *e = getenv("TMOE_OUT_PAIRS"); return e ? (atoi(e) != 0 ? 1 : 0) : -1; }();
+  const int64_t tiles256 = ((M + 2 * OM - 1) / (2 * OM)) * ((N + ON - 1) / ON);
+  const bool use_pairs = pairs_env >= 0 ? pairs_env == 1 : tiles256 >= 2 * (int64_t)(sms / 2);
   if (use_pairs) {
     static bool attr2_done[64] = {};
     if (dev < 64 && !attr2_done[dev]) {
@@ -512,7 +302,8 @@ int launch_tc_gemm_bf16(const void *A, const void *B_t, const float *bias, const
     q.T = M; q.N = N; q.K = K;
     q.num_m = (int)((M + 2 * OM - 1) / (2 * OM)); q.num_n = (N + ON - 1) / ON;
     q.status = status;
-    const int tiles2 = q.num_m * q.num_n;
+    if (ho && ho->n_helpers > 0) { q.tile_begin = (ho->m_tiles / 2) * q.num_n; q.ready_clear = ho->ready; q.ready_words = ho->m_tiles * 8; }
+    const int tiles2 = q.num_m * q.num_n - q.tile_begin;
     // a persistent grid must be fully co-resident: ask how many 2-CTA clusters the device can hold at once
     static int max_pairs[64] = {};
     if (dev < 64 && max_pairs[dev] == 0) {
@@ -538,7 +329,8 @@ int launch_tc_gemm_bf16(const void *A, const void *B_t, const float *bias, const
   p.T = M; p.N = N; p.K = K;
   p.num_m = (int)((M + OM - 1) / OM); p.num_n = (N + ON - 1) / ON;
   p.status = status;
-  const int tiles = p.num_m * p.num_n;
+  if (ho && ho->n_helpers > 0) { p.tile_begin = ho->m_tiles * p.num_n; p.ready_clear = ho->ready; p.ready_words = ho->m_tiles * 8; }
+  const int tiles = p.num_m * p.num_n - p.tile_begin;
   const int grid = tiles < sms ? tiles : sms;
   tc_out_kernel<<<grid, O_THREADS, O_SMEM_BYTES, st>>>(tmA, tmB, tmY, p);
   count_launch();
@@ -546,8 +338,34 @@ int launch_tc_gemm_bf16(const void *A, const void *B_t, const float *bias, const
 }
 
 int launch_tc_out(const tmoe_layer_t &L, const void *z, const void *uout_t, const float *bias, const OutEpilogue &epi,
-                  int64_t T_, void *y, int32_t *status, cudaStream_t st) {
-  return launch_tc_gemm_bf16(z, uout_t, bias, epi, T_, L.d_out, L.r2, y, status, st);
+                  int64_t T_, void *y, int32_t *status, cudaStream_t st, const OutHandoff *ho) {
+  return launch_tc_gemm_bf16(z, uout_t, bias, epi, T_, L.d_out, L.r2, y, status, st, ho);
+}
+
+// A helper CTA has about the time of one token tile of the in/core kernel: the tiles it can take follow from the two
+// kernels' FLOPs per tile, with a margin because the in/core kernel runs at a lower rate than the GEMM.
+void plan_out_handoff(const tmoe_layer_t &L, int64_t T, int sms, OutHandoff *h) {
+  *h = OutHandoff{};
+  static const bool off = []() { const char *e = getenv("TMOE_HANDOFF"); return e && atoi(e) == 0; }();
+  if (off || sms <= 0) return;
+  const int64_t token_tiles = (T + OM - 1) / OM;
+  const int tail = (int)(token_tiles % sms);
+  if (token_tiles <= sms || tail == 0) return;
+  const int helpers = sms - tail;
+  if (helpers < 4) return;
+  const double e_pad = (double)align_up(L.n_experts, 16);
+  const double f_in = 128.0 * (2.0 * L.d_in * (L.r3 + e_pad) + 2.0 * L.r3 * L.r1 * (double)L.r2);
+  const double f_out = 2.0 * 128.0 * 256.0 * L.r2;
+  const int per_helper = (int)(0.85 * f_in / f_out);
+  const int num_n = (L.d_out + ON - 1) / ON;
+  int m_tiles = (int)((int64_t)helpers * per_helper / num_n);
+  if (m_tiles > sms) m_tiles = sms;                      // only tiles of the first wave
+  if (m_tiles > kMaxHandoffTiles) m_tiles = kMaxHandoffTiles;
+  if (m_tiles > T / OM) m_tiles = (int)(T / OM);         // whole tiles only
+  m_tiles &= ~1;
+  if (m_tiles < 2) return;
+  h->m_tiles = m_tiles;
+  h->n_helpers = helpers;
 }
 
 }  // namespace tmoe

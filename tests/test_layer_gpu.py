@@ -111,6 +111,58 @@ def test_tensor_path_matches_oracle(shape, T):
     assert torch.equal(m(x.cuda()), y)
 
 
+HANDOFF_SHAPES = [
+    # more 128-token tiles than SMs, with a partial last wave: the in/core grid is padded with helper CTAs that run
+    # out-projection tiles of the first wave's token tiles (tmoe_handoff_plan)
+    (LayerShape(128, 64, 16, 2, 4, 64, 128, 1e-6), 20037),
+    (LayerShape(256, 520, 8, 2, 8, 128, 256, 1e-6), 19333),
+]
+
+
+@pytest.mark.parametrize("shape,T", HANDOFF_SHAPES)
+def test_helper_ctas_hand_off(shape, T):
+    """Forward with helper CTAs vs the oracle, and bit-for-bit vs the two stages called separately (no helpers there)."""
+    import ctypes as C
+    from mamba_tuckermoe_b200 import _lib
+    from gpu_util import layer_struct
+    lib = _lib.load()
+    nh, nt = C.c_int32(0), C.c_int32(0)
+    L = layer_struct(shape, torch.bfloat16)
+    assert lib.tmoe_handoff_plan(C.byref(L), T, C.byref(nh), C.byref(nt)) == 0
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    if (T + 127) // 128 <= sms:
+        pytest.skip("this device has more SMs than the case has token tiles")
+    assert nh.value > 0 and nt.value >= 2, "the case is meant to exercise the hand-off"
+    x, f = _tensor_case(shape, T, seed=77)
+    m = build_module(shape, f, torch.bfloat16, path=PATH_TENSOR)
+    xd = x.cuda()
+    y, taps = m.forward_with_routing(xd)
+    torch.cuda.synchronize()
+    assert read_device_status() == (0, 0, 0, 0)
+    y_ref, rt = layer_forward(x, f, shape.top_k, shape.eps, return_taps=True, chunk_tokens=1024)
+    check_against(y, taps, y_ref, rt["idx"], rt["scores"], torch.bfloat16, x, f, shape)
+    # a second call reuses the hand-off words (cleared by the out-projection kernel of the first)
+    y2 = m(xd)
+    torch.cuda.synchronize()
+    assert torch.equal(y2, y)
+    assert read_device_status() == (0, 0, 0, 0)
+    # the stage entry points never use helpers: same kernels, same arithmetic per output tile
+    from gpu_util import factors_struct, alloc_workspace, alloc_prepared, cuda_stream_ptr
+    fd = {k: v.cuda() for k, v in f.items()}
+    F = factors_struct(fd)
+    ws = alloc_workspace(lib, L, T, PATH_TENSOR)
+    prep = alloc_prepared(lib, L, F)
+    z = torch.empty(T, shape.r2, dtype=torch.bfloat16, device="cuda")
+    y3 = torch.empty(T, shape.d_out, dtype=torch.bfloat16, device="cuda")
+    c = taps[2].float().contiguous()
+    assert lib.tmoe_in_core(C.byref(L), C.byref(F), prep.data_ptr(), xd.data_ptr(), T, c.data_ptr(), z.data_ptr(),
+                            ws.data_ptr(), ws.numel(), PATH_TENSOR, cuda_stream_ptr()) == 0
+    assert lib.tmoe_out(C.byref(L), C.byref(F), prep.data_ptr(), z.data_ptr(), T, y3.data_ptr(), None, ws.data_ptr(),
+                        ws.numel(), PATH_TENSOR, cuda_stream_ptr()) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(y3, y.reshape(T, shape.d_out))
+
+
 DECODE_SHAPES = [
     (LayerShape(1536, 2304, 8, 2, 4, 256, 1024, 1e-6), 1),
     (LayerShape(1536, 2304, 8, 2, 4, 256, 1024, 1e-6), 8),
