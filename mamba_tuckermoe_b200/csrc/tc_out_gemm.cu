@@ -343,7 +343,9 @@ int launch_tc_out(const tmoe_layer_t &L, const void *z, const void *uout_t, cons
 }
 
 // A helper CTA has about the time of one token tile of the in/core kernel: the tiles it can take follow from the two
-// kernels' FLOPs per tile, with a margin because the in/core kernel runs at a lower rate than the GEMM.
+// kernels' FLOPs per tile, with a margin (measured on the prefill configuration: 3-4 tiles per helper gain 1.5 %, 5 lose
+// it again because the helpers then outlast the last wave; TMOE_HANDOFF_SCALE overrides the margin, TMOE_HANDOFF=0 turns
+// the hand-off off).
 void plan_out_handoff(const tmoe_layer_t &L, int64_t T, int sms, OutHandoff *h) {
   *h = OutHandoff{};
   static const bool off = []() { const char *e = getenv("TMOE_HANDOFF"); return e && atoi(e) == 0; }();
@@ -356,7 +358,8 @@ void plan_out_handoff(const tmoe_layer_t &L, int64_t T, int sms, OutHandoff *h) 
   const double e_pad = (double)align_up(L.n_experts, 16);
   const double f_in = 128.0 * (2.0 * L.d_in * (L.r3 + e_pad) + 2.0 * L.r3 * L.r1 * (double)L.r2);
   const double f_out = 2.0 * 128.0 * 256.0 * L.r2;
-  const int per_helper = (int)(0.85 * f_in / f_out);
+  static const double scale = []() { const char *e = getenv("TMOE_HANDOFF_SCALE"); return e ? atof(e) : 0.7; }();
+  const int per_helper = (int)(scale * f_in / f_out);
   const int num_n = (L.d_out + ON - 1) / ON;
   int m_tiles = (int)((int64_t)helpers * per_helper / num_n);
   if (m_tiles > sms) m_tiles = sms;                      // only tiles of the first wave
