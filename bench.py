@@ -53,7 +53,7 @@ for _e in (8, 64, 256, 1024):
                                           f"sweep bf16 T=16384 d_in=1536 d_out=2304 E={_e} top{_k} r=(4,256,1024)")
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised in
 # profiles/ncu_full_tc_kernels_prefill_cfg2.txt (same workload, same kernels); None where no capture exists.
-NCU_TRAFFIC_BYTES = {("cfg2", "tc_out_gemm"): 71_887_616 + 98_201_856, ("cfg2", "tc_in_core"): 104_485_120 + 21_466_112}
+NCU_TRAFFIC_BYTES = {("cfg2", "tc_out_gemm"): 67_702_016 + 89_337_344, ("cfg2", "tc_in_core"): 110_617_344 + 34_054_400}
 N_INPUT_SETS = 4  # rotating x buffers so that no step re-reads the previous step's lines from L2
 
 
