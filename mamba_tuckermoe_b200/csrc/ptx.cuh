@@ -96,6 +96,13 @@ __device__ __forceinline__ void mbar_wait_or_exit(uint32_t bar, uint32_t parity,
   if (!mbar_try_wait(bar, parity)) mbar_wait_slow_or_exit(bar, parity, status, kernel_id, tag);
 }
 
+// ---------------- programmatic dependent launch ----------------
+// A kernel launched with cudaLaunchAttributeProgrammaticStreamSerialization may start once every CTA of the kernel before
+// it in the stream has executed griddep_launch_dependents (or exited); griddep_wait then blocks until that kernel has
+// completed and its writes are visible.  Both are no-ops in a kernel launched without the attribute / without a dependent.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---------------- fences ----------------
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }

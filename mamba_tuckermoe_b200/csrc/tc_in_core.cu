@@ -116,6 +116,9 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                   const __grid_constant__ OutHelperCfg hc) {
   constexpr int N2 = 256 / R1;
   extern __shared__ uint8_t smem_raw[];
+  // every CTA of this grid is running once the last one has said this: the next kernel of the stream (the out-projection)
+  // may then take SMs as they free up and do its set-up while this grid drains
+  griddep_launch_dependents();
   if ((int)blockIdx.x >= p.n_token_ctas) {
     // grid padding: this CTA would idle during the last wave; it computes out-projection tiles of finished token tiles
     tc_out_body(&hc.tmA, &hc.tmB, &hc.tmY, hc.p, (int)blockIdx.x - p.n_token_ctas, hc.n_helpers, hc.n_tiles, smem_raw);

@@ -104,7 +104,7 @@ __device__ __forceinline__ bool rows_ready_wait(const uint32_t *flags, uint32_t 
 // Must be entered by all O_THREADS threads of a CTA that holds O_SMEM_BYTES of dynamic shared memory and no TMEM.
 __device__ __forceinline__ void tc_out_body(const CUtensorMap *tmA, const CUtensorMap *tmB, const CUtensorMap *tmY,
                                             const OutParams &p, int tile_first, int tile_step, int tile_end,
-                                            uint8_t *smem_raw) {
+                                            uint8_t *smem_raw, bool dependent = false) {
   __shared__ __align__(8) uint64_t bar_full[OSTAGES], bar_empty[OSTAGES], bar_tfull[2], bar_tempty[2];
   __shared__ uint32_t tmem_base_s;
 
@@ -124,6 +124,8 @@ __device__ __forceinline__ void tc_out_body(const CUtensorMap *tmA, const CUtens
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_s;
+  // the barriers, the TMEM columns and the tensor-map prefetches above do not depend on the kernel that produces A
+  if (dependent) griddep_wait();
 
   const int KB = (p.K + OKB - 1) / OKB;
 #ifdef TMOE_TRACE

@@ -57,9 +57,10 @@ __global__ void __launch_bounds__(O_THREADS, 1)
 tc_out_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
               const __grid_constant__ CUtensorMap tmY, OutParams p) {
   extern __shared__ uint8_t smem_raw[];
-  if (p.ready_clear && blockIdx.x == 0)   // the hand-off flags of this forward have served (the kernel that set them is complete)
+  tc_out_body(&tmA, &tmB, &tmY, p, p.tile_begin + (int)blockIdx.x, (int)gridDim.x, p.num_m * p.num_n, smem_raw, true);
+  // the hand-off flags of this forward have served: the kernel that set and read them is complete (griddep_wait in the body)
+  if (p.ready_clear && blockIdx.x == 0)
     for (int i = threadIdx.x; i < p.ready_words; i += blockDim.x) p.ready_clear[i] = 0u;
-  tc_out_body(&tmA, &tmB, &tmY, p, p.tile_begin + (int)blockIdx.x, (int)gridDim.x, p.num_m * p.num_n, smem_raw);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -86,8 +87,6 @@ tc_out_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t rank = cluster_ctarank();
   const int pair_id = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-  if (p.ready_clear && blockIdx.x == 0)
-    for (int i = threadIdx.x; i < p.ready_words; i += blockDim.x) p.ready_clear[i] = 0u;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < P_STAGES; ++s) { mbar_init(smem_u32(&bar_full[s]), 1); mbar_init(smem_u32(&bar_empty[s]), 1); }
@@ -104,6 +103,9 @@ tc_out_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   cluster_wait();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_s;
+  griddep_wait();   // everything above is independent of the kernel that produces A
+  if (p.ready_clear && blockIdx.x == 0)
+    for (int i = threadIdx.x; i < p.ready_words; i += blockDim.x) p.ready_clear[i] = 0u;
 
   const int num_tiles = p.num_m * p.num_n;  // num_m counts 256-row tiles here
   const int KB = (p.K + OKB - 1) / OKB;
@@ -260,6 +262,21 @@ tc_out_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   }
 }
 
+// Launch that may begin while the previous kernel of the stream is draining (programmatic dependent launch): the GEMM
+// kernels do their set-up, then griddep_wait() before they touch anything another kernel produced.
+template <typename Kern>
+static cudaError_t launch_dependent(Kern kern, int grid, int smem, cudaStream_t st, const CUtensorMap &a, const CUtensorMap &b,
+                                    const CUtensorMap &y, const OutParams &p) {
+  static const bool off = []() { const char *e = getenv("TMOE_PDL"); return e && atoi(e) == 0; }();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid); cfg.blockDim = dim3(O_THREADS); cfg.dynamicSmemBytes = (size_t)smem; cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at; cfg.numAttrs = off ? 0 : 1;
+  return cudaLaunchKernelEx(&cfg, kern, a, b, y, p);
+}
+
 // y[M, N] (bf16) = A[M, K] (bf16, row-major) @ B_t[N, K]^T (bf16, K-major) + bias[N] (fp32, optional),
 // then the optional OutEpilogue tail.  N and K multiples of 8.
 int launch_tc_gemm_bf16(const void *A, const void *B_t, const float *bias, const OutEpilogue &epi, int64_t M, int N,
@@ -319,7 +336,7 @@ int launch_tc_gemm_bf16(const void *A, const void *B_t, const float *bias, const
     }
     int pairs = dev < 64 ? max_pairs[dev] : sms / 2;
     if (tiles2 < pairs) pairs = tiles2;
-    tc_out_pair_kernel<<<2 * pairs, O_THREADS, P_SMEM_BYTES, st>>>(tmA, tmBh, tmY, q);
+    if (launch_dependent(tc_out_pair_kernel, 2 * pairs, P_SMEM_BYTES, st, tmA, tmBh, tmY, q) != cudaSuccess) return TMOE_ERR_CUDA;
     count_launch();
     return launch_status();
   }
@@ -332,7 +349,7 @@ int launch_tc_gemm_bf16(const void *A, const void *B_t, const float *bias, const
   if (ho && ho->n_helpers > 0) { p.tile_begin = ho->m_tiles * p.num_n; p.ready_clear = ho->ready; p.ready_words = ho->m_tiles * 8; }
   const int tiles = p.num_m * p.num_n - p.tile_begin;
   const int grid = tiles < sms ? tiles : sms;
-  tc_out_kernel<<<grid, O_THREADS, O_SMEM_BYTES, st>>>(tmA, tmB, tmY, p);
+  if (launch_dependent(tc_out_kernel, grid, O_SMEM_BYTES, st, tmA, tmB, tmY, p) != cudaSuccess) return TMOE_ERR_CUDA;
   count_launch();
   return launch_status();
 }

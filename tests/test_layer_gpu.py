@@ -114,7 +114,7 @@ def test_tensor_path_matches_oracle(shape, T):
 HANDOFF_SHAPES = [
     # more 128-token tiles than SMs, with a partial last wave: the in/core grid is padded with helper CTAs that run
     # out-projection tiles of the first wave's token tiles (tmoe_handoff_plan)
-    (LayerShape(128, 64, 16, 2, 4, 64, 128, 1e-6), 20037),
+    (LayerShape(256, 64, 16, 2, 4, 64, 128, 1e-6), 20037),
     (LayerShape(256, 520, 8, 2, 8, 128, 256, 1e-6), 19333),
 ]
 
