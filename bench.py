@@ -325,7 +325,7 @@ def main():
             "bound": "hbm", "kernel": "decode forward (3 kernels + clear)", "achieved": d["gbs_cold"],
             "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": d["gbs_cold"] / peaks["hbm_gbs"], "traffic": None,
             "peak_source": f"{peaks['source']} (copy bandwidth)", "bytes_per_call": d["bytes"],
-            "us_per_call_cold_l2": d["us_cold"], "us_per_call_warm": d["us_warm"], "us_per_call_graph": d["us_graph"],
+            "us_per_call_cold_l2": d["us_cold"], "us_per_call_warm": d["us_warm"], "us_per_call_graph": d["us_graph"], "us_per_call_graph_24_layers": d["us_graph_24_layers"],
         }
     else:
         roofline = {
@@ -421,11 +421,42 @@ def decode_times(lib, _lib, layer, shape, dtype, x, T, reps=30):
         torch.cuda.current_stream().wait_stream(side)
     except Exception as e:  # graph capture is a convenience measurement, not the product path
         us_graph = None
+    # the same graph measurement with a different factor set per call, as in a decode step that walks through many
+    # layers: 24 copies of the prepared buffer (> L2), so every call streams its factors from HBM
+    us_graph_layers = None
+    try:
+        n_layers = 24
+        preps = [prep.clone() for _ in range(n_layers)]
+        wss = [_lib.alloc_workspace(L, T, 3) for _ in range(n_layers)]
+
+        def call_layer(i):
+            rc = lib.tmoe_forward(C.byref(L), C.byref(F), preps[i].data_ptr(), x.data_ptr(), T, y.data_ptr(), None,
+                                  wss[i].data_ptr(), wss[i].numel(), 3, _lib.current_stream_ptr())
+            assert rc == 0, _lib.status_string(rc)
+
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            call_layer(0)
+            g2 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g2, stream=side):
+                for i in range(n_layers):
+                    call_layer(i)
+            g2.replay(); side.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(side)
+            for _ in range(5):
+                g2.replay()
+            b.record(side); side.synchronize()
+            us_graph_layers = a.elapsed_time(b) * 1e3 / (5 * n_layers)
+        torch.cuda.current_stream().wait_stream(side)
+    except Exception as e:
+        us_graph_layers = None
     es = x.element_size()
     factor_bytes = shape.factor_elems() * es
     alg_bytes = factor_bytes + T * (shape.d_in + shape.d_out) * es
-    return {"us_cold": us_cold, "us_warm": us_warm, "us_graph": us_graph, "bytes": alg_bytes,
-            "gbs_cold": alg_bytes / us_cold / 1e3}
+    return {"us_cold": us_cold, "us_warm": us_warm, "us_graph": us_graph, "us_graph_24_layers": us_graph_layers,
+            "bytes": alg_bytes, "gbs_cold": alg_bytes / us_cold / 1e3}
 
 
 def per_kernel_times(lib, _lib, layer, shape, dtype, x, T, path, reps=20):

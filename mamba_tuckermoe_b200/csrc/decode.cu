@@ -12,6 +12,8 @@
 #include "common.cuh"
 #include "kernels.h"
 #include "routing.cuh"
+#include "ptx.cuh"
+#include <cstdlib>
 
 namespace tmoe {
 
@@ -36,6 +38,27 @@ __device__ __forceinline__ float dot8(const float (&a)[8], const float (&b)[8]) 
 #pragma unroll
   for (int q = 0; q < 8; ++q) s = fmaf(a[q], b[q], s);
   return s;
+}
+
+// One warp asks L2 for [p, p + bytes) (128-byte lines).  Used for weight rows before griddep_wait(): they do not depend on
+// the previous kernel, so their trip from HBM overlaps that kernel's tail.
+__device__ __forceinline__ void warp_prefetch_l2(const void *p, int bytes, int lane) {
+  const char *c = reinterpret_cast<const char *>(p);
+  for (int o = lane * 128; o < bytes; o += 32 * 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(c + o));
+}
+
+// Launch that may begin while the previous kernel of the stream drains (programmatic dependent launch); the kernel calls
+// ptx::griddep_wait() before it reads what that kernel wrote.  TMOE_PDL=0 turns the attribute off.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
+  static const bool off = []() { const char *e = getenv("TMOE_PDL"); return e && atoi(e) == 0; }();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at; cfg.numAttrs = off ? 0 : 1;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 
 // Sums N per-lane partial values over the warp.  On return v[0] of lane l holds the total of
@@ -69,6 +92,7 @@ __global__ void __launch_bounds__(kDecWarps * 32)
 decode_inproj_kernel(const bf16 *__restrict__ x, const bf16 *__restrict__ uin_t, const bf16 *__restrict__ wr, int T,
                      int d_in, int r3, int E, float *__restrict__ h_raw, float *__restrict__ scores) {
   __shared__ __align__(16) bf16 xs[TMAX][kKSlice];
+  ptx::griddep_launch_dependents();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int k0 = blockIdx.y * kKSlice;
   // stage the K slice of all token rows (zeros beyond T or d_in)
@@ -106,6 +130,66 @@ decode_inproj_kernel(const bf16 *__restrict__ x, const bf16 *__restrict__ uin_t,
   }
 }
 
+// In-projection for T <= 8: every warp owns one column of h / the scores and the whole contraction, so there is no
+// split-K, no atomics and nothing to clear beforehand (one launch fewer per call than the split-K form).  The few token
+// rows sit in shared memory; a lane's weight loads of one batch are all issued before the first is used.
+template <int TMAX>
+__global__ void __launch_bounds__(kDecWarps * 32)
+decode_inproj_fullk_kernel(const bf16 *__restrict__ x, const bf16 *__restrict__ uin_t, const bf16 *__restrict__ wr, int T,
+                           int d_in, int r3, int E, float *__restrict__ h_raw, float *__restrict__ scores) {
+  extern __shared__ __align__(16) uint8_t dsm[];
+  bf16 *xs = reinterpret_cast<bf16 *>(dsm);  // [TMAX][d_in]
+  ptx::griddep_launch_dependents();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n = blockIdx.x * kDecWarps + warp;
+  const bf16 *row = nullptr;
+  if (n < r3 + E) {
+    row = (n < r3) ? uin_t + (int64_t)n * d_in : wr + (int64_t)(n - r3) * d_in;
+    warp_prefetch_l2(row, d_in * 2, lane);
+  }
+  ptx::griddep_wait();  // x may come from the kernel before this one
+  for (int i = threadIdx.x; i < TMAX * (d_in / 8); i += blockDim.x) {
+    const int t = i / (d_in / 8), kk = (i % (d_in / 8)) * 8;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (t < T) v = __ldg(reinterpret_cast<const uint4 *>(x + (int64_t)t * d_in + kk));
+    *reinterpret_cast<uint4 *>(&xs[t * d_in + kk]) = v;
+  }
+  __syncthreads();
+  if (!row) return;
+  float acc[TMAX];
+#pragma unroll
+  for (int t = 0; t < TMAX; ++t) acc[t] = 0.f;
+  constexpr int B = 6;  // weight loads in flight per lane
+  for (int k0 = lane * 8; k0 < d_in; k0 += 256 * B) {
+    uint4 wv[B];
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+      const int k = k0 + b * 256;
+      wv[b] = (k < d_in) ? __ldg(reinterpret_cast<const uint4 *>(row + k)) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+      const int k = k0 + b * 256;
+      if (k < d_in) {
+        float w8[8];
+        unpack8(wv[b], w8);
+#pragma unroll
+        for (int t = 0; t < TMAX; ++t) {
+          float x8[8];
+          unpack8(*reinterpret_cast<const uint4 *>(&xs[t * d_in + k]), x8);
+          acc[t] += dot8(x8, w8);
+        }
+      }
+    }
+  }
+  warp_reduce_many<TMAX>(acc, lane);
+  const int t = lane % TMAX;
+  if (lane < TMAX && t < T) {
+    if (n < r3) h_raw[(int64_t)t * r3 + n] = acc[0];
+    else scores[(int64_t)t * E + (n - r3)] = acc[0];
+  }
+}
+
 // ------------------------------------------------------------------------------------------
 template <int TMAX, int R1, int KMAX>
 __global__ void __launch_bounds__(kDecWarps * 32)
@@ -118,6 +202,16 @@ decode_core_kernel(const float *__restrict__ h_raw, const float *__restrict__ sc
   bf16 *hw = reinterpret_cast<bf16 *>(dsm);                                  // [TMAX][r3]
   float *cs = reinterpret_cast<float *>(dsm + (size_t)TMAX * r3 * 2);       // [TMAX][R1]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  ptx::griddep_launch_dependents();
+  {
+    const int s_pf = blockIdx.x * kDecWarps + warp;  // this warp's core rows: r1 pieces of r3 values
+    if (s_pf < r2) {
+      const int j_pf = s_pf / N2;
+      const bf16 *rows_pf = g_t + ((int64_t)j_pf * 256 + (s_pf - j_pf * N2)) * r3;
+      for (int a = 0; a < R1; ++a) warp_prefetch_l2(rows_pf + (int64_t)a * N2 * r3, r3 * 2, lane);
+    }
+  }
+  ptx::griddep_wait();  // h_raw and scores come from the in-projection kernel
 
   // prologue (redundant per CTA, T is tiny): norm statistics, h*w -> bf16, routing, c' = c / rms
   for (int t = warp; t < TMAX; t += kDecWarps) {
@@ -193,6 +287,9 @@ decode_out_kernel(const bf16 *__restrict__ z, const bf16 *__restrict__ uout_t, c
   bf16 *zs = reinterpret_cast<bf16 *>(dsm);  // [TMAX][kc]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int n = blockIdx.x * kOutWarps + warp;
+  ptx::griddep_launch_dependents();
+  if (n < d_out) warp_prefetch_l2(uout_t + (int64_t)n * r2, r2 * 2, lane);
+  ptx::griddep_wait();  // z comes from the core kernel
   constexpr int NB = TMAX < 32 ? TMAX : 32;
   constexpr int NG = TMAX / NB;
   float acc[NG][NB];
@@ -246,22 +343,32 @@ template <int TMAX>
 int launch_decode_t(const tmoe_layer_t &L, const void *x, const char *pb, const PreparedLayout &P, int T, float *h_raw,
                     float *scores, void *z, int32_t *idx_out, float *gates_out, float *c_out, const OutEpilogue &epi,
                     void *y, cudaStream_t st) {
-  // h_raw and scores are adjacent in the workspace: one clear for the split-K atomics
-  const size_t clear_bytes = (size_t)((char *)(scores + (size_t)T * L.n_experts) - (char *)h_raw);
-  if (cudaMemsetAsync(h_raw, 0, clear_bytes, st) != cudaSuccess) return TMOE_ERR_CUDA;
   const int ncols = L.r3 + L.n_experts;
-  dim3 g1((ncols + kDecWarps * kInprojColsPerWarp - 1) / (kDecWarps * kInprojColsPerWarp), (L.d_in + kKSlice - 1) / kKSlice);
-  decode_inproj_kernel<TMAX><<<g1, kDecWarps * 32, 0, st>>>((const bf16 *)x, (const bf16 *)(pb + P.uin_t),
-                                                           (const bf16 *)(pb + P.wr_b), T, L.d_in, L.r3, L.n_experts,
-                                                           h_raw, scores);
+  cudaError_t e = cudaSuccess;
+  if (TMAX <= 8) {
+    const size_t smem1 = (size_t)TMAX * L.d_in * 2;
+    e = cudaFuncSetAttribute(decode_inproj_fullk_kernel<TMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
+    if (e == cudaSuccess)
+      e = launch_pdl(decode_inproj_fullk_kernel<TMAX>, dim3((ncols + kDecWarps - 1) / kDecWarps), dim3(kDecWarps * 32), smem1, st,
+                     (const bf16 *)x, (const bf16 *)(pb + P.uin_t), (const bf16 *)(pb + P.wr_b), T, L.d_in, L.r3,
+                     L.n_experts, h_raw, scores);
+    if (e != cudaSuccess) return TMOE_ERR_CUDA;
+  } else {
+    // h_raw and scores are adjacent in the workspace: one clear for the split-K atomics
+    const size_t clear_bytes = (size_t)((char *)(scores + (size_t)T * L.n_experts) - (char *)h_raw);
+    if (cudaMemsetAsync(h_raw, 0, clear_bytes, st) != cudaSuccess) return TMOE_ERR_CUDA;
+    dim3 g1((ncols + kDecWarps * kInprojColsPerWarp - 1) / (kDecWarps * kInprojColsPerWarp), (L.d_in + kKSlice - 1) / kKSlice);
+    decode_inproj_kernel<TMAX><<<g1, kDecWarps * 32, 0, st>>>((const bf16 *)x, (const bf16 *)(pb + P.uin_t),
+                                                             (const bf16 *)(pb + P.wr_b), T, L.d_in, L.r3, L.n_experts,
+                                                             h_raw, scores);
+  }
   const size_t smem2 = (size_t)TMAX * L.r3 * 2 + (size_t)TMAX * L.r1 * 4;
   const dim3 g2((L.r2 + kDecWarps - 1) / kDecWarps);
-  cudaError_t e = cudaSuccess;
 #define TMOE_DC(R, K)                                                                                              \
   do {                                                                                                             \
     e = cudaFuncSetAttribute(decode_core_kernel<TMAX, R, K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2); \
     if (e == cudaSuccess)                                                                                          \
-      decode_core_kernel<TMAX, R, K><<<g2, kDecWarps * 32, smem2, st>>>(                                           \
+      e = launch_pdl(decode_core_kernel<TMAX, R, K>, g2, dim3(kDecWarps * 32), smem2, st,                           \
           h_raw, scores, (const float *)(pb + P.normw), (const float *)(pb + P.uexp), (const bf16 *)(pb + P.g_t), T, \
           L.r3, L.r2, L.n_experts, L.top_k, L.eps, (bf16 *)z, idx_out, gates_out, c_out, router_cfg(L));                           \
   } while (0)
@@ -278,9 +385,10 @@ int launch_decode_t(const tmoe_layer_t &L, const void *x, const char *pb, const 
   const size_t smem3 = (size_t)TMAX * kc * 2;
   e = cudaFuncSetAttribute(decode_out_kernel<TMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem3);
   if (e != cudaSuccess) return TMOE_ERR_CUDA;
-  decode_out_kernel<TMAX><<<(L.d_out + kOutWarps - 1) / kOutWarps, kOutWarps * 32, smem3, st>>>(
+  e = launch_pdl(decode_out_kernel<TMAX>, dim3((L.d_out + kOutWarps - 1) / kOutWarps), dim3(kOutWarps * 32), smem3, st,
       (const bf16 *)z, (const bf16 *)(pb + P.uout_t), (const float *)(pb + P.bias), (const bf16 *)epi.residual,
       (const bf16 *)epi.layer_scale, (const bf16 *)epi.silu_gate, T, L.r2, L.d_out, (bf16 *)y);
+  if (e != cudaSuccess) return TMOE_ERR_CUDA;
   count_launch(3);
   return launch_status();
 }
