@@ -478,14 +478,21 @@ class TuckerMoE(nn.Module):
 
     @torch.no_grad()
     def forward_host(self, x_host: torch.Tensor, out: Optional[torch.Tensor] = None,
-                     chunk_tokens: int = 8192) -> torch.Tensor:
+                     chunk_tokens: int = 4096, pipelined: bool = False) -> torch.Tensor:
         """Forward for activations that live in host memory: ``x_host`` (..., d_in) on the CPU (pinned
         memory for full copy speed) -> CPU tensor (..., d_out).
 
         The token range is cut into chunks; the host->device copy of chunk i+1, the kernels of chunk i
         and the device->host copy of chunk i-1 run on three streams, so one call costs about the longer
         of the two PCIe transfers instead of their sum plus the compute.  The result is complete when
-        the current stream has caught up (``torch.cuda.current_stream().synchronize()``)."""
+        the current stream has caught up (``torch.cuda.current_stream().synchronize()``).
+
+        ``pipelined=True`` is for a loop of calls: the host->device copies no longer wait for the work already
+        queued on the current stream (which includes the previous call's device->host copies), so the input
+        copy of one call overlaps the output copy of the one before and a step costs about one PCIe direction.
+        The caller then guarantees that ``x_host`` is ready on the host when the call is made (it was not
+        filled by a copy still in flight on the current stream) and passes a different ``out`` if the previous
+        result has not been consumed yet."""
         dev = self.U_in.device
         if dev.type != "cuda":
             raise RuntimeError("tmoe_b200: move the layer to a CUDA device first (no CPU fallback)")
@@ -502,13 +509,30 @@ class TuckerMoE(nn.Module):
             return out.reshape(*lead, d_out)
         with torch.cuda.device(dev):
             cur = torch.cuda.current_stream(dev)
-            if getattr(self, "_host_streams", None) is None or self._host_streams[0].device != dev:
-                self._host_streams = (torch.cuda.Stream(dev), torch.cuda.Stream(dev))
-            h2d, d2h = self._host_streams
-            h2d.wait_stream(cur)
+            st = getattr(self, "_host_state", None)
+            if st is None or st["dev"] != dev:
+                # two device input buffers used in turn (the copy of one call may run under the kernels of the one
+                # before), each with the event after which its last readers are done
+                st = {"dev": dev, "streams": (torch.cuda.Stream(dev), torch.cuda.Stream(dev)), "buf": [None, None],
+                      "free": [None, None], "n": 0}
+                self._host_state = st
+            h2d, d2h = st["streams"]
+            b = st["n"] & 1
+            st["n"] += 1
+            xb = st["buf"][b]
+            if xb is None or xb.dtype != xh.dtype or xb.numel() < T * d_in:
+                if xb is not None:
+                    xb.record_stream(h2d)
+                xb = torch.empty(T * d_in, dtype=xh.dtype, device=dev)
+                st["buf"][b] = xb
+                st["free"][b] = None
+                h2d.wait_stream(cur)          # a fresh block from the caching allocator is ordered on the current stream
+            elif not pipelined:
+                h2d.wait_stream(cur)
+            if st["free"][b] is not None:
+                h2d.wait_event(st["free"][b])  # the kernels of the call that last read this buffer
             d2h.wait_stream(cur)
-            x_dev = torch.empty((T, d_in), dtype=xh.dtype, device=dev)
-            x_dev.record_stream(h2d)
+            x_dev = xb[: T * d_in].view(T, d_in)
             step = max(1, int(chunk_tokens))
             copied = []
             for lo in range(0, T, step):
@@ -527,6 +551,7 @@ class TuckerMoE(nn.Module):
                     d2h.wait_event(done)
                     oh[lo:hi].copy_(y, non_blocking=True)
                 y.record_stream(d2h)
+            st["free"][b] = done
             cur.wait_stream(d2h)
         return out.reshape(*lead, d_out)
 

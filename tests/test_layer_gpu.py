@@ -308,6 +308,27 @@ def test_forward_host_equals_device_forward(T, chunk):
     assert y2.shape == (1, T, shape.d_out) and rel_fro(y2.float().reshape(T, -1), y_host.float()) < 5e-3
 
 
+def test_forward_host_pipelined_loop():
+    """A loop of pipelined host calls (input copy of one call under the output copy of the one before, two device input
+    buffers used in turn, growing token counts) returns, per call, what the plain call returns."""
+    shape = LayerShape(256, 264, 8, 2, 4, 128, 256, 1e-5)
+    m = None
+    xs, outs = [], []
+    for i, T in enumerate([500, 1300, 900, 1300, 70]):
+        x, f = _tensor_case(shape, T, seed=300 + i)
+        if m is None:
+            m = build_module(shape, make_factors(shape, 300, torch.bfloat16, 0.02, 0.1), torch.bfloat16)
+        xs.append(x.pin_memory())
+        outs.append(torch.empty(T, shape.d_out, dtype=torch.bfloat16).pin_memory())
+    for xh, out in zip(xs, outs):
+        m.forward_host(xh, out=out, chunk_tokens=384, pipelined=True)
+    torch.cuda.current_stream().synchronize()
+    for xh, out in zip(xs, outs):
+        ref = m.forward_host(xh, chunk_tokens=384)
+        torch.cuda.current_stream().synchronize()
+        assert torch.equal(ref, out)
+
+
 @pytest.mark.parametrize("dtype,T", [(torch.float32, 50), (torch.bfloat16, 300), (torch.bfloat16, 7)])
 def test_rms_norm_matches_reference_formula(dtype, T):
     g = torch.Generator().manual_seed(5)
