@@ -199,8 +199,8 @@ def main():
 
     import mamba_tuckermoe_b200 as pkg
     from mamba_tuckermoe_b200 import _lib
-    from oracle.tucker_moe_oracle import (BENCH_SHAPES, ZIPF_SHAPES, apply_zipf_router_bias, make_factors,
-                                          make_tokens)
+    from mamba_tuckermoe_b200.synthetic import (BENCH_SHAPES, ZIPF_SHAPES, apply_zipf_router_bias, make_factors,
+                                                make_tokens)
 
     shape_key, T, desc = WORKLOADS[args.workload]
     shape, _, dtype, seed, rstd = BENCH_SHAPES[shape_key]

@@ -65,6 +65,21 @@ WsLayout ws_layout(const tmoe_layer_t &L, int64_t T, int rpath) {
   return W;
 }
 
+// SM count of the calling thread's current device, looked up once per device (0 on error).
+int current_device_sms() {
+  static std::atomic<int> cache[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  if (dev >= 0 && dev < 64) {
+    const int c = cache[dev].load(std::memory_order_relaxed);
+    if (c > 0) return c;
+  }
+  int sms = 0;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+  if (dev >= 0 && dev < 64) cache[dev].store(sms, std::memory_order_relaxed);
+  return sms;
+}
+
 bool misaligned(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0; }
 
 int check_factors(const tmoe_factors_t *F) {
@@ -286,9 +301,8 @@ int tmoe_forward(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const
   // token tiles that do not fill whole waves of CTAs: pad the in/core grid with helper CTAs that run out-projection tiles
   OutHelperArgs helper{};
   {
-    int dev = 0, sms = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return TMOE_ERR_CUDA;
-    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return TMOE_ERR_CUDA;
+    const int sms = current_device_sms();
+    if (sms <= 0) return TMOE_ERR_CUDA;
     plan_out_handoff(L, T, sms, &helper.ho);
     if (helper.ho.n_helpers > 0) {
       static std::atomic<uint32_t> epoch_counter{1};
@@ -348,9 +362,8 @@ int tmoe_handoff_plan(const tmoe_layer_t *layer, int64_t T, int32_t *n_helper_ct
   if (!n_helper_ctas || !n_token_tiles) return TMOE_ERR_NULL;
   *n_helper_ctas = 0; *n_token_tiles = 0;
   if (T <= 0 || resolve(*layer, T, TMOE_PATH_AUTO) != TMOE_PATH_TENSOR) return TMOE_OK;
-  int dev = 0, sms = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return TMOE_ERR_CUDA;
-  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return TMOE_ERR_CUDA;
+  const int sms = current_device_sms();
+  if (sms <= 0) return TMOE_ERR_CUDA;
   OutHandoff h;
   plan_out_handoff(*layer, T, sms, &h);
   *n_helper_ctas = h.n_helpers; *n_token_tiles = h.m_tiles;
