@@ -169,12 +169,104 @@ def run_reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
+def run_decode_step(args, dev):
+    """The Tucker-MoE share of one decode step of the reference's language model (``pure_torch_mlx/model.py:390-397``,
+    block pattern ``config.py:35-42``): 24 Mamba blocks x (x_up_proj 1536->6144; out_proj 768->768 behind its pre-norm,
+    LayerScale + residual in the epilogue) and 6 transformer blocks x (ffn_gate, ffn_up 768->4608 on one normalised
+    input with silu(gate)*up in the epilogue; ffn_down 4608->768 with the residual) = 66 layer calls per token, T = 1,
+    the shipped ranks (r1, r2, r3) = (32, 512, 256), E = 8, top-2, every layer with its own factors (700 MB in all, so
+    each call streams its factors from HBM).  The SSM / attention arithmetic between the calls is not part of this
+    library: every layer gets a synthetic input of its shape.  The 66 calls are captured in one CUDA graph."""
+    import mamba_tuckermoe_b200 as pkg
+    from mamba_tuckermoe_b200 import _lib
+    from mamba_tuckermoe_b200.synthetic import LayerShape, make_factors
+    lib = _lib.load()
+    dtype = torch.bfloat16
+
+    def make(d_in, d_out, seed):
+        shape = LayerShape(d_in, d_out, 8, 2, 32, 256, 512, 1e-5)
+        m = pkg.TuckerMoE(d_in, d_out, pkg.TuckerMoEConfig(8, 2, 32, 512, 256, 1e-5))
+        f = make_factors(shape, seed, torch.float32, 0.02)
+        m.load_state_dict({"router.weight": f["router_w"], "U_in": f["U_in"], "inner_norm.weight": f["inner_norm_w"],
+                           "U_expert": f["U_expert"], "core": f["core"], "U_out": f["U_out"], "bias": f["bias"]})
+        return m.to(device=dev, dtype=dtype), shape
+
+    blocks, factor_bytes, flops = [], 0, 0
+    for b in range(30):
+        if b % 5 < 4:
+            layers = [make(1536, 6144, 5000 + 3 * b), make(768, 768, 5001 + 3 * b)]
+        else:
+            layers = [make(768, 4608, 5000 + 3 * b), make(768, 4608, 5001 + 3 * b), make(4608, 768, 5002 + 3 * b)]
+        blocks.append([m for m, _ in layers])
+        factor_bytes += sum(sh.factor_elems() * 2 for _, sh in layers)
+        flops += sum(sh.flops_per_token() for _, sh in layers)
+    n_calls = sum(len(b) for b in blocks)
+    g = torch.Generator(device="cpu").manual_seed(77)
+    x1536 = torch.randn(1, 1, 1536, generator=g).to(dev, dtype)
+    x768 = torch.randn(1, 1, 768, generator=g).to(dev, dtype)
+    norm_w = torch.ones(768, device=dev, dtype=dtype)
+    gamma = torch.full((768,), 0.1, device=dev, dtype=dtype)
+
+    def step():
+        acc = x768
+        for layers in blocks:
+            if len(layers) == 2:
+                layers[0](x1536)                                           # x_up_proj
+                acc = pkg.fused_out_proj(layers[1], acc, (norm_w, 1e-5), gamma)   # norm -> out_proj -> residual
+            else:
+                acc = pkg.fused_ffn(layers[0], layers[1], layers[2], acc, (norm_w, 1e-5), gamma)
+        return acc
+
+    with torch.no_grad():
+        for _ in range(3):
+            y = step()
+        torch.cuda.synchronize()
+        launches0 = lib.tmoe_launch_count()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for _ in range(args.steps):
+            y = step()
+        ev1.record(); torch.cuda.synchronize()
+        launches = lib.tmoe_launch_count() - launches0
+        us_eager = ev0.elapsed_time(ev1) * 1e3 / args.steps
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                y = step()
+            graph.replay(); side.synchronize()
+            a, b2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(side)
+            for _ in range(args.steps):
+                graph.replay()
+            b2.record(side); side.synchronize()
+            us_graph = a.elapsed_time(b2) * 1e3 / args.steps
+        torch.cuda.current_stream().wait_stream(side)
+    peaks = load_peaks()
+    line = {
+        "metric": "tucker_moe_decode_step_tokens_per_sec", "value": 1e6 / us_graph, "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": 3, "ms_per_step": us_graph / 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "decode_step: the 66 Tucker-MoE calls of one token of the reference LM (24 x {1536->6144, "
+                               "768->768} + 6 x {768->4608, 768->4608, 4608->768}), T=1, E=8 top2 r=(32,256,512), one CUDA graph",
+                   "layer_calls_per_token": n_calls, "l2": f"{factor_bytes / 1e6:.0f} MB of factors per token > 126 MB L2"},
+        "us_per_token_graph": us_graph, "us_per_token_eager": us_eager, "us_per_layer_call_graph": us_graph / n_calls,
+        "roofline": {"bound": "hbm", "kernel": "decode forward (3 kernels per layer call)", "achieved": factor_bytes / us_graph / 1e3,
+                     "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": factor_bytes / us_graph / 1e3 / peaks["hbm_gbs"],
+                     "traffic": None, "peak_source": f"{peaks['source']} (copy bandwidth)", "bytes_per_token": factor_bytes},
+        "flops_per_token": flops, "gpu_launches": int(launches),
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="cfg2", choices=list(WORKLOADS))
+    ap.add_argument("--workload", default="cfg2", choices=list(WORKLOADS) + ["decode_step"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=8)
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -196,6 +288,11 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
+
+    if args.workload == "decode_step":
+        if rank == 0:
+            run_decode_step(args, dev)
+        return
 
     import mamba_tuckermoe_b200 as pkg
     from mamba_tuckermoe_b200 import _lib
