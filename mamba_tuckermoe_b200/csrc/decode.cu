@@ -204,11 +204,12 @@ decode_core_kernel(const float *__restrict__ h_raw, const float *__restrict__ sc
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   ptx::griddep_launch_dependents();
   {
-    const int s_pf = blockIdx.x * kDecWarps + warp;  // this warp's core rows: r1 pieces of r3 values
+    constexpr int AC_PF = R1 < 8 ? R1 : 8, SPLIT_PF = R1 / AC_PF;
+    const int s_pf = blockIdx.x * (kDecWarps / SPLIT_PF) + warp / SPLIT_PF;  // this warp's core rows: AC pieces of r3 values
     if (s_pf < r2) {
       const int j_pf = s_pf / N2;
       const bf16 *rows_pf = g_t + ((int64_t)j_pf * 256 + (s_pf - j_pf * N2)) * r3;
-      for (int a = 0; a < R1; ++a) warp_prefetch_l2(rows_pf + (int64_t)a * N2 * r3, r3 * 2, lane);
+      for (int a = 0; a < AC_PF; ++a) warp_prefetch_l2(rows_pf + (int64_t)((warp % SPLIT_PF) * AC_PF + a) * N2 * r3, r3 * 2, lane);
     }
   }
   ptx::griddep_wait();  // h_raw and scores come from the in-projection kernel
@@ -244,9 +245,18 @@ decode_core_kernel(const float *__restrict__ h_raw, const float *__restrict__ sc
   }
   __syncthreads();
 
-  const int s = blockIdx.x * kDecWarps + warp;  // z column of this warp
-  if (s >= r2) return;
-  const int j = s / N2, sl = s - j * N2;
+  // A z column needs r1 core rows of r3 values.  Up to 8 slices fit a warp's registers at a time; with more slices
+  // (r1 = 16, 32) SPLIT warps share a column, each with its own 8 slices, and their partial sums meet in shared memory:
+  // 2-4 x as many CTAs stream the core tensor (8.4 MB at r1 = 32) than with one warp per column.
+  constexpr int AC = R1 < 8 ? R1 : 8;
+  constexpr int SPLIT = R1 / AC;
+  constexpr int CPB = kDecWarps / SPLIT;  // z columns per CTA
+  __shared__ float part[kDecWarps][32];
+  const int s = blockIdx.x * CPB + warp / SPLIT;  // z column of this warp
+  const int a0 = (warp % SPLIT) * AC;             // first core slice of this warp
+  const bool valid = s < r2;
+  const int sc = valid ? s : 0;
+  const int j = sc / N2, sl = sc - j * N2;
   const bf16 *rows = g_t + ((int64_t)j * 256 + sl) * r3;  // slice a is N2 rows further
 #pragma unroll
   for (int tb = 0; tb < TMAX; tb += 32) {
@@ -254,10 +264,8 @@ decode_core_kernel(const float *__restrict__ h_raw, const float *__restrict__ sc
     float acc[NB];
 #pragma unroll
     for (int t = 0; t < NB; ++t) acc[t] = 0.f;
-    constexpr int AC = R1 < 8 ? R1 : 8;  // core slices held in registers at a time
-    for (int k = lane * 8; k < r3; k += 256) {
-#pragma unroll 1
-      for (int a0 = 0; a0 < R1; a0 += AC) {
+    if (valid) {
+      for (int k = lane * 8; k < r3; k += 256) {
         float g8[AC][8];
 #pragma unroll
         for (int a = 0; a < AC; ++a)
@@ -273,7 +281,19 @@ decode_core_kernel(const float *__restrict__ h_raw, const float *__restrict__ sc
     }
     warp_reduce_many<NB>(acc, lane);
     const int t = tb + (lane % NB);
-    if (lane < NB && t < T) z[(int64_t)t * r2 + s] = __float2bfloat16_rn(acc[0]);
+    if (SPLIT == 1) {
+      if (valid && lane < NB && t < T) z[(int64_t)t * r2 + s] = __float2bfloat16_rn(acc[0]);
+    } else {
+      if (lane < NB) part[warp][lane] = acc[0];
+      __syncthreads();
+      if ((warp % SPLIT) == 0 && valid && lane < NB && t < T) {
+        float v = 0.f;
+#pragma unroll
+        for (int q = 0; q < SPLIT; ++q) v += part[warp + q][lane];
+        z[(int64_t)t * r2 + s] = __float2bfloat16_rn(v);
+      }
+      __syncthreads();
+    }
   }
 }
 
@@ -363,7 +383,9 @@ int launch_decode_t(const tmoe_layer_t &L, const void *x, const char *pb, const 
                                                              h_raw, scores);
   }
   const size_t smem2 = (size_t)TMAX * L.r3 * 2 + (size_t)TMAX * L.r1 * 4;
-  const dim3 g2((L.r2 + kDecWarps - 1) / kDecWarps);
+  const int split = L.r1 > 8 ? L.r1 / 8 : 1;      // warps per z column in decode_core_kernel
+  const int cpb = kDecWarps / split;
+  const dim3 g2((L.r2 + cpb - 1) / cpb);
 #define TMOE_DC(R, K)                                                                                              \
   do {                                                                                                             \
     e = cudaFuncSetAttribute(decode_core_kernel<TMAX, R, K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2); \
