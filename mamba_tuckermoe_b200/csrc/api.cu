@@ -269,8 +269,8 @@ int tmoe_forward(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const
   const tmoe_layer_t &L = *layer;
   WsLayout W = ws_layout(L, T, rp);
   if (workspace_bytes < W.total) return TMOE_ERR_WORKSPACE;
-  // the in-kernel pre-norm exists on the tensor-core path with the in-kernel router only
-  if (pre_norm && !(rp == TMOE_PATH_TENSOR && W.tc_router_fused)) return TMOE_ERR_UNSUPPORTED;
+  // the in-kernel pre-norm exists on the tensor-core path with the in-kernel router and on the decode path
+  if (pre_norm && !((rp == TMOE_PATH_TENSOR && W.tc_router_fused) || rp == TMOE_PATH_DECODE)) return TMOE_ERR_UNSUPPORTED;
   char *ws = reinterpret_cast<char *>(workspace);
   cudaStream_t st = (cudaStream_t)stream;
   int32_t *idx = (extras && extras->idx_out) ? extras->idx_out : reinterpret_cast<int32_t *>(ws + W.idx);
@@ -296,7 +296,7 @@ int tmoe_forward(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const
     const bool taps = extras && (extras->idx_out || extras->gates_out || extras->c_out);
     return launch_decode(L, x, prepared, P, T, reinterpret_cast<float *>(ws + W.h), scores, z,
                          taps ? extras->idx_out : nullptr, taps ? extras->gates_out : nullptr,
-                         taps ? extras->c_out : nullptr, epi, y, st);
+                         taps ? extras->c_out : nullptr, epi, y, st, pre_norm, pre_norm ? extras->pre_norm_eps : 0.f);
   }
   // token tiles that do not fill whole waves of CTAs: pad the in/core grid with helper CTAs that run out-projection tiles
   OutHelperArgs helper{};

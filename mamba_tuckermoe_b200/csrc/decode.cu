@@ -196,7 +196,8 @@ __global__ void __launch_bounds__(kDecWarps * 32)
 decode_core_kernel(const float *__restrict__ h_raw, const float *__restrict__ scores, const float *__restrict__ normw,
                    const float *__restrict__ uexp, const bf16 *__restrict__ g_t, int T, int r3, int r2, int E, int top_k,
                    float eps, bf16 *__restrict__ z, int32_t *__restrict__ idx_out, float *__restrict__ gates_out,
-                   float *__restrict__ c_out, RouterCfg rc) {
+                   float *__restrict__ c_out, RouterCfg rc, const bf16 *__restrict__ x, int d_in, int pre_norm,
+                   float pre_norm_eps) {
   constexpr int N2 = 256 / R1;
   extern __shared__ __align__(16) uint8_t dsm[];
   bf16 *hw = reinterpret_cast<bf16 *>(dsm);                                  // [TMAX][r3]
@@ -217,6 +218,19 @@ decode_core_kernel(const float *__restrict__ h_raw, const float *__restrict__ sc
   // prologue (redundant per CTA, T is tiny): norm statistics, h*w -> bf16, routing, c' = c / rms
   for (int t = warp; t < TMAX; t += kDecWarps) {
     if (t < T) {
+      // callers' pre-norm applied here: its weight is folded into the prepared U_in / router rows, so h_raw and the scores
+      // only lack the row's 1/rms(x) (same arithmetic as the tensor-core kernel's in-kernel pre-norm)
+      float inv_x = 1.f;
+      if (pre_norm) {
+        float sx = 0.f;
+        for (int i = lane * 8; i < d_in; i += 256) {
+          float x8[8];
+          unpack8(__ldg(reinterpret_cast<const uint4 *>(x + (int64_t)t * d_in + i)), x8);
+          sx += dot8(x8, x8);
+        }
+        sx = warp_sum(sx);
+        inv_x = 1.f / sqrtf(sx / (float)d_in + pre_norm_eps);
+      }
       float ss = 0.f;
       for (int i = lane; i < r3; i += 32) {
         const float v = h_raw[(int64_t)t * r3 + i];
@@ -224,12 +238,12 @@ decode_core_kernel(const float *__restrict__ h_raw, const float *__restrict__ sc
         hw[t * r3 + i] = __float2bfloat16_rn(v * normw[i]);
       }
       ss = warp_sum(ss);
-      const float inv_rms = 1.f / sqrtf(ss / (float)r3 + eps);
+      const float inv_rms = inv_x / sqrtf(inv_x * inv_x * ss / (float)r3 + eps);
       TopList<KMAX> sel;
       sel.init();
-      warp_select_topk<bf16, KMAX>(scores + (int64_t)t * E, E, top_k, lane, sel);
+      warp_select_topk<bf16, KMAX>(scores + (int64_t)t * E, E, top_k, lane, sel, inv_x);
       const bool tap = (blockIdx.x == 0);
-      const float z_all = rc.mode == 1 ? warp_softmax_denominator<bf16, float>(scores + (int64_t)t * E, E, lane, rc, sel.v[0]) : 1.f;
+      const float z_all = rc.mode == 1 ? warp_softmax_denominator<bf16, float>(scores + (int64_t)t * E, E, lane, rc, sel.v[0], inv_x) : 1.f;
       emit_token<bf16, KMAX, float>(sel, top_k, E, R1, uexp, 0, lane, tap && idx_out ? idx_out + (int64_t)t * top_k : nullptr,
                                     tap && gates_out ? gates_out + (int64_t)t * top_k : nullptr, cs + t * R1, rc, z_all);
       __syncwarp();
@@ -362,7 +376,7 @@ decode_out_kernel(const bf16 *__restrict__ z, const bf16 *__restrict__ uout_t, c
 template <int TMAX>
 int launch_decode_t(const tmoe_layer_t &L, const void *x, const char *pb, const PreparedLayout &P, int T, float *h_raw,
                     float *scores, void *z, int32_t *idx_out, float *gates_out, float *c_out, const OutEpilogue &epi,
-                    void *y, cudaStream_t st) {
+                    void *y, int pre_norm, float pre_norm_eps, cudaStream_t st) {
   const int ncols = L.r3 + L.n_experts;
   cudaError_t e = cudaSuccess;
   if (TMAX <= 8) {
@@ -392,7 +406,8 @@ int launch_decode_t(const tmoe_layer_t &L, const void *x, const char *pb, const 
     if (e == cudaSuccess)                                                                                          \
       e = launch_pdl(decode_core_kernel<TMAX, R, K>, g2, dim3(kDecWarps * 32), smem2, st,                           \
           h_raw, scores, (const float *)(pb + P.normw), (const float *)(pb + P.uexp), (const bf16 *)(pb + P.g_t), T, \
-          L.r3, L.r2, L.n_experts, L.top_k, L.eps, (bf16 *)z, idx_out, gates_out, c_out, router_cfg(L));                           \
+          L.r3, L.r2, L.n_experts, L.top_k, L.eps, (bf16 *)z, idx_out, gates_out, c_out, router_cfg(L),          \
+          (const bf16 *)x, L.d_in, pre_norm, pre_norm_eps);                           \
   } while (0)
   const bool k2 = L.top_k <= 2, k8 = L.top_k <= 8;
   if (L.r1 == 2) { if (k2) TMOE_DC(2, 2); else if (k8) TMOE_DC(2, 8); else TMOE_DC(2, 16); }
@@ -419,12 +434,12 @@ int launch_decode_t(const tmoe_layer_t &L, const void *x, const char *pb, const 
 
 int launch_decode(const tmoe_layer_t &L, const void *x, const void *prepared, const PreparedLayout &P, int64_t T,
                   float *h_raw, float *scores, void *z, int32_t *idx_out, float *gates_out, float *c_out,
-                  const OutEpilogue &epi, void *y, cudaStream_t st) {
+                  const OutEpilogue &epi, void *y, cudaStream_t st, int pre_norm, float pre_norm_eps) {
   const char *pb = reinterpret_cast<const char *>(prepared);
   if (T > 64) return TMOE_ERR_UNSUPPORTED;
   if (T <= 8)
-    return launch_decode_t<8>(L, x, pb, P, (int)T, h_raw, scores, z, idx_out, gates_out, c_out, epi, y, st);
-  return launch_decode_t<64>(L, x, pb, P, (int)T, h_raw, scores, z, idx_out, gates_out, c_out, epi, y, st);
+    return launch_decode_t<8>(L, x, pb, P, (int)T, h_raw, scores, z, idx_out, gates_out, c_out, epi, y, pre_norm, pre_norm_eps, st);
+  return launch_decode_t<64>(L, x, pb, P, (int)T, h_raw, scores, z, idx_out, gates_out, c_out, epi, y, pre_norm, pre_norm_eps, st);
 }
 
 }  // namespace tmoe

@@ -98,6 +98,6 @@ int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared
 // fp32 atomics into h_raw/scores (adjacent in memory, cleared here), norm + routing + core, out-projection.
 int launch_decode(const tmoe_layer_t &L, const void *x, const void *prepared, const PreparedLayout &P, int64_t T,
                   float *h_raw, float *scores, void *z, int32_t *idx_out, float *gates_out, float *c_out,
-                  const OutEpilogue &epi, void *y, cudaStream_t st);
+                  const OutEpilogue &epi, void *y, cudaStream_t st, int pre_norm = 0, float pre_norm_eps = 0.f);
 
 }  // namespace tmoe

@@ -121,16 +121,18 @@ template <> struct Vec16<bf16> {
 
 
 // Top-k of one token's scores [E] by k passes over the row (all lanes end with the same list).
-// Scores are rounded to the storage type T before they are compared.
+// Scores are multiplied by `scale` (1/rms(x) when the callers' pre-norm is applied in-kernel) and rounded to the storage
+// type T before they are compared.
 template <typename T, int KMAX, typename TS = float>
-__device__ __forceinline__ void warp_select_topk(const TS *__restrict__ sr, int E, int k, int lane, TopList<KMAX> &sel) {
+__device__ __forceinline__ void warp_select_topk(const TS *__restrict__ sr, int E, int k, int lane, TopList<KMAX> &sel,
+                                                 float scale = 1.f) {
   float pv = INFINITY; int pi = -1;
 #pragma unroll
   for (int j = 0; j < KMAX; ++j) {
     if (j < k) {
       float bv = -INFINITY; int bi = 0x7fffffff;
       for (int e = lane; e < E; e += 32) {
-        float v = round_to<T>(to_f32(sr[e]));
+        float v = round_to<T>(to_f32(sr[e]) * scale);
         if (ranks_before(pv, pi, v, e) && ranks_before(v, e, bv, bi)) { bv = v; bi = e; }
       }
 #pragma unroll
@@ -147,10 +149,10 @@ __device__ __forceinline__ void warp_select_topk(const TS *__restrict__ sr, int 
 // sum over all experts of exp(logit(score_e) - logit(top score)) for one token's score row (mode 1 only)
 template <typename T, typename TS>
 __device__ __forceinline__ float warp_softmax_denominator(const TS *__restrict__ sr, int E, int lane, const RouterCfg &rc,
-                                                          float top_score) {
+                                                          float top_score, float scale = 1.f) {
   const float l0 = rc.logit(top_score);
   float z = 0.f;
-  for (int e = lane; e < E; e += 32) z += expf(rc.logit(round_to<T>(to_f32(sr[e]))) - l0);
+  for (int e = lane; e < E; e += 32) z += expf(rc.logit(round_to<T>(to_f32(sr[e]) * scale)) - l0);
   return warp_sum(z);
 }
 

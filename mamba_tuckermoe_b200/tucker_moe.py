@@ -351,14 +351,23 @@ class TuckerMoE(nn.Module):
         return self._prep
 
     def _prepared_prenorm_for(self, x: torch.Tensor, norm_weight: torch.Tensor) -> Optional[torch.Tensor]:
-        """Prepared factors with `norm_weight` folded in, when this call can run the pre-norm inside the tensor-core
-        kernels (bf16, more than 64 tokens, in-kernel router: E <= 256, top_k <= 8, r3 <= 256); else None."""
-        if not x.is_cuda or x.dtype != torch.bfloat16 or self.path not in (PATH_AUTO, PATH_TENSOR):
+        """Prepared factors with `norm_weight` folded in, when this call can run the pre-norm inside the kernels: bf16
+        and either more than 64 tokens on the tensor-core path with its in-kernel router (E <= 256, top_k <= 8,
+        r3 <= 256, r1 <= 16) or at most 64 tokens on the decode path (r1 <= 32); else None."""
+        if not x.is_cuda or x.dtype != torch.bfloat16:
             return None
         T = x.numel() // max(x.shape[-1], 1)
         r1, r3, _ = self.core.shape
         E = self.router.weight.shape[0]
-        if T <= 64 or r3 > 256 or r1 > 16 or (E + 15) // 16 * 16 > 256 or self.top_k > 8:
+        if T <= 64:
+            if self.path not in (PATH_AUTO, PATH_DECODE) or T == 0:
+                return None
+            L = _layer_struct(x, self.router.weight, self.U_in, self.U_expert, self.core, self.U_out, self.top_k,
+                              self.inner_norm.eps)
+            if _lib.load().tmoe_resolve_path(C.byref(L), T, PATH_AUTO) != PATH_DECODE:
+                return None
+        elif (self.path not in (PATH_AUTO, PATH_TENSOR) or r3 > 256 or r1 > 16 or (E + 15) // 16 * 16 > 256
+              or self.top_k > 8):
             return None
         ps = self._params()
         key = _param_key(ps) + _param_key((norm_weight,))
@@ -454,7 +463,8 @@ class TuckerMoE(nn.Module):
             prep_pn = self._prepared_prenorm_for(x, w)
             if prep_pn is not None:
                 # norm weight folded into the prepared factors, 1/rms(x) found inside the in-projection kernel
-                y, _ = _run(x, rw, ui, nw, self.inner_norm.eps, ue, co, uo, b, self.top_k, PATH_TENSOR, residual,
+                T_ = x.numel() // max(x.shape[-1], 1)
+                y, _ = _run(x, rw, ui, nw, self.inner_norm.eps, ue, co, uo, b, self.top_k, PATH_DECODE if T_ <= 64 else PATH_TENSOR, residual,
                             layer_scale, prepared=prep_pn, silu_gate=silu_gate, router=self._router(),
                             pre_norm_eps=float(e))
                 return y
