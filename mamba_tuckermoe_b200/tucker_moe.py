@@ -581,11 +581,16 @@ def fused_out_proj(out_proj: TuckerMoE, mid: torch.Tensor, norm, layer_scale: to
 def fused_ffn(ffn_gate: TuckerMoE, ffn_up: TuckerMoE, ffn_down: TuckerMoE, x_res: torch.Tensor, norm,
               layer_scale: torch.Tensor) -> torch.Tensor:
     """``x_res + gamma * ffn_down(silu(ffn_gate(x_f)) * ffn_up(x_f))`` with ``x_f = norm(x_res)`` -- the FFN of the
-    reference's transformer block (``model.py:337-341``).  ``x_f`` is computed once and shared by the gate and up
-    layers, ``silu(gate) * up`` is the epilogue of the up layer and the residual add is the epilogue of the down
+    reference's transformer block (``model.py:337-341``).  The norm runs inside the gate and up layers' in-projection kernels where those
+    support it (else ``x_f`` is computed once and shared), ``silu(gate) * up`` is the epilogue of the up layer and the residual add is the epilogue of the down
     layer, so no element-wise pass over the 6x-wide activations remains."""
     w, e = (norm.weight, norm.eps) if hasattr(norm, "weight") else norm
-    x_f = rms_norm(x_res, w, e)
-    gate = ffn_gate(x_f)
-    act = ffn_up.forward_fused(x_f, silu_gate=gate)
+    if ffn_gate._prepared_prenorm_for(x_res, w) is not None and ffn_up._prepared_prenorm_for(x_res, w) is not None:
+        # both layers apply the norm inside their in-projection kernels: no separate pass over x_res
+        gate = ffn_gate.forward_fused(x_res, pre_norm=(w, e))
+        act = ffn_up.forward_fused(x_res, pre_norm=(w, e), silu_gate=gate)
+    else:
+        x_f = rms_norm(x_res, w, e)
+        gate = ffn_gate(x_f)
+        act = ffn_up.forward_fused(x_f, silu_gate=gate)
     return ffn_down.forward_fused(act, residual=x_res, layer_scale=layer_scale)
