@@ -301,7 +301,7 @@ class _Plan:
     validated contiguous parameters, the C structs, the prepared factor set and, per token count, the resolved
     kernel path and workspace size.  Rebuilt when a parameter's storage or version changes."""
     __slots__ = ("key", "params", "layer", "factors", "layer_ref", "factors_ref", "prepared", "prepared_ptr", "per_T",
-                 "dev", "d_in", "d_out", "lib")
+                 "dev", "d_in", "d_out", "lib", "pn")
 
 
 class TuckerMoE(nn.Module):
@@ -401,13 +401,29 @@ class TuckerMoE(nn.Module):
         plan.prepared = self._prepared_for(x)
         plan.prepared_ptr = plan.prepared.data_ptr() if plan.prepared is not None else None
         plan.per_T = {}
+        plan.pn = {}
         plan.dev, plan.d_in, plan.d_out = x.device, ui.shape[0], uo.shape[1]
         self._plan = plan
         return plan
 
-    def _fast_forward(self, x: torch.Tensor) -> torch.Tensor:
+    def _fast_prenorm(self, plan: _Plan, x: torch.Tensor, w: torch.Tensor, T: int):
+        """(prepared set with `w` folded in, kernel path) when a call of T tokens can apply the pre-norm in-kernel, else
+        None; remembered per (norm weight, T <= 64) on the plan."""
+        key = (w.data_ptr(), w._version, T <= 64)
+        hit = plan.pn.get(key)
+        if hit is None:
+            prep = self._prepared_prenorm_for(x, w)
+            hit = (prep, (PATH_DECODE if T <= 64 else PATH_TENSOR)) if prep is not None else (None, 0)
+            if len(plan.pn) < 64:
+                plan.pn[key] = hit
+        return hit if hit[0] is not None else None
+
+    def _fast_forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None,
+                      layer_scale: Optional[torch.Tensor] = None, silu_gate: Optional[torch.Tensor] = None,
+                      pre_norm=None) -> torch.Tensor:
         """Eager call without the dispatcher: the same C entry point as the custom op, with the per-call
-        Python work cut to a cache lookup (decode-sized calls cost more in Python than on the GPU)."""
+        Python work cut to a cache lookup (decode-sized calls cost more in Python than on the GPU).
+        The optional arguments are those of ``forward_fused`` (``pre_norm`` as a ``(weight, eps)`` pair)."""
         plan = self._plan_for(x)
         if x.shape[-1] != plan.d_in:
             raise RuntimeError(f"tmoe_b200: x has {x.shape[-1]} features, the layer expects {plan.d_in}")
@@ -418,24 +434,56 @@ class TuckerMoE(nn.Module):
         y = torch.empty((T, plan.d_out), dtype=x.dtype, device=x.device)
         if T:
             lib, dev = plan.lib, plan.dev
-            info = plan.per_T.get(T)
+            prepared_ptr, force_path, ex_ref, keep = plan.prepared_ptr, None, None, None
+            if residual is not None or silu_gate is not None or pre_norm is not None:
+                ex = Extras()
+                keep = []
+                if pre_norm is not None:
+                    w, e = pre_norm
+                    pn = self._fast_prenorm(plan, x, w, T)
+                    if pn is None:
+                        x2 = rms_norm(x2, w, e)
+                    else:
+                        prepared_ptr, force_path = pn[0].data_ptr(), pn[1]
+                        ex.pre_norm, ex.pre_norm_eps = 1, float(e)
+                if residual is not None:
+                    res2 = residual.reshape(-1, plan.d_out)
+                    if not res2.is_contiguous():
+                        res2 = res2.contiguous()
+                    ls = layer_scale if layer_scale.is_contiguous() else layer_scale.contiguous()
+                    if res2.shape[0] != T or res2.dtype != x.dtype or ls.dtype != x.dtype or ls.shape != (plan.d_out,) \
+                            or res2.device != dev or ls.device != dev:
+                        raise RuntimeError("tmoe_b200: residual must be (..., d_out) and layer_scale (d_out,) in x's dtype")
+                    ex.residual, ex.layer_scale = res2.data_ptr(), ls.data_ptr()
+                    keep += [res2, ls]
+                if silu_gate is not None:
+                    g2 = silu_gate.reshape(-1, plan.d_out)
+                    if not g2.is_contiguous():
+                        g2 = g2.contiguous()
+                    if g2.shape[0] != T or g2.dtype != x.dtype or g2.device != dev:
+                        raise RuntimeError("tmoe_b200: silu_gate must be (..., d_out) in x's dtype on x's device")
+                    ex.silu_gate = g2.data_ptr()
+                    keep.append(g2)
+                ex_ref = C.byref(ex)
+            info = plan.per_T.get((T, force_path))
             if info is None:
-                rpath = _lib.check(lib.tmoe_resolve_path(plan.layer_ref, T, self.path), "tmoe_resolve_path")
+                rpath = _lib.check(lib.tmoe_resolve_path(plan.layer_ref, T, self.path if force_path is None else force_path),
+                                   "tmoe_resolve_path")
                 info = (rpath, _lib.check(lib.tmoe_workspace_bytes(plan.layer_ref, T, rpath), "tmoe_workspace_bytes"))
                 if len(plan.per_T) < 4096:
-                    plan.per_T[T] = info
+                    plan.per_T[(T, force_path)] = info
             rpath, ws_bytes = info
             if torch.cuda.current_device() == dev.index:
                 stream = torch.cuda.current_stream().cuda_stream
                 ws = _workspace(dev, ws_bytes, stream)
-                rc = lib.tmoe_forward(plan.layer_ref, plan.factors_ref, plan.prepared_ptr, x2.data_ptr(), T, y.data_ptr(),
-                                      None, ws.data_ptr(), ws.numel(), rpath, stream)
+                rc = lib.tmoe_forward(plan.layer_ref, plan.factors_ref, prepared_ptr, x2.data_ptr(), T, y.data_ptr(),
+                                      ex_ref, ws.data_ptr(), ws.numel(), rpath, stream)
             else:
                 with torch.cuda.device(dev):
                     stream = torch.cuda.current_stream(dev).cuda_stream
                     ws = _workspace(dev, ws_bytes, stream)
-                    rc = lib.tmoe_forward(plan.layer_ref, plan.factors_ref, plan.prepared_ptr, x2.data_ptr(), T,
-                                          y.data_ptr(), None, ws.data_ptr(), ws.numel(), rpath, stream)
+                    rc = lib.tmoe_forward(plan.layer_ref, plan.factors_ref, prepared_ptr, x2.data_ptr(), T,
+                                          y.data_ptr(), ex_ref, ws.data_ptr(), ws.numel(), rpath, stream)
             if rc < 0:
                 _lib.check(rc, "tmoe_forward")
         return y.reshape(*x.shape[:-1], plan.d_out)
@@ -457,9 +505,13 @@ class TuckerMoE(nn.Module):
         ``silu_gate`` ``silu(silu_gate) * layer(...)`` in the out-projection's epilogue (``model.py:340``);
         ``residual``, ``layer_scale``  ``residual + layer_scale * (...)`` in the same epilogue (``model.py:260, 341``).
         """
+        if pre_norm is not None and hasattr(pre_norm, "weight"):
+            pre_norm = (pre_norm.weight, pre_norm.eps)
+        if x.is_cuda and not torch.compiler.is_compiling():
+            return self._fast_forward(x, residual, layer_scale, silu_gate, pre_norm)
         rw, ui, nw, ue, co, uo, b = self._params()
         if pre_norm is not None:
-            w, e = (pre_norm.weight, pre_norm.eps) if hasattr(pre_norm, "weight") else pre_norm
+            w, e = pre_norm
             prep_pn = self._prepared_prenorm_for(x, w)
             if prep_pn is not None:
                 # norm weight folded into the prepared factors, 1/rms(x) found inside the in-projection kernel
