@@ -85,7 +85,7 @@ def run_reference(ref_root, shape, x, f, dtype):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="root of a checkout of the reference project (s990093/Mamba-TuckerMoE)")
     ap.add_argument("--only", default=None)
     a = ap.parse_args()
     torch.manual_seed(0)
