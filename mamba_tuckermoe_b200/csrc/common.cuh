@@ -1,5 +1,6 @@
 // Shared host/device helpers for the Tucker-MoE kernels (sm_100a).
 #pragma once
+#include <cstdlib>
 
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -64,6 +65,20 @@ __device__ __forceinline__ void gates_from_selection(const float *sel_v, int k, 
   for (int j = 0; j < k; ++j) { gate[j] = __expf(sel_v[j] - m); den += gate[j]; }
   float inv = 1.f / den;
   for (int j = 0; j < k; ++j) gate[j] = round_to<T>(gate[j] * inv);
+}
+
+// Launch that may begin while the previous kernel of the stream drains (programmatic dependent launch); the kernel calls
+// ptx::griddep_wait() before it reads what that kernel wrote.  TMOE_PDL=0 turns the attribute off.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
+  static const bool off = []() { const char *e = getenv("TMOE_PDL"); return e && atoi(e) == 0; }();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at; cfg.numAttrs = off ? 0 : 1;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 
 }  // namespace tmoe

@@ -47,20 +47,6 @@ __device__ __forceinline__ void warp_prefetch_l2(const void *p, int bytes, int l
   for (int o = lane * 128; o < bytes; o += 32 * 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(c + o));
 }
 
-// Launch that may begin while the previous kernel of the stream drains (programmatic dependent launch); the kernel calls
-// ptx::griddep_wait() before it reads what that kernel wrote.  TMOE_PDL=0 turns the attribute off.
-template <typename... KArgs, typename... Args>
-cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
-  static const bool off = []() { const char *e = getenv("TMOE_PDL"); return e && atoi(e) == 0; }();
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
-  cudaLaunchAttribute at[1];
-  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  at[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = at; cfg.numAttrs = off ? 0 : 1;
-  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
-}
-
 // Sums N per-lane partial values over the warp.  On return v[0] of lane l holds the total of
 // value index (l % N) (N = 8 or 32): N + ... shuffles instead of 5 per value.
 template <int N>

@@ -121,7 +121,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
   griddep_launch_dependents();
   if ((int)blockIdx.x >= p.n_token_ctas) {
     // grid padding: this CTA would idle during the last wave; it computes out-projection tiles of finished token tiles
-    tc_out_body(&hc.tmA, &hc.tmB, &hc.tmY, hc.p, (int)blockIdx.x - p.n_token_ctas, hc.n_helpers, hc.n_tiles, smem_raw);
+    tc_out_body(&hc.tmA, &hc.tmB, &hc.tmY, hc.p, (int)blockIdx.x - p.n_token_ctas, hc.n_helpers, hc.n_tiles, smem_raw, true);
     return;
   }
   __shared__ __align__(8) uint64_t bar_fullA[A_STAGES_MAX], bar_emptyA[A_STAGES_MAX], bar_fullB[G_STAGES_MAX],
@@ -165,6 +165,9 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_s;
   const uint32_t ringB = ring + h_bytes;
+  // this kernel may have been started while its predecessor in the stream drains: nothing above depends on that kernel,
+  // everything below may (x, and the z / c rows this kernel overwrites may still be read by it)
+  griddep_wait();
 #ifdef TMOE_TRACE
   const long long trace_t0 = clock64();
   unsigned long long trace_ns0;
@@ -566,7 +569,7 @@ int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared
 #define TMOE_IC(R, K)                                                                                              \
   do {                                                                                                             \
     e = cudaFuncSetAttribute(tc_in_core_kernel<R, K>, cudaFuncAttributeMaxDynamicSharedMemorySize, IC_SMEM_BYTES); \
-    if (e == cudaSuccess) tc_in_core_kernel<R, K><<<grid, IC_THREADS, IC_SMEM_BYTES, st>>>(tmX, tmU, tmW, tmG, p, *hc);    \
+    if (e == cudaSuccess) e = launch_pdl(tc_in_core_kernel<R, K>, dim3(grid), dim3(IC_THREADS), (size_t)IC_SMEM_BYTES, st, tmX, tmU, tmW, tmG, p, *hc); \
   } while (0)
   const bool small_k = L.top_k <= 2;
   if (L.r1 == 2) { if (small_k) TMOE_IC(2, 2); else TMOE_IC(2, 8); }

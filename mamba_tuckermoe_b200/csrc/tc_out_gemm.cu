@@ -57,6 +57,7 @@ __global__ void __launch_bounds__(O_THREADS, 1)
 tc_out_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
               const __grid_constant__ CUtensorMap tmY, OutParams p) {
   extern __shared__ uint8_t smem_raw[];
+  griddep_launch_dependents();   // all CTAs of this persistent grid are resident: the next kernel may set up on SMs as they free
   tc_out_body(&tmA, &tmB, &tmY, p, p.tile_begin + (int)blockIdx.x, (int)gridDim.x, p.num_m * p.num_n, smem_raw, true);
   // the hand-off flags of this forward have served: the kernel that set and read them is complete (griddep_wait in the body)
   if (p.ready_clear && blockIdx.x == 0)
@@ -87,6 +88,7 @@ tc_out_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t rank = cluster_ctarank();
   const int pair_id = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  griddep_launch_dependents();
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < P_STAGES; ++s) { mbar_init(smem_u32(&bar_full[s]), 1); mbar_init(smem_u32(&bar_empty[s]), 1); }
