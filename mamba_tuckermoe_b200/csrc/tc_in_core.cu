@@ -82,9 +82,10 @@ struct InCoreParams {
   uint32_t epoch;
 };
 
-// Phase-A issue loop of the MMA thread.  TWO_BOX: r3 = 512, h takes two 256-column MMAs per k step (the second piece of
-// U_in^T starts 256 rows = 32 KB further).  SCORES: the router tile follows U_in^T in the stage and a third, N = e_pad MMA
-// accumulates the scores at TMEM column SCORE_COL.
+// Phase-A issue loop of the MMA thread.  TWO_BOX: r3 = 512; a stage holding x and all 512 rows of U_in^T is 80 KB, two
+// stages deep, and starves (measured 2300 cycles per k block against 1024 of tensor-pipe time), so h is made in two passes
+// over K, each streaming x again (from L2) with one 256-row piece of U_in^T: 48 KB stages, four deep.  SCORES: the router
+// tile follows U_in^T in the stage and a second, N = e_pad MMA accumulates the scores at TMEM column SCORE_COL.
 template <bool TWO_BOX, bool SCORES>
 __device__ __forceinline__ void issue_phase_a(uint32_t tmem_base, uint64_t desc0, uint32_t stage16, uint32_t u16, int KA, int nA,
                                               int u_box_rows, int e_pad, uint64_t *bar_full, uint64_t *bar_empty, int32_t *status) {
@@ -92,19 +93,22 @@ __device__ __forceinline__ void issue_phase_a(uint32_t tmem_base, uint64_t desc0
   const uint32_t idescS = umma_idesc_bf16(TM, e_pad);
   constexpr uint32_t xtile16 = X_TILE_BYTES >> 4;
   uint32_t sA = 0, phA = 0;
-  for (int kb = 0; kb < KA; ++kb) {
-    mbar_wait_or_exit(smem_u32(&bar_full[sA]), phA, status, kKernelInCore, 1);
-    const uint64_t dx = desc0 + sA * stage16, du = dx + xtile16, dw = du + u16;
-    const uint32_t acc0 = kb != 0;
+#pragma unroll 1
+  for (int pass = 0; pass < (TWO_BOX ? 2 : 1); ++pass) {
+    const uint32_t d_h = tmem_base + pass * 256;
+    for (int kb = 0; kb < KA; ++kb) {
+      mbar_wait_or_exit(smem_u32(&bar_full[sA]), phA, status, kKernelInCore, 1);
+      const uint64_t dx = desc0 + sA * stage16, du = dx + xtile16, dw = du + u16;
+      const uint32_t acc0 = kb != 0;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const uint32_t acc = acc0 | (uint32_t)(k != 0);
-      umma_bf16(tmem_base, dx + 2 * k, du + 2 * k, idescH, acc);
-      if (TWO_BOX) umma_bf16(tmem_base + 256, dx + 2 * k, du + 2048 + 2 * k, idescH, acc);
-      if (SCORES) umma_bf16(tmem_base + SCORE_COL, dx + 2 * k, dw + 2 * k, idescS, acc);
+      for (int k = 0; k < 4; ++k) {
+        const uint32_t acc = acc0 | (uint32_t)(k != 0);
+        umma_bf16(d_h, dx + 2 * k, du + 2 * k, idescH, acc);
+        if (SCORES) umma_bf16(tmem_base + SCORE_COL, dx + 2 * k, dw + 2 * k, idescS, acc);
+      }
+      umma_commit(smem_u32(&bar_empty[sA]));
+      if (++sA == (uint32_t)nA) { sA = 0; phA ^= 1; }
     }
-    umma_commit(smem_u32(&bar_empty[sA]));
-    if (++sA == (uint32_t)nA) { sA = 0; phA ^= 1; }
   }
 }
 
@@ -134,7 +138,9 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int m0 = blockIdx.x * TM;
 
-  const int u_bytes = p.r3 * 128, w_bytes = p.e_pad * 128;
+  const int u_boxes = (p.r3 + 255) / 256;         // U_in^T is streamed in pieces of <= 256 rows, one pass over K per piece
+  const int u_box_rows = p.r3 / u_boxes;
+  const int u_bytes = u_box_rows * 128, w_bytes = p.e_pad * 128;
   const int stageA_bytes = X_TILE_BYTES + u_bytes + w_bytes;
   int nA = IC_RING_BYTES / stageA_bytes;
   nA = nA > A_STAGES_MAX ? A_STAGES_MAX : nA;
@@ -143,8 +149,6 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
   const int h_bytes = KH * H_KBLOCK_BYTES;        // 64 KB for r3 = 256, 128 KB for r3 = 512
   int nG = (IC_RING_BYTES - h_bytes) / G_STAGE_BYTES;
   nG = nG > G_STAGES_MAX ? G_STAGES_MAX : nG;
-  const int u_boxes = (p.r3 + 255) / 256;         // U_in^T rows are loaded (and multiplied) in pieces of <= 256
-  const int u_box_rows = p.r3 / u_boxes;
 
   for (int i = threadIdx.x; i < p.r3; i += blockDim.x) wnorm_s[i] = __float2bfloat16_rn(p.normw[i]);
   if (threadIdx.x == 0) {
@@ -179,17 +183,18 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
     if (lane == 0) {
       bool ok = true;
       uint32_t sA = 0, phA = 0, sB = 0, phB = 0;
-      for (int kb = 0; kb < KA && ok; ++kb) {
-        const uint32_t s = sA, ph = phA;
-        if (++sA == (uint32_t)nA) { sA = 0; phA ^= 1; }  // ring position kept incrementally: no division in this loop
-        if (!(ok = mbar_wait(smem_u32(&bar_emptyA[s]), ph ^ 1, p.status, kKernelInCore, 2))) break;
-        const uint32_t full = smem_u32(&bar_fullA[s]);
-        mbar_arrive_expect_tx(full, stageA_bytes);
-        const uint32_t sa = ring + s * stageA_bytes;
-        tma_load_2d(sa, &tmX, kb * 64, m0, full);
-        tma_load_2d(sa + X_TILE_BYTES, &tmU, kb * 64, 0, full);
-        if (u_boxes == 2) tma_load_2d(sa + X_TILE_BYTES + 256 * 128, &tmU, kb * 64, 256, full);
-        if (p.e_pad) tma_load_2d(sa + X_TILE_BYTES + u_bytes, &tmW, kb * 64, 0, full);
+      for (int pass = 0; pass < u_boxes && ok; ++pass) {
+        for (int kb = 0; kb < KA && ok; ++kb) {
+          const uint32_t s = sA, ph = phA;
+          if (++sA == (uint32_t)nA) { sA = 0; phA ^= 1; }  // ring position kept incrementally: no division in this loop
+          if (!(ok = mbar_wait(smem_u32(&bar_emptyA[s]), ph ^ 1, p.status, kKernelInCore, 2))) break;
+          const uint32_t full = smem_u32(&bar_fullA[s]);
+          mbar_arrive_expect_tx(full, stageA_bytes);
+          const uint32_t sa = ring + s * stageA_bytes;
+          tma_load_2d(sa, &tmX, kb * 64, m0, full);
+          tma_load_2d(sa + X_TILE_BYTES, &tmU, kb * 64, pass * u_box_rows, full);
+          if (p.e_pad) tma_load_2d(sa + X_TILE_BYTES + u_bytes, &tmW, kb * 64, 0, full);
+        }
       }
       // ring A aliases h and the core-tile ring: wait until every phase-A MMA has retired
       if (ok) ok = mbar_wait(smem_u32(&bar_accA), 0, p.status, kKernelInCore, 3);
@@ -540,7 +545,7 @@ int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared
   p.uexp = reinterpret_cast<const float *>(base + P.uexp);
   p.c_in = c_in; p.c_work = c_work; p.idx_out = idx_out; p.gates_out = gates_out; p.c_out = c_out;
   p.z = (bf16 *)z; p.status = status;
-  if (X_TILE_BYTES + p.r3 * 128 + p.e_pad * 128 > IC_RING_BYTES) return TMOE_ERR_UNSUPPORTED;
+  if (X_TILE_BYTES + (p.r3 > 256 ? 256 : p.r3) * 128 + p.e_pad * 128 > IC_RING_BYTES) return TMOE_ERR_UNSUPPORTED;
 
   unsigned grid = (unsigned)((T_ + TM - 1) / TM);
   p.n_token_ctas = (int)grid;
