@@ -28,14 +28,20 @@ int check_layer(const tmoe_layer_t *L) {
 
 // allow_decode: tmoe_forward (and the sizing queries) may pick the decode kernels; the stage entry
 // points cannot, so for them AUTO with T <= 64 means the CUDA-core path.
+constexpr int kDecodeAutoTokens = 24;
+
 int resolve(const tmoe_layer_t &L, int64_t T, int path, bool allow_decode = true) {
   if (path == TMOE_PATH_SIMT) return TMOE_PATH_SIMT;
   const bool tensor_ok = tensor_path_covers(L), decode_ok = prepared_covers(L) && allow_decode && T <= 64;
   if (path == TMOE_PATH_TENSOR) return tensor_ok ? (int)TMOE_PATH_TENSOR : (int)TMOE_ERR_UNSUPPORTED;
   if (path == TMOE_PATH_DECODE) return decode_ok ? (int)TMOE_PATH_DECODE : (int)TMOE_ERR_UNSUPPORTED;
   if (path != TMOE_PATH_AUTO) return TMOE_ERR_UNSUPPORTED;
+  // Up to 24 tokens the decode-shaped kernels win; from there the tensor-core kernels do (one 128-token tile costs the
+  // same 52 us for any T, the decode kernels grow from 48 us at T = 9 to 67 us at T = 64 on the decode configuration)
+  // and, unlike the split-K decode in-projection, they are run-to-run reproducible.
   if (T > 64) return tensor_ok ? TMOE_PATH_TENSOR : TMOE_PATH_SIMT;
-  return decode_ok ? TMOE_PATH_DECODE : TMOE_PATH_SIMT;
+  if (T > kDecodeAutoTokens && tensor_ok) return TMOE_PATH_TENSOR;
+  return decode_ok ? TMOE_PATH_DECODE : (tensor_ok ? TMOE_PATH_TENSOR : TMOE_PATH_SIMT);
 }
 
 WsLayout ws_layout(const tmoe_layer_t &L, int64_t T, int rpath) {

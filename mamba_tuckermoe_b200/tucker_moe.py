@@ -350,24 +350,29 @@ class TuckerMoE(nn.Module):
             self._prep_key = key
         return self._prep
 
-    def _prepared_prenorm_for(self, x: torch.Tensor, norm_weight: torch.Tensor) -> Optional[torch.Tensor]:
-        """Prepared factors with `norm_weight` folded in, when this call can run the pre-norm inside the kernels: bf16
-        and either more than 64 tokens on the tensor-core path with its in-kernel router (E <= 256, top_k <= 8,
-        r3 <= 256, r1 <= 16) or at most 64 tokens on the decode path (r1 <= 32); else None."""
+    def _prenorm_path(self, x: torch.Tensor) -> int:
+        """Kernel path on which a call with this x can apply the callers' pre-norm in-kernel (0: none): the decode
+        path, or the tensor-core path with its in-kernel router (E <= 256, top_k <= 8, r3 <= 256, r1 <= 16)."""
         if not x.is_cuda or x.dtype != torch.bfloat16:
-            return None
+            return 0
         T = x.numel() // max(x.shape[-1], 1)
+        if T == 0 or self.path == PATH_SIMT:
+            return 0
+        L = _layer_struct(x, self.router.weight, self.U_in, self.U_expert, self.core, self.U_out, self.top_k,
+                          self.inner_norm.eps)
+        rp = _lib.load().tmoe_resolve_path(C.byref(L), T, self.path)
+        if rp == PATH_DECODE:
+            return PATH_DECODE
         r1, r3, _ = self.core.shape
         E = self.router.weight.shape[0]
-        if T <= 64:
-            if self.path not in (PATH_AUTO, PATH_DECODE) or T == 0:
-                return None
-            L = _layer_struct(x, self.router.weight, self.U_in, self.U_expert, self.core, self.U_out, self.top_k,
-                              self.inner_norm.eps)
-            if _lib.load().tmoe_resolve_path(C.byref(L), T, PATH_AUTO) != PATH_DECODE:
-                return None
-        elif (self.path not in (PATH_AUTO, PATH_TENSOR) or r3 > 256 or r1 > 16 or (E + 15) // 16 * 16 > 256
-              or self.top_k > 8):
+        if rp == PATH_TENSOR and r3 <= 256 and r1 <= 16 and (E + 15) // 16 * 16 <= 256 and self.top_k <= 8:
+            return PATH_TENSOR
+        return 0
+
+    def _prepared_prenorm_for(self, x: torch.Tensor, norm_weight: torch.Tensor) -> Optional[torch.Tensor]:
+        """Prepared factors with `norm_weight` folded in when this call can run the pre-norm inside the kernels
+        (``_prenorm_path``); else None."""
+        if self._prenorm_path(x) == 0:
             return None
         ps = self._params()
         key = _param_key(ps) + _param_key((norm_weight,))
@@ -409,11 +414,11 @@ class TuckerMoE(nn.Module):
     def _fast_prenorm(self, plan: _Plan, x: torch.Tensor, w: torch.Tensor, T: int):
         """(prepared set with `w` folded in, kernel path) when a call of T tokens can apply the pre-norm in-kernel, else
         None; remembered per (norm weight, T <= 64) on the plan."""
-        key = (w.data_ptr(), w._version, T <= 64)
+        key = (w.data_ptr(), w._version, T)
         hit = plan.pn.get(key)
         if hit is None:
             prep = self._prepared_prenorm_for(x, w)
-            hit = (prep, (PATH_DECODE if T <= 64 else PATH_TENSOR)) if prep is not None else (None, 0)
+            hit = (prep, self._prenorm_path(x)) if prep is not None else (None, 0)
             if len(plan.pn) < 64:
                 plan.pn[key] = hit
         return hit if hit[0] is not None else None
@@ -516,7 +521,7 @@ class TuckerMoE(nn.Module):
             if prep_pn is not None:
                 # norm weight folded into the prepared factors, 1/rms(x) found inside the in-projection kernel
                 T_ = x.numel() // max(x.shape[-1], 1)
-                y, _ = _run(x, rw, ui, nw, self.inner_norm.eps, ue, co, uo, b, self.top_k, PATH_DECODE if T_ <= 64 else PATH_TENSOR, residual,
+                y, _ = _run(x, rw, ui, nw, self.inner_norm.eps, ue, co, uo, b, self.top_k, self._prenorm_path(x), residual,
                             layer_scale, prepared=prep_pn, silu_gate=silu_gate, router=self._router(),
                             pre_norm_eps=float(e))
                 return y
