@@ -473,7 +473,7 @@ def decode_times(lib, _lib, layer, shape, dtype, x, T, reps=30):
     fd = {"router_w": layer.router.weight, "U_in": layer.U_in, "inner_norm_w": layer.inner_norm.weight,
           "U_expert": layer.U_expert, "core": layer.core, "U_out": layer.U_out, "bias": layer.bias}
     F = _lib.factors_struct(fd)
-    rpath = lib.tmoe_resolve_path(C.byref(L), T, 0)   # what a caller gets: decode-shaped kernels up to 24 tokens, one tensor-core tile above
+    rpath = lib.tmoe_resolve_path(C.byref(L), T, 0)   # what a caller gets: decode-shaped kernels up to 8 tokens, one tensor-core tile above
     ws = _lib.alloc_workspace(L, T, rpath)
     prep = _lib.alloc_prepared(L, F)
     y = torch.empty(T, shape.d_out, dtype=dtype, device=x.device)

@@ -50,7 +50,7 @@ typedef enum tmoe_dtype { TMOE_F32 = 0, TMOE_BF16 = 1 } tmoe_dtype_t;
  *          d_in and r2 multiples of 64.  Needs the prepared factor set.
  *  DECODE  bandwidth-shaped kernels for T <= 64 tokens on the same shapes plus r1 = 32, same prepared
  *          set (tmoe_forward only).
- *  AUTO    DECODE up to 24 tokens (up to 64 where TENSOR does not cover the shape), TENSOR above, when the shape is
+ *  AUTO    DECODE up to 8 tokens (up to 64 where TENSOR does not cover the shape), TENSOR above, when the shape is
  *          covered; else SIMT. */
 typedef enum tmoe_path {
   TMOE_PATH_AUTO = 0, TMOE_PATH_SIMT = 1, TMOE_PATH_TENSOR = 2, TMOE_PATH_DECODE = 3

@@ -28,7 +28,7 @@ int check_layer(const tmoe_layer_t *L) {
 
 // allow_decode: tmoe_forward (and the sizing queries) may pick the decode kernels; the stage entry
 // points cannot, so for them AUTO with T <= 64 means the CUDA-core path.
-constexpr int kDecodeAutoTokens = 24;
+constexpr int kDecodeAutoTokens = 8;
 
 int resolve(const tmoe_layer_t &L, int64_t T, int path, bool allow_decode = true) {
   if (path == TMOE_PATH_SIMT) return TMOE_PATH_SIMT;
@@ -36,9 +36,10 @@ int resolve(const tmoe_layer_t &L, int64_t T, int path, bool allow_decode = true
   if (path == TMOE_PATH_TENSOR) return tensor_ok ? (int)TMOE_PATH_TENSOR : (int)TMOE_ERR_UNSUPPORTED;
   if (path == TMOE_PATH_DECODE) return decode_ok ? (int)TMOE_PATH_DECODE : (int)TMOE_ERR_UNSUPPORTED;
   if (path != TMOE_PATH_AUTO) return TMOE_ERR_UNSUPPORTED;
-  // Up to 24 tokens the decode-shaped kernels win; from there the tensor-core kernels do (one 128-token tile costs the
-  // same 52 us for any T, the decode kernels grow from 48 us at T = 9 to 67 us at T = 64 on the decode configuration)
-  // and, unlike the split-K decode in-projection, they are run-to-run reproducible.
+  // Up to 8 tokens the decode-shaped kernels win (16-18 us per call on the decode configuration); from there the
+  // tensor-core kernels do: one 128-token tile shared by up to 16 CTAs costs the same 32 us for any T, the decode kernels
+  // 47 us at T = 9 growing to 67 us at T = 64, and unlike their split-K in-projection the tensor path is run-to-run
+  // reproducible.
   if (T > 64) return tensor_ok ? TMOE_PATH_TENSOR : TMOE_PATH_SIMT;
   if (T > kDecodeAutoTokens && tensor_ok) return TMOE_PATH_TENSOR;
   return decode_ok ? TMOE_PATH_DECODE : (tensor_ok ? TMOE_PATH_TENSOR : TMOE_PATH_SIMT);
@@ -50,7 +51,8 @@ WsLayout ws_layout(const tmoe_layer_t &L, int64_t T, int rpath) {
   auto take = [&](int64_t bytes) { int64_t o = off; off = align_up(off + bytes, 256); return o; };
   W.idx = take(T * L.top_k * 4);
   W.gates = take(T * L.top_k * 4);
-  W.c = take(T * L.r1 * 4);
+  // the tensor-core in/core kernel keeps extra [T, r1] blocks for small T (tiles shared between CTAs)
+  W.c = take(T * L.r1 * 4 * (rpath == TMOE_PATH_TENSOR ? in_core_c_blocks(T) : 1));
   W.simt_router_fused = (L.n_experts <= 32) || (T <= 256);
   W.tc_router_fused = (align_up(L.n_experts, 16) <= 256) && (L.top_k <= 8) && (L.r3 <= 256);
   if (rpath == TMOE_PATH_SIMT) {
@@ -69,21 +71,6 @@ WsLayout ws_layout(const tmoe_layer_t &L, int64_t T, int rpath) {
   }
   W.total = off;
   return W;
-}
-
-// SM count of the calling thread's current device, looked up once per device (0 on error).
-int current_device_sms() {
-  static std::atomic<int> cache[64];
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
-  if (dev >= 0 && dev < 64) {
-    const int c = cache[dev].load(std::memory_order_relaxed);
-    if (c > 0) return c;
-  }
-  int sms = 0;
-  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
-  if (dev >= 0 && dev < 64) cache[dev].store(sms, std::memory_order_relaxed);
-  return sms;
 }
 
 bool misaligned(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0; }
@@ -229,7 +216,7 @@ int tmoe_in_core(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const
   }
   if (!prepared) return TMOE_ERR_NULL;
   return launch_tc_in_core(*layer, x, prepared, prepared_layout(*layer), T, 0, 0.f, 0, c,
-                           reinterpret_cast<float *>(ws + W.c), nullptr, nullptr, nullptr, z,
+                           reinterpret_cast<float *>(ws + W.c), in_core_c_blocks(T), nullptr, nullptr, nullptr, z,
                            reinterpret_cast<int32_t *>(ws), st);
 }
 
@@ -326,7 +313,7 @@ int tmoe_forward(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const
   if (W.tc_router_fused) {
     const bool taps = extras && (extras->idx_out || extras->gates_out || extras->c_out);
     rc = launch_tc_in_core(L, x, prepared, P, T, pre_norm, pre_norm ? extras->pre_norm_eps : 0.f, 1, nullptr,
-                           reinterpret_cast<float *>(ws + W.c),
+                           reinterpret_cast<float *>(ws + W.c), in_core_c_blocks(T),
                            taps ? extras->idx_out : nullptr,
                            taps ? extras->gates_out : nullptr, taps ? extras->c_out : nullptr, z, status, st, hp);
   } else {
@@ -335,7 +322,7 @@ int tmoe_forward(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const
       return rc;
     if ((rc = launch_select_bf16_scores(L, scores, P.e_pad, factors->U_expert, T, idx, gates, c, st))) return rc;
     // c_work may alias c: every row is read by its own thread before that thread overwrites it
-    rc = launch_tc_in_core(L, x, prepared, P, T, 0, 0.f, 0, c, reinterpret_cast<float *>(ws + W.c), nullptr, nullptr, nullptr, z,
+    rc = launch_tc_in_core(L, x, prepared, P, T, 0, 0.f, 0, c, reinterpret_cast<float *>(ws + W.c), in_core_c_blocks(T), nullptr, nullptr, nullptr, z,
                            status, st, hp);
   }
   if (rc) return rc;

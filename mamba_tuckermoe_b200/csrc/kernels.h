@@ -2,10 +2,27 @@
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <atomic>
 
 #include "tmoe_b200.h"
 
 namespace tmoe {
+
+// SM count of the calling thread's current device, looked up once per device (0 on error).
+inline int current_device_sms() {
+  static std::atomic<int> cache[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  if (dev >= 0 && dev < 64) {
+    const int c = cache[dev].load(std::memory_order_relaxed);
+    if (c > 0) return c;
+  }
+  int sms = 0;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+  if (dev >= 0 && dev < 64) cache[dev].store(sms, std::memory_order_relaxed);
+  return sms;
+}
+
 
 // Optional element-wise tail of the out-projection, applied in fp32 to v = acc + bias, in this order:
 //   silu_gate   v = silu(g[t, n]) * v                      (the FFN's silu(gate) * up, model.py:340)
@@ -89,8 +106,17 @@ struct OutHelperArgs {
 // otherwise c_in [T, r1] is read.  c_work [T, r1] is scratch in both cases.
 // pre_norm != 0: `prepared` carries the pre-norm weight folded into U_in / router rows; the kernel then computes every
 // row's 1/rms(x) from the x tiles passing through shared memory and applies it to the scores and to the RMS statistics.
+// c_work holds c_work_blocks blocks of [T, r1] floats.  With in_core_c_blocks(T) blocks and few token tiles, each tile
+// is shared by several CTAs that split the core tiles between them (block 0 may alias c_in / c_out, the others may not).
+constexpr int kMaxJSplit = 16;
+inline int in_core_c_blocks(int64_t T) {
+  const int64_t tiles = (T + 127) / 128;   // sized for up to 160 SMs, whatever device the sizing query runs on
+  if (tiles < 1 || tiles * 2 > 160) return 1;
+  const int per_tile = (int)(160 / tiles);
+  return 1 + (per_tile < kMaxJSplit ? per_tile : kMaxJSplit);
+}
 int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared, const PreparedLayout &P, int64_t T,
-                      int pre_norm, float pre_norm_eps, int fuse_router, const float *c_in, float *c_work, int32_t *idx_out, float *gates_out, float *c_out,
+                      int pre_norm, float pre_norm_eps, int fuse_router, const float *c_in, float *c_work, int c_work_blocks, int32_t *idx_out, float *gates_out, float *c_out,
                       void *z, int32_t *status, cudaStream_t st, const OutHelperArgs *helper = nullptr);
 
 // ---- decode.cu ----

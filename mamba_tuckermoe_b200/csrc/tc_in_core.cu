@@ -78,6 +78,10 @@ struct InCoreParams {
   // CTAs [0, n_token_ctas) own token tiles; the rest are helper CTAs that run out-projection tiles (OutHelperCfg).
   // A token CTA with blockIdx.x < n_ready_m publishes `epoch` in ready[8 * blockIdx.x + epilogue warp] once its z rows are stored.
   int n_token_ctas, n_ready_m;
+  // Few token tiles (small T): every tile is shared by j_split CTAs, each repeating phase A and taking n_tiles2 / j_split of
+  // the core tiles, so that one tile's 40 us of work is spread over up to 16 SMs.  Split s > 0 keeps its c hand-off in
+  // block s + 1 of c_work ([T, r1] each); block 0 may alias c_in / c_out.
+  int j_split;
   uint32_t *ready;
   uint32_t epoch;
 };
@@ -136,7 +140,10 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const int m0 = blockIdx.x * TM;
+  const int sp = p.j_split > 1 ? (int)blockIdx.x % p.j_split : 0;
+  const int m0 = (p.j_split > 1 ? (int)blockIdx.x / p.j_split : (int)blockIdx.x) * TM;
+  const int jn = p.n_tiles2 / p.j_split, j0 = sp * jn;   // this CTA's core tiles [j0, j0 + jn)
+  float *const c_work = p.c_work + (p.j_split > 1 ? (int64_t)(sp + 1) * p.T * R1 : 0);
 
   const int u_boxes = (p.r3 + 255) / 256;         // U_in^T is streamed in pieces of <= 256 rows, one pass over K per piece
   const int u_box_rows = p.r3 / u_boxes;
@@ -198,8 +205,8 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       }
       // ring A aliases h and the core-tile ring: wait until every phase-A MMA has retired
       if (ok) ok = mbar_wait(smem_u32(&bar_accA), 0, p.status, kKernelInCore, 3);
-      const int total = p.n_tiles2 * KH;
-      int j = 0, kbB = 0;
+      const int total = jn * KH;
+      int j = j0, kbB = 0;
       for (int it = 0; it < total && ok; ++it) {
         const uint32_t s = sB, ph = phB;
         if (++sB == (uint32_t)nG) { sB = 0; phB ^= 1; }
@@ -237,7 +244,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       const uint32_t idescP = umma_idesc_bf16(TM, 256);
       const uint64_t descB0 = desc0 + ((uint32_t)h_bytes >> 4);
       uint32_t sB = 0, phB = 0;
-      for (int j = 0; j < p.n_tiles2; ++j) {
+      for (int j = 0; j < jn; ++j) {
         const uint32_t slot = j & 1, pph = (j >> 1) & 1;
         mbar_wait_or_exit(smem_u32(&bar_pempty[slot]), pph ^ 1, p.status, kKernelInCore, 8);
         tc_fence_after();
@@ -309,9 +316,9 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       tc_fence_after();
       if (threadIdx.x == 64) TMOE_STAMP(2);  // phase A complete (accumulators readable)
       if (p.pre_norm) {  // hand 1/rms(x) from the secondary warp of each row to its primary twin (through the workspace)
-        if (grp == 1 && live) p.c_work[grow * R1] = inv_x;
+        if (grp == 1 && live) c_work[grow * R1] = inv_x;
         named_bar_sync(5, 256);
-        if (grp == 0) inv_x = live ? p.c_work[grow * R1] : 1.f;
+        if (grp == 0) inv_x = live ? c_work[grow * R1] : 1.f;
       }
       if (grp == 0) {
         if (p.fuse_router) {
@@ -378,14 +385,14 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
               const int e = min(max(si[j], 0), p.E - 1);
 #pragma unroll
               for (int a = 0; a < R1; ++a) c[a] = fmaf(gate[j], __ldg(p.uexp + e * R1 + a), c[a]);
-              if (live) {
+              if (live && sp == 0) {
                 if (p.idx_out) p.idx_out[grow * p.top_k + j] = si[j];
                 if (p.gates_out) p.gates_out[grow * p.top_k + j] = gate[j];
               }
             }
           }
           if (threadIdx.x == 64) TMOE_STAMP(7);  // gates and c done
-          if (live && p.c_out) {
+          if (live && p.c_out && sp == 0) {
 #pragma unroll
             for (int a = 0; a < R1; ++a) p.c_out[grow * R1 + a] = c[a];
           }
@@ -401,7 +408,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         for (int a = 0; a < R1; ++a) c[a] *= inv_rms;
         if (live) {
 #pragma unroll
-          for (int a = 0; a < R1; ++a) p.c_work[grow * R1 + a] = c[a];
+          for (int a = 0; a < R1; ++a) c_work[grow * R1 + a] = c[a];
         }
       } else {
         // h row: statistics, weight, bf16, swizzled store (16-byte chunk index XOR row%8 inside 128-byte rows)
@@ -439,19 +446,20 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       named_bar_sync(4, 256);                // c_work of every row is written
       if (grp == 1) {
 #pragma unroll
-        for (int a = 0; a < R1; ++a) c[a] = live ? p.c_work[grow * R1 + a] : 0.f;
+        for (int a = 0; a < R1; ++a) c[a] = live ? c_work[grow * R1 + a] : 0.f;
       }
 
       // epilogue B: tile j belongs to group (j / JPU) & 1, JPU = tiles per 64-column unit of z
       constexpr int JPU = (N2 >= 64) ? 1 : 64 / N2;
-      for (int j = 0; j < p.n_tiles2 && ok; ++j) {
+      for (int jl = 0; jl < jn && ok; ++jl) {
         // every warp waits for every tile, also the ones its group does not own: a parity wait is only
         // meaningful for a waiter that has seen the barrier's previous phase complete
-        const uint32_t slot = j & 1, pph = (j >> 1) & 1;
+        const int j = j0 + jl;
+        const uint32_t slot = jl & 1, pph = (jl >> 1) & 1;
         ok = mbar_wait(smem_u32(&bar_pfull[slot]), pph, p.status, kKernelInCore, 7);
         ok = __all_sync(0xffffffffu, ok);  // TMEM loads are warp-collective
         if (!ok) break;
-        if (((j / JPU) & 1) != grp) continue;
+        if (((jl / JPU) & 1) != grp) continue;
         tc_fence_after();
         const uint32_t t_p = t_lane + slot * 256;
 #pragma unroll 1
@@ -517,7 +525,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
 }
 
 int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared, const PreparedLayout &P, int64_t T_,
-                      int pre_norm, float pre_norm_eps, int fuse_router, const float *c_in, float *c_work, int32_t *idx_out, float *gates_out, float *c_out,
+                      int pre_norm, float pre_norm_eps, int fuse_router, const float *c_in, float *c_work, int c_work_blocks, int32_t *idx_out, float *gates_out, float *c_out,
                       void *z, int32_t *status, cudaStream_t st, const OutHelperArgs *helper) {
   const char *base = reinterpret_cast<const char *>(prepared);
   if (fuse_router && (P.e_pad > 256 || L.top_k > 8 || L.r3 > 256)) return TMOE_ERR_UNSUPPORTED;
@@ -548,6 +556,22 @@ int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared
   if (X_TILE_BYTES + (p.r3 > 256 ? 256 : p.r3) * 128 + p.e_pad * 128 > IC_RING_BYTES) return TMOE_ERR_UNSUPPORTED;
 
   unsigned grid = (unsigned)((T_ + TM - 1) / TM);
+  // Few token tiles: share each tile between j_split CTAs (every one repeats phase A, then takes its share of the core
+  // tiles).  j_split is the largest divisor of n_tiles2 that fits the SM count and the scratch blocks and keeps whole
+  // 64-column units of z per CTA.
+  p.j_split = 1;
+  {
+    const int sms = current_device_sms();
+    const int n2 = 256 / L.r1, jpu = n2 >= 64 ? 1 : 64 / n2;
+    int cap = sms > 0 ? sms / (int)grid : 1;
+    if (cap > c_work_blocks - 1) cap = c_work_blocks - 1;
+    if (cap > kMaxJSplit) cap = kMaxJSplit;
+    static const int env_split = [] { const char *s = getenv("TMOE_JSPLIT"); return s ? atoi(s) : -1; }();
+    if (env_split >= 0 && cap > env_split) cap = env_split;
+    for (int d = cap; d >= 2; --d)
+      if (P.n_tiles2 % d == 0 && (P.n_tiles2 / d) % jpu == 0) { p.j_split = d; break; }
+  }
+  grid *= (unsigned)p.j_split;
   p.n_token_ctas = (int)grid;
   static OutHelperCfg hc_none;   // zero-initialised: no helper CTAs
   OutHelperCfg hc_local;

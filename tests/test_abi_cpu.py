@@ -70,8 +70,8 @@ def test_path_resolution_and_sizes():
     lib = _lib.load()
     cfg2 = _layer(d_in=1536, d_out=2304, n_experts=64, top_k=2, r1=4, r2=1024, r3=256, dtype=_lib.TMOE_BF16, eps=1e-6)
     assert lib.tmoe_resolve_path(C.byref(cfg2), 32768, 0) == 2
-    assert lib.tmoe_resolve_path(C.byref(cfg2), 24, 0) == 3     # decode-shaped kernels up to 24 tokens
-    assert lib.tmoe_resolve_path(C.byref(cfg2), 25, 0) == 2     # one tensor-core tile from there
+    assert lib.tmoe_resolve_path(C.byref(cfg2), 8, 0) == 3      # decode-shaped kernels up to 8 tokens
+    assert lib.tmoe_resolve_path(C.byref(cfg2), 9, 0) == 2      # one tensor-core tile (shared between CTAs) from there
     assert lib.tmoe_resolve_path(C.byref(cfg2), 64, 3) == 3     # still available on request up to 64
     assert lib.tmoe_resolve_path(C.byref(cfg2), 65, 3) == -6
     assert lib.tmoe_resolve_path(C.byref(cfg2), 1, 3) == 3

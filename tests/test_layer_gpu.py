@@ -111,6 +111,30 @@ def test_tensor_path_matches_oracle(shape, T):
     assert torch.equal(m(x.cuda()), y)
 
 
+@pytest.mark.parametrize("shape,T", [
+    (LayerShape(1536, 2304, 8, 2, 4, 256, 1024, 1e-6), 9),
+    (LayerShape(768, 1536, 8, 2, 16, 256, 512, 1e-5), 300),
+    (LayerShape(256, 264, 8, 2, 2, 128, 256, 1e-5), 1100),
+    (LayerShape(256, 128, 512, 8, 8, 64, 128, 1e-6), 2500),   # routing by the select kernel (c arrives from memory)
+])
+def test_token_tiles_shared_between_ctas(shape, T):
+    """With few token tiles each tile's core tiles are split over several CTAs: same bits as the same tokens at the
+    head of a batch large enough that every tile has a CTA of its own."""
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    T_big = 128 * (sms // 2 + 6)
+    x, f = _tensor_case(shape, T_big, seed=515)
+    m = build_module(shape, f, torch.bfloat16, path=PATH_TENSOR)
+    xd = x.cuda()
+    y_big, taps_big = m.forward_with_routing(xd)
+    y, taps = m.forward_with_routing(xd[:T].contiguous())
+    torch.cuda.synchronize()
+    assert read_device_status() == (0, 0, 0, 0)
+    assert torch.equal(y, y_big[:T])
+    for a, b in zip(taps, taps_big):
+        assert torch.equal(a, b[:T])
+    assert torch.equal(m(xd[:T].contiguous()), y)
+
+
 HANDOFF_SHAPES = [
     # more 128-token tiles than SMs, with a partial last wave: the in/core grid is padded with helper CTAs that run
     # out-projection tiles of the first wave's token tiles (tmoe_handoff_plan)
