@@ -51,6 +51,9 @@ for _e in (8, 64, 256, 1024):
     for _k in (2, 8):
         WORKLOADS[f"cfg3_e{_e}_k{_k}"] = (f"cfg3_e{_e}_k{_k}", 16384,
                                           f"sweep bf16 T=16384 d_in=1536 d_out=2304 E={_e} top{_k} r=(4,256,1024)")
+for _n, _di, _do in (("x_up", 1536, 6144), ("out_proj", 768, 768), ("ffn_up", 768, 4608), ("ffn_down", 4608, 768)):
+    WORKLOADS[f"shipped_{_n}"] = (f"shipped_{_n}", 16384,
+                                  f"prefill bf16 T=16384 d_in={_di} d_out={_do} E=8 top2 r=(32,256,512): the reference model's shipped ranks")
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised in
 # profiles/ncu_full_tc_kernels_prefill_cfg2.txt (same workload, same kernels); None where no capture exists.
 NCU_TRAFFIC_BYTES = {("cfg2", "tc_out_gemm"): 67_702_016 + 89_337_344, ("cfg2", "tc_in_core"): 110_617_344 + 34_054_400}

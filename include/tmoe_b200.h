@@ -46,12 +46,10 @@ typedef enum tmoe_dtype { TMOE_F32 = 0, TMOE_BF16 = 1 } tmoe_dtype_t;
 
 /* Which kernels run.
  *  SIMT    CUDA-core fp32-FMA kernels: any shape, fp32 or bf16 (the accuracy path).
- *  TENSOR  tcgen05 tensor-core kernels: bf16, r1 in {2,4,8,16}, r3 in {64,128,192,256,512},
+ *  TENSOR  tcgen05 tensor-core kernels: bf16, r1 in {2,4,8,16,32}, r3 in {64,128,192,256,512},
  *          d_in and r2 multiples of 64.  Needs the prepared factor set.
- *  DECODE  bandwidth-shaped kernels for T <= 64 tokens on the same shapes plus r1 = 32, same prepared
- *          set (tmoe_forward only).
- *  AUTO    DECODE up to 8 tokens (up to 64 where TENSOR does not cover the shape), TENSOR above, when the shape is
- *          covered; else SIMT. */
+ *  DECODE  bandwidth-shaped kernels for T <= 64 tokens on the same shapes, same prepared set (tmoe_forward only).
+ *  AUTO    DECODE up to 8 tokens, TENSOR above, when the shape is covered; else SIMT. */
 typedef enum tmoe_path {
   TMOE_PATH_AUTO = 0, TMOE_PATH_SIMT = 1, TMOE_PATH_TENSOR = 2, TMOE_PATH_DECODE = 3
 } tmoe_path_t;

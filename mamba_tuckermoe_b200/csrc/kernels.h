@@ -64,7 +64,7 @@ struct PreparedLayout {
   int e_pad, n2, n_tiles2;
 };
 bool prepared_covers(const tmoe_layer_t &L);     // prepared layout + decode kernels (r1 in {2,...,32})
-bool tensor_path_covers(const tmoe_layer_t &L);  // tcgen05 kernels (r1 <= 16)
+bool tensor_path_covers(const tmoe_layer_t &L);  // tcgen05 kernels
 PreparedLayout prepared_layout(const tmoe_layer_t &L);
 // pre_norm_w (optional, [d_in], layer dtype): folded into the U_in and router copies (see prepare.cu)
 int launch_prepare(const tmoe_layer_t &L, const tmoe_factors_t &F, const void *pre_norm_w, void *prepared, cudaStream_t st);

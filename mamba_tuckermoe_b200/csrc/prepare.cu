@@ -27,9 +27,9 @@ bool prepared_covers(const tmoe_layer_t &L) {
   return true;
 }
 
-// Shapes the tcgen05 kernels handle: the epilogue reads the r1 slices of a tile in 16-column groups, so a
-// slice needs at least 16 columns of the 256-column accumulator (r1 <= 16).
-bool tensor_path_covers(const tmoe_layer_t &L) { return prepared_covers(L) && L.r1 <= 16; }
+// Shapes the tcgen05 kernels handle: every prepared shape (a slice of the 256-column accumulator has 256 / r1 >= 8
+// columns; the epilogue reads 16 columns per load, two adjacent slices at r1 = 32).
+bool tensor_path_covers(const tmoe_layer_t &L) { return prepared_covers(L); }
 
 PreparedLayout prepared_layout(const tmoe_layer_t &L) {
   PreparedLayout P{};

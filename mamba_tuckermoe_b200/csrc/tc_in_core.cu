@@ -462,6 +462,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         if (((jl / JPU) & 1) != grp) continue;
         tc_fence_after();
         const uint32_t t_p = t_lane + slot * 256;
+        if constexpr (N2 >= 16) {
 #pragma unroll 1
         for (int sc = 0; sc < N2 / 16; ++sc) {
           const int zc = j * N2 + sc * 16;  // first z column of this 16-column group
@@ -496,6 +497,36 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
             o1.z = pack_bf16x2(acc[12], acc[13]); o1.w = pack_bf16x2(acc[14], acc[15]);
             *reinterpret_cast<uint4 *>(dst) = o0;
             *reinterpret_cast<uint4 *>(dst + 8) = o1;
+          }
+        }
+        } else {
+          // N2 = 8 (r1 = 32): one 16-column load covers two adjacent slices; 8 columns of z per tile and thread
+          static_assert(N2 >= 16 || (N2 == 8 && R1 % 4 == 0), "slice widths below 8 columns are not covered");
+          float acc[8];
+#pragma unroll
+          for (int q = 0; q < 8; ++q) acc[q] = 0.f;
+#pragma unroll
+          for (int a = 0; a < R1; a += 4) {
+            uint32_t r0[16], r1v[16];
+            tmem_ld16(t_p + a * 8, r0);
+            tmem_ld16(t_p + (a + 2) * 8, r1v);
+            tmem_ld_wait(r0, r1v);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              acc[q] = fmaf(c[a], __uint_as_float(r0[q]), acc[q]);
+              acc[q] = fmaf(c[a + 1], __uint_as_float(r0[8 + q]), acc[q]);
+              acc[q] = fmaf(c[a + 2], __uint_as_float(r1v[q]), acc[q]);
+              acc[q] = fmaf(c[a + 3], __uint_as_float(r1v[8 + q]), acc[q]);
+            }
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&bar_pempty[slot]));
+          if (live) {
+            uint4 o;
+            o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+            o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+            *reinterpret_cast<uint4 *>(p.z + grow * p.r2 + j * 8) = o;
           }
         }
       }
@@ -605,6 +636,7 @@ int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared
   else if (L.r1 == 4) { if (small_k) TMOE_IC(4, 2); else TMOE_IC(4, 8); }
   else if (L.r1 == 8) { if (small_k) TMOE_IC(8, 2); else TMOE_IC(8, 8); }
   else if (L.r1 == 16) { if (small_k) TMOE_IC(16, 2); else TMOE_IC(16, 8); }
+  else if (L.r1 == 32) { if (small_k) TMOE_IC(32, 2); else TMOE_IC(32, 8); }
   else return TMOE_ERR_UNSUPPORTED;
 #undef TMOE_IC
   if (e != cudaSuccess) return TMOE_ERR_CUDA;

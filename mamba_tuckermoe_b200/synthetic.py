@@ -96,4 +96,7 @@ for _e in (8, 64, 256, 1024):
     for _k in (2, 8):
         BENCH_SHAPES[f"cfg3_e{_e}_k{_k}"] = (LayerShape(1536, 2304, _e, _k, 4, 256, 1024), 16384, torch.bfloat16,
                                               1003, 0.02)
+# prefill-sized calls of the reference language model's four layer shapes at its shipped ranks (r1, r2, r3) = (32, 512, 256)
+for _n, _di, _do in (("x_up", 1536, 6144), ("out_proj", 768, 768), ("ffn_up", 768, 4608), ("ffn_down", 4608, 768)):
+    BENCH_SHAPES[f"shipped_{_n}"] = (LayerShape(_di, _do, 8, 2, 32, 256, 512, 1e-5), 16384, torch.bfloat16, 1005, 0.02)
 ZIPF_SHAPES = {"cfg4"}  # skewed routing through apply_zipf_router_bias

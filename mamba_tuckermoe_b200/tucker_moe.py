@@ -352,7 +352,7 @@ class TuckerMoE(nn.Module):
 
     def _prenorm_path(self, x: torch.Tensor) -> int:
         """Kernel path on which a call with this x can apply the callers' pre-norm in-kernel (0: none): the decode
-        path, or the tensor-core path with its in-kernel router (E <= 256, top_k <= 8, r3 <= 256, r1 <= 16)."""
+        path, or the tensor-core path with its in-kernel router (E <= 256, top_k <= 8, r3 <= 256)."""
         if not x.is_cuda or x.dtype != torch.bfloat16:
             return 0
         T = x.numel() // max(x.shape[-1], 1)
@@ -365,7 +365,7 @@ class TuckerMoE(nn.Module):
             return PATH_DECODE
         r1, r3, _ = self.core.shape
         E = self.router.weight.shape[0]
-        if rp == PATH_TENSOR and r3 <= 256 and r1 <= 16 and (E + 15) // 16 * 16 <= 256 and self.top_k <= 8:
+        if rp == PATH_TENSOR and r3 <= 256 and (E + 15) // 16 * 16 <= 256 and self.top_k <= 8:
             return PATH_TENSOR
         return 0
 

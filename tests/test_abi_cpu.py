@@ -86,9 +86,12 @@ def test_path_resolution_and_sizes():
     ws = lib.tmoe_workspace_bytes(C.byref(cfg2), 32768, 0)
     assert ws >= 32768 * 1024 * 2 + 256
     shipped = _layer(d_in=768, d_out=768, r1=32, r2=512, r3=256, dtype=_lib.TMOE_BF16)
-    assert lib.tmoe_resolve_path(C.byref(shipped), 4096, 0) == 1      # r1=32 is served by the CUDA-core path
-    assert lib.tmoe_resolve_path(C.byref(shipped), 4096, 2) == -6
-    assert lib.tmoe_resolve_path(C.byref(shipped), 1, 0) == 3          # ... and by the decode kernels for T <= 64
+    assert lib.tmoe_resolve_path(C.byref(shipped), 4096, 0) == 2      # r1=32: tensor-core kernels (8-column slices)
+    assert lib.tmoe_resolve_path(C.byref(shipped), 4096, 2) == 2
+    assert lib.tmoe_resolve_path(C.byref(shipped), 1, 0) == 3          # ... and the decode kernels up to 8 tokens
+    odd = _layer(d_in=768, d_out=768, r1=3, r2=512, r3=256, dtype=_lib.TMOE_BF16)
+    assert lib.tmoe_resolve_path(C.byref(odd), 4096, 0) == 1           # other r1: CUDA-core path
+    assert lib.tmoe_resolve_path(C.byref(odd), 4096, 2) == -6
     assert lib.tmoe_prepared_bytes(C.byref(shipped)) > 0
 
 

@@ -93,6 +93,9 @@ TENSOR_SHAPES = [
     (LayerShape(512, 384, 256, 8, 8, 512, 256, 1e-6), 200),  # r3 = 512: h fills all of TMEM, scores by a separate GEMM
     (LayerShape(3072, 4608, 256, 8, 8, 512, 2048, 1e-6), 130),  # the large skewed configuration's shapes
     (LayerShape(768, 1536, 8, 2, 16, 256, 512, 1e-5), 300),     # r1 = 16: sixteen 16-column slices per accumulator
+    (LayerShape(768, 4608, 8, 2, 32, 256, 512, 1e-5), 333),     # r1 = 32 (the shipped model's ranks): 8-column slices
+    (LayerShape(4608, 768, 8, 2, 32, 256, 512, 1e-5), 19000),   # ... more token tiles than SMs
+    (LayerShape(192, 72, 300, 8, 32, 64, 64, 1e-6), 140),       # r1 = 32, one 64-column unit of z, routing by the select kernel
 ]
 
 
@@ -116,6 +119,7 @@ def test_tensor_path_matches_oracle(shape, T):
     (LayerShape(768, 1536, 8, 2, 16, 256, 512, 1e-5), 300),
     (LayerShape(256, 264, 8, 2, 2, 128, 256, 1e-5), 1100),
     (LayerShape(256, 128, 512, 8, 8, 64, 128, 1e-6), 2500),   # routing by the select kernel (c arrives from memory)
+    (LayerShape(768, 768, 8, 2, 32, 256, 512, 1e-5), 70),     # r1 = 32
 ])
 def test_token_tiles_shared_between_ctas(shape, T):
     """With few token tiles each tile's core tiles are split over several CTAs: same bits as the same tokens at the
