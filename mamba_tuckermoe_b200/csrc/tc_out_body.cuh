@@ -70,6 +70,63 @@ struct alignas(64) OutHelperCfg {
   int n_tiles;
 };
 
+// Epilogue of one 64-column chunk of an output row: accumulator registers r (two 32-column TMEM loads) + bias, optional
+// silu(gate) * v and residual + layer_scale * v, rounded to bf16 into this lane's 128-byte row of the warp's staging
+// tile (16-byte chunks XOR-swizzled as the TMA box expects).  The shared stores carry no "memory" clobber: the staging
+// tile is touched by nothing else the compiler sees, volatile asm statements keep their order, and the proxy fence
+// that follows is the barrier.  With the clobber every store pinned the next group's bias loads behind it and the
+// chunk became a chain of sixteen load latencies (out-projection with K = 512: 118 -> measured below in the callers).
+__device__ __forceinline__ void out_epilogue_chunk(const OutParams &p, const uint32_t (&r)[2][32], int col0, int64_t row,
+                                                   int lane, uint32_t stage_buf) {
+  const bool extras = (p.silu_gate != nullptr) | (p.residual != nullptr);
+#pragma unroll
+  for (int h2 = 0; h2 < 2; ++h2) {
+    // the half's 32 bias values first, so that their loads are in flight together (N % 8 == 0: a group of 8 columns
+    // is entirely in or out; columns >= N are clipped by the store, their values do not matter)
+    float4 b[8];
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      const int col = col0 + h2 * 32 + g * 4;
+      b[g] = (p.bias && col < p.N) ? __ldg(reinterpret_cast<const float4 *>(p.bias + col)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const int col = col0 + h2 * 32 + g * 8;
+      float v[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) v[q] = __uint_as_float(r[h2][g * 8 + q]);
+      v[0] += b[2 * g].x; v[1] += b[2 * g].y; v[2] += b[2 * g].z; v[3] += b[2 * g].w;
+      v[4] += b[2 * g + 1].x; v[5] += b[2 * g + 1].y; v[6] += b[2 * g + 1].z; v[7] += b[2 * g + 1].w;
+      if (extras && col < p.N && row < p.T) {
+        if (p.silu_gate) {
+          const uint4 gv = __ldg(reinterpret_cast<const uint4 *>(p.silu_gate + row * p.N + col));
+          const uint32_t gw2[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float g0 = __uint_as_float(gw2[q] << 16), g1 = __uint_as_float(gw2[q] & 0xffff0000u);
+            v[2 * q] *= g0 / (1.f + __expf(-g0));
+            v[2 * q + 1] *= g1 / (1.f + __expf(-g1));
+          }
+        }
+        if (p.residual) {
+          const uint4 rr = __ldg(reinterpret_cast<const uint4 *>(p.residual + row * p.N + col));
+          const uint4 gg = __ldg(reinterpret_cast<const uint4 *>(p.gamma + col));
+          const uint32_t rw[4] = {rr.x, rr.y, rr.z, rr.w}, gw[4] = {gg.x, gg.y, gg.z, gg.w};
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            v[2 * q] = __uint_as_float(rw[q] << 16) + __uint_as_float(gw[q] << 16) * v[2 * q];
+            v[2 * q + 1] = __uint_as_float(rw[q] & 0xffff0000u) + __uint_as_float(gw[q] & 0xffff0000u) * v[2 * q + 1];
+          }
+        }
+      }
+      const uint32_t chunk = (uint32_t)(h2 * 4 + g) ^ (uint32_t)(lane & 7);
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_buf + lane * 128 + chunk * 16),
+                   "r"(pack_bf16x2(v[0], v[1])), "r"(pack_bf16x2(v[2], v[3])), "r"(pack_bf16x2(v[4], v[5])),
+                   "r"(pack_bf16x2(v[6], v[7])));
+    }
+  }
+}
+
 // Bounded wait for the eight hand-off words of one 128-row tile of A (written with st.global after a __threadfence by the
 // producing CTA's epilogue warps).  The TMA loads that follow read through the async proxy, hence the proxy fence.
 __device__ __forceinline__ bool rows_ready_wait(const uint32_t *flags, uint32_t epoch, int32_t *status) {
@@ -220,50 +277,7 @@ __device__ __forceinline__ void tc_out_body(const CUtensorMap *tmA, const CUtens
         if (lane == 0) tma_store_wait_read<0>();  // the previous store has finished reading the staging tile
         if (threadIdx.x == 64) TMOE_TOC(4);  // epilogue warp 2 waiting for its previous TMA store
         __syncwarp();
-#pragma unroll
-        for (int h2 = 0; h2 < 2; ++h2) {
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const int col = col0 + h2 * 32 + g * 8;
-            float v[8];
-#pragma unroll
-            for (int q = 0; q < 8; ++q) v[q] = __uint_as_float(r[h2][g * 8 + q]);
-            if (col < p.N) {  // N % 8 == 0: a group of 8 is entirely in or out; columns >= N are clipped by the store
-              if (p.bias) {
-                const float4 b0 = __ldg(reinterpret_cast<const float4 *>(p.bias + col));
-                const float4 b1 = __ldg(reinterpret_cast<const float4 *>(p.bias + col + 4));
-                v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
-                v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
-              }
-              if (p.silu_gate && row < p.T) {
-                const uint4 gv = __ldg(reinterpret_cast<const uint4 *>(p.silu_gate + row * p.N + col));
-                const uint32_t gw2[4] = {gv.x, gv.y, gv.z, gv.w};
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                  const float g0 = __uint_as_float(gw2[q] << 16), g1 = __uint_as_float(gw2[q] & 0xffff0000u);
-                  v[2 * q] *= g0 / (1.f + __expf(-g0));
-                  v[2 * q + 1] *= g1 / (1.f + __expf(-g1));
-                }
-              }
-              if (p.residual && row < p.T) {
-                const uint4 rr = __ldg(reinterpret_cast<const uint4 *>(p.residual + row * p.N + col));
-                const uint4 gg = __ldg(reinterpret_cast<const uint4 *>(p.gamma + col));
-                const uint32_t rw[4] = {rr.x, rr.y, rr.z, rr.w}, gw[4] = {gg.x, gg.y, gg.z, gg.w};
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                  v[2 * q] = __uint_as_float(rw[q] << 16) + __uint_as_float(gw[q] << 16) * v[2 * q];
-                  v[2 * q + 1] = __uint_as_float(rw[q] & 0xffff0000u) + __uint_as_float(gw[q] & 0xffff0000u) * v[2 * q + 1];
-                }
-              }
-            }
-            // 16-byte chunk (h2*4+g) of this lane's 128-byte row, XOR-swizzled as the TMA box expects
-            const uint32_t chunk = (uint32_t)(h2 * 4 + g) ^ (uint32_t)(lane & 7);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_buf + lane * 128 + chunk * 16),
-                         "r"(pack_bf16x2(v[0], v[1])), "r"(pack_bf16x2(v[2], v[3])), "r"(pack_bf16x2(v[4], v[5])),
-                         "r"(pack_bf16x2(v[6], v[7]))
-                         : "memory");
-          }
-        }
+        out_epilogue_chunk(p, r, col0, row, lane, stage_buf);
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0 && col0 < p.N) {

@@ -196,50 +196,7 @@ tc_out_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         }
         if (lane == 0) tma_store_wait_read<0>();  // the previous store has finished reading the staging tile
         __syncwarp();
-#pragma unroll
-        for (int h2 = 0; h2 < 2; ++h2) {
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const int col = col0 + h2 * 32 + g * 8;
-            float v[8];
-#pragma unroll
-            for (int q = 0; q < 8; ++q) v[q] = __uint_as_float(r[h2][g * 8 + q]);
-            if (col < p.N) {  // N % 8 == 0: a group of 8 is entirely in or out; columns >= N are clipped by the store
-              if (p.bias) {
-                const float4 b0 = __ldg(reinterpret_cast<const float4 *>(p.bias + col));
-                const float4 b1 = __ldg(reinterpret_cast<const float4 *>(p.bias + col + 4));
-                v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
-                v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
-              }
-              if (p.silu_gate && row < p.T) {
-                const uint4 gv = __ldg(reinterpret_cast<const uint4 *>(p.silu_gate + row * p.N + col));
-                const uint32_t gw2[4] = {gv.x, gv.y, gv.z, gv.w};
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                  const float g0 = __uint_as_float(gw2[q] << 16), g1 = __uint_as_float(gw2[q] & 0xffff0000u);
-                  v[2 * q] *= g0 / (1.f + __expf(-g0));
-                  v[2 * q + 1] *= g1 / (1.f + __expf(-g1));
-                }
-              }
-              if (p.residual && row < p.T) {
-                const uint4 rr = __ldg(reinterpret_cast<const uint4 *>(p.residual + row * p.N + col));
-                const uint4 gg = __ldg(reinterpret_cast<const uint4 *>(p.gamma + col));
-                const uint32_t rw[4] = {rr.x, rr.y, rr.z, rr.w}, gw[4] = {gg.x, gg.y, gg.z, gg.w};
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                  v[2 * q] = __uint_as_float(rw[q] << 16) + __uint_as_float(gw[q] << 16) * v[2 * q];
-                  v[2 * q + 1] = __uint_as_float(rw[q] & 0xffff0000u) + __uint_as_float(gw[q] & 0xffff0000u) * v[2 * q + 1];
-                }
-              }
-            }
-            // 16-byte chunk (h2*4+g) of this lane's 128-byte row, XOR-swizzled as the TMA box expects
-            const uint32_t chunk = (uint32_t)(h2 * 4 + g) ^ (uint32_t)(lane & 7);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_buf + lane * 128 + chunk * 16),
-                         "r"(pack_bf16x2(v[0], v[1])), "r"(pack_bf16x2(v[2], v[3])), "r"(pack_bf16x2(v[4], v[5])),
-                         "r"(pack_bf16x2(v[6], v[7]))
-                         : "memory");
-          }
-        }
+        out_epilogue_chunk(p, r, col0, row, lane, stage_buf);
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0 && col0 < p.N) {
