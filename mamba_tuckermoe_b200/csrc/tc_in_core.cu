@@ -136,7 +136,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       bar_emptyB[G_STAGES_MAX], bar_accA, bar_hready, bar_pfull[2], bar_pempty[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ float inv_rms_s[TM];
-  __shared__ bf16 wnorm_s[512];  // inner_norm weight; the layer is bf16, so this copy is exact
+  __shared__ __align__(16) bf16 wnorm_s[512];  // inner_norm weight; the layer is bf16, so this copy is exact
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -418,20 +418,25 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
           tmem_ld32(t_lane + cc * 32, r);
           tmem_ld_wait(r);
           const uint32_t kblk_base = ring + (cc >> 1) * H_KBLOCK_BYTES + row * 128;
+          // the 32 weights of this column group as four 16-byte broadcast loads, all ahead of the stores
+          uint4 wq[4];
+#pragma unroll
+          for (int g = 0; g < 4; ++g) wq[g] = *reinterpret_cast<const uint4 *>(&wnorm_s[cc * 32 + g * 8]);
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             float v[8];
+            const uint32_t ww[4] = {wq[g].x, wq[g].y, wq[g].z, wq[g].w};
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
               const float a = __uint_as_float(r[g * 8 + q]);
               ss = fmaf(a, a, ss);
-              v[q] = a * __bfloat162float(wnorm_s[cc * 32 + g * 8 + q]);
+              v[q] = a * __uint_as_float((q & 1) ? (ww[q >> 1] & 0xffff0000u) : (ww[q >> 1] << 16));
             }
             const uint32_t chunk = (uint32_t)((cc & 1) * 4 + g) ^ (uint32_t)(row & 7);
             const uint32_t addr = kblk_base + chunk * 16;
             asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pack_bf16x2(v[0], v[1])),
-                         "r"(pack_bf16x2(v[2], v[3])), "r"(pack_bf16x2(v[4], v[5])), "r"(pack_bf16x2(v[6], v[7]))
-                         : "memory");
+                         "r"(pack_bf16x2(v[2], v[3])), "r"(pack_bf16x2(v[4], v[5])), "r"(pack_bf16x2(v[6], v[7])));
+            // no "memory" clobber: nothing the compiler sees touches the h tile, and the proxy fence below orders it
           }
         }
         // h = inv_x * h_raw: RMSNorm(h) = h_raw * inv_x / sqrt(inv_x^2 * mean(h_raw^2) + eps)
