@@ -56,7 +56,7 @@ for _n, _di, _do in (("x_up", 1536, 6144), ("out_proj", 768, 768), ("ffn_up", 76
                                   f"prefill bf16 T=16384 d_in={_di} d_out={_do} E=8 top2 r=(32,256,512): the reference model's shipped ranks")
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised in
 # profiles/ncu_full_tc_kernels_prefill_cfg2.txt (same workload, same kernels); None where no capture exists.
-NCU_TRAFFIC_BYTES = {("cfg2", "tc_out_gemm"): 67_702_016 + 89_337_344, ("cfg2", "tc_in_core"): 110_617_344 + 34_054_400}
+NCU_TRAFFIC_BYTES = {("cfg2", "tc_out_gemm"): 67_705_856 + 90_118_400, ("cfg2", "tc_in_core"): 110_244_864 + 34_057_216}
 N_INPUT_SETS = 4  # rotating x buffers so that no step re-reads the previous step's lines from L2
 
 
