@@ -164,8 +164,12 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
     for (int s = 0; s < A_STAGES_MAX; ++s) { mbar_init(smem_u32(&bar_fullA[s]), 1); mbar_init(smem_u32(&bar_emptyA[s]), p.pre_norm ? 5 : 1); }
     for (int s = 0; s < G_STAGES_MAX; ++s) { mbar_init(smem_u32(&bar_fullB[s]), 1); mbar_init(smem_u32(&bar_emptyB[s]), 1); }
     mbar_init(smem_u32(&bar_accA), 1);
-    mbar_init(smem_u32(&bar_hready), IC_EPI_WARPS);
-    for (int s = 0; s < 2; ++s) { mbar_init(smem_u32(&bar_pfull[s]), 1); mbar_init(smem_u32(&bar_pempty[s]), 4); }
+    // h is staged (and its TMEM columns free) once the four secondary warps say so; the score columns, which lie in
+    // accumulator slot 1, are released through bar_pempty[1] (see the MMA thread's wait).  An accumulator slot is handed
+    // back by all eight warps: the four that read it, and the four that only watched its 'full' barrier, so that the MMA
+    // thread can never complete that barrier twice before a slow watcher has seen the first completion
+    mbar_init(smem_u32(&bar_hready), IC_EPI_WARPS / 2);
+    for (int s = 0; s < 2; ++s) { mbar_init(smem_u32(&bar_pfull[s]), 1); mbar_init(smem_u32(&bar_pempty[s]), IC_EPI_WARPS); }
     fence_mbar_init();
     prefetch_tmap(&tmX); prefetch_tmap(&tmU); prefetch_tmap(&tmG);
     if (p.e_pad) prefetch_tmap(&tmW);
@@ -246,7 +250,9 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       uint32_t sB = 0, phB = 0;
       for (int j = 0; j < jn; ++j) {
         const uint32_t slot = j & 1, pph = (j >> 1) & 1;
-        mbar_wait_or_exit(smem_u32(&bar_pempty[slot]), pph ^ 1, p.status, kKernelInCore, 8);
+        // slot 0 is free from the start (parity trick); slot 1 holds the router scores first, so its first wait is for a
+        // real arrival of the routing warps and its parity runs one phase ahead of slot 0's
+        mbar_wait_or_exit(smem_u32(&bar_pempty[slot]), pph ^ 1 ^ slot, p.status, kKernelInCore, 8);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + slot * 256;
         for (int kb = 0; kb < KH; ++kb) {
@@ -375,6 +381,10 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
               }
             }
           }
+          // last read of the score columns: accumulator slot 1 may be overwritten from here on
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&bar_pempty[1]));
           float gate[RK];
           gates_of<bf16, RK>(sv, p.top_k, p.rc, z_all, gate);
 #pragma unroll
@@ -397,6 +407,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
             for (int a = 0; a < R1; ++a) p.c_out[grow * R1 + a] = c[a];
           }
         } else {
+          if (lane == 0) mbar_arrive(smem_u32(&bar_pempty[1]));   // no scores in TMEM: slot 1 is free at once
 #pragma unroll
           for (int a = 0; a < R1; ++a) c[a] = live ? __ldg(p.c_in + grow * R1 + a) : 0.f;
         }
@@ -443,10 +454,13 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         inv_rms_s[row] = inv_x / sqrtf(inv_x * inv_x * ss / (float)p.r3 + p.eps);
         fence_proxy_async_smem();
         tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(smem_u32(&bar_hready));     // 4 arrivals: h is in shared memory, its TMEM columns are free
+          mbar_arrive(smem_u32(&bar_pempty[1]));  // this warp does not read the score columns
+        }
         named_bar_sync(3, 256);
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bar_hready));  // 8 arrivals: h is in shared memory, TMEM columns are free
       if (threadIdx.x == 64) TMOE_STAMP(4);  // epilogue A done
       named_bar_sync(4, 256);                // c_work of every row is written
       if (grp == 1) {
@@ -464,7 +478,10 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         ok = mbar_wait(smem_u32(&bar_pfull[slot]), pph, p.status, kKernelInCore, 7);
         ok = __all_sync(0xffffffffu, ok);  // TMEM loads are warp-collective
         if (!ok) break;
-        if (((jl / JPU) & 1) != grp) continue;
+        if (((jl / JPU) & 1) != grp) {  // not this group's tile: seen, nothing to read
+          if (lane == 0) mbar_arrive(smem_u32(&bar_pempty[slot]));
+          continue;
+        }
         tc_fence_after();
         const uint32_t t_p = t_lane + slot * 256;
         if constexpr (N2 >= 16) {
