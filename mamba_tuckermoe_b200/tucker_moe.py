@@ -413,7 +413,7 @@ class TuckerMoE(nn.Module):
 
     def _fast_prenorm(self, plan: _Plan, x: torch.Tensor, w: torch.Tensor, T: int):
         """(prepared set with `w` folded in, kernel path) when a call of T tokens can apply the pre-norm in-kernel, else
-        None; remembered per (norm weight, T <= 64) on the plan."""
+        None; remembered per (norm weight, T) on the plan."""
         key = (w.data_ptr(), w._version, T)
         hit = plan.pn.get(key)
         if hit is None:
