@@ -48,6 +48,9 @@ struct OutParams {
   int64_t T;
   int N, K;
   int num_m, num_n;
+  // Output columns per tile of the single-CTA kernel: 256 (0 means 256), or 128 when 256-wide tiles would leave more than
+  // half of the SMs without one (few token rows); num_n counts tiles of this width and tmB's box has this many rows.
+  int on;
   int32_t *status;
   // Tiles [0, tile_begin) of this GEMM were computed by helper CTAs of the kernel that produced A; this launch starts
   // at tile_begin (in its own tile units) and clears the hand-off flags.
@@ -185,6 +188,7 @@ __device__ __forceinline__ void tc_out_body(const CUtensorMap *tmA, const CUtens
   if (dependent) griddep_wait();
 
   const int KB = (p.K + OKB - 1) / OKB;
+  const int on = p.on ? p.on : ON;
 #ifdef TMOE_TRACE
   const long long trace_t0 = clock64();
   long long trace_tic = 0;
@@ -195,7 +199,7 @@ __device__ __forceinline__ void tc_out_body(const CUtensorMap *tmA, const CUtens
       uint32_t it = 0;
       bool ok = true;
       for (int tile = tile_first; tile < tile_end && ok; tile += tile_step) {
-        const int m0 = (tile / p.num_n) * OM, n0 = (tile % p.num_n) * ON;
+        const int m0 = (tile / p.num_n) * OM, n0 = (tile % p.num_n) * on;
         if (p.ready && !(ok = rows_ready_wait(p.ready + (tile / p.num_n) * 8, p.epoch, p.status))) break;
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const uint32_t s = it % OSTAGES, ph = (it / OSTAGES) & 1;
@@ -203,7 +207,7 @@ __device__ __forceinline__ void tc_out_body(const CUtensorMap *tmA, const CUtens
           if (!(ok = mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1, p.status, kKernelOut, 2))) break;
           TMOE_TOC(0);  // producer waiting for a free stage
           const uint32_t full = smem_u32(&bar_full[s]);
-          mbar_arrive_expect_tx(full, O_STAGE_BYTES);
+          mbar_arrive_expect_tx(full, O_A_BYTES + on * 128);
           const uint32_t sa = ring + s * O_STAGE_BYTES;
           tma_load_2d(sa, tmA, kb * OKB, m0, full);
           tma_load_2d(sa + O_A_BYTES, tmB, kb * OKB, n0, full);
@@ -214,7 +218,7 @@ __device__ __forceinline__ void tc_out_body(const CUtensorMap *tmA, const CUtens
     if (lane == 0) {
       // The issuing thread's loop is the serial path (see mbar_wait_or_exit): fixed trip counts, no side exits,
       // ring position and descriptors kept incrementally.
-      const uint32_t idesc = umma_idesc_bf16(OM, ON);
+      const uint32_t idesc = umma_idesc_bf16(OM, on);
       const uint64_t desc0 = umma_desc_k_sw128(ring);
       uint32_t s = 0, ph = 0, tcount = 0;
       for (int tile = tile_first; tile < tile_end; tile += tile_step, ++tcount) {
@@ -251,7 +255,7 @@ __device__ __forceinline__ void tc_out_body(const CUtensorMap *tmA, const CUtens
     uint32_t tcount = 0;
     bool ok = true;
     for (int tile = tile_first; tile < tile_end && ok; tile += tile_step, ++tcount) {
-      const int m0 = (tile / p.num_n) * OM, n0 = (tile % p.num_n) * ON;
+      const int m0 = (tile / p.num_n) * OM, n0 = (tile % p.num_n) * on;
       const uint32_t slot = tcount & 1, aph = (tcount >> 1) & 1;
       TMOE_TIC();
       ok = mbar_wait(smem_u32(&bar_tfull[slot]), aph, p.status, kKernelOut, 3);
@@ -260,15 +264,16 @@ __device__ __forceinline__ void tc_out_body(const CUtensorMap *tmA, const CUtens
       if (!ok) break;
       tc_fence_after();
       const int64_t row = (int64_t)m0 + row_in_tile;
-      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + slot * ON + half * 128;
+      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + slot * ON + half * (on >> 1);
+      const int ncc = on >> 7;   // 64-column chunks per warp: 2 for 256-wide tiles, 1 for 128-wide
 #pragma unroll 1
-      for (int cc = 0; cc < 2; ++cc) {
-        const int col0 = n0 + half * 128 + cc * 64;
+      for (int cc = 0; cc < ncc; ++cc) {
+        const int col0 = n0 + half * (on >> 1) + cc * 64;
         uint32_t r[2][32];
         tmem_ld32(t_row + cc * 64, r[0]);
         tmem_ld32(t_row + cc * 64 + 32, r[1]);
         tmem_ld_wait(r[0], r[1]);
-        if (cc == 1) {  // this warp has read its whole share of the accumulator
+        if (cc == ncc - 1) {  // this warp has read its whole share of the accumulator
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[slot]));

@@ -304,6 +304,14 @@ int launch_tc_gemm_bf16(const void *A, const void *B_t, const float *bias, const
   p.silu_gate = (const bf16 *)epi.silu_gate;
   p.T = M; p.N = N; p.K = K;
   p.num_m = (int)((M + OM - 1) / OM); p.num_n = (N + ON - 1) / ON;
+  p.on = ON;
+  // few token rows: 128-column tiles put twice as many SMs to work (each CTA then streams half of B per k block)
+  static const int narrow_env = [] { const char *e = getenv("TMOE_OUT_NARROW"); return e ? atoi(e) : 1; }();
+  if (narrow_env && !(ho && ho->n_helpers > 0) && N > ON / 2 && (int64_t)p.num_m * p.num_n * 2 <= sms) {
+    p.on = ON / 2;
+    p.num_n = (N + p.on - 1) / p.on;
+    if ((rc = encode_tmap_bf16_2d(&tmB, B_t, (uint64_t)N, (uint64_t)K, (uint32_t)p.on))) return rc;
+  }
   p.status = status;
   if (ho && ho->n_helpers > 0) { p.tile_begin = ho->m_tiles * p.num_n; p.ready_clear = ho->ready; p.ready_words = ho->m_tiles * 8; }
   const int tiles = p.num_m * p.num_n - p.tile_begin;
