@@ -85,6 +85,10 @@ def test_path_resolution_and_sizes():
     assert raw <= n <= raw + 8 * 1024
     ws = lib.tmoe_workspace_bytes(C.byref(cfg2), 32768, 0)
     assert ws >= 32768 * 1024 * 2 + 256
+    # few token tiles: the tensor-core path keeps one [T, r1] block of c per CTA sharing a tile (up to 16) plus the visible one
+    small, big = lib.tmoe_workspace_bytes(C.byref(cfg2), 64, 2), lib.tmoe_workspace_bytes(C.byref(cfg2), 64 * 300, 2)
+    assert small >= 17 * 64 * 4 * 4 + 64 * 1024 * 2
+    assert big < 300 * small                      # ... and only for small calls
     shipped = _layer(d_in=768, d_out=768, r1=32, r2=512, r3=256, dtype=_lib.TMOE_BF16)
     assert lib.tmoe_resolve_path(C.byref(shipped), 4096, 0) == 2      # r1=32: tensor-core kernels (8-column slices)
     assert lib.tmoe_resolve_path(C.byref(shipped), 4096, 2) == 2
