@@ -170,7 +170,8 @@ int tmoe_out(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const voi
 
 /* The whole forward of TuckerMoE.forward (pure_torch_mlx/model.py:68-102) on one stream:
  * x [T, d_in] -> y [T, d_out].  `prepared` may be NULL when the resolved path is SIMT.
- * The stage entry points above serve SIMT and TENSOR; for them AUTO means SIMT when T <= 64.
+ * The stage entry points above serve SIMT and TENSOR; for them AUTO never resolves to DECODE (TENSOR when the shape is
+ * covered, else SIMT).
  * T == 0 is valid and enqueues nothing. */
 int tmoe_forward(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const void *prepared,
                  const void *x, int64_t T, void *y, const tmoe_extras_t *extras, void *workspace,

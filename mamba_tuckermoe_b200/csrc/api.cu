@@ -27,7 +27,7 @@ int check_layer(const tmoe_layer_t *L) {
 }
 
 // allow_decode: tmoe_forward (and the sizing queries) may pick the decode kernels; the stage entry
-// points cannot, so for them AUTO with T <= 64 means the CUDA-core path.
+// points cannot, so for them AUTO means the tensor-core path when it covers the shape, else the CUDA-core path.
 constexpr int kDecodeAutoTokens = 8;
 
 int resolve(const tmoe_layer_t &L, int64_t T, int path, bool allow_decode = true) {
