@@ -13,8 +13,14 @@ The JSON line also carries
                 against the measured bf16 peak in MEASURED_PEAKS.json
   e2e           the same metric through the public call for host-resident activations
                 (TuckerMoE.forward_host): pinned host -> device copy of x, the kernels and the
-                device -> host copy of y are all inside the timed region, chunk-pipelined on 3 streams
+                device -> host copy of y are all inside the timed region, chunk-pipelined on 3 streams;
+                with the copy rate of each direction alone, per rank
+  strong        the workload's T tokens split over the N GPUs (T/N per GPU), same timing rules
+  allgather     (N > 1) that split followed by the NCCL all-gather of y into a [T, d_out] buffer on every rank,
+                unchunked and in 4 chunks overlapped with the kernels (sharding.py)
+  parity        the run's output against the CPU oracle on a fixed token subset, outside the timed region
   cpu_baseline  the CPU restatement of the reference layer on this host (rank 0, N=1 only)
+  gpu_eager_baseline  the same restatement as eager PyTorch on this GPU (rank 0, N=1 only)
   clocks        SM clock / throttle reasons sampled with nvidia-smi during the timed region
 
 `--impl reference` times the reference algorithm's CPU path (the oracle restatement of
@@ -54,9 +60,23 @@ for _e in (8, 64, 256, 1024):
 for _n, _di, _do in (("x_up", 1536, 6144), ("out_proj", 768, 768), ("ffn_up", 768, 4608), ("ffn_down", 4608, 768)):
     WORKLOADS[f"shipped_{_n}"] = (f"shipped_{_n}", 16384,
                                   f"prefill bf16 T=16384 d_in={_di} d_out={_do} E=8 top2 r=(32,256,512): the reference model's shipped ranks")
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised in
-# profiles/ncu_full_tc_kernels_prefill_cfg2.txt (same workload, same kernels); None where no capture exists.
-NCU_TRAFFIC_BYTES = {("cfg2", "tc_out_gemm"): 67_705_856 + 90_118_400, ("cfg2", "tc_in_core"): 110_244_864 + 34_057_216}
+
+
+def ncu_traffic(workload: str, kernel: str):
+    """dram__bytes_read.sum + dram__bytes_write.sum per launch of `kernel` on `workload`, from the line
+    `# traffic_bytes_per_launch <workload> <kernel> <bytes> commit <hash>` of a summary under profiles/ (None if absent)."""
+    d = os.path.join(ROOT, "profiles")
+    try:
+        for name in sorted(os.listdir(d)):
+            for line in open(os.path.join(d, name), errors="replace"):
+                parts = line.split()
+                if len(parts) >= 5 and parts[:2] == ["#", "traffic_bytes_per_launch"] and parts[2] == workload and parts[3] == kernel:
+                    return {"bytes": int(parts[4]), "commit": parts[6] if len(parts) > 6 else None, "file": f"profiles/{name}"}
+    except OSError:
+        pass
+    return None
+
+
 N_INPUT_SETS = 4  # rotating x buffers so that no step re-reads the previous step's lines from L2
 
 
@@ -264,6 +284,86 @@ def run_decode_step(args, dev):
     print(json.dumps(line), flush=True)
 
 
+def timed_steps(fn, steps, barrier, dev, world):
+    """CUDA-event time of `steps` calls of fn(i) bracketed by a barrier + synchronize on both sides; max over ranks (ms)."""
+    import torch.distributed as dist
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for i in range(steps):
+        fn(i)
+    ev1.record()
+    barrier()
+    t_ms = torch.tensor([ev0.elapsed_time(ev1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
+    return float(t_ms.item())
+
+
+def copy_rates(x_host, y_host, x_dev, dev, world, reps=4):
+    """Host<->device copy rate of each direction alone (GB/s, this rank), all ranks copying at the same time."""
+    import torch.distributed as dist
+    y_dev = torch.empty(y_host.shape, dtype=y_host.dtype, device=dev)
+    out = []
+    for src, dst in ((x_host, x_dev), (y_dev, y_host)):
+        dst.copy_(src, non_blocking=True)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            dst.copy_(src, non_blocking=True)
+        b.record()
+        torch.cuda.synchronize()
+        out.append(src.numel() * src.element_size() * reps / (a.elapsed_time(b) * 1e-3) / 1e9)
+    rates = torch.tensor(out, dtype=torch.float64, device=dev)
+    if world > 1:
+        allr = [torch.zeros_like(rates) for _ in range(world)]
+        dist.all_gather(allr, rates)
+        return [[round(float(v), 2) for v in r] for r in allr]
+    return [[round(float(v), 2) for v in rates]]
+
+
+def parity_block(layer, shape, dtype, x_host0, f_typed, zipf):
+    """The run's own output on a fixed token subset against the CPU oracle (outside every timed region)."""
+    from oracle.parity import parity_report, subset_indices
+    T = x_host0.shape[0]
+    heavy = shape.r1 * shape.r3 * shape.r2 > 4 * 256 * 1024          # the largest layer costs 8x more per token on the CPU
+    sub = subset_indices(T, 1024 if heavy else 4096, 1024 if heavy else 4096)
+    with torch.no_grad():
+        y, (idx, _, _) = layer.forward_with_routing(x_host0.to(layer.U_in.device))
+    torch.cuda.synchronize()
+    rep = parity_report(y[sub.to(y.device)], idx[sub.to(y.device)], x_host0[sub], f_typed, shape.top_k, shape.eps, dtype)
+    rep["subset"] = f"first {min(T, 1024 if heavy else 4096)} + strided rest of one {T}-token step ({rep['tokens_checked']} tokens)"
+    rep["reference"] = "CPU restatement of pure_torch_mlx/model.py:68-102 in the layer dtype; ties vs float64"
+    return rep
+
+
+def gpu_eager_rate(workload, dev, sample_tokens, reps=3):
+    """tokens/s of the reference restatement run as eager PyTorch on this GPU (same box, no custom kernels), token-chunked
+    so that the [chunk, r3, r2] intermediate of model.py:95 stays below 1 GiB."""
+    from oracle.tucker_moe_oracle import BENCH_SHAPES, layer_forward, make_factors, make_tokens
+    shape, _, dtype, seed, rstd = BENCH_SHAPES[WORKLOADS[workload][0]]
+    f = {k: v.to(dev) for k, v in make_factors(shape, seed, dtype, rstd).items()}
+    x = make_tokens(sample_tokens, shape.d_in, seed, dtype).to(dev)
+    es = 2 if dtype == torch.bfloat16 else 4
+    chunk = max(1, min(sample_tokens, (1 << 30) // (shape.r3 * shape.r2 * es)))
+    with torch.no_grad():
+        layer_forward(x, f, shape.top_k, shape.eps, chunk_tokens=chunk)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            layer_forward(x, f, shape.top_k, shape.eps, chunk_tokens=chunk)
+        b.record()
+        torch.cuda.synchronize()
+    dt = a.elapsed_time(b) * 1e-3 / reps
+    return {"value": sample_tokens / dt, "unit": "tokens/s", "kind": "reference restatement, eager PyTorch on this GPU",
+            "dtype": "bf16" if dtype == torch.bfloat16 else "f32",
+            "sample": f"{sample_tokens} tokens of the workload in chunks of {chunk}, mean of {reps} ({dt * 1e3:.1f} ms)"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -273,9 +373,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=8)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity", action="store_true")
     ap.add_argument("--path", type=int, default=0, help="0 auto, 1 CUDA-core, 2 tensor-core")
-    ap.add_argument("--allgather", action="store_true",
-                    help="also time the forward followed by the optional NCCL all-gather of y (N > 1), chunk-overlapped")
+    ap.add_argument("--allgather", type=int, default=-1,
+                    help="time the strong-sharded forward followed by the NCCL all-gather of y (default: on when N > 1)")
     ap.add_argument("--profile", action="store_true",
                     help="short run for use under ncu: device-resident steps only (no per-kernel, e2e or CPU legs)")
     args = ap.parse_args()
@@ -318,12 +419,15 @@ def main():
     layer = layer.to(device=dev, dtype=dtype)
     layer.path = args.path
 
-    # this rank's token shard: seeded per rank; host copies stay pinned for the end-to-end leg
-    x_host = [make_tokens(T, shape.d_in, seed + 17 * rank + 1000 * i, dtype).pin_memory() for i in range(N_INPUT_SETS)]
+    # this rank's token shard: seeded per rank; two of the host copies stay pinned for the end-to-end leg
+    n_pinned = 2
+    x_host = [make_tokens(T, shape.d_in, seed + 17 * rank + 1000 * i, dtype) for i in range(N_INPUT_SETS)]
     if zipf:
         for xh in x_host:
             xh[:, 0] = 1.0  # the constant input channel that carries the per-expert bias
     x_dev = [x.to(dev) for x in x_host]
+    x_pin = [x_host[i].pin_memory() for i in range(n_pinned)]
+    x_host = [x_host[0]]   # one pageable copy is kept for the parity subset
     y_host = torch.empty((T, shape.d_out), dtype=dtype).pin_memory()
 
     def barrier():
@@ -331,6 +435,7 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    gather_info = strong = None
     with torch.no_grad():
         for i in range(max(args.warmup, 3)):
             y = layer(x_dev[i % N_INPUT_SETS])
@@ -344,23 +449,12 @@ def main():
         if rank == 0:
             sampler.start()
             time.sleep(0.25)
-        barrier()
         launches0 = lib.tmoe_launch_count()
-        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        ev0.record()
-        for i in range(args.steps):
-            y = layer(x_dev[i % N_INPUT_SETS])
-        ev1.record()
-        barrier()
+        ms_total = timed_steps(lambda i: layer(x_dev[i % N_INPUT_SETS]), args.steps, barrier, dev, world)
         launches = lib.tmoe_launch_count() - launches0
-        ms_total = ev0.elapsed_time(ev1)
         if rank == 0:
             time.sleep(0.15)
             clocks = sampler.stop()
-        t_ms = torch.tensor([ms_total], dtype=torch.float64, device=dev)
-        if world > 1:
-            dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
-        ms_total = float(t_ms.item())
         ms_step = ms_total / args.steps
         value = world * T * args.steps / (ms_total * 1e-3)
 
@@ -372,46 +466,56 @@ def main():
                 dist.destroy_process_group()
             return
 
+        # ---------------- strong sharding: the workload's T tokens split over the ranks ----------------
+        if T % world == 0 and T // world >= 1:
+            Ts = T // world
+            if world == 1:
+                strong = {"tokens_per_gpu": Ts, "global_tokens": T, "ms_per_step": ms_step, "tokens_per_s": value,
+                          "note": "N = 1: identical to the line's own timing"}
+            else:
+                xs = [x[:Ts] for x in x_dev]
+                for i in range(3):
+                    layer(xs[i % N_INPUT_SETS])
+                s_ms = timed_steps(lambda i: layer(xs[i % N_INPUT_SETS]), args.steps, barrier, dev, world) / args.steps
+                strong = {"tokens_per_gpu": Ts, "global_tokens": T, "ms_per_step": s_ms, "tokens_per_s": T / (s_ms * 1e-3),
+                          "note": "same T as at N = 1, T/N tokens per GPU, no collective; max over ranks"}
+                # ---------------- ... followed by the all-gather of y ----------------
+                want_gather = args.allgather != 0
+                if want_gather:
+                    from mamba_tuckermoe_b200.sharding import sharded_forward
+                    gather_info = {}
+                    y_all = torch.empty((T, shape.d_out), dtype=dtype, device=dev)
+                    for chunks in (1, 4):
+                        if T % (world * chunks):
+                            continue
+                        for i in range(2):
+                            sharded_forward(layer, xs[i % N_INPUT_SETS], n_tokens=T, gather=True, chunks=chunks, out=y_all)
+                        g_ms = timed_steps(lambda i: sharded_forward(layer, xs[i % N_INPUT_SETS], n_tokens=T, gather=True,
+                                                                     chunks=chunks, out=y_all),
+                                           max(5, args.steps // 4), barrier, dev, world) / max(5, args.steps // 4)
+                        recv = (world - 1) * Ts * shape.d_out * y_all.element_size()
+                        gather_info[f"chunks{chunks}"] = {
+                            "ms_per_step": g_ms, "tokens_per_s": T / (g_ms * 1e-3),
+                            "ms_over_compute_only": g_ms - s_ms,
+                            "gather_gbs_per_gpu_if_not_overlapped": recv / max(g_ms - s_ms, 1e-6) / 1e6}
+                    gather_info["bytes_received_per_gpu"] = (world - 1) * Ts * shape.d_out * y_all.element_size()
+                    gather_info["note"] = ("strong-sharded forward + in-place all_gather_into_tensor of y into a [T, d_out] "
+                                           "buffer on every rank, per token chunk on a side stream (sharding.py)")
+                    del y_all
+
         # ---------------- per-kernel timing of the two dominant kernels (stage API) ----------------
         kern = per_kernel_times(lib, _lib, layer, shape, dtype, x_dev[0], T, args.path)
 
         # ---------------- end to end with host buffers ----------------
         e2e_steps = max(2, min(args.e2e_steps, args.steps))
         for i in range(2):
-            layer.forward_host(x_host[i % N_INPUT_SETS], out=y_host, pipelined=True)
-        barrier()
-        ev0.record()
-        for i in range(e2e_steps):
-            # the host inputs are ready before the loop and nothing reads y_host between steps: the copies of
-            # consecutive steps may overlap; ev1 is recorded after the current stream has waited for the last copy out
-            layer.forward_host(x_host[i % N_INPUT_SETS], out=y_host, pipelined=True)
-        ev1.record()
-        barrier()
-        e_ms = torch.tensor([ev0.elapsed_time(ev1)], dtype=torch.float64, device=dev)
-        if world > 1:
-            dist.all_reduce(e_ms, op=dist.ReduceOp.MAX)
-        e2e_value = world * T * e2e_steps / (float(e_ms.item()) * 1e-3)
-
-    gather_info = None
-    if args.allgather and world > 1:
-        from mamba_tuckermoe_b200.sharding import sharded_forward
-        with torch.no_grad():
-            for chunks in (1, 4):
-                for _ in range(2):
-                    sharded_forward(layer, x_dev[0], n_tokens=T * world, gather=True, chunks=chunks)
-                barrier()
-                ev0.record()
-                for i in range(5):
-                    y_all = sharded_forward(layer, x_dev[i % N_INPUT_SETS], n_tokens=T * world, gather=True, chunks=chunks)
-                ev1.record()
-                barrier()
-                g_ms = torch.tensor([ev0.elapsed_time(ev1) / 5], dtype=torch.float64, device=dev)
-                dist.all_reduce(g_ms, op=dist.ReduceOp.MAX)
-                gather_info = gather_info or {}
-                gather_info[f"chunks{chunks}"] = {"ms_per_step": float(g_ms.item()),
-                                                  "tokens_per_s": world * T / (float(g_ms.item()) * 1e-3)}
-            gather_info["bytes_received_per_gpu"] = (world - 1) * T * shape.d_out * y_all.element_size()
-            gather_info["note"] = "forward + all_gather_into_tensor of y on a side stream per token chunk (sharding.py)"
+            layer.forward_host(x_pin[i % n_pinned], out=y_host, pipelined=True)
+        # the host inputs are ready before the loop and nothing reads y_host between steps: the copies of
+        # consecutive steps may overlap; the closing event is recorded after the current stream has waited for the last copy out
+        e_ms = timed_steps(lambda i: layer.forward_host(x_pin[i % n_pinned], out=y_host, pipelined=True), e2e_steps, barrier,
+                           dev, world)
+        e2e_value = world * T * e2e_steps / (e_ms * 1e-3)
+        rates = copy_rates(x_pin[0], y_host, x_dev[0], dev, world)
 
     if rank != 0:
         if world > 1:
@@ -430,10 +534,11 @@ def main():
             "us_per_call_cold_l2": d["us_cold"], "us_per_call_warm": d["us_warm"], "us_per_call_graph": d["us_graph"], "us_per_call_graph_24_layers": d["us_graph_24_layers"],
         }
     else:
+        tr = ncu_traffic(args.workload, dom["name"])
         roofline = {
             "bound": "tensor", "kernel": dom["name"], "achieved": dom["tflops"], "peak": peak_tf, "unit": "TFLOP/s",
-            "frac": dom["tflops"] / peak_tf, "traffic": NCU_TRAFFIC_BYTES.get((args.workload, dom["name"])),
-            "traffic_unit": "bytes per launch (ncu dram read+write, see profiles/)",
+            "frac": dom["tflops"] / peak_tf, "traffic": tr["bytes"] if tr else None,
+            "traffic_source": (f"{tr['file']} (ncu dram read+write per launch, taken at commit {tr['commit']})" if tr else None),
             "peak_source": f"{peaks['source']} (burst bf16)",
             "flops_per_launch": dom["flops"], "us_per_launch": dom["us"],
         }
@@ -452,17 +557,27 @@ def main():
         "flops_per_token": flops_tok,
         "roofline": roofline,
         "kernels": kern["all"],
-        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": T * shape.d_in * x_host[0].element_size(),
-                "d2h_bytes_per_step": T * shape.d_out * y_host.element_size(), "steps": e2e_steps},
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": T * shape.d_in * x_pin[0].element_size(),
+                "d2h_bytes_per_step": T * shape.d_out * y_host.element_size(), "steps": e2e_steps,
+                "copy_gbs_per_rank_h2d_d2h": rates,
+                "copy_gbs_all_ranks": [round(sum(r[0] for r in rates), 1), round(sum(r[1] for r in rates), 1)],
+                "note": "copy_gbs: each direction alone, all ranks copying at once, pinned buffers"},
         "gpu_launches": int(launches),
         "clocks": clocks,
     }
+    if strong:
+        line["strong"] = strong
     if gather_info:
         line["allgather"] = gather_info
+    if not args.no_parity:
+        f_typed = {k: v.to(dtype) for k, v in f.items()}
+        line["parity"] = parity_block(layer, shape, dtype, x_host[0], f_typed, zipf)
     if world == 1 and not args.no_cpu_baseline:
         rate, threads, dt = cpu_reference_rate(args.workload, min(T, 8192), 2)
         line["cpu_baseline"] = {"value": rate, "unit": "tokens/s", "cores": threads, "kind": "port",
                                 "sample": f"{min(T, 8192)} tokens of the workload, best of 2 ({dt:.2f} s)"}
+        if dtype == torch.bfloat16 or T <= 4096:
+            line["gpu_eager_baseline"] = gpu_eager_rate(args.workload, dev, min(T, 8192))
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -32,11 +32,13 @@ extern "C" {
 typedef enum tmoe_status {
   TMOE_OK = 0,
   TMOE_ERR_NULL = -1,        /* a required pointer is NULL                               */
-  TMOE_ERR_SHAPE = -2,       /* a size is <= 0, top_k > n_experts, or not a multiple of 8 */
+  TMOE_ERR_SHAPE = -2,       /* a size is <= 0 or not a multiple of 8, top_k > n_experts (top_k is NOT clamped
+                                to n_experts as the trained-checkpoint module does: pass min(top_k, E)), T out of
+                                range, or a non-positive / non-finite router cap or temperature in mode 1 */
   TMOE_ERR_DTYPE = -3,       /* dtype is neither TMOE_F32 nor TMOE_BF16                   */
   TMOE_ERR_ALIGN = -4,       /* a device pointer is not 16-byte aligned                   */
   TMOE_ERR_WORKSPACE = -5,   /* workspace / prepared buffer too small                     */
-  TMOE_ERR_UNSUPPORTED = -6, /* the requested path does not cover this shape / dtype      */
+  TMOE_ERR_UNSUPPORTED = -6, /* the requested path does not cover this shape / dtype, or router_mode is unknown */
   TMOE_ERR_CUDA = -7,        /* a CUDA runtime call or kernel launch failed               */
   TMOE_ERR_DRIVER = -8,      /* tensor-map encoding is unavailable or failed              */
   TMOE_ERR_DEVICE_WAIT = -9  /* a bounded wait inside a kernel expired (device status)    */
@@ -71,8 +73,8 @@ typedef struct tmoe_layer {
   int32_t dtype;  /* tmoe_dtype_t */
   float eps;      /* inner_norm epsilon */
   int32_t router_mode;      /* tmoe_router_mode_t; 0 = the pure-PyTorch module's rule */
-  float router_cap;         /* TMOE_ROUTER_CAPPED_SOFTMAX: soft cap of the scores (reference: 10) */
-  float router_temperature; /* TMOE_ROUTER_CAPPED_SOFTMAX: softmax temperature (reference at inference: 0.5) */
+  float router_cap;         /* TMOE_ROUTER_CAPPED_SOFTMAX: soft cap of the scores (reference: 10); finite, > 0 */
+  float router_temperature; /* TMOE_ROUTER_CAPPED_SOFTMAX: softmax temperature (reference at inference: 0.5); finite, > 0 */
 } tmoe_layer_t;
 
 /* The seven parameters in the reference's own layouts (pure_torch_mlx/model.py:60-66,
@@ -140,8 +142,11 @@ int tmoe_prepare_factors_prenorm(const tmoe_layer_t *layer, const tmoe_factors_t
                                  void *prepared, int64_t prepared_bytes, void *stream);
 
 /* Bytes of scratch that tmoe_forward / tmoe_router / tmoe_in_core / tmoe_out need for T
- * tokens on `path`, or a negative status.  The workspace must be 256-byte aligned.  Its
- * first 256 bytes hold device status words; zero them once after allocation. */
+ * tokens on `path`, or a negative status.  The workspace must be 256-byte aligned.  Its first 256 bytes hold
+ * device status words and the 4096 bytes after them hold flags and counters that the kernels of one forward hand
+ * to one another and leave cleared or superseded: zero the whole workspace once after allocation (stale non-zero
+ * words there can release a waiting CTA early).  A workspace serves one forward at a time: calls that may overlap
+ * on the GPU (different streams) need a workspace each.  T is limited to 2^30 tokens. */
 int64_t tmoe_workspace_bytes(const tmoe_layer_t *layer, int64_t T, int path);
 
 /* Router: scores = x @ router_w^T, top-k of the raw scores, softmax over the k winners
@@ -195,8 +200,10 @@ int tmoe_read_device_status(void *workspace, int32_t *device_status, void *strea
  * every GPU that loads it until the process exits.
  *  - same arguments and results as tmoe_forward(..., path = TMOE_PATH_SIMT) minus workspace/prepared;
  *  - returns TMOE_ERR_WORKSPACE when tmoe_workspace_bytes(layer, T, TMOE_PATH_SIMT) exceeds
- *    TMOE_STATIC_SCRATCH_BYTES (T is then too large for the array: about 800 tokens for r3 = 256,
- *    r2 = 1024; 64 tokens for r3 = 512, r2 = 2048);
+ *    TMOE_STATIC_SCRATCH_BYTES (T is then too large for the array; size a call with tmoe_workspace_bytes, which
+ *    gives about 4 * (r3 + r2) bytes per token: some 800 tokens for r3 = 256, r2 = 1024 and some 370 for r3 = 512,
+ *    r2 = 2048);
+ *  - arguments are validated as by tmoe_forward before anything is enqueued, also when T == 0;
  *  - the first call on each device looks the array's device address up (a one-time host-side step);
  *    make that first call outside of any stream capture;
  *  - all calls on a device share the one array: two calls whose kernels overlap on the GPU (different
@@ -204,6 +211,13 @@ int tmoe_read_device_status(void *workspace, int32_t *device_status, void *strea
 #define TMOE_STATIC_SCRATCH_BYTES (4u << 20)
 int tmoe_forward_static_scratch(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const void *x,
                                 int64_t T, void *y, const tmoe_extras_t *extras, void *stream);
+
+/* Self-test of the bounded-wait reporting: launches one small CTA that waits on an mbarrier nobody arrives on, with a
+ * limit of `limit_cycles` SM clock cycles (clamped to [1e4, 2e8], i.e. at most ~0.1 s) instead of the production
+ * second.  The kernel gives up by itself, writes {TMOE_ERR_DEVICE_WAIT, kernel id 9, tag 42, block 0} to the
+ * workspace's status words and exits; nothing is ever left waiting.  Read the words back with
+ * tmoe_read_device_status.  No reference counterpart. */
+int tmoe_selftest_bounded_wait(void *workspace, int64_t limit_cycles, void *stream);
 
 /* Number of kernels the library has launched in this process (monotonic counter). */
 int64_t tmoe_launch_count(void);

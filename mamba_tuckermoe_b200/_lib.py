@@ -19,7 +19,7 @@ EXPORTS = (
     "tmoe_version", "tmoe_status_string", "tmoe_resolve_path", "tmoe_prepared_bytes",
     "tmoe_prepare_factors", "tmoe_workspace_bytes", "tmoe_router", "tmoe_in_core", "tmoe_out",
     "tmoe_forward", "tmoe_read_device_status", "tmoe_launch_count", "tmoe_forward_static_scratch", "tmoe_rms_norm", "tmoe_handoff_plan",
-    "tmoe_prepare_factors_prenorm",
+    "tmoe_prepare_factors_prenorm", "tmoe_selftest_bounded_wait",
 )
 STATIC_SCRATCH_BYTES = 4 << 20
 
@@ -98,6 +98,8 @@ def load():
         lib.tmoe_read_device_status.restype = i32
         lib.tmoe_read_device_status.argtypes = [vp, C.POINTER(C.c_int32), vp]
         lib.tmoe_launch_count.restype = i64
+        lib.tmoe_selftest_bounded_wait.restype = i32
+        lib.tmoe_selftest_bounded_wait.argtypes = [vp, i64, vp]
         lib.tmoe_handoff_plan.restype = i32
         lib.tmoe_handoff_plan.argtypes = [LP, i64, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]
         if lib.tmoe_version() != 1:

@@ -75,25 +75,67 @@ def _fingerprint(layer: TuckerMoE) -> str:
     return h.hexdigest()
 
 
+# Version of the byte layout that tmoe_prepare_factors writes (block order, tile interleave of the core, padding).  Bump it
+# whenever csrc/prepare.cu's layout changes: a sidecar written for another layout is then refused instead of being read
+# through the wrong offsets.
+PREPARED_LAYOUT_VERSION = 1
+
+
+def _layer_tuple(layer: TuckerMoE):
+    r1, r3, r2 = layer.core.shape
+    return [int(layer.U_in.shape[0]), int(layer.U_out.shape[1]), int(layer.router.weight.shape[0]), int(r1), int(r2),
+            int(r3), str(layer.U_in.dtype)]
+
+
+def _prepared_bytes(layer: TuckerMoE) -> int:
+    """Size the library expects of this layer's prepared set (0: shape / dtype not covered).  Host-side query."""
+    import ctypes as C
+    from . import _lib
+    from .tucker_moe import _layer_struct
+    if layer.U_in.dtype not in (torch.float32, torch.bfloat16):
+        return 0
+    L = _layer_struct(layer.U_in, layer.router.weight, layer.U_in, layer.U_expert, layer.core, layer.U_out, layer.top_k,
+                      layer.inner_norm.eps)
+    return int(_lib.load().tmoe_prepared_bytes(C.byref(L)))
+
+
 def save_prepared_sidecar(layer: TuckerMoE, path: str) -> None:
-    """Writes the layer's prepared factor set with a fingerprint of the parameters it was made from."""
+    """Writes the layer's prepared factor set with what a loader needs to decide whether it may install it: a
+    fingerprint of the parameters it was made from, the library's ABI version, the layout version and the layer sizes."""
+    from . import _lib
     ps = layer._params()
     prep = prepare_factors(ps[0], ps[1], ps[2], layer.inner_norm.eps, ps[3], ps[4], ps[5], ps[6], layer.top_k)
     if prep is None:
         raise RuntimeError("tmoe_b200: this layer's shape/dtype is not covered by the prepared-factor kernels")
     torch.cuda.current_stream(prep.device).synchronize()
     np.savez(path, prepared=prep.cpu().numpy(), fingerprint=np.array(_fingerprint(layer)),
-             top_k=np.array(layer.top_k), eps=np.array(layer.inner_norm.eps, dtype=np.float64))
+             top_k=np.array(layer.top_k), eps=np.array(layer.inner_norm.eps, dtype=np.float64),
+             abi=np.array(_lib.load().tmoe_version()), layout=np.array(PREPARED_LAYOUT_VERSION),
+             layer=np.array(_layer_tuple(layer), dtype=object).astype(str))
 
 
 def load_prepared_sidecar(layer: TuckerMoE, path: str) -> bool:
-    """Installs a saved prepared factor set if it matches the layer's current parameters.
-    Returns False (and leaves the layer untouched) when the fingerprint differs."""
+    """Installs a saved prepared factor set if it was written for this library build's layout, for a layer of these
+    sizes, from exactly the layer's current parameters, and has the size the kernels will read.  Returns False (and
+    leaves the layer untouched) otherwise: the kernels address the buffer through raw offsets, so a set from another
+    layout or a truncated file must never reach them."""
+    from . import _lib
     z = np.load(path if str(path).endswith(".npz") else str(path) + ".npz")
-    if str(z["fingerprint"]) != _fingerprint(layer) or int(z["top_k"]) != layer.top_k:
+    need = ("prepared", "fingerprint", "top_k", "abi", "layout", "layer")
+    if any(k not in z.files for k in need):
+        return False
+    if int(z["abi"]) != _lib.load().tmoe_version() or int(z["layout"]) != PREPARED_LAYOUT_VERSION:
+        return False
+    if [str(v) for v in z["layer"].tolist()] != [str(v) for v in _layer_tuple(layer)] or int(z["top_k"]) != layer.top_k:
+        return False
+    prepared = z["prepared"]
+    expect = _prepared_bytes(layer)
+    if expect <= 0 or prepared.dtype != np.uint8 or prepared.ndim != 1 or prepared.size != expect:
+        return False
+    if str(z["fingerprint"]) != _fingerprint(layer):
         return False
     dev = layer.U_in.device
-    layer._prep = torch.from_numpy(z["prepared"]).to(dev)
+    layer._prep = torch.from_numpy(prepared).to(dev)
     layer._prep_key = _param_key(layer._params())
     layer._plan = None
     return True

@@ -2,7 +2,9 @@
 // dispatch between the CUDA-core path and the tcgen05 tensor-core path.
 #include "common.cuh"
 #include "kernels.h"
+#include "ptx.cuh"
 #include <atomic>
+#include <cmath>
 
 namespace tmoe {
 
@@ -23,8 +25,19 @@ int check_layer(const tmoe_layer_t *L) {
     return TMOE_ERR_SHAPE;
   if (L->top_k > L->n_experts || L->top_k > TMOE_MAX_TOPK || L->r1 > TMOE_MAX_R1) return TMOE_ERR_SHAPE;
   if ((L->d_in | L->d_out | L->r2 | L->r3) & 7) return TMOE_ERR_SHAPE;
+  if (L->router_mode != TMOE_ROUTER_TOPK_SOFTMAX && L->router_mode != TMOE_ROUTER_CAPPED_SOFTMAX) return TMOE_ERR_UNSUPPORTED;
+  if (L->router_mode == TMOE_ROUTER_CAPPED_SOFTMAX) {
+    // the cap divides the scores and the temperature divides the logits: both must be finite and positive
+    if (!(L->router_cap > 0.f) || !(L->router_temperature > 0.f) || std::isinf(L->router_cap) ||
+        std::isinf(L->router_temperature))
+      return TMOE_ERR_SHAPE;
+  }
   return TMOE_OK;
 }
+
+// Token counts are carried as 32-bit row indices by the CUDA-core kernels and as tensor-map extents by the others.
+constexpr int64_t kMaxTokens = (int64_t)1 << 30;
+inline int check_tokens(int64_t T) { return (T < 0 || T > kMaxTokens) ? (int)TMOE_ERR_SHAPE : (int)TMOE_OK; }
 
 // allow_decode: tmoe_forward (and the sizing queries) may pick the decode kernels; the stage entry
 // points cannot, so for them AUTO means the tensor-core path when it covers the shape, else the CUDA-core path.
@@ -134,7 +147,7 @@ const char *tmoe_status_string(int status) {
 int tmoe_resolve_path(const tmoe_layer_t *layer, int64_t T, int path) {
   int rc = check_layer(layer);
   if (rc) return rc;
-  if (T < 0) return TMOE_ERR_SHAPE;
+  if (check_tokens(T)) return TMOE_ERR_SHAPE;
   return resolve(*layer, T, path);
 }
 
@@ -172,7 +185,7 @@ int tmoe_prepare_factors_prenorm(const tmoe_layer_t *layer, const tmoe_factors_t
 int64_t tmoe_workspace_bytes(const tmoe_layer_t *layer, int64_t T, int path) {
   int rc = check_layer(layer);
   if (rc) return rc;
-  if (T < 0) return TMOE_ERR_SHAPE;
+  if (check_tokens(T)) return TMOE_ERR_SHAPE;
   int rp = resolve(*layer, T, path);
   if (rp < 0) return rp;
   return ws_layout(*layer, T, rp).total;
@@ -183,14 +196,28 @@ int tmoe_router(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const 
   int rc = check_layer(layer);
   if (rc) return rc;
   if ((rc = check_factors(factors))) return rc;
-  if (T < 0) return TMOE_ERR_SHAPE;
+  if (check_tokens(T)) return TMOE_ERR_SHAPE;
   if (T == 0) return TMOE_OK;
   if (!x || !idx || !gates || !c || !workspace) return TMOE_ERR_NULL;
   if (misaligned(x) || (reinterpret_cast<uintptr_t>(workspace) & 255)) return TMOE_ERR_ALIGN;
   WsLayout W = ws_layout(*layer, T, TMOE_PATH_SIMT);
   if (workspace_bytes < W.total) return TMOE_ERR_WORKSPACE;
   char *ws = reinterpret_cast<char *>(workspace);
-  return router_simt(*layer, *factors, x, T, W.simt_router_fused, reinterpret_cast<float *>(ws + W.scores), idx, gates,
+  const tmoe_layer_t &L = *layer;
+  // bf16 layers with enough tokens: the scores are a [T, d_in] x [d_in, E] contraction whose only HBM traffic is one read of
+  // x, but at E >= 16 its FMA count exceeds what the CUDA cores do in that time.  router_w [E, d_in] is already the K-major
+  // operand the tensor-core GEMM kernel wants, its bf16 output is the reference's rounding of the scores, and the keyed
+  // select kernel finishes the job.  Needs E % 8 == 0 (16-byte rows of scores) and room for [T, E] bf16 in the workspace.
+  const int64_t sc_off = kStatusBytes + kHandoffBytes;
+  if (L.dtype == TMOE_BF16 && T >= 512 && L.n_experts % 8 == 0 && L.n_experts <= 1024 &&
+      workspace_bytes >= sc_off + T * L.n_experts * 2) {
+    void *scores = ws + sc_off;
+    if ((rc = launch_tc_gemm_bf16(x, factors->router_w, nullptr, OutEpilogue{}, T, L.n_experts, L.d_in, scores,
+                                  reinterpret_cast<int32_t *>(ws), (cudaStream_t)stream)))
+      return rc;
+    return launch_select_bf16_scores(L, scores, L.n_experts, factors->U_expert, T, idx, gates, c, (cudaStream_t)stream);
+  }
+  return router_simt(L, *factors, x, T, W.simt_router_fused, reinterpret_cast<float *>(ws + W.scores), idx, gates,
                      c, (cudaStream_t)stream);
 }
 
@@ -199,7 +226,7 @@ int tmoe_in_core(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const
   int rc = check_layer(layer);
   if (rc) return rc;
   if ((rc = check_factors(factors))) return rc;
-  if (T < 0) return TMOE_ERR_SHAPE;
+  if (check_tokens(T)) return TMOE_ERR_SHAPE;
   if (T == 0) return TMOE_OK;
   if (!x || !c || !z || !workspace) return TMOE_ERR_NULL;
   if (misaligned(x) || misaligned(z) || misaligned(c) || (reinterpret_cast<uintptr_t>(workspace) & 255)) return TMOE_ERR_ALIGN;
@@ -225,7 +252,7 @@ int tmoe_out(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const voi
   int rc = check_layer(layer);
   if (rc) return rc;
   if ((rc = check_factors(factors))) return rc;
-  if (T < 0) return TMOE_ERR_SHAPE;
+  if (check_tokens(T)) return TMOE_ERR_SHAPE;
   if (T == 0) return TMOE_OK;
   if (!z || !y || !workspace) return TMOE_ERR_NULL;
   if (misaligned(z) || misaligned(y) || (reinterpret_cast<uintptr_t>(workspace) & 255)) return TMOE_ERR_ALIGN;
@@ -250,7 +277,7 @@ int tmoe_forward(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const
   int rc = check_layer(layer);
   if (rc) return rc;
   if ((rc = check_factors(factors))) return rc;
-  if (T < 0) return TMOE_ERR_SHAPE;
+  if (check_tokens(T)) return TMOE_ERR_SHAPE;
   if (T == 0) return TMOE_OK;
   if (!x || !y || !workspace) return TMOE_ERR_NULL;
   if (misaligned(x) || misaligned(y) || (reinterpret_cast<uintptr_t>(workspace) & 255)) return TMOE_ERR_ALIGN;
@@ -347,6 +374,30 @@ int tmoe_read_device_status(void *workspace, int32_t *device_status, void *strea
   for (int i = 0; i < 4; ++i) device_status[i] = words[i];
   if (words[0] != 0 && cudaMemset(workspace, 0, kStatusBytes) != cudaSuccess) return TMOE_ERR_CUDA;
   return TMOE_OK;
+}
+
+namespace tmoe {
+namespace {
+constexpr int kKernelSelfTest = 9;
+// One warp; lane 0 waits on a barrier that nobody arrives on and lets the bounded wait run out.
+__global__ void selftest_wait_kernel(int32_t *status, long long limit_cycles) {
+  __shared__ __align__(8) uint64_t bar;
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(ptx::smem_u32(&bar), 1);
+    ptx::fence_mbar_init();
+    (void)ptx::mbar_wait_slow(ptx::smem_u32(&bar), 0, status, kKernelSelfTest, 42, limit_cycles);
+  }
+}
+}  // namespace
+}  // namespace tmoe
+
+int tmoe_selftest_bounded_wait(void *workspace, int64_t limit_cycles, void *stream) {
+  if (!workspace) return TMOE_ERR_NULL;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return TMOE_ERR_ALIGN;
+  long long lim = limit_cycles < 10000 ? 10000 : (limit_cycles > 200000000 ? 200000000 : (long long)limit_cycles);
+  tmoe::selftest_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(reinterpret_cast<int32_t *>(workspace), lim);
+  count_launch();
+  return launch_status();
 }
 
 int tmoe_handoff_plan(const tmoe_layer_t *layer, int64_t T, int32_t *n_helper_ctas, int32_t *n_token_tiles) {

@@ -56,17 +56,6 @@ __device__ __forceinline__ bool ranks_before(float va, int ia, float vb, int ib)
   return (va > vb) || (va == vb && ia < ib);
 }
 
-// Softmax over the k selected scores (sorted descending, so sel_v[0] is the maximum), gate
-// rounding to the storage type, and c[a] = sum_j gate_j * U_expert[idx_j, a].
-// Executed redundantly by every lane of a warp (inputs are warp-uniform); lane `a` keeps c[a].
-template <typename T>
-__device__ __forceinline__ void gates_from_selection(const float *sel_v, int k, float *gate) {
-  float m = sel_v[0], den = 0.f;
-  for (int j = 0; j < k; ++j) { gate[j] = __expf(sel_v[j] - m); den += gate[j]; }
-  float inv = 1.f / den;
-  for (int j = 0; j < k; ++j) gate[j] = round_to<T>(gate[j] * inv);
-}
-
 // Launch that may begin while the previous kernel of the stream drains (programmatic dependent launch); the kernel calls
 // ptx::griddep_wait() before it reads what that kernel wrote.  TMOE_PDL=0 turns the attribute off.
 template <typename... KArgs, typename... Args>

@@ -42,14 +42,15 @@ constexpr long long kWaitLimitCycles = 2000000000LL;
 // Bounded wait.  On expiry (or when another waiter of this launch already reported one) it
 // records {TMOE_ERR_DEVICE_WAIT, kernel id, tag, block} in the status words and returns false;
 // the caller must then leave its role loop and fall through to the kernel's teardown.
-static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, int32_t *status, int kernel_id, int tag) {
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, int32_t *status, int kernel_id, int tag,
+                                                   long long limit_cycles = kWaitLimitCycles) {
   const long long t0 = clock64();
   uint32_t spins = 0;
   for (;;) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 0xffu) == 0) {
       if (*reinterpret_cast<volatile int32_t *>(status) != 0) return false;
-      if (clock64() - t0 > kWaitLimitCycles) break;
+      if (clock64() - t0 > limit_cycles) break;
     }
   }
   if (atomicCAS(status, 0, (int32_t)TMOE_ERR_DEVICE_WAIT) == 0) {
@@ -119,13 +120,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst_smem),
       "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1)
       : "memory");
-}
-
-// Ask L2 to fetch the box at (c0, c1) of a tiled tensor; no shared-memory destination, no completion signal.
-__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap *m, int c0, int c1) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(m)),
-               "r"(c0), "r"(c1)
-               : "memory");
 }
 
 // 2-D tiled store shared (this CTA) -> global, tracked by the thread's bulk async-group.

@@ -71,7 +71,7 @@ __global__ void __launch_bounds__(256) simt_gemm_kernel(GemmP p, Epi epi) {
   __shared__ __align__(16) float Bs[BK][BN + PAD];
   const int tid = threadIdx.x;
   const int tx = tid & 15, ty = tid >> 4;
-  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;   // token tiles on grid.x: no 65535 limit on them
   float acc[4][4];
 #pragma unroll
   for (int i = 0; i < 4; ++i)
@@ -152,7 +152,7 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(float *__restrict__ h
   for (int i = lane; i < r3; i += 32) row[i] = row[i] / den * to_f32(w[i]);
 }
 
-static dim3 gemm_grid(int64_t M, int N) { return dim3((unsigned)((N + BN - 1) / BN), (unsigned)((M + BM - 1) / BM)); }
+static dim3 gemm_grid(int64_t M, int N) { return dim3((unsigned)((M + BM - 1) / BM), (unsigned)((N + BN - 1) / BN)); }
 
 template <typename T>
 static int scores_t(const tmoe_layer_t &L, const void *x, const void *wr, int64_t T_, float *scores, cudaStream_t st) {

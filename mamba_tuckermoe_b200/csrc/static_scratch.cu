@@ -12,8 +12,9 @@
 
 namespace {
 
-// 4 MiB: enough for 64 decode tokens of the largest benchmark layer (r3 = 512, r2 = 2048, top-8)
-// and for about 800 tokens of the (r3, r2) = (256, 1024) layers.
+// 4 MiB.  What fits is whatever tmoe_workspace_bytes(layer, T, TMOE_PATH_SIMT) says fits: the CUDA-core layout keeps
+// idx, gates, c, h [T, r3] and z [T, r2] in fp32, about 4 * (r3 + r2 + r1 + 2 * top_k) bytes per token -- roughly 800 tokens
+// for (r3, r2) = (256, 1024) and 400 for (512, 2048).
 static __device__ __align__(256) unsigned char g_static_scratch[TMOE_STATIC_SCRATCH_BYTES];
 
 std::mutex g_setup_mutex;
@@ -39,16 +40,27 @@ int scratch_address(void **out) {
 
 extern "C" int tmoe_forward_static_scratch(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const void *x,
                                            int64_t T, void *y, const tmoe_extras_t *extras, void *stream) {
-  // size check first: tmoe_workspace_bytes validates the layer and touches no CUDA state
+  // size check first: tmoe_workspace_bytes validates the layer and the token count and touches no CUDA state
   const int64_t need = tmoe_workspace_bytes(layer, T, TMOE_PATH_SIMT);
   if (need < 0) return (int)need;
   if (need > (int64_t)TMOE_STATIC_SCRATCH_BYTES) return TMOE_ERR_WORKSPACE;
+  // the same argument checks as tmoe_forward, before anything is enqueued (also for T == 0)
+  if (!factors) return TMOE_ERR_NULL;
+  const void *fp[7] = {factors->router_w, factors->U_in, factors->inner_norm_w, factors->U_expert, factors->core,
+                       factors->U_out, factors->bias};
+  for (const void *q : fp) {
+    if (!q) return TMOE_ERR_NULL;
+    if (reinterpret_cast<uintptr_t>(q) & 15) return TMOE_ERR_ALIGN;
+  }
   if (T == 0) return TMOE_OK;
+  if (!x || !y) return TMOE_ERR_NULL;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) return TMOE_ERR_ALIGN;
   void *scratch = nullptr;
   int rc = scratch_address(&scratch);
   if (rc) return rc;
-  // the array keeps whatever the previous call left; only the status words have to start at zero
-  if (cudaMemsetAsync(scratch, 0, tmoe::kStatusBytes, (cudaStream_t)stream) != cudaSuccess) return TMOE_ERR_CUDA;
+  // the array keeps whatever the previous call left; the status and hand-off words have to start at zero
+  if (cudaMemsetAsync(scratch, 0, tmoe::kStatusBytes + tmoe::kHandoffBytes, (cudaStream_t)stream) != cudaSuccess)
+    return TMOE_ERR_CUDA;
   return tmoe_forward(layer, factors, nullptr, x, T, y, extras, scratch, (int64_t)TMOE_STATIC_SCRATCH_BYTES,
                       TMOE_PATH_SIMT, stream);
 }

@@ -307,7 +307,8 @@ int launch_tc_gemm_bf16(const void *A, const void *B_t, const float *bias, const
   p.on = ON;
   // few token rows: 128-column tiles put twice as many SMs to work (each CTA then streams half of B per k block)
   static const int narrow_env = [] { const char *e = getenv("TMOE_OUT_NARROW"); return e ? atoi(e) : 1; }();
-  if (narrow_env && !(ho && ho->n_helpers > 0) && N > ON / 2 && (int64_t)p.num_m * p.num_n * 2 <= sms) {
+  // ... and an output of at most 128 columns (the router-scores GEMM at E <= 128) never needs the wide tile
+  if (narrow_env && !(ho && ho->n_helpers > 0) && (N <= ON / 2 || (int64_t)p.num_m * p.num_n * 2 <= sms)) {
     p.on = ON / 2;
     p.num_n = (N + p.on - 1) / p.on;
     if ((rc = encode_tmap_bf16_2d(&tmB, B_t, (uint64_t)N, (uint64_t)K, (uint32_t)p.on))) return rc;

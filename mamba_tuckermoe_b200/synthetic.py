@@ -91,7 +91,7 @@ BENCH_SHAPES = {
     "cfg3": (LayerShape(1536, 2304, 64, 2, 4, 256, 1024), 16384, torch.bfloat16, 1003, 0.02),
     "cfg4": (LayerShape(3072, 4608, 256, 8, 8, 512, 2048), 131072, torch.bfloat16, 1004, 0.02),
 }
-# expert-count sweep: E x top-k at T=16384 (BASELINE config 3)
+# expert-count sweep: E x top-k at T=16384
 for _e in (8, 64, 256, 1024):
     for _k in (2, 8):
         BENCH_SHAPES[f"cfg3_e{_e}_k{_k}"] = (LayerShape(1536, 2304, _e, _k, 4, 256, 1024), 16384, torch.bfloat16,

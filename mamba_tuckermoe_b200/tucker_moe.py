@@ -304,6 +304,11 @@ class _Plan:
                  "dev", "d_in", "d_out", "lib", "pn")
 
 
+def _drop_caches_after_load(module, incompatible_keys) -> None:
+    """load_state_dict post-hook: whatever was derived from the old parameter values is dropped."""
+    module.invalidate_cache()
+
+
 class TuckerMoE(nn.Module):
     """Low-rank Tucker-decomposed Mixture-of-Experts, B200 forward.
 
@@ -335,6 +340,7 @@ class TuckerMoE(nn.Module):
         self._prep_pn_key = None
         self._prep_pn = None
         self._plan = None
+        self.register_load_state_dict_post_hook(_drop_caches_after_load)
 
     def _prepared_for(self, x: torch.Tensor) -> Optional[torch.Tensor]:
         """Prepared factor set for the tensor-core path, rebuilt when a parameter's storage,
@@ -425,10 +431,11 @@ class TuckerMoE(nn.Module):
 
     def _fast_forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None,
                       layer_scale: Optional[torch.Tensor] = None, silu_gate: Optional[torch.Tensor] = None,
-                      pre_norm=None) -> torch.Tensor:
+                      pre_norm=None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Eager call without the dispatcher: the same C entry point as the custom op, with the per-call
         Python work cut to a cache lookup (decode-sized calls cost more in Python than on the GPU).
-        The optional arguments are those of ``forward_fused`` (``pre_norm`` as a ``(weight, eps)`` pair)."""
+        The optional arguments are those of ``forward_fused`` (``pre_norm`` as a ``(weight, eps)`` pair);
+        ``out`` is an optional contiguous (T, d_out) result buffer."""
         plan = self._plan_for(x)
         if x.shape[-1] != plan.d_in:
             raise RuntimeError(f"tmoe_b200: x has {x.shape[-1]} features, the layer expects {plan.d_in}")
@@ -436,7 +443,13 @@ class TuckerMoE(nn.Module):
         if not x2.is_contiguous():
             x2 = x2.contiguous()
         T = x2.shape[0]
-        y = torch.empty((T, plan.d_out), dtype=x.dtype, device=x.device)
+        if out is None:
+            y = torch.empty((T, plan.d_out), dtype=x.dtype, device=x.device)
+        else:
+            if out.numel() != T * plan.d_out or out.dtype != x.dtype or out.device != x.device or not out.is_contiguous() \
+                    or (out.data_ptr() & 15):
+                raise RuntimeError("tmoe_b200: `out` must be a contiguous, 16-byte aligned (..., d_out) tensor of x's dtype on x's device")
+            y = out
         if T:
             lib, dev = plan.lib, plan.dev
             prepared_ptr, force_path, ex_ref, keep = plan.prepared_ptr, None, None, None
@@ -501,17 +514,43 @@ class TuckerMoE(nn.Module):
         return tucker_moe_forward(x, rw, ui, nw, self.inner_norm.eps, ue, co, uo, b, self.top_k, path=self.path,
                                   prepared=self._prepared_for(x), router=self._router())
 
+    def forward_into(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """``forward`` with the result written into ``out`` (contiguous, (..., d_out), x's dtype and device): lets a
+        caller place the output where the next step wants it, e.g. in its slot of an all-gather buffer."""
+        if not x.is_cuda:
+            raise RuntimeError("tmoe_b200: the layer forward runs on CUDA tensors only (no CPU fallback)")
+        self._fast_forward(x, out=out)
+        return out
+
     def forward_fused(self, x: torch.Tensor, *, pre_norm=None, residual: Optional[torch.Tensor] = None,
-                      layer_scale: Optional[torch.Tensor] = None, silu_gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      layer_scale: Optional[torch.Tensor] = None, silu_gate: Optional[torch.Tensor] = None,
+                      return_routing: bool = False):
         """The layer with the callers' element-wise work attached:
 
         ``pre_norm``  an RMSNorm module (anything with ``.weight`` and ``.eps``) or a ``(weight, eps)`` pair
                       applied to ``x`` first (``norm_out_proj`` / ``norm_ffn``, ``model.py:258, 337``);
         ``silu_gate`` ``silu(silu_gate) * layer(...)`` in the out-projection's epilogue (``model.py:340``);
         ``residual``, ``layer_scale``  ``residual + layer_scale * (...)`` in the same epilogue (``model.py:260, 341``).
+        ``return_routing``  also return ``(idx, gates, c)`` of the call (same kernels, same output).
         """
         if pre_norm is not None and hasattr(pre_norm, "weight"):
             pre_norm = (pre_norm.weight, pre_norm.eps)
+        if (residual is None) != (layer_scale is None):
+            raise RuntimeError("tmoe_b200: residual and layer_scale go together")
+        if return_routing:
+            rw, ui, nw, ue, co, uo, b = self._params()
+            path, prep, pn_eps = self.path, None, None
+            if pre_norm is not None:
+                w, e = pre_norm
+                prep = self._prepared_prenorm_for(x, w)
+                if prep is not None:
+                    path, pn_eps = self._prenorm_path(x), float(e)
+                else:
+                    x = rms_norm(x, w, e)
+            if prep is None:
+                prep = self._prepared_for(x)
+            return _run(x, rw, ui, nw, self.inner_norm.eps, ue, co, uo, b, self.top_k, path, residual, layer_scale,
+                        want_taps=True, prepared=prep, silu_gate=silu_gate, router=self._router(), pre_norm_eps=pn_eps)
         if x.is_cuda and not torch.compiler.is_compiling():
             return self._fast_forward(x, residual, layer_scale, silu_gate, pre_norm)
         rw, ui, nw, ue, co, uo, b = self._params()

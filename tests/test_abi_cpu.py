@@ -48,6 +48,52 @@ def test_invalid_layers_are_rejected(kw, code):
     assert lib.tmoe_resolve_path(C.byref(L), 16, 0) == code
 
 
+def test_router_rule_parameters_are_validated():
+    """An unknown gate rule, or a cap / temperature the capped rule cannot divide by, is an error, not a silent default."""
+    lib = _lib.load()
+    assert lib.tmoe_workspace_bytes(C.byref(_layer(router_mode=2)), 16, 0) == -6
+    assert lib.tmoe_workspace_bytes(C.byref(_layer(router_mode=-1)), 16, 0) == -6
+    for kw in (dict(router_cap=0.0), dict(router_cap=-1.0), dict(router_temperature=0.0), dict(router_cap=float("nan")),
+               dict(router_temperature=float("inf"))):
+        assert lib.tmoe_workspace_bytes(C.byref(_layer(router_mode=1, **kw)), 16, 0) == -2, kw
+        assert lib.tmoe_workspace_bytes(C.byref(_layer(router_mode=0, **kw)), 16, 0) > 0, kw   # rule 0 ignores them
+    assert lib.tmoe_workspace_bytes(C.byref(_layer(router_mode=1)), 16, 0) > 0
+    # top_k is not clamped to the expert count (the trained-checkpoint module clamps; callers pass min(top_k, E))
+    assert lib.tmoe_workspace_bytes(C.byref(_layer(top_k=9, n_experts=8)), 16, 0) == -2
+
+
+def test_token_count_bound():
+    lib = _lib.load()
+    L = _layer()
+    F = _lib.Factors(*[4096] * 7)
+    assert lib.tmoe_workspace_bytes(C.byref(L), 1 << 30, 1) > 0
+    assert lib.tmoe_workspace_bytes(C.byref(L), (1 << 30) + 1, 1) == -2
+    assert lib.tmoe_resolve_path(C.byref(L), 1 << 40, 0) == -2
+    assert lib.tmoe_forward(C.byref(L), C.byref(F), None, 4096, (1 << 30) + 1, 4096, None, 4096, 1 << 20, 1, None) == -2
+    assert lib.tmoe_router(C.byref(L), C.byref(F), 4096, 1 << 31, 4096, 4096, 4096, 4096, 1 << 20, None) == -2
+
+
+def test_static_scratch_validates_before_enqueueing():
+    lib = _lib.load()
+    L = _layer()
+    F = _lib.Factors(*[4096] * 7)
+    # also at T == 0: bad factors, then a clean no-op
+    assert lib.tmoe_forward_static_scratch(C.byref(L), None, 4096, 0, 4096, None, None) == -1
+    Fbad = _lib.Factors(4096, 4096, 4100, 4096, 4096, 4096, 4096)
+    assert lib.tmoe_forward_static_scratch(C.byref(L), C.byref(Fbad), 4096, 0, 4096, None, None) == -4
+    assert lib.tmoe_forward_static_scratch(C.byref(L), C.byref(F), 4096, 0, 4096, None, None) == 0
+    assert lib.tmoe_forward_static_scratch(C.byref(L), C.byref(F), None, 4, 4096, None, None) == -1
+    assert lib.tmoe_forward_static_scratch(C.byref(L), C.byref(F), 4100, 4, 4096, None, None) == -4
+    # the largest T that fits is what tmoe_workspace_bytes says, and one more token is refused
+    t = 1
+    while lib.tmoe_workspace_bytes(C.byref(L), t + 1, 1) <= _lib.STATIC_SCRATCH_BYTES:
+        t += 1 if t < 64 else t // 16
+    while lib.tmoe_workspace_bytes(C.byref(L), t, 1) > _lib.STATIC_SCRATCH_BYTES:
+        t -= 1
+    assert lib.tmoe_workspace_bytes(C.byref(L), t, 1) <= _lib.STATIC_SCRATCH_BYTES < lib.tmoe_workspace_bytes(C.byref(L), t + 1, 1)
+    assert lib.tmoe_forward_static_scratch(C.byref(L), C.byref(F), 4096, t + 1, 4096, None, None) == -5
+
+
 def test_null_and_alignment_errors_before_any_cuda_call():
     lib = _lib.load()
     L = _layer()

@@ -37,8 +37,7 @@ def check_against(y, taps, y_ref, idx_ref, scores_ref, dtype, x, f, shape):
     tol = F32_TOL if dtype == torch.float32 else BF16_TOL
     scale = float(rk.abs().max()) if rk.numel() else 1.0
     assert rel_fro(yk, rk) <= tol, f"rel-Fro {rel_fro(yk, rk):.3e} (max-abs {max_abs(yk, rk):.3e})"
-    assert max_abs(yk, rk) <= tol * max(scale, 1.0) * (1 if dtype == torch.float32 else 4), \
-        f"max-abs {max_abs(yk, rk):.3e} vs |y|max {scale:.3f}"
+    assert max_abs(yk, rk) <= tol * max(scale, 1.0), f"max-abs {max_abs(yk, rk):.3e} vs |y|max {scale:.3f}"
     # tokens that broke a tie differently: compare with the float64 oracle under this run's own selection
     if rep.mismatch_tokens:
         t = torch.tensor(rep.mismatch_tokens)
@@ -243,14 +242,36 @@ def test_tensor_path_matches_reference_golden(name):
     check_against(y, taps, g["y"], g["idx"], g["scores"], dtype, x, f, shape)
 
 
+def assert_selection_explained(idx_run, x_in, f, shape, ulps=1.0, router=(0, 10.0, 0.5)):
+    """Every selection that differs from the float64 oracle's (scores rounded to bf16, computed from the very input the
+    layer was given) must be a near-tie: the competing experts' scores within `ulps` bf16 units in the last place."""
+    _, nat = layer_forward_f64(x_in, f, shape.top_k, shape.eps, round_scores_to=torch.bfloat16, router=router)
+    rep = classify_topk(idx_run.cpu(), nat["idx"], nat["scores"], ulps * bf16_ulp(nat["scores"]))
+    assert rep.unexplained == 0, f"{rep.unexplained} selections differ without a score tie (tokens {rep.mismatch_tokens[:8]})"
+    return rep
+
+
+def assert_tokens_close(a, b, tol):
+    """Per-token relative error, every token."""
+    err = (a.double() - b.double()).norm(dim=-1) / b.double().norm(dim=-1).clamp(min=1e-30)
+    assert float(err.max()) < tol, f"token {int(err.argmax())} is off by {float(err.max()):.3e} (tolerance {tol})"
+
+
 def test_tensor_and_simt_paths_agree():
     shape = LayerShape(1536, 2304, 64, 2, 4, 256, 1024, 1e-6)
     x, f = _tensor_case(shape, 515, seed=77, router_std=None)
     a, ta = build_module(shape, f, torch.bfloat16, path=PATH_TENSOR).forward_with_routing(x.cuda())
     b, tb = build_module(shape, f, torch.bfloat16, path=PATH_SIMT).forward_with_routing(x.cuda())
+    # the two paths sum the router dot products in different orders: a selection may differ only at a bf16 near-tie
+    assert_selection_explained(ta[0], x, f, shape)
+    assert_selection_explained(tb[0], x, f, shape)
     same = (ta[0] == tb[0]).all(-1).cpu()
-    assert same.float().mean() > 0.97
     assert rel_fro(a.float().cpu()[same], b.float().cpu()[same]) < 1e-2
+    for y, taps in ((a, ta), (b, tb)):   # the tie-broken tokens, each against float64 under its own selection
+        if not bool(same.all()):
+            t = torch.nonzero(~same).flatten()
+            y64, _ = layer_forward_f64(x[t], f, shape.top_k, shape.eps, idx=taps[0].cpu()[t], round_scores_to=torch.bfloat16)
+            assert_tokens_close(y.float().cpu()[t], y64, BF16_TOL)
 
 
 @pytest.mark.parametrize("path", [PATH_SIMT, PATH_TENSOR, PATH_DECODE])
@@ -374,7 +395,11 @@ def test_rms_norm_matches_reference_formula(dtype, T):
 
 @pytest.mark.parametrize("T", [5, 200])
 def test_fused_ffn_and_out_proj_match_callers_composition(T):
-    """fused_ffn / fused_out_proj against the literal composition of model.py:337-341 and 258-260 on the oracle."""
+    """fused_ffn / fused_out_proj against the literal composition of model.py:337-341 and 258-260 in float64.
+
+    Three bf16 layers in a chain: a token whose rounded scores tie may pick another expert than float64 does.  Every
+    such difference is classified (it must be a near-tie in the float64 scores of the layer's actual input), and the
+    float64 chain is then evaluated under the run's own selections, where every token has to agree."""
     import torch.nn.functional as F
     from mamba_tuckermoe_b200 import fused_ffn, fused_out_proj
     from oracle.tucker_moe_oracle import rms_norm as ref_norm
@@ -387,28 +412,31 @@ def test_fused_ffn_and_out_proj_match_callers_composition(T):
     nw = (1 + 0.1 * torch.randn(d, generator=g)).bfloat16()
     gamma = (0.5 + 0.1 * torch.randn(d, generator=g)).bfloat16()
     mg, mu, md = build_module(s_up, fg, torch.bfloat16), build_module(s_up, fu, torch.bfloat16), build_module(s_dn, fd, torch.bfloat16)
-    out = fused_ffn(mg, mu, md, x.cuda(), (nw.cuda(), 1e-5), gamma.cuda()).float().cpu()
-    # float64 statement of the same composition (bf16 reference chains are too noisy to be a tight check)
+    norm = (nw.cuda(), 1e-5)
+    out = fused_ffn(mg, mu, md, x.cuda(), norm, gamma.cuda())
+    # the same three calls one by one, with their routing results
+    gate, tg = mg.forward_fused(x.cuda(), pre_norm=norm, return_routing=True)
+    act, tu = mu.forward_fused(x.cuda(), pre_norm=norm, silu_gate=gate, return_routing=True)
+    out2, td = md.forward_fused(act, residual=x.cuda(), layer_scale=gamma.cuda(), return_routing=True)
+    assert torch.equal(out2, out)
     xf = ref_norm(x.double(), nw.double(), 1e-5)
-    lay = lambda t, f, s: layer_forward_f64(t, f, s.top_k, s.eps, round_scores_to=torch.bfloat16)[0]
-    ref = x.double() + gamma.double() * lay(F.silu(lay(xf, fg, s_up)) * lay(xf, fu, s_up), fd, s_dn)
-
-    def close_tokens(a, b, tol):
-        """Per-token relative error.  Three bf16 layers in a chain: a token whose rounded scores tie picks another
-        expert than float64 does and is legitimately far off, so the check is on the bulk of the tokens."""
-        err = (a.double() - b).norm(dim=-1) / b.norm(dim=-1)
-        good = err < tol
-        assert float(good.float().mean()) >= 0.9, f"only {int(good.sum())}/{len(good)} tokens within {tol}"
-        assert rel_fro(a[good], b[good]) < tol
-
-    close_tokens(out, ref, 3e-2)
+    # the norm weight is folded into bf16 copies of the router rows, which moves a score by a fraction of an ulp
+    assert_selection_explained(tg[0], xf, fg, s_up, ulps=2)
+    assert_selection_explained(tu[0], xf, fu, s_up, ulps=2)
+    assert_selection_explained(td[0], act.double().cpu(), fd, s_dn)
+    lay = lambda t, f, s, idx: layer_forward_f64(t, f, s.top_k, s.eps, idx=idx.cpu(), round_scores_to=torch.bfloat16)[0]
+    ref = x.double() + gamma.double() * lay(F.silu(lay(xf, fg, s_up, tg[0])) * lay(xf, fu, s_up, tu[0]), fd, s_dn, td[0])
+    assert_tokens_close(out.float().cpu(), ref, 3e-2)
     # out_proj tail: mid + gamma * layer(norm(mid))
     s_o = LayerShape(d, d, 8, 2, 4, 128, 256, 1e-5)
     fo = make_factors(s_o, 90, torch.bfloat16, 0.02, 0.05)
     mo = build_module(s_o, fo, torch.bfloat16)
-    got = fused_out_proj(mo, x.cuda(), (nw.cuda(), 1e-5), gamma.cuda()).float().cpu()
-    want = x.double() + gamma.double() * lay(ref_norm(x.double(), nw.double(), 1e-5), fo, s_o)
-    close_tokens(got, want, 2e-2)
+    got = fused_out_proj(mo, x.cuda(), norm, gamma.cuda())
+    got2, to = mo.forward_fused(x.cuda(), pre_norm=norm, residual=x.cuda(), layer_scale=gamma.cuda(), return_routing=True)
+    assert torch.equal(got2, got)
+    assert_selection_explained(to[0], xf, fo, s_o, ulps=2)
+    want = x.double() + gamma.double() * lay(xf, fo, s_o, to[0])
+    assert_tokens_close(got.float().cpu(), want, BF16_TOL)
 
 
 @pytest.mark.parametrize("dtype,path,T", [
@@ -458,20 +486,25 @@ def test_in_kernel_pre_norm_matches_separate_norm(T):
     g = torch.Generator().manual_seed(2)
     nw = (1 + 0.3 * torch.randn(shape.d_in, generator=g)).bfloat16()
     m = build_module(shape, f, torch.bfloat16)
-    y_fused, = (m.forward_fused(x.cuda(), pre_norm=(nw.cuda(), 1e-5)),)
+    y_fused, taps = m.forward_fused(x.cuda(), pre_norm=(nw.cuda(), 1e-5), return_routing=True)
     torch.cuda.synchronize()
     assert read_device_status() == (0, 0, 0, 0)
     assert m._prep_pn is not None                                  # the in-kernel route was taken
+    assert torch.equal(m.forward_fused(x.cuda(), pre_norm=(nw.cuda(), 1e-5)), y_fused)
     from mamba_tuckermoe_b200 import rms_norm
-    y_two = m(rms_norm(x.cuda(), nw.cuda(), 1e-5))
+    xn = rms_norm(x.cuda(), nw.cuda(), 1e-5)
+    y_two, taps_two = m.forward_with_routing(xn)
     xn64 = ref_norm(x.double(), nw.double(), 1e-5)
-    y64, _ = layer_forward_f64(xn64, f, shape.top_k, shape.eps, round_scores_to=torch.bfloat16)
-    err = (y_fused.float().cpu().double() - y64).norm(dim=-1) / y64.norm(dim=-1)
-    assert float((err < 2e-2).float().mean()) >= (0.94 if T > 8 else 0.87)   # a few tokens flip a near-tie of bf16 scores
-    good = err < 2e-2
-    assert rel_fro(y_fused.float().cpu()[good], y64[good]) < 1e-2
-    err2 = (y_fused.float() - y_two.float()).norm(dim=-1) / y_two.float().norm(dim=-1)
-    assert float((err2 < 2e-2).float().mean()) >= (0.94 if T > 8 else 0.87)
+    # selections: the fused call against float64 of the exact normalised input (the bf16 fold of the norm weight into
+    # the router rows moves a score by a fraction of an ulp), the two-kernel call against float64 of ITS input
+    assert_selection_explained(taps[0], xn64, f, shape, ulps=2)
+    assert_selection_explained(taps_two[0], xn.double().cpu(), f, shape)
+    y64, _ = layer_forward_f64(xn64, f, shape.top_k, shape.eps, idx=taps[0].cpu(), round_scores_to=torch.bfloat16)
+    assert_tokens_close(y_fused.float().cpu(), y64, BF16_TOL)
+    assert rel_fro(y_fused.float().cpu(), y64) < 1e-2
+    same = (taps[0] == taps_two[0]).all(-1)
+    if bool(same.any()):
+        assert_tokens_close(y_fused.float()[same].cpu(), y_two.float()[same].cpu(), BF16_TOL)
     # residual + silu epilogues ride along unchanged
     res = torch.randn(T, shape.d_out, generator=g).bfloat16().cuda()
     gam = torch.ones(shape.d_out).bfloat16().cuda()

@@ -75,3 +75,22 @@ def test_capped_softmax_rule_properties():
     y64, t64 = layer_forward_f64(x, f, shape.top_k, shape.eps, router=router)
     assert rel_fro(y64, y) < 1e-5
     assert not torch.allclose(y, g["y"], atol=1e-3)    # and it is a different function from rule 0
+
+
+def test_parity_report_rules():
+    """The acceptance rule used by the GPU tests and the benchmark report, on the oracle's own outputs."""
+    from oracle.parity import parity_report, subset_indices
+    sub = subset_indices(131072)
+    assert sub[0] == 0 and sub[4095] == 4095 and sub[-1] == 131071 and 8000 < len(sub) <= 8192
+    assert torch.equal(subset_indices(100), torch.arange(100))
+    shape, x, f, dtype, g = load_case("ragged_e64_k8_f32")
+    y, taps = layer_forward(x, f, shape.top_k, shape.eps, return_taps=True)
+    rep = parity_report(y, taps["idx"], x, f, shape.top_k, shape.eps, dtype)
+    assert rep["ok"] and rep["topk_exact"] == x.shape[0] and rep["rel_fro"] == 0.0
+    # a wrong expert without a score tie is reported as unexplained; a wrong output breaks the tolerance
+    bad_idx = taps["idx"].clone()
+    bad_idx[0, 0] = (bad_idx[0, 0] + 1) % shape.E if int((bad_idx[0, 0] + 1) % shape.E) not in bad_idx[0, 1:].tolist() else (bad_idx[0, 0] + 2) % shape.E
+    rep = parity_report(y, bad_idx, x, f, shape.top_k, shape.eps, dtype)
+    assert rep["topk_unexplained"] == 1 and not rep["ok"]
+    rep = parity_report(y * 1.01, taps["idx"], x, f, shape.top_k, shape.eps, dtype)
+    assert not rep["ok"] and rep["rel_fro"] > 1e-3

@@ -11,7 +11,8 @@ import torch.multiprocessing as mp
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 
-from mamba_tuckermoe_b200.sharding import all_shard_bounds, shard_bounds, sharded_forward  # noqa: E402
+from mamba_tuckermoe_b200.sharding import (all_shard_bounds, cyclic_rows, local_tokens, shard_bounds,  # noqa: E402
+                                            sharded_forward)
 
 
 def test_shard_bounds_cover_and_balance():
@@ -26,6 +27,38 @@ def test_shard_bounds_cover_and_balance():
         shard_bounds(10, 2, 2)
 
 
+def test_block_cyclic_rows_partition_the_tokens():
+    for n, w, c in ((64, 2, 4), (32768, 8, 4), (48, 4, 1), (131072, 8, 4)):
+        seen = torch.zeros(n, dtype=torch.int32)
+        for r in range(w):
+            rows = cyclic_rows(n, w, r, c)
+            assert len(rows) == c and all(h - l == n // (w * c) for l, h in rows)
+            for l, h in rows:
+                seen[l:h] += 1
+        assert bool((seen == 1).all())
+        # chunk c of all ranks is one contiguous block of the output
+        for ci in range(c):
+            los = sorted(cyclic_rows(n, w, r, c)[ci][0] for r in range(w))
+            assert los == [ci * n // c + r * (n // (w * c)) for r in range(w)]
+    assert cyclic_rows(48, 4, 1, 1) == [shard_bounds(48, 4, 1)]
+    with pytest.raises(ValueError):
+        cyclic_rows(37, 2, 0, 3)
+
+
+class _IntoLayer:
+    """Stand-in with the module's two entry points (the CPU oracle does the arithmetic)."""
+
+    def __init__(self, fn, d_out):
+        self.fn, self.d_out, self.into_calls = fn, d_out, 0
+
+    def __call__(self, t):
+        return self.fn(t)
+
+    def forward_into(self, t, out):
+        self.into_calls += 1
+        out.copy_(self.fn(t))
+
+
 def _worker(rank, world, port, n_tokens, chunks, ret):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -35,20 +68,27 @@ def _worker(rank, world, port, n_tokens, chunks, ret):
         shape = LayerShape(64, 96, 8, 2, 4, 32, 64, 1e-5)
         f = make_factors(shape, 3, torch.float32, 0.02, 0.1)
         x = make_tokens(n_tokens, shape.d_in, 3)
-        layer = lambda t: layer_forward(t, f, shape.top_k, shape.eps)
+        fn = lambda t: layer_forward(t, f, shape.top_k, shape.eps)
+        layer = _IntoLayer(fn, shape.d_out)
         lo, hi = shard_bounds(n_tokens, world, rank)
         y_local = sharded_forward(layer, x[lo:hi], n_tokens=n_tokens)
-        y_full = sharded_forward(layer, x[lo:hi], n_tokens=n_tokens, gather=True, chunks=chunks)
-        ref = layer(x)
+        mine = local_tokens(x, world, rank, chunks)
+        y_full = sharded_forward(layer, mine, n_tokens=n_tokens, gather=True, chunks=chunks, d_out=shape.d_out)
+        ref = fn(x)
         ok = torch.allclose(y_local, ref[lo:hi], atol=1e-5) and torch.allclose(y_full, ref, atol=1e-5)
-        ok = ok and y_full.shape == ref.shape
+        ok = ok and y_full.shape == ref.shape and layer.into_calls > 0
+        # caller-provided result buffer, plain callable as the layer
+        buf = torch.full((n_tokens, shape.d_out), float("nan"))
+        got = sharded_forward(fn, mine, n_tokens=n_tokens, gather=True, chunks=chunks, out=buf, d_out=shape.d_out)
+        ok = ok and got.data_ptr() == buf.data_ptr() and torch.allclose(buf, ref, atol=1e-5)
         ret[rank] = bool(ok)
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("n_tokens,chunks", [(37, 1), (37, 3), (64, 4), (2, 2)])
+@pytest.mark.parametrize("n_tokens,chunks", [(37, 1), (37, 3), (64, 4), (64, 1), (2, 2), (48, 3)])
 def test_two_rank_shard_and_gather(n_tokens, chunks):
+    """Even splits take the block-cyclic in-place gather, ragged ones the padded staging path."""
     world = 2
     port = 29500 + (os.getpid() + n_tokens * 7 + chunks) % 2000
     mgr = mp.Manager()

@@ -17,6 +17,11 @@ CASES = [
     (LayerShape(256, 384, 1024, 16, 3, 64, 128, 1e-6), 290, torch.float32),  # top-16 of 1024, odd r1
     (LayerShape(1536, 2304, 8, 2, 4, 256, 1024, 1e-6), 8, torch.bfloat16),
     (LayerShape(1536, 2304, 64, 2, 4, 256, 1024, 1e-6), 257, torch.bfloat16),
+    # bf16 with >= 512 tokens: the stand-alone router takes its scores from the tensor-core GEMM kernel (router_w is its
+    # K-major operand as stored) and selects with the keyed kernel
+    (LayerShape(1536, 2304, 64, 2, 4, 256, 1024, 1e-6), 2100, torch.bfloat16),
+    (LayerShape(256, 384, 1024, 16, 4, 64, 128, 1e-6), 600, torch.bfloat16),   # top-16 of 1024
+    (LayerShape(1536, 2304, 8, 2, 4, 256, 1024, 1e-6), 777, torch.bfloat16),   # E = 8: a 128-column tile, 8 of them used
 ]
 
 
@@ -92,3 +97,29 @@ def test_in_core_and_out_stages(shape, T, dtype, path):
     torch.cuda.synchronize()
     assert lib.tmoe_read_device_status(ws.data_ptr(), st, cuda_stream_ptr()) == 0 and list(st) == [0, 0, 0, 0]
     assert rel_fro(y.float().cpu(), y64) < (1e-5 if dtype == torch.float32 else 1e-2)
+
+
+def test_bounded_wait_reports_and_returns():
+    """A wait that can never be satisfied gives up by itself after its limit, records where it gave up in the status
+    words and leaves the context usable; tmoe_read_device_status returns the words and clears them."""
+    lib = _lib.load()
+    shape = LayerShape(64, 96, 8, 2, 4, 32, 64, 1e-5)
+    L = layer_struct(shape, torch.float32)
+    ws = alloc_workspace(lib, L, 16, 1)
+    st = (C.c_int32 * 4)()
+    assert lib.tmoe_read_device_status(ws.data_ptr(), st, cuda_stream_ptr()) == 0 and list(st) == [0, 0, 0, 0]
+    assert lib.tmoe_selftest_bounded_wait(ws.data_ptr(), 2_000_000, cuda_stream_ptr()) == 0    # ~1 ms
+    assert lib.tmoe_read_device_status(ws.data_ptr(), st, cuda_stream_ptr()) == 0
+    assert list(st) == [_lib.ERR_DEVICE_WAIT, 9, 42, 0]
+    assert "bounded wait" in _lib.status_string(st[0])
+    assert lib.tmoe_read_device_status(ws.data_ptr(), st, cuda_stream_ptr()) == 0 and list(st) == [0, 0, 0, 0]
+    # the context is healthy: an ordinary forward on the same workspace still works
+    x, f, fd = _setup(shape, 16, torch.float32)
+    F = factors_struct(fd)
+    y = torch.empty(16, shape.d_out, device="cuda")
+    xd = x.cuda()
+    assert lib.tmoe_forward(C.byref(L), C.byref(F), None, xd.data_ptr(), 16, y.data_ptr(), None, ws.data_ptr(), ws.numel(),
+                            1, cuda_stream_ptr()) == 0
+    torch.cuda.synchronize()
+    y64, _ = layer_forward_f64(x, f, shape.top_k, shape.eps)
+    assert rel_fro(y.cpu(), y64) < 1e-5

@@ -61,3 +61,28 @@ def test_static_scratch_rejects_sizes_beyond_the_array():
     assert "too small" in _lib.status_string(-5)
     bad = _lib.layer_struct(LayerShape(1530, 2304, 8, 2, 4, 256, 1024, 1e-6), torch.float32)
     assert lib.tmoe_forward_static_scratch(C.byref(bad), C.byref(F), 4096, 8, 4096, None, None) == -2
+
+
+def test_static_scratch_largest_call_that_fits():
+    """The limit is the one tmoe_workspace_bytes states: the largest token count that fits runs and agrees with the
+    workspace forward, one more token is refused."""
+    lib = _lib.load()
+    shape = LayerShape(1536, 2304, 8, 2, 4, 256, 1024, 1e-6)
+    dtype = torch.bfloat16
+    f = {k: v.cuda() for k, v in make_factors(shape, 43, dtype, 0.02, 0.1).items()}
+    L, F = _lib.layer_struct(shape, dtype), _lib.factors_struct(f)
+    T = 1
+    while lib.tmoe_workspace_bytes(C.byref(L), T + 1, _lib.PATH_SIMT) <= _lib.STATIC_SCRATCH_BYTES:
+        T += 1
+    assert 600 < T < 1000
+    x = make_tokens(T + 1, shape.d_in, 7, dtype).cuda()
+    y_ref = torch.empty(T, shape.d_out, dtype=dtype, device="cuda")
+    y_new = torch.full((T + 1, shape.d_out), float("nan"), dtype=dtype, device="cuda")
+    _forward_with_workspace(lib, L, F, x[:T].contiguous(), y_ref)
+    rc = lib.tmoe_forward_static_scratch(C.byref(L), C.byref(F), x.data_ptr(), T, y_new.data_ptr(), None,
+                                         _lib.current_stream_ptr())
+    assert rc == 0, _lib.status_string(rc)
+    torch.cuda.synchronize()
+    assert torch.equal(y_new[:T], y_ref) and bool(torch.isnan(y_new[T].float()).all())
+    assert lib.tmoe_forward_static_scratch(C.byref(L), C.byref(F), x.data_ptr(), T + 1, y_new.data_ptr(), None,
+                                           _lib.current_stream_ptr()) == -5
