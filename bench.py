@@ -276,12 +276,73 @@ def run_decode_step(args, dev):
                                "768->768} + 6 x {768->4608, 768->4608, 4608->768}), T=1, E=8 top2 r=(32,256,512), one CUDA graph",
                    "layer_calls_per_token": n_calls, "l2": f"{factor_bytes / 1e6:.0f} MB of factors per token > 126 MB L2"},
         "us_per_token_graph": us_graph, "us_per_token_eager": us_eager, "us_per_layer_call_graph": us_graph / n_calls,
-        "roofline": {"bound": "hbm", "kernel": "decode forward (3 kernels per layer call)", "achieved": factor_bytes / us_graph / 1e3,
+        "roofline": {"bound": "hbm", "kernel": "decode forward (one launch per layer call)", "achieved": factor_bytes / us_graph / 1e3,
                      "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": factor_bytes / us_graph / 1e3 / peaks["hbm_gbs"],
                      "traffic": None, "peak_source": f"{peaks['source']} (copy bandwidth)", "bytes_per_token": factor_bytes},
         "flops_per_token": flops, "gpu_launches": int(launches),
     }
     print(json.dumps(line), flush=True)
+
+
+def run_ffn_pair(args, dev):
+    """The feed-forward block of the reference's transformer block (``pure_torch_mlx/model.py:337-341``) at the shipped
+    widths and ranks: x_res [T, 768] -> x_res + gamma * ffn_down(silu(ffn_gate(x_f)) * ffn_up(x_f)), x_f = RMSNorm(x_res),
+    768 -> 4608 -> 768, E = 8 top-2, r = (32, 256, 512), T = 16384.  Times ``fused_ffn`` (gate and up in-projection / core
+    stages in one launch: 5 launches) against the same three layers called one by one (6 launches)."""
+    import mamba_tuckermoe_b200 as pkg
+    from mamba_tuckermoe_b200 import _lib
+    from mamba_tuckermoe_b200.synthetic import LayerShape, make_factors, make_tokens
+    lib = _lib.load()
+    dtype, T = torch.bfloat16, args.tokens if args.tokens > 0 else 16384
+
+    def make(d_in, d_out, seed):
+        shape = LayerShape(d_in, d_out, 8, 2, 32, 256, 512, 1e-5)
+        m = pkg.TuckerMoE(d_in, d_out, pkg.TuckerMoEConfig(8, 2, 32, 512, 256, 1e-5))
+        f = make_factors(shape, seed, torch.float32, 0.02)
+        m.load_state_dict({"router.weight": f["router_w"], "U_in": f["U_in"], "inner_norm.weight": f["inner_norm_w"],
+                           "U_expert": f["U_expert"], "core": f["core"], "U_out": f["U_out"], "bias": f["bias"]})
+        return m.to(device=dev, dtype=dtype), shape
+
+    (mg, sg), (mu, _), (md, sd) = make(768, 4608, 6001), make(768, 4608, 6002), make(4608, 768, 6003)
+    xs = [make_tokens(T, 768, 6100 + i, dtype).to(dev) for i in range(N_INPUT_SETS)]
+    nw = torch.ones(768, device=dev, dtype=dtype)
+    gamma = torch.full((768,), 0.1, device=dev, dtype=dtype)
+
+    def fused(x):
+        return pkg.fused_ffn(mg, mu, md, x, (nw, 1e-5), gamma)
+
+    def separate(x):
+        gate = mg.forward_fused(x, pre_norm=(nw, 1e-5))
+        act = mu.forward_fused(x, pre_norm=(nw, 1e-5), silu_gate=gate)
+        return md.forward_fused(act, residual=x, layer_scale=gamma)
+
+    res = {}
+    with torch.no_grad():
+        same = torch.equal(fused(xs[0]), separate(xs[0]))
+        for name, fn in (("one_launch_gate_up", fused), ("separate_calls", separate)):
+            for i in range(3):
+                fn(xs[i % N_INPUT_SETS])
+            torch.cuda.synchronize()
+            n0 = lib.tmoe_launch_count()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for i in range(args.steps):
+                fn(xs[i % N_INPUT_SETS])
+            b.record(); torch.cuda.synchronize()
+            res[name] = {"us_per_block": a.elapsed_time(b) * 1e3 / args.steps,
+                         "launches_per_block": (lib.tmoe_launch_count() - n0) // args.steps}
+    flops = T * (2 * sg.flops_per_token() + sd.flops_per_token())
+    us = res["one_launch_gate_up"]["us_per_block"]
+    peaks = load_peaks()
+    print(json.dumps({
+        "metric": "tucker_moe_ffn_block_tokens_per_sec", "value": T / (us * 1e-6), "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": 3, "ms_per_step": us / 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"shipped_ffn_pair: FFN block 768 -> 4608 -> 768, E=8 top2 r=(32,256,512), T={T}, pre-norm, "
+                               "silu(gate)*up and LayerScale residual fused"},
+        "variants": res, "bit_identical": bool(same),
+        "block_tflops": flops / us / 1e6, "block_frac_of_bf16_peak": flops / us / 1e6 / peaks["bf16_tflops"],
+        "gpu_launches": int(res["one_launch_gate_up"]["launches_per_block"] * args.steps)}), flush=True)
 
 
 def timed_steps(fn, steps, barrier, dev, world):
@@ -369,7 +430,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="cfg2", choices=list(WORKLOADS) + ["decode_step"])
+    ap.add_argument("--workload", default="cfg2", choices=list(WORKLOADS) + ["decode_step", "shipped_ffn_pair"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=8)
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -377,8 +438,10 @@ def main():
     ap.add_argument("--path", type=int, default=0, help="0 auto, 1 CUDA-core, 2 tensor-core")
     ap.add_argument("--allgather", type=int, default=-1,
                     help="time the strong-sharded forward followed by the NCCL all-gather of y (default: on when N > 1)")
-    ap.add_argument("--profile", action="store_true",
-                    help="short run for use under ncu: device-resident steps only (no per-kernel, e2e or CPU legs)")
+    ap.add_argument("--profile", nargs="?", const="forward", default=None, choices=["forward", "router"],
+                    help="short run for use under ncu: 'forward' = device-resident steps only (no per-kernel, e2e or CPU "
+                         "legs); 'router' = the stand-alone router entry point (tmoe_router) on the workload's tokens")
+    ap.add_argument("--tokens", type=int, default=0, help="override the workload's token count (profiling of small cases)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
@@ -397,6 +460,10 @@ def main():
         if rank == 0:
             run_decode_step(args, dev)
         return
+    if args.workload == "shipped_ffn_pair":
+        if rank == 0:
+            run_ffn_pair(args, dev)
+        return
 
     import mamba_tuckermoe_b200 as pkg
     from mamba_tuckermoe_b200 import _lib
@@ -404,6 +471,8 @@ def main():
                                                 make_tokens)
 
     shape_key, T, desc = WORKLOADS[args.workload]
+    if args.tokens > 0:
+        T = args.tokens
     shape, _, dtype, seed, rstd = BENCH_SHAPES[shape_key]
     peaks = load_peaks()
     lib = _lib.load()
@@ -436,6 +505,11 @@ def main():
         torch.cuda.synchronize()
 
     gather_info = strong = None
+    if args.profile == "router":
+        if rank == 0:
+            profile_router(lib, _lib, layer, shape, dtype, x_dev, T, args.steps)
+        return
+
     with torch.no_grad():
         for i in range(max(args.warmup, 3)):
             y = layer(x_dev[i % N_INPUT_SETS])
@@ -460,7 +534,7 @@ def main():
 
         if args.profile:
             if rank == 0:
-                print(json.dumps({"profile_run": True, "ms_per_step": ms_step, "tokens_per_s": value,
+                print(json.dumps({"profile_run": "forward", "tokens": T, "ms_per_step": ms_step, "tokens_per_s": value,
                                   "gpu_launches": int(launches)}), flush=True)
             if world > 1:
                 dist.destroy_process_group()
@@ -581,6 +655,30 @@ def main():
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def profile_router(lib, _lib, layer, shape, dtype, x_dev, T, steps):
+    """A few calls of the stand-alone router entry point (subsystem 1) for a profiler to capture."""
+    L = _lib.layer_struct(shape, dtype)
+    fd = {"router_w": layer.router.weight, "U_in": layer.U_in, "inner_norm_w": layer.inner_norm.weight,
+          "U_expert": layer.U_expert, "core": layer.core, "U_out": layer.U_out, "bias": layer.bias}
+    F = _lib.factors_struct(fd)
+    ws = _lib.alloc_workspace(L, T, 1)
+    dev = x_dev[0].device
+    idx = torch.empty(T, shape.top_k, dtype=torch.int32, device=dev)
+    gates = torch.empty(T, shape.top_k, dtype=torch.float32, device=dev)
+    c = torch.empty(T, shape.r1, dtype=torch.float32, device=dev)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for i in range(steps + 1):
+        if i == 1:
+            a.record()
+        rc = lib.tmoe_router(C.byref(L), C.byref(F), x_dev[i % len(x_dev)].data_ptr(), T, idx.data_ptr(), gates.data_ptr(),
+                             c.data_ptr(), ws.data_ptr(), ws.numel(), _lib.current_stream_ptr())
+        assert rc == 0, _lib.status_string(rc)
+    b.record(); torch.cuda.synchronize()
+    us = a.elapsed_time(b) * 1e3 / steps
+    print(json.dumps({"profile_run": "router", "tokens": T, "us_per_call": us,
+                      "gbs": T * shape.d_in * x_dev[0].element_size() / us / 1e3}), flush=True)
 
 
 def decode_times(lib, _lib, layer, shape, dtype, x, T, reps=30):

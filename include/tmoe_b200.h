@@ -182,6 +182,20 @@ int tmoe_forward(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const
                  const void *x, int64_t T, void *y, const tmoe_extras_t *extras, void *workspace,
                  int64_t workspace_bytes, int path, void *stream);
 
+/* The gate and up projections of the reference's feed-forward block on one input (pure_torch_mlx/model.py:337-340):
+ *     act = silu(ffn_gate(x_f)) * ffn_up(x_f),      x_f = x, or RMSNorm(x) with extras->pre_norm as in tmoe_forward,
+ * for two layers of the same sizes (`layer`), given by their prepared factor sets.  Tensor-core path with the in-kernel
+ * router only (bf16, n_experts <= 256, top_k <= 8, r3 <= 256; TMOE_ERR_UNSUPPORTED otherwise -- use two tmoe_forward
+ * calls).  Three launches instead of four: the two layers' in-projection / core stages run as ONE launch whose CTAs
+ * alternate between the layers, so each tile of x comes from HBM once; then the gate layer's out-projection into `gate_y`
+ * ([T, d_out], caller-provided scratch) and the up layer's with silu(gate) * up in its epilogue into `act_y`.  Results are
+ * bit-identical to tmoe_forward(gate) followed by tmoe_forward(up, extras.silu_gate = gate_y).
+ * `workspace`: 2 * tmoe_workspace_bytes(layer, T, TMOE_PATH_TENSOR) bytes (rounded up to 256 each).  Of `extras` only
+ * pre_norm / pre_norm_eps apply (both prepared sets then come from tmoe_prepare_factors_prenorm with the same weight). */
+int tmoe_ffn_gate_up(const tmoe_layer_t *layer, const void *prepared_gate, const void *prepared_up, const void *x, int64_t T,
+                     void *gate_y, void *act_y, const tmoe_extras_t *extras, void *workspace, int64_t workspace_bytes,
+                     void *stream);
+
 /* RMSNorm of typed rows: y[t] = x[t] / sqrt(mean(x[t]^2) + eps) * weight (pure_torch_mlx/model.py:25-27),
  * the callers' pre-norms in front of the layer (model.py:258, 337).  x, weight, y of `dtype`; d % 8 == 0;
  * fp32 arithmetic with one rounding to the storage type.  y may equal x. */
@@ -222,11 +236,12 @@ int tmoe_selftest_bounded_wait(void *workspace, int64_t limit_cycles, void *stre
 /* Number of kernels the library has launched in this process (monotonic counter). */
 int64_t tmoe_launch_count(void);
 
-/* Scheduling detail of tmoe_forward on the tensor-core path, for diagnostics.  When the 128-token tiles of a call do not
- * fill whole waves of CTAs on the current device, the in/core kernel's grid is padded with "helper" CTAs that compute
- * the out-projection of token tiles finished in the first wave while the last wave runs.  Writes the number of helper
- * CTAs (0: none for this shape) and of 128-token tiles whose out-projection they take.  No reference counterpart. */
-int tmoe_handoff_plan(const tmoe_layer_t *layer, int64_t T, int32_t *n_helper_ctas, int32_t *n_token_tiles);
+/* Scheduling detail of tmoe_forward on the tensor-core path, for diagnostics.  With TMOE_HANDOFF=1 in the environment, a
+ * call with more 128-token tiles than the device has SMs does not make the out-projection wait for the whole
+ * in-projection/core kernel: its CTAs start on the SMs that kernel's last, partial wave of token tiles leaves free and
+ * take the token tiles that are already finished.  Writes the number of such SMs (0: the hand-over is not used for this
+ * call) and the number of token tiles of the waves before the last.  No reference counterpart. */
+int tmoe_handoff_plan(const tmoe_layer_t *layer, int64_t T, int32_t *n_early_sms, int32_t *n_token_tiles);
 
 #ifdef __cplusplus
 }

@@ -19,7 +19,7 @@ EXPORTS = (
     "tmoe_version", "tmoe_status_string", "tmoe_resolve_path", "tmoe_prepared_bytes",
     "tmoe_prepare_factors", "tmoe_workspace_bytes", "tmoe_router", "tmoe_in_core", "tmoe_out",
     "tmoe_forward", "tmoe_read_device_status", "tmoe_launch_count", "tmoe_forward_static_scratch", "tmoe_rms_norm", "tmoe_handoff_plan",
-    "tmoe_prepare_factors_prenorm", "tmoe_selftest_bounded_wait",
+    "tmoe_prepare_factors_prenorm", "tmoe_selftest_bounded_wait", "tmoe_ffn_gate_up",
 )
 STATIC_SCRATCH_BYTES = 4 << 20
 
@@ -91,6 +91,8 @@ def load():
         lib.tmoe_out.argtypes = [LP, FP, vp, vp, i64, vp, EP, vp, i64, i32, vp]
         lib.tmoe_forward.restype = i32
         lib.tmoe_forward.argtypes = [LP, FP, vp, vp, i64, vp, EP, vp, i64, i32, vp]
+        lib.tmoe_ffn_gate_up.restype = i32
+        lib.tmoe_ffn_gate_up.argtypes = [LP, vp, vp, vp, i64, vp, vp, EP, vp, i64, vp]
         lib.tmoe_forward_static_scratch.restype = i32
         lib.tmoe_forward_static_scratch.argtypes = [LP, FP, vp, i64, vp, EP, vp]
         lib.tmoe_rms_norm.restype = i32

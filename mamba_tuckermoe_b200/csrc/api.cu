@@ -13,7 +13,7 @@ unsigned long long g_launch_count = 0;
 namespace {
 
 struct WsLayout {
-  int64_t idx, gates, c, scores, h, z, total;
+  int64_t idx, gates, c, scores, h, z, partial, ready, total;
   bool simt_router_fused;  // CUDA-core path: warp-per-token router (else tiled scores + select)
   bool tc_router_fused;    // tensor-core path: scores and selection inside the in/core kernel
 };
@@ -60,7 +60,7 @@ int resolve(const tmoe_layer_t &L, int64_t T, int path, bool allow_decode = true
 
 WsLayout ws_layout(const tmoe_layer_t &L, int64_t T, int rpath) {
   WsLayout W{};
-  int64_t off = kStatusBytes + kHandoffBytes;
+  int64_t off = kHeaderBytes;
   auto take = [&](int64_t bytes) { int64_t o = off; off = align_up(off + bytes, 256); return o; };
   W.idx = take(T * L.top_k * 4);
   W.gates = take(T * L.top_k * 4);
@@ -77,10 +77,13 @@ WsLayout ws_layout(const tmoe_layer_t &L, int64_t T, int rpath) {
     W.h = take(T * (L.r3 + L.n_experts) * 4);
     W.scores = W.h + T * L.r3 * 4;
     W.z = take(T * L.r2 * 2);
+    // one-launch kernel for the smallest calls: per-cluster partial sums of y
+    W.partial = T <= kFusedDecodeMaxTokens ? take((int64_t)kMaxDecodeClusters * T * L.d_out * 4) : 0;
   } else {
     W.scores = W.tc_router_fused ? 0 : take(T * align_up(L.n_experts, 16) * 2);  // bf16 [T, e_pad], made by the GEMM kernel
     W.h = 0;
     W.z = take(T * L.r2 * 2);
+    W.ready = take(((T + 127) / 128) * 8 * 4);   // hand-over words, 8 per 128-token tile
   }
   W.total = off;
   return W;
@@ -208,7 +211,13 @@ int tmoe_router(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const 
   // x, but at E >= 16 its FMA count exceeds what the CUDA cores do in that time.  router_w [E, d_in] is already the K-major
   // operand the tensor-core GEMM kernel wants, its bf16 output is the reference's rounding of the scores, and the keyed
   // select kernel finishes the job.  Needs E % 8 == 0 (16-byte rows of scores) and room for [T, E] bf16 in the workspace.
-  const int64_t sc_off = kStatusBytes + kHandoffBytes;
+  const int64_t sc_off = kHeaderBytes;
+  if (L.dtype == TMOE_BF16 && T >= 512) {
+    // up to 256 experts and top-8: one launch that accumulates the scores in TMEM and selects from there
+    rc = launch_tc_router(L, x, factors->router_w, factors->U_expert, T, idx, gates, c, reinterpret_cast<int32_t *>(ws),
+                          (cudaStream_t)stream);
+    if (rc != TMOE_ERR_UNSUPPORTED) return rc;
+  }
   if (L.dtype == TMOE_BF16 && T >= 512 && L.n_experts % 8 == 0 && L.n_experts <= 1024 &&
       workspace_bytes >= sc_off + T * L.n_experts * 2) {
     void *scores = ws + sc_off;
@@ -314,35 +323,38 @@ int tmoe_forward(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const
   int32_t *status = reinterpret_cast<int32_t *>(ws);
   if (rp == TMOE_PATH_DECODE) {
     const bool taps = extras && (extras->idx_out || extras->gates_out || extras->c_out);
+    if (T <= kFusedDecodeMaxTokens) {
+      rc = launch_decode_fused(L, x, prepared, P, T, reinterpret_cast<float *>(ws + W.partial),
+                               reinterpret_cast<unsigned int *>(ws + kStatusBytes + kHandoffBytes),
+                               taps ? extras->idx_out : nullptr, taps ? extras->gates_out : nullptr,
+                               taps ? extras->c_out : nullptr, epi, y, st, pre_norm, pre_norm ? extras->pre_norm_eps : 0.f);
+      if (rc != TMOE_ERR_UNSUPPORTED) return rc;   // shapes outside its shared-memory plan take the three-kernel form
+    }
     return launch_decode(L, x, prepared, P, T, reinterpret_cast<float *>(ws + W.h), scores, z,
                          taps ? extras->idx_out : nullptr, taps ? extras->gates_out : nullptr,
                          taps ? extras->c_out : nullptr, epi, y, st, pre_norm, pre_norm ? extras->pre_norm_eps : 0.f);
   }
-  // token tiles that do not fill whole waves of CTAs: pad the in/core grid with helper CTAs that run out-projection tiles
-  OutHelperArgs helper{};
+  // more token tiles than SMs: the out-projection's CTA pairs take finished token tiles while the last wave still runs
+  OutFlags flags{};
   {
     const int sms = current_device_sms();
     if (sms <= 0) return TMOE_ERR_CUDA;
-    plan_out_handoff(L, T, sms, &helper.ho);
-    if (helper.ho.n_helpers > 0) {
+    if (plan_out_handoff(L, T, sms)) {
       static std::atomic<uint32_t> epoch_counter{1};
       uint32_t e = epoch_counter.fetch_add(1, std::memory_order_relaxed);
-      if (e == 0) e = epoch_counter.fetch_add(1, std::memory_order_relaxed);   // 0 is what a cleared word holds
-      helper.ho.epoch = e;
-      helper.ho.ready = reinterpret_cast<uint32_t *>(ws + kStatusBytes);
-      helper.uout_t = pb + P.uout_t;
-      helper.bias = reinterpret_cast<const float *>(pb + P.bias);
-      helper.epi = epi;
-      helper.y = y;
+      if (e == 0) e = epoch_counter.fetch_add(1, std::memory_order_relaxed);   // 0 is what a zeroed word holds
+      flags.epoch = e;
+      flags.ready = reinterpret_cast<uint32_t *>(ws + W.ready);
+      flags.queue = reinterpret_cast<unsigned long long *>(ws + kStatusBytes + kHandoffBytes + 128);
     }
   }
-  const OutHelperArgs *hp = helper.ho.n_helpers > 0 ? &helper : nullptr;
+  const OutFlags *fp = flags.ready ? &flags : nullptr;
   if (W.tc_router_fused) {
     const bool taps = extras && (extras->idx_out || extras->gates_out || extras->c_out);
     rc = launch_tc_in_core(L, x, prepared, P, T, pre_norm, pre_norm ? extras->pre_norm_eps : 0.f, 1, nullptr,
                            reinterpret_cast<float *>(ws + W.c), in_core_c_blocks(T),
                            taps ? extras->idx_out : nullptr,
-                           taps ? extras->gates_out : nullptr, taps ? extras->c_out : nullptr, z, status, st, hp);
+                           taps ? extras->gates_out : nullptr, taps ? extras->c_out : nullptr, z, status, st, fp);
   } else {
     // scores = x @ router_w^T on the tensor cores (bf16 out = the reference's rounding), then the select kernel
     if ((rc = launch_tc_gemm_bf16(x, pb + P.wr_b, nullptr, OutEpilogue{}, T, P.e_pad, L.d_in, scores, status, st)))
@@ -350,11 +362,50 @@ int tmoe_forward(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const
     if ((rc = launch_select_bf16_scores(L, scores, P.e_pad, factors->U_expert, T, idx, gates, c, st))) return rc;
     // c_work may alias c: every row is read by its own thread before that thread overwrites it
     rc = launch_tc_in_core(L, x, prepared, P, T, 0, 0.f, 0, c, reinterpret_cast<float *>(ws + W.c), in_core_c_blocks(T), nullptr, nullptr, nullptr, z,
-                           status, st, hp);
+                           status, st, fp);
   }
   if (rc) return rc;
-  return launch_tc_out(L, z, pb + P.uout_t, reinterpret_cast<const float *>(pb + P.bias), epi, T, y, status, st,
-                       hp ? &helper.ho : nullptr);
+  return launch_tc_out(L, z, pb + P.uout_t, reinterpret_cast<const float *>(pb + P.bias), epi, T, y, status, st, fp);
+}
+
+int tmoe_ffn_gate_up(const tmoe_layer_t *layer, const void *prepared_gate, const void *prepared_up, const void *x, int64_t T,
+                     void *gate_y, void *act_y, const tmoe_extras_t *extras, void *workspace, int64_t workspace_bytes,
+                     void *stream) {
+  int rc = check_layer(layer);
+  if (rc) return rc;
+  if (check_tokens(T)) return TMOE_ERR_SHAPE;
+  if (T == 0) return TMOE_OK;
+  if (!prepared_gate || !prepared_up || !x || !gate_y || !act_y || !workspace) return TMOE_ERR_NULL;
+  if (misaligned(x) || misaligned(gate_y) || misaligned(act_y) || (reinterpret_cast<uintptr_t>(workspace) & 255) ||
+      (reinterpret_cast<uintptr_t>(prepared_gate) & 255) || (reinterpret_cast<uintptr_t>(prepared_up) & 255))
+    return TMOE_ERR_ALIGN;
+  const tmoe_layer_t &L = *layer;
+  if (!tensor_path_covers(L)) return TMOE_ERR_UNSUPPORTED;
+  const WsLayout W = ws_layout(L, T, TMOE_PATH_TENSOR);
+  if (!W.tc_router_fused) return TMOE_ERR_UNSUPPORTED;       // the paired launch needs the in-kernel router
+  const int64_t half = align_up(W.total, 256);
+  if (workspace_bytes < 2 * half) return TMOE_ERR_WORKSPACE;
+  if (extras && (extras->residual || extras->layer_scale || extras->silu_gate || extras->idx_out || extras->gates_out ||
+                 extras->c_out))
+    return TMOE_ERR_UNSUPPORTED;                             // only the pre-norm applies here
+  const int pre_norm = (extras && extras->pre_norm) ? 1 : 0;
+  const float pn_eps = pre_norm ? extras->pre_norm_eps : 0.f;
+  char *ws = reinterpret_cast<char *>(workspace);
+  char *ws2 = ws + half;                                     // the up layer's c and z (status words are the first half's)
+  int32_t *status = reinterpret_cast<int32_t *>(ws);
+  cudaStream_t st = (cudaStream_t)stream;
+  const PreparedLayout P = prepared_layout(L);
+  const char *pg = reinterpret_cast<const char *>(prepared_gate), *pu = reinterpret_cast<const char *>(prepared_up);
+  InCoreTwin twin{prepared_up, reinterpret_cast<float *>(ws2 + W.c), ws2 + W.z};
+  if ((rc = launch_tc_in_core(L, x, prepared_gate, P, T, pre_norm, pn_eps, 1, nullptr, reinterpret_cast<float *>(ws + W.c),
+                              in_core_c_blocks(T), nullptr, nullptr, nullptr, ws + W.z, status, st, nullptr, &twin)))
+    return rc;
+  if ((rc = launch_tc_out(L, ws + W.z, pg + P.uout_t, reinterpret_cast<const float *>(pg + P.bias), OutEpilogue{}, T, gate_y,
+                          status, st)))
+    return rc;
+  OutEpilogue epi;
+  epi.silu_gate = gate_y;
+  return launch_tc_out(L, ws2 + W.z, pu + P.uout_t, reinterpret_cast<const float *>(pu + P.bias), epi, T, act_y, status, st);
 }
 
 int tmoe_rms_norm(int dtype, const void *x, const void *weight, float eps, int64_t T, int32_t d, void *y, void *stream) {
@@ -372,7 +423,8 @@ int tmoe_read_device_status(void *workspace, int32_t *device_status, void *strea
   int32_t words[4] = {0, 0, 0, 0};
   if (cudaMemcpy(words, workspace, sizeof(words), cudaMemcpyDeviceToHost) != cudaSuccess) return TMOE_ERR_CUDA;
   for (int i = 0; i < 4; ++i) device_status[i] = words[i];
-  if (words[0] != 0 && cudaMemset(workspace, 0, kStatusBytes) != cudaSuccess) return TMOE_ERR_CUDA;
+  // after a reported wait the flags and counters behind the status words may be left mid-protocol: clear them all
+  if (words[0] != 0 && cudaMemset(workspace, 0, kHeaderBytes) != cudaSuccess) return TMOE_ERR_CUDA;
   return TMOE_OK;
 }
 
@@ -400,17 +452,19 @@ int tmoe_selftest_bounded_wait(void *workspace, int64_t limit_cycles, void *stre
   return launch_status();
 }
 
-int tmoe_handoff_plan(const tmoe_layer_t *layer, int64_t T, int32_t *n_helper_ctas, int32_t *n_token_tiles) {
+int tmoe_handoff_plan(const tmoe_layer_t *layer, int64_t T, int32_t *n_early_sms, int32_t *n_token_tiles) {
   int rc = check_layer(layer);
   if (rc) return rc;
-  if (!n_helper_ctas || !n_token_tiles) return TMOE_ERR_NULL;
-  *n_helper_ctas = 0; *n_token_tiles = 0;
-  if (T <= 0 || resolve(*layer, T, TMOE_PATH_AUTO) != TMOE_PATH_TENSOR) return TMOE_OK;
+  if (!n_early_sms || !n_token_tiles) return TMOE_ERR_NULL;
+  *n_early_sms = 0; *n_token_tiles = 0;
+  if (T <= 0 || check_tokens(T) || resolve(*layer, T, TMOE_PATH_AUTO) != TMOE_PATH_TENSOR) return TMOE_OK;
   const int sms = current_device_sms();
   if (sms <= 0) return TMOE_ERR_CUDA;
-  OutHandoff h;
-  plan_out_handoff(*layer, T, sms, &h);
-  *n_helper_ctas = h.n_helpers; *n_token_tiles = h.m_tiles;
+  if (!plan_out_handoff(*layer, T, sms)) return TMOE_OK;
+  const int64_t tiles = (T + 127) / 128;
+  const int tail = (int)(tiles % sms);
+  *n_early_sms = tail ? sms - tail : 0;                 // SMs the last wave of token tiles leaves to the out-projection
+  *n_token_tiles = (int32_t)(tiles - (tail ? tail : sms));   // token tiles of the complete waves before it
   return TMOE_OK;
 }
 

@@ -17,6 +17,10 @@ using bf16 = __nv_bfloat16;
 constexpr int kStatusBytes = 256;
 // hand-off words between the in/core kernel's helper CTAs and the out-projection: 8 per 128-token tile, after the status words
 constexpr int kHandoffBytes = 128 * 8 * 4;
+// counters of the fused decode kernel (one per CTA rank of a cluster), after the hand-off words; zero between calls
+constexpr int kCounterBytes = 256;
+// everything in front of the per-call buffers: must be zero when a workspace is first used
+constexpr int kHeaderBytes = kStatusBytes + kHandoffBytes + kCounterBytes;
 
 // Counts kernel launches made by this library (read through tmoe_launch_count()).
 extern unsigned long long g_launch_count;

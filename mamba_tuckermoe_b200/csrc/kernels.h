@@ -70,37 +70,29 @@ PreparedLayout prepared_layout(const tmoe_layer_t &L);
 int launch_prepare(const tmoe_layer_t &L, const tmoe_factors_t &F, const void *pre_norm_w, void *prepared, cudaStream_t st);
 
 // ---- tc_out_gemm.cu ----
-// Hand-off between the in/core kernel and the out-projection when the token tiles do not fill whole waves of CTAs: the
-// in/core grid is padded with `n_helpers` CTAs that compute the out-projection of the first `m_tiles` 128-token tiles
-// (finished in the first wave) while the last wave runs, and the out kernel starts behind them.  ready: 8 words per
-// 128-token tile in the workspace, set to `epoch` by the CTA that wrote the tile's z rows, cleared by the out kernel.
-struct OutHandoff {
-  int m_tiles = 0;    // even, <= kMaxHandoffTiles
-  int n_helpers = 0;
+// Tile-by-tile hand-over of z from the in/core kernel to the out-projection (used when the token tiles need more than one
+// wave of CTAs: the out-projection's CTA pairs then start on the SMs the last wave leaves free instead of waiting for the
+// whole in/core grid).  ready: 8 words per 128-token tile in the workspace, each set to `epoch` by one epilogue warp of the
+// CTA that stored the tile's z rows; queue: the 64-bit word {epoch, tiles handed out} the pairs draw their tiles from.
+// Nothing is ever cleared: a forward's epoch supersedes the previous one's.
+struct OutFlags {
   uint32_t *ready = nullptr;
   uint32_t epoch = 0;
+  unsigned long long *queue = nullptr;
 };
-constexpr int kMaxHandoffTiles = 128;
-// Fills `h` for a forward of T tokens on a device with `sms` SMs (n_helpers = 0: no hand-off for this shape).
-void plan_out_handoff(const tmoe_layer_t &L, int64_t T, int sms, OutHandoff *h);
+// Whether a forward of T tokens on a device with `sms` SMs uses the hand-over.
+bool plan_out_handoff(const tmoe_layer_t &L, int64_t T, int sms);
+bool tc_gemm_uses_pairs(int64_t M, int N, int sms);
 
 // y[T, N] = z[T, K] (bf16) @ W_t[N, K]^T (bf16, K-major) + bias (fp32) on tcgen05 tensor cores.
 int launch_tc_out(const tmoe_layer_t &L, const void *z, const void *uout_t, const float *bias, const OutEpilogue &epi,
-                  int64_t T, void *y, int32_t *status, cudaStream_t st, const OutHandoff *ho = nullptr);
+                  int64_t T, void *y, int32_t *status, cudaStream_t st, const OutFlags *flags = nullptr);
 
 // General form of the same kernel (used for the router scores when E is too large for the in-kernel router).
 int launch_tc_gemm_bf16(const void *A, const void *B_t, const float *bias, const OutEpilogue &epi, int64_t M, int N,
-                        int K, void *y, int32_t *status, cudaStream_t st, const OutHandoff *ho = nullptr);
+                        int K, void *y, int32_t *status, cudaStream_t st, const OutFlags *flags = nullptr);
 
 // ---- tc_in_core.cu ----
-// Arguments of the out-projection that the in/core kernel's helper CTAs run (see OutHandoff).
-struct OutHelperArgs {
-  const void *uout_t;
-  const float *bias;
-  OutEpilogue epi;
-  void *y;
-  OutHandoff ho;
-};
 // Fused x@U_in (+ router scores) -> RMS statistics -> h@G tiles with c-weighted epilogue -> z bf16.
 // fuse_router != 0: scores/top-k/softmax/c are computed inside (c_in ignored, taps optional);
 // otherwise c_in [T, r1] is read.  c_work [T, r1] is scratch in both cases.
@@ -115,9 +107,21 @@ inline int in_core_c_blocks(int64_t T) {
   const int per_tile = (int)(160 / tiles);
   return 1 + (per_tile < kMaxJSplit ? per_tile : kMaxJSplit);
 }
+// `twin` (optional): a second layer of the same sizes applied to the same x in the same launch (the FFN's gate and up
+// projections): its prepared set, its own c scratch and its own z.  In-kernel router only, no taps, no hand-over.
+struct InCoreTwin {
+  const void *prepared;
+  float *c_work;
+  void *z;
+};
 int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared, const PreparedLayout &P, int64_t T,
                       int pre_norm, float pre_norm_eps, int fuse_router, const float *c_in, float *c_work, int c_work_blocks, int32_t *idx_out, float *gates_out, float *c_out,
-                      void *z, int32_t *status, cudaStream_t st, const OutHelperArgs *helper = nullptr);
+                      void *z, int32_t *status, cudaStream_t st, const OutFlags *flags = nullptr, const InCoreTwin *twin = nullptr);
+
+// Stand-alone router for bf16 layers on the tensor cores (the kernel above in router-only mode): idx / gates / c from x and
+// the layer's own router_w / U_expert.  TMOE_ERR_UNSUPPORTED for E > 256 (padded), top_k > 8, d_in % 64 != 0 or other r1.
+int launch_tc_router(const tmoe_layer_t &L, const void *x, const void *router_w, const void *uexp_bf16, int64_t T, int32_t *idx,
+                     float *gates, float *c, int32_t *status, cudaStream_t st);
 
 // ---- decode.cu ----
 // Whole forward for T <= 64 bf16 tokens on the prepared (K-major) factors: split-K in-projection with
@@ -125,5 +129,18 @@ int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared
 int launch_decode(const tmoe_layer_t &L, const void *x, const void *prepared, const PreparedLayout &P, int64_t T,
                   float *h_raw, float *scores, void *z, int32_t *idx_out, float *gates_out, float *c_out,
                   const OutEpilogue &epi, void *y, cudaStream_t st, int pre_norm = 0, float pre_norm_eps = 0.f);
+
+
+// ---- decode_fused.cu ----
+// The same forward for T <= kFusedDecodeMaxTokens in one launch of thread-block clusters (above that the per-token arithmetic
+// it repeats in every cluster outweighs the launches it saves: measured 36 us against 17 us at T = 8).  partial: [kMaxDecodeClusters, T, d_out] floats of
+// scratch; counters: kDecodeCounterWords zeroed words that the kernel leaves zeroed.  TMOE_ERR_UNSUPPORTED when the shape
+// does not fit its shared-memory plan (the caller then uses launch_decode).
+constexpr int kMaxDecodeClusters = 24;
+constexpr int kFusedDecodeMaxTokens = 4;
+constexpr int kDecodeCounterWords = 16;
+int launch_decode_fused(const tmoe_layer_t &L, const void *x, const void *prepared, const PreparedLayout &P, int64_t T,
+                        float *partial, unsigned int *counters, int32_t *idx_out, float *gates_out, float *c_out,
+                        const OutEpilogue &epi, void *y, cudaStream_t st, int pre_norm = 0, float pre_norm_eps = 0.f);
 
 }  // namespace tmoe

@@ -66,6 +66,38 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int32_t
   return mbar_wait_slow(bar, parity, status, kernel_id, tag);
 }
 
+// The same bounded wait with the acquire at cluster scope: for barriers whose arrival comes from another CTA of the
+// cluster together with data that CTA wrote into this CTA's shared memory (st.shared::cluster + arrive.release.cluster).
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+static __device__ __noinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, int32_t *status, int kernel_id, int tag) {
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  for (;;) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if ((++spins & 0xffu) == 0) {
+      if (*reinterpret_cast<volatile int32_t *>(status) != 0) return false;
+      if (clock64() - t0 > kWaitLimitCycles) break;
+    }
+  }
+  if (atomicCAS(status, 0, (int32_t)TMOE_ERR_DEVICE_WAIT) == 0) {
+    status[1] = kernel_id;
+    status[2] = tag;
+    status[3] = (int32_t)blockIdx.x;
+    __threadfence();
+  }
+  return false;
+}
+
 // Wait for the thread that issues the MMAs.  That thread is the serial path of a tensor-core kernel: it spends
 // ~50 cycles per tcgen05.mma, ~100 per tcgen05.commit and ~55 per satisfied wait, against 128 cycles of tensor-pipe
 // time per 128x256x16 MMA, and a loop with a side exit (a `break` on a failed wait) was measured ~100 cycles per
@@ -223,6 +255,10 @@ __device__ __forceinline__ uint32_t mapa_u32(uint32_t local_smem_addr, uint32_t 
   uint32_t r;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_smem_addr), "r"(rank));
   return r;
+}
+// 32-bit store into the shared memory of a CTA of this cluster (address from mapa_u32)
+__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
 }
 // arrive on an mbarrier that lives in another CTA of the cluster (address from mapa_u32)
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {

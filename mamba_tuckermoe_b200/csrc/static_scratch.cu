@@ -59,7 +59,7 @@ extern "C" int tmoe_forward_static_scratch(const tmoe_layer_t *layer, const tmoe
   int rc = scratch_address(&scratch);
   if (rc) return rc;
   // the array keeps whatever the previous call left; the status and hand-off words have to start at zero
-  if (cudaMemsetAsync(scratch, 0, tmoe::kStatusBytes + tmoe::kHandoffBytes, (cudaStream_t)stream) != cudaSuccess)
+  if (cudaMemsetAsync(scratch, 0, tmoe::kHeaderBytes, (cudaStream_t)stream) != cudaSuccess)
     return TMOE_ERR_CUDA;
   return tmoe_forward(layer, factors, nullptr, x, T, y, extras, scratch, (int64_t)TMOE_STATIC_SCRATCH_BYTES,
                       TMOE_PATH_SIMT, stream);

@@ -26,7 +26,6 @@
 #include "kernels.h"
 #include "ptx.cuh"
 #include "routing.cuh"
-#include "tc_out_body.cuh"
 
 namespace tmoe {
 
@@ -53,16 +52,17 @@ constexpr int IC_EPI_WARPS = 8;
 constexpr int IC_THREADS = (2 + IC_EPI_WARPS) * 32;
 constexpr int IC_RING_BYTES = 224 * 1024;
 constexpr int IC_SMEM_BYTES = IC_RING_BYTES + 1024;
-constexpr int A_STAGES_MAX = 4;
+constexpr int A_STAGES_MAX = 8;   // 4 fit with the U_in tile in the stage; the router-only mode (x + router tile) uses all 8
 constexpr int SCORE_COL = 256;  // TMEM column of the router scores during phase A
 constexpr int kKernelInCore = 2;
-static_assert(IC_THREADS == O_THREADS && IC_SMEM_BYTES >= O_SMEM_BYTES, "helper CTAs run the out-projection body inside this kernel's CTA shape");
 
 struct InCoreParams {
   int64_t T;
   int d_in, r3, r2, E, e_pad, top_k, n_tiles2;
   float eps;
   int fuse_router;
+  int router_only;     // 1: stop after the routing (stand-alone router: scores by the tensor cores, idx / gates / c out; no U_in, no core)
+  int uexp_bf16;       // 1: uexp points at the layer's own bf16 U_expert instead of the prepared fp32 copy
   int pre_norm;        // 1: apply the callers' RMSNorm to x in-kernel (its weight is folded into the prepared U_in / router rows)
   float pre_norm_eps;
   RouterCfg rc;  // gate rule (tmoe_layer_t::router_mode)
@@ -75,22 +75,23 @@ struct InCoreParams {
   float *c_out;
   bf16 *z;  // [T, r2]
   int32_t *status;
-  // CTAs [0, n_token_ctas) own token tiles; the rest are helper CTAs that run out-projection tiles (OutHelperCfg).
-  // A token CTA with blockIdx.x < n_ready_m publishes `epoch` in ready[8 * blockIdx.x + epilogue warp] once its z rows are stored.
-  int n_token_ctas, n_ready_m;
+  // ready != nullptr: every epilogue warp raises ready[8 * token tile + warp] = epoch once its z rows are stored (the
+  // out-projection's CTA pairs pick the tile up from there; j_split == 1 in that case)
   // Few token tiles (small T): every tile is shared by j_split CTAs, each repeating phase A and taking n_tiles2 / j_split of
   // the core tiles, so that one tile's 40 us of work is spread over up to 16 SMs.  Split s > 0 keeps its c hand-off in
   // block s + 1 of c_work ([T, r1] each); block 0 may alias c_in / c_out.
   int j_split;
   uint32_t *ready;
   uint32_t epoch;
+  unsigned long long *queue;   // the out-projection's tile queue word, tagged here with this forward's epoch
+  int pair;                    // 1: the grid interleaves two layers on the same x (second parameter block / tensor maps)
 };
 
 // Phase-A issue loop of the MMA thread.  TWO_BOX: r3 = 512; a stage holding x and all 512 rows of U_in^T is 80 KB, two
 // stages deep, and starves (measured 2300 cycles per k block against 1024 of tensor-pipe time), so h is made in two passes
 // over K, each streaming x again (from L2) with one 256-row piece of U_in^T: 48 KB stages, four deep.  SCORES: the router
 // tile follows U_in^T in the stage and a second, N = e_pad MMA accumulates the scores at TMEM column SCORE_COL.
-template <bool TWO_BOX, bool SCORES>
+template <bool TWO_BOX, bool SCORES, bool HACC = true>
 __device__ __forceinline__ void issue_phase_a(uint32_t tmem_base, uint64_t desc0, uint32_t stage16, uint32_t u16, int KA, int nA,
                                               int u_box_rows, int e_pad, uint64_t *bar_full, uint64_t *bar_empty, int32_t *status) {
   const uint32_t idescH = umma_idesc_bf16(TM, u_box_rows);
@@ -107,7 +108,7 @@ __device__ __forceinline__ void issue_phase_a(uint32_t tmem_base, uint64_t desc0
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         const uint32_t acc = acc0 | (uint32_t)(k != 0);
-        umma_bf16(d_h, dx + 2 * k, du + 2 * k, idescH, acc);
+        if (HACC) umma_bf16(d_h, dx + 2 * k, du + 2 * k, idescH, acc);
         if (SCORES) umma_bf16(tmem_base + SCORE_COL, dx + 2 * k, dw + 2 * k, idescS, acc);
       }
       umma_commit(smem_u32(&bar_empty[sA]));
@@ -119,19 +120,26 @@ __device__ __forceinline__ void issue_phase_a(uint32_t tmem_base, uint64_t desc0
 // R1: Tucker rank r1 (core slices per r2 tile); RK: capacity of the in-kernel top-k list (>= top_k)
 template <int R1, int RK>
 __global__ void __launch_bounds__(IC_THREADS, 1)
-tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmU,
-                  const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmG, InCoreParams p,
-                  const __grid_constant__ OutHelperCfg hc) {
+tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmU1,
+                  const __grid_constant__ CUtensorMap tmW1, const __grid_constant__ CUtensorMap tmG1,
+                  const __grid_constant__ InCoreParams pa, const __grid_constant__ CUtensorMap tmU2,
+                  const __grid_constant__ CUtensorMap tmW2, const __grid_constant__ CUtensorMap tmG2,
+                  const __grid_constant__ InCoreParams pb) {
   constexpr int N2 = 256 / R1;
   extern __shared__ uint8_t smem_raw[];
+  // Two layers on one input (pa.pair: the FFN's gate and up projections, model.py:337-339): CTA 2m works on token tile m
+  // for the first layer, CTA 2m + 1 on the same tile for the second -- neighbours in launch order, so the tile of x that one
+  // of them brings in from HBM is in L2 for the other.  Everything below runs on this CTA's own copy of the parameters.
+  const bool second = pa.pair && (blockIdx.x & 1u);
+  const InCoreParams p = second ? pb : pa;
+  const CUtensorMap *const tU = second ? &tmU2 : &tmU1;
+  const CUtensorMap *const tW = second ? &tmW2 : &tmW1;
+  const CUtensorMap *const tG = second ? &tmG2 : &tmG1;
+  const int bid = pa.pair ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
   // every CTA of this grid is running once the last one has said this: the next kernel of the stream (the out-projection)
-  // may then take SMs as they free up and do its set-up while this grid drains
+  // may then take SMs as they free up -- to do its set-up while this grid drains or, with the tile-by-tile hand-over, to
+  // start on the token tiles that are already finished
   griddep_launch_dependents();
-  if ((int)blockIdx.x >= p.n_token_ctas) {
-    // grid padding: this CTA would idle during the last wave; it computes out-projection tiles of finished token tiles
-    tc_out_body(&hc.tmA, &hc.tmB, &hc.tmY, hc.p, (int)blockIdx.x - p.n_token_ctas, hc.n_helpers, hc.n_tiles, smem_raw, true);
-    return;
-  }
   __shared__ __align__(8) uint64_t bar_fullA[A_STAGES_MAX], bar_emptyA[A_STAGES_MAX], bar_fullB[G_STAGES_MAX],
       bar_emptyB[G_STAGES_MAX], bar_accA, bar_hready, bar_pfull[2], bar_pempty[2];
   __shared__ uint32_t tmem_base_s;
@@ -140,14 +148,14 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const int sp = p.j_split > 1 ? (int)blockIdx.x % p.j_split : 0;
-  const int m0 = (p.j_split > 1 ? (int)blockIdx.x / p.j_split : (int)blockIdx.x) * TM;
+  const int sp = p.j_split > 1 ? bid % p.j_split : 0;
+  const int m0 = (p.j_split > 1 ? bid / p.j_split : bid) * TM;
   const int jn = p.n_tiles2 / p.j_split, j0 = sp * jn;   // this CTA's core tiles [j0, j0 + jn)
   float *const c_work = p.c_work + (p.j_split > 1 ? (int64_t)(sp + 1) * p.T * R1 : 0);
 
   const int u_boxes = (p.r3 + 255) / 256;         // U_in^T is streamed in pieces of <= 256 rows, one pass over K per piece
   const int u_box_rows = p.r3 / u_boxes;
-  const int u_bytes = u_box_rows * 128, w_bytes = p.e_pad * 128;
+  const int u_bytes = p.router_only ? 0 : u_box_rows * 128, w_bytes = p.e_pad * 128;
   const int stageA_bytes = X_TILE_BYTES + u_bytes + w_bytes;
   int nA = IC_RING_BYTES / stageA_bytes;
   nA = nA > A_STAGES_MAX ? A_STAGES_MAX : nA;
@@ -157,7 +165,8 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
   int nG = (IC_RING_BYTES - h_bytes) / G_STAGE_BYTES;
   nG = nG > G_STAGES_MAX ? G_STAGES_MAX : nG;
 
-  for (int i = threadIdx.x; i < p.r3; i += blockDim.x) wnorm_s[i] = __float2bfloat16_rn(p.normw[i]);
+  if (!p.router_only)
+    for (int i = threadIdx.x; i < p.r3; i += blockDim.x) wnorm_s[i] = __float2bfloat16_rn(p.normw[i]);
   if (threadIdx.x == 0) {
     // a phase-A stage is free once its MMAs have retired and, with the in-kernel pre-norm, the four secondary
     // warps have read its x tile for the row statistics
@@ -171,8 +180,9 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
     mbar_init(smem_u32(&bar_hready), IC_EPI_WARPS / 2);
     for (int s = 0; s < 2; ++s) { mbar_init(smem_u32(&bar_pfull[s]), 1); mbar_init(smem_u32(&bar_pempty[s]), IC_EPI_WARPS); }
     fence_mbar_init();
-    prefetch_tmap(&tmX); prefetch_tmap(&tmU); prefetch_tmap(&tmG);
-    if (p.e_pad) prefetch_tmap(&tmW);
+    prefetch_tmap(&tmX);
+    if (!p.router_only) { prefetch_tmap(tU); prefetch_tmap(tG); }
+    if (p.e_pad) prefetch_tmap(tW);
   }
   if (warp == 2) { tmem_alloc(smem_u32(&tmem_base_s), 512); tmem_relinquish(); }  // an epilogue warp: its lanes never retire early
   tc_fence_before();
@@ -183,6 +193,14 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
   // this kernel may have been started while its predecessor in the stream drains: nothing above depends on that kernel,
   // everything below may (x, and the z / c rows this kernel overwrites may still be read by it)
   griddep_wait();
+  if (p.queue && bid == 0 && !second && threadIdx.x == 0) {
+    // tile queue of the out-projection that follows: this forward's epoch, no tile handed out yet.  No CTA of that kernel
+    // can run before every CTA of this grid has started, and those of the last wave start only when CTAs that are past
+    // this point have finished.
+    *reinterpret_cast<volatile unsigned long long *>(p.queue) = (unsigned long long)p.epoch << 32;
+    *reinterpret_cast<volatile unsigned long long *>(p.queue + 1) = (unsigned long long)p.epoch << 32;   // CTAs of this grid that are done
+    __threadfence();
+  }
 #ifdef TMOE_TRACE
   const long long trace_t0 = clock64();
   unsigned long long trace_ns0;
@@ -203,8 +221,8 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
           mbar_arrive_expect_tx(full, stageA_bytes);
           const uint32_t sa = ring + s * stageA_bytes;
           tma_load_2d(sa, &tmX, kb * 64, m0, full);
-          tma_load_2d(sa + X_TILE_BYTES, &tmU, kb * 64, pass * u_box_rows, full);
-          if (p.e_pad) tma_load_2d(sa + X_TILE_BYTES + u_bytes, &tmW, kb * 64, 0, full);
+          if (!p.router_only) tma_load_2d(sa + X_TILE_BYTES, tU, kb * 64, pass * u_box_rows, full);
+          if (p.e_pad) tma_load_2d(sa + X_TILE_BYTES + u_bytes, tW, kb * 64, 0, full);
         }
       }
       // ring A aliases h and the core-tile ring: wait until every phase-A MMA has retired
@@ -220,7 +238,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         if (!(ok = mbar_wait(smem_u32(&bar_emptyB[s]), ph ^ 1, p.status, kKernelInCore, 6))) break;
         const uint32_t full = smem_u32(&bar_fullB[s]);
         mbar_arrive_expect_tx(full, G_STAGE_BYTES);
-        tma_load_2d(ringB + s * G_STAGE_BYTES, &tmG, kb * 64, row0, full);
+        tma_load_2d(ringB + s * G_STAGE_BYTES, tG, kb * 64, row0, full);
       }
     }
   } else if (warp == 1) {
@@ -234,7 +252,9 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       // reads; the fence is only needed where another thread's tcgen05.ld preceded (accumulator / h hand-offs).
       const uint64_t desc0 = umma_desc_k_sw128(ring);          // descriptor of the ring base; tiles add (bytes >> 4)
       const uint32_t stageA16 = (uint32_t)stageA_bytes >> 4;
-      if (p.e_pad)
+      if (p.router_only)
+        issue_phase_a<false, true, false>(tmem_base, desc0, stageA16, 0u, KA, nA, 16, p.e_pad, bar_fullA, bar_emptyA, p.status);
+      else if (p.e_pad)
         issue_phase_a<false, true>(tmem_base, desc0, stageA16, (uint32_t)u_bytes >> 4, KA, nA, u_box_rows, p.e_pad, bar_fullA, bar_emptyA, p.status);
       else if (u_boxes == 2)
         issue_phase_a<true, false>(tmem_base, desc0, stageA16, (uint32_t)u_bytes >> 4, KA, nA, u_box_rows, 16, bar_fullA, bar_emptyA, p.status);
@@ -242,6 +262,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         issue_phase_a<false, false>(tmem_base, desc0, stageA16, (uint32_t)u_bytes >> 4, KA, nA, u_box_rows, 16, bar_fullA, bar_emptyA, p.status);
       umma_commit(smem_u32(&bar_accA));
       TMOE_STAMP(0);  // last phase-A MMA issued
+      if (!p.router_only) {
       mbar_wait_or_exit(smem_u32(&bar_hready), 0, p.status, kKernelInCore, 4);
       tc_fence_after();
       TMOE_STAMP(1);  // MMA thread saw h ready
@@ -266,6 +287,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
           if (++sB == (uint32_t)nG) { sB = 0; phB ^= 1; }
         }
         umma_commit(smem_u32(&bar_pfull[slot]));
+      }
       }
     }
   } else {
@@ -394,7 +416,11 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
             if (j < p.top_k) {
               const int e = min(max(si[j], 0), p.E - 1);
 #pragma unroll
-              for (int a = 0; a < R1; ++a) c[a] = fmaf(gate[j], __ldg(p.uexp + e * R1 + a), c[a]);
+              for (int a = 0; a < R1; ++a) {
+                const float ue = p.uexp_bf16 ? __bfloat162float(__ldg(reinterpret_cast<const bf16 *>(p.uexp) + e * R1 + a))
+                                             : __ldg(p.uexp + e * R1 + a);
+                c[a] = fmaf(gate[j], ue, c[a]);
+              }
               if (live && sp == 0) {
                 if (p.idx_out) p.idx_out[grow * p.top_k + j] = si[j];
                 if (p.gates_out) p.gates_out[grow * p.top_k + j] = gate[j];
@@ -417,10 +443,13 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         const float inv_rms = inv_rms_s[row];
 #pragma unroll
         for (int a = 0; a < R1; ++a) c[a] *= inv_rms;
-        if (live) {
+        if (live && !p.router_only) {
 #pragma unroll
           for (int a = 0; a < R1; ++a) c_work[grow * R1 + a] = c[a];
         }
+      } else if (p.router_only) {
+        inv_rms_s[row] = 1.f;          // no h in this mode: c stays unscaled
+        named_bar_sync(3, 256);
       } else {
         // h row: statistics, weight, bf16, swizzled store (16-byte chunk index XOR row%8 inside 128-byte rows)
         float ss = 0.f;
@@ -463,7 +492,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       }
       if (threadIdx.x == 64) TMOE_STAMP(4);  // epilogue A done
       named_bar_sync(4, 256);                // c_work of every row is written
-      if (grp == 1) {
+      if (grp == 1 && !p.router_only) {
 #pragma unroll
         for (int a = 0; a < R1; ++a) c[a] = live ? c_work[grow * R1 + a] : 0.f;
       }
@@ -552,11 +581,11 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
           }
         }
       }
-      if (p.ready && (int)blockIdx.x < p.n_ready_m && ok) {
+      if (p.ready && ok) {
         // this warp's z rows are written: make them visible device-wide, then raise the warp's hand-off word
         __threadfence();
         __syncwarp();
-        if (lane == 0) *reinterpret_cast<volatile uint32_t *>(p.ready + blockIdx.x * 8 + (warp - 2)) = p.epoch;
+        if (lane == 0) *reinterpret_cast<volatile uint32_t *>(p.ready + (size_t)bid * 8 + (warp - 2)) = p.epoch;
       }
       if (threadIdx.x == 64) TMOE_STAMP(5);  // z stored
 #ifdef TMOE_TRACE
@@ -570,6 +599,12 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
   }
   tc_fence_before();
   __syncthreads();
+  if (p.queue && threadIdx.x == 0) {
+    // every epilogue warp of this CTA has fenced its z rows and raised its word: count the CTA as done (a CTA of the
+    // out-projection that finds all of them done skips the per-tile words)
+    __threadfence();
+    atomicAdd(p.queue + 1, 1ull);
+  }
   if (warp == 2) {
     __syncwarp();
     tc_fence_after();
@@ -579,36 +614,45 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
 
 int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared, const PreparedLayout &P, int64_t T_,
                       int pre_norm, float pre_norm_eps, int fuse_router, const float *c_in, float *c_work, int c_work_blocks, int32_t *idx_out, float *gates_out, float *c_out,
-                      void *z, int32_t *status, cudaStream_t st, const OutHelperArgs *helper) {
-  const char *base = reinterpret_cast<const char *>(prepared);
+                      void *z, int32_t *status, cudaStream_t st, const OutFlags *flags, const InCoreTwin *twin) {
   if (fuse_router && (P.e_pad > 256 || L.top_k > 8 || L.r3 > 256)) return TMOE_ERR_UNSUPPORTED;
   if ((!fuse_router && !c_in) || !c_work) return TMOE_ERR_NULL;
-  CUtensorMap tmX, tmU, tmW, tmG;
+  if (pre_norm && !fuse_router) return TMOE_ERR_UNSUPPORTED;
+  if (twin && (!fuse_router || !twin->prepared || !twin->c_work || !twin->z || flags)) return TMOE_ERR_UNSUPPORTED;
+  if (X_TILE_BYTES + (L.r3 > 256 ? 256 : L.r3) * 128 + (fuse_router ? P.e_pad : 0) * 128 > IC_RING_BYTES) return TMOE_ERR_UNSUPPORTED;
+  CUtensorMap tmX, tmU, tmW, tmG, tmU2, tmW2, tmG2;
   int rc = encode_tmap_bf16_2d(&tmX, x, (uint64_t)T_, (uint64_t)L.d_in, TM);
   if (rc) return rc;
-  rc = encode_tmap_bf16_2d(&tmU, base + P.uin_t, (uint64_t)L.r3, (uint64_t)L.d_in,
-                           (uint32_t)(L.r3 / ((L.r3 + 255) / 256)));
-  if (rc) return rc;
-  // the router tile is only loaded when the scores are computed in-kernel (e_pad <= 256 checked above)
-  rc = encode_tmap_bf16_2d(&tmW, base + P.wr_b, (uint64_t)P.e_pad, (uint64_t)L.d_in,
-                           fuse_router ? (uint32_t)P.e_pad : 16u);
-  if (rc) return rc;
-  rc = encode_tmap_bf16_2d(&tmG, base + P.g_t, (uint64_t)L.r1 * L.r2, (uint64_t)L.r3, 256);
-  if (rc) return rc;
-
-  InCoreParams p{};
-  p.T = T_; p.d_in = L.d_in; p.r3 = L.r3; p.r2 = L.r2; p.E = L.n_experts; p.top_k = L.top_k;
-  p.e_pad = fuse_router ? P.e_pad : 0;
-  p.n_tiles2 = P.n_tiles2; p.eps = L.eps; p.fuse_router = fuse_router; p.rc = router_cfg(L);
-  p.pre_norm = pre_norm; p.pre_norm_eps = pre_norm_eps;
-  if (pre_norm && !fuse_router) return TMOE_ERR_UNSUPPORTED;
-  p.normw = reinterpret_cast<const float *>(base + P.normw);
-  p.uexp = reinterpret_cast<const float *>(base + P.uexp);
-  p.c_in = c_in; p.c_work = c_work; p.idx_out = idx_out; p.gates_out = gates_out; p.c_out = c_out;
-  p.z = (bf16 *)z; p.status = status;
-  if (X_TILE_BYTES + (p.r3 > 256 ? 256 : p.r3) * 128 + p.e_pad * 128 > IC_RING_BYTES) return TMOE_ERR_UNSUPPORTED;
+  // tensor maps and parameter block of one layer's factor set
+  auto fill = [&](const void *prep, float *cw, void *zz, int32_t *io, float *go, float *co, CUtensorMap *mU, CUtensorMap *mW,
+                  CUtensorMap *mG, InCoreParams *q) -> int {
+    const char *base = reinterpret_cast<const char *>(prep);
+    int r = encode_tmap_bf16_2d(mU, base + P.uin_t, (uint64_t)L.r3, (uint64_t)L.d_in, (uint32_t)(L.r3 / ((L.r3 + 255) / 256)));
+    if (r) return r;
+    // the router tile is only loaded when the scores are computed in-kernel (e_pad <= 256 checked above)
+    if ((r = encode_tmap_bf16_2d(mW, base + P.wr_b, (uint64_t)P.e_pad, (uint64_t)L.d_in, fuse_router ? (uint32_t)P.e_pad : 16u))) return r;
+    if ((r = encode_tmap_bf16_2d(mG, base + P.g_t, (uint64_t)L.r1 * L.r2, (uint64_t)L.r3, 256))) return r;
+    *q = InCoreParams{};
+    q->T = T_; q->d_in = L.d_in; q->r3 = L.r3; q->r2 = L.r2; q->E = L.n_experts; q->top_k = L.top_k;
+    q->e_pad = fuse_router ? P.e_pad : 0;
+    q->n_tiles2 = P.n_tiles2; q->eps = L.eps; q->fuse_router = fuse_router; q->rc = router_cfg(L);
+    q->pre_norm = pre_norm; q->pre_norm_eps = pre_norm_eps;
+    q->normw = reinterpret_cast<const float *>(base + P.normw);
+    q->uexp = reinterpret_cast<const float *>(base + P.uexp);
+    q->c_in = c_in; q->c_work = cw; q->idx_out = io; q->gates_out = go; q->c_out = co;
+    q->z = (bf16 *)zz; q->status = status;
+    return TMOE_OK;
+  };
+  InCoreParams p, p2;
+  if ((rc = fill(prepared, c_work, z, idx_out, gates_out, c_out, &tmU, &tmW, &tmG, &p))) return rc;
+  if (twin) {
+    if ((rc = fill(twin->prepared, twin->c_work, twin->z, nullptr, nullptr, nullptr, &tmU2, &tmW2, &tmG2, &p2))) return rc;
+  } else {
+    tmU2 = tmU; tmW2 = tmW; tmG2 = tmG; p2 = p;
+  }
 
   unsigned grid = (unsigned)((T_ + TM - 1) / TM);
+  const unsigned layers = twin ? 2u : 1u;
   // Few token tiles: share each tile between j_split CTAs (every one repeats phase A, then takes its share of the core
   // tiles).  j_split is the largest divisor of n_tiles2 that fits the SM count and the scratch blocks and keeps whole
   // 64-column units of z per CTA.
@@ -616,7 +660,7 @@ int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared
   {
     const int sms = current_device_sms();
     const int n2 = 256 / L.r1, jpu = n2 >= 64 ? 1 : 64 / n2;
-    int cap = sms > 0 ? sms / (int)grid : 1;
+    int cap = sms > 0 ? sms / (int)(grid * layers) : 1;
     if (cap > c_work_blocks - 1) cap = c_work_blocks - 1;
     if (cap > kMaxJSplit) cap = kMaxJSplit;
     static const int env_split = [] { const char *s = getenv("TMOE_JSPLIT"); return s ? atoi(s) : -1; }();
@@ -624,34 +668,18 @@ int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared
     for (int d = cap; d >= 2; --d)
       if (P.n_tiles2 % d == 0 && (P.n_tiles2 / d) % jpu == 0) { p.j_split = d; break; }
   }
-  grid *= (unsigned)p.j_split;
-  p.n_token_ctas = (int)grid;
-  static OutHelperCfg hc_none;   // zero-initialised: no helper CTAs
-  OutHelperCfg hc_local;
-  const OutHelperCfg *hc = &hc_none;
-  if (helper && helper->ho.n_helpers > 0) {
-    OutHelperCfg &h = hc_local;
-    h = OutHelperCfg{};
-    if ((rc = encode_tmap_bf16_2d(&h.tmY, helper->y, (uint64_t)T_, (uint64_t)L.d_out, 32))) return rc;
-    if ((rc = encode_tmap_bf16_2d(&h.tmA, z, (uint64_t)T_, (uint64_t)L.r2, OM))) return rc;
-    if ((rc = encode_tmap_bf16_2d(&h.tmB, helper->uout_t, (uint64_t)L.d_out, (uint64_t)L.r2, ON))) return rc;
-    h.p.y = (bf16 *)helper->y; h.p.bias = helper->bias; h.p.residual = (const bf16 *)helper->epi.residual;
-    h.p.gamma = (const bf16 *)helper->epi.layer_scale; h.p.silu_gate = (const bf16 *)helper->epi.silu_gate;
-    h.p.T = T_; h.p.N = L.d_out; h.p.K = L.r2;
-    h.p.num_m = (int)((T_ + OM - 1) / OM); h.p.num_n = (L.d_out + ON - 1) / ON;
-    h.p.status = status;
-    h.p.ready = helper->ho.ready; h.p.epoch = helper->ho.epoch;
-    h.n_helpers = helper->ho.n_helpers;
-    h.n_tiles = helper->ho.m_tiles * h.p.num_n;
-    p.n_ready_m = helper->ho.m_tiles; p.ready = helper->ho.ready; p.epoch = helper->ho.epoch;
-    grid += (unsigned)h.n_helpers;
-    hc = &hc_local;
+  p2.j_split = p.j_split;
+  grid *= (unsigned)p.j_split * layers;
+  p.pair = p2.pair = twin ? 1 : 0;
+  if (flags && flags->ready) {
+    if (p.j_split != 1) return TMOE_ERR_UNSUPPORTED;   // the hand-over is for calls with more token tiles than SMs
+    p.ready = flags->ready; p.epoch = flags->epoch; p.queue = flags->queue;
   }
   cudaError_t e = cudaSuccess;
 #define TMOE_IC(R, K)                                                                                              \
   do {                                                                                                             \
     e = cudaFuncSetAttribute(tc_in_core_kernel<R, K>, cudaFuncAttributeMaxDynamicSharedMemorySize, IC_SMEM_BYTES); \
-    if (e == cudaSuccess) e = launch_pdl(tc_in_core_kernel<R, K>, dim3(grid), dim3(IC_THREADS), (size_t)IC_SMEM_BYTES, st, tmX, tmU, tmW, tmG, p, *hc); \
+    if (e == cudaSuccess) e = launch_pdl(tc_in_core_kernel<R, K>, dim3(grid), dim3(IC_THREADS), (size_t)IC_SMEM_BYTES, st, tmX, tmU, tmW, tmG, p, tmU2, tmW2, tmG2, p2); \
   } while (0)
   const bool small_k = L.top_k <= 2;
   if (L.r1 == 2) { if (small_k) TMOE_IC(2, 2); else TMOE_IC(2, 8); }
@@ -661,6 +689,44 @@ int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared
   else if (L.r1 == 32) { if (small_k) TMOE_IC(32, 2); else TMOE_IC(32, 8); }
   else return TMOE_ERR_UNSUPPORTED;
 #undef TMOE_IC
+  if (e != cudaSuccess) return TMOE_ERR_CUDA;
+  count_launch();
+  return launch_status();
+}
+
+
+// Stand-alone router on the tensor cores (subsystem 1 for bf16 layers): the kernel above in its router-only mode.  One
+// launch, HBM traffic = one read of x: phase A accumulates only the scores (x tile and router tile per stage, eight stages
+// deep), the primary epilogue warps select and write idx / gates / c.  router_w [E, d_in] as the layer stores it is the
+// K-major operand; rows E .. e_pad of the tile are out of bounds and arrive as zeros.
+int launch_tc_router(const tmoe_layer_t &L, const void *x, const void *router_w, const void *uexp_bf16, int64_t T_, int32_t *idx,
+                     float *gates, float *c, int32_t *status, cudaStream_t st) {
+  const int e_pad = (int)align_up(L.n_experts, 16);
+  if (e_pad > 256 || L.top_k > 8 || (L.d_in % 64) != 0) return TMOE_ERR_UNSUPPORTED;
+  if (!(L.r1 == 2 || L.r1 == 4 || L.r1 == 8 || L.r1 == 16 || L.r1 == 32)) return TMOE_ERR_UNSUPPORTED;
+  CUtensorMap tmX, tmW;
+  int rc = encode_tmap_bf16_2d(&tmX, x, (uint64_t)T_, (uint64_t)L.d_in, TM);
+  if (rc) return rc;
+  if ((rc = encode_tmap_bf16_2d(&tmW, router_w, (uint64_t)L.n_experts, (uint64_t)L.d_in, (uint32_t)e_pad))) return rc;
+  InCoreParams p{};
+  p.T = T_; p.d_in = L.d_in; p.r3 = 64; p.r2 = 0; p.E = L.n_experts; p.top_k = L.top_k; p.e_pad = e_pad;
+  p.n_tiles2 = 0; p.eps = L.eps; p.fuse_router = 1; p.router_only = 1; p.uexp_bf16 = 1; p.rc = router_cfg(L);
+  p.uexp = reinterpret_cast<const float *>(uexp_bf16);
+  p.idx_out = idx; p.gates_out = gates; p.c_out = c; p.status = status; p.j_split = 1;
+  const unsigned grid = (unsigned)((T_ + TM - 1) / TM);
+  cudaError_t e = cudaSuccess;
+#define TMOE_RT(R, K)                                                                                              \
+  do {                                                                                                             \
+    e = cudaFuncSetAttribute(tc_in_core_kernel<R, K>, cudaFuncAttributeMaxDynamicSharedMemorySize, IC_SMEM_BYTES); \
+    if (e == cudaSuccess) e = launch_pdl(tc_in_core_kernel<R, K>, dim3(grid), dim3(IC_THREADS), (size_t)IC_SMEM_BYTES, st, tmX, tmX, tmW, tmX, p, tmX, tmW, tmX, p); \
+  } while (0)
+  const bool small_k = L.top_k <= 2;
+  if (L.r1 == 2) { if (small_k) TMOE_RT(2, 2); else TMOE_RT(2, 8); }
+  else if (L.r1 == 4) { if (small_k) TMOE_RT(4, 2); else TMOE_RT(4, 8); }
+  else if (L.r1 == 8) { if (small_k) TMOE_RT(8, 2); else TMOE_RT(8, 8); }
+  else if (L.r1 == 16) { if (small_k) TMOE_RT(16, 2); else TMOE_RT(16, 8); }
+  else { if (small_k) TMOE_RT(32, 2); else TMOE_RT(32, 8); }
+#undef TMOE_RT
   if (e != cudaSuccess) return TMOE_ERR_CUDA;
   count_launch();
   return launch_status();

@@ -1,6 +1,6 @@
-// Body of the out-projection GEMM kernel (see tc_out_gemm.cu for the description), as a device function so that
-// two kernels can run it: tc_out_kernel itself, and the in/core kernel, whose grid is padded to whole waves with
-// "helper" CTAs that compute out-projection tiles of token tiles finished in the first wave instead of idling.
+// Body of the single-CTA out-projection GEMM kernel (see tc_out_gemm.cu for the description) and the pieces it shares
+// with the CTA-pair kernel: the parameter block, the epilogue of one 64-column chunk and the bounded wait for the
+// "rows ready" words through which the kernel that produces A releases 128-row tiles one by one.
 #pragma once
 #include "common.cuh"
 #include "kernels.h"
@@ -52,25 +52,16 @@ struct OutParams {
   // half of the SMs without one (few token rows); num_n counts tiles of this width and tmB's box has this many rows.
   int on;
   int32_t *status;
-  // Tiles [0, tile_begin) of this GEMM were computed by helper CTAs of the kernel that produced A; this launch starts
-  // at tile_begin (in its own tile units) and clears the hand-off flags.
-  int tile_begin;
-  uint32_t *ready_clear;
-  int ready_words;
-  // Helper CTAs only: rows [128 m, 128 m + 128) of A may be read once ready[8 m .. 8 m + 7] all equal `epoch` (one word
-  // per epilogue warp of the producing CTA).
+  // Tile-by-tile hand-over from the kernel that produces A (CTA-pair kernel only; all three null / 0 otherwise).
+  //   ready   8 words per 128-row tile of A, each set to `epoch` by one epilogue warp of the producing CTA once its rows
+  //           are stored: rows [128 m, 128 m + 128) may be read when ready[8 m .. 8 m + 7] all equal `epoch`
+  //   queue   64-bit word {epoch : 32 | tiles handed out : 32}: the pairs draw their output tiles from it in order, so a
+  //           pair that becomes resident late (while the producing kernel's last wave still runs) simply takes what is left;
+  //           queue[1] = {epoch : 32 | producing CTAs finished : 32}, n_producers of them in all
   const uint32_t *ready;
   uint32_t epoch;
-};
-
-
-// What a helper CTA of the in/core kernel needs to run out-projection tiles: the three tensor maps and parameters of the
-// GEMM, the number of helper CTAs and the number of tiles they share (tile t goes to helper t mod n_helpers).
-struct alignas(64) OutHelperCfg {
-  CUtensorMap tmA, tmB, tmY;
-  OutParams p;
-  int n_helpers;
-  int n_tiles;
+  unsigned long long *queue;
+  int n_producers;
 };
 
 // Epilogue of one 64-column chunk of an output row: accumulator registers r (two 32-column TMEM loads) + bias, optional
@@ -130,20 +121,20 @@ __device__ __forceinline__ void out_epilogue_chunk(const OutParams &p, const uin
   }
 }
 
-// Bounded wait for the eight hand-off words of one 128-row tile of A (written with st.global after a __threadfence by the
-// producing CTA's epilogue warps).  The TMA loads that follow read through the async proxy, hence the proxy fence.
+// Bounded wait for the eight hand-off words of one 128-row tile of A (32-byte aligned; written with st.global after a
+// __threadfence by the producing CTA's epilogue warps).  The words are polled with two 16-byte relaxed loads -- one trip
+// to L2 per poll, this sits in front of every tile's first operand load -- and the acquire is a single fence once all
+// eight match.  The TMA loads that follow read through the async proxy, hence the proxy fence.
 __device__ __forceinline__ bool rows_ready_wait(const uint32_t *flags, uint32_t epoch, int32_t *status) {
   const long long t0 = clock64();
   uint32_t spins = 0;
   for (;;) {
-    int n = 0;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      uint32_t v;
-      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + i) : "memory");
-      n += (v == epoch);
-    }
-    if (n == 8) break;
+    uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+    asm volatile("ld.relaxed.gpu.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3) : "l"(flags) : "memory");
+    asm volatile("ld.relaxed.gpu.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "l"(flags + 4) : "memory");
+    const bool all = (a0 == epoch) & (a1 == epoch) & (a2 == epoch) & (a3 == epoch) & (b0 == epoch) & (b1 == epoch) &
+                     (b2 == epoch) & (b3 == epoch);
+    if (all) break;
     if ((++spins & 0x3fu) == 0) {
       if (*reinterpret_cast<volatile int32_t *>(status) != 0) return false;
       if (clock64() - t0 > kWaitLimitCycles) {
@@ -156,12 +147,14 @@ __device__ __forceinline__ bool rows_ready_wait(const uint32_t *flags, uint32_t 
     }
     __nanosleep(100);
   }
+  asm volatile("fence.acq_rel.gpu;" ::: "memory");
   asm volatile("fence.proxy.async;" ::: "memory");
   return true;
 }
 
 // Processes tiles tile_first, tile_first + tile_step, ... < tile_end (tile = m * num_n + n, 128 x 256 outputs each).
 // Must be entered by all O_THREADS threads of a CTA that holds O_SMEM_BYTES of dynamic shared memory and no TMEM.
+// A must be complete when `dependent` is false; otherwise the body waits for the kernel before it in the stream.
 __device__ __forceinline__ void tc_out_body(const CUtensorMap *tmA, const CUtensorMap *tmB, const CUtensorMap *tmY,
                                             const OutParams &p, int tile_first, int tile_step, int tile_end,
                                             uint8_t *smem_raw, bool dependent = false) {
@@ -200,7 +193,6 @@ __device__ __forceinline__ void tc_out_body(const CUtensorMap *tmA, const CUtens
       bool ok = true;
       for (int tile = tile_first; tile < tile_end && ok; tile += tile_step) {
         const int m0 = (tile / p.num_n) * OM, n0 = (tile % p.num_n) * on;
-        if (p.ready && !(ok = rows_ready_wait(p.ready + (tile / p.num_n) * 8, p.epoch, p.status))) break;
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const uint32_t s = it % OSTAGES, ph = (it / OSTAGES) & 1;
           TMOE_TIC();

@@ -58,10 +58,7 @@ tc_out_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
               const __grid_constant__ CUtensorMap tmY, OutParams p) {
   extern __shared__ uint8_t smem_raw[];
   griddep_launch_dependents();   // all CTAs of this persistent grid are resident: the next kernel may set up on SMs as they free
-  tc_out_body(&tmA, &tmB, &tmY, p, p.tile_begin + (int)blockIdx.x, (int)gridDim.x, p.num_m * p.num_n, smem_raw, true);
-  // the hand-off flags of this forward have served: the kernel that set and read them is complete (griddep_wait in the body)
-  if (p.ready_clear && blockIdx.x == 0)
-    for (int i = threadIdx.x; i < p.ready_words; i += blockDim.x) p.ready_clear[i] = 0u;
+  tc_out_body(&tmA, &tmB, &tmY, p, (int)blockIdx.x, (int)gridDim.x, p.num_m * p.num_n, smem_raw, true);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -72,27 +69,79 @@ tc_out_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
 // (128 B/clk of shared-memory bandwidth against 96 B/clk of operand reads plus the TMA fills).
 // Barriers: full[s] lives in CTA 0 and counts the bytes of both CTAs' loads; empty[s] and tfull[slot] are
 // signalled in both CTAs by multicast commits; tempty[slot] lives in CTA 0 and collects 16 warp arrivals.
+//
+// Tile-by-tile hand-over (OutParams::queue != nullptr).  When the kernel that produces A runs its CTAs in more than one wave
+// (256 token tiles on 148 SMs), the SMs its last, partial wave leaves free would idle until that kernel has completed.
+// Launched as its programmatic dependent, this kernel's pairs become resident on exactly those SMs as soon as every CTA of
+// the producer has started; instead of waiting for the producer to complete (griddepcontrol.wait) they draw output tiles
+// from a queue in row order and wait, per 128-row tile of A, for the words the producing CTA sets once its rows are stored.
+// Every producing CTA is running or done by then, so such a wait always ends; it is bounded all the same.  Pairs that become
+// resident later (as the producer's last wave retires) take what is left.  The queue word carries the forward's epoch: a
+// forward re-tags it instead of anybody resetting it, and a straggler of an older forward that finds a newer tag stops.
 constexpr int P_STAGES = 6;
 constexpr int P_STAGE_BYTES = O_A_BYTES + O_A_BYTES;  // 16 KB of A + 16 KB (half) of B
 constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + O_EPI_WARPS * O_Y_BYTES + 1024;
+constexpr int P_SCHED = 16;   // ring of scheduled tile indices; the producer is never this many tiles ahead of the epilogue
 constexpr int kKernelOutPair = 4;
+
+// Next ticket of forward `epoch` from the queue word {epoch : 32 | tickets handed out : 32}, or -1 when all `total` are
+// handed out.  The producing kernel tags the word with the forward's epoch (count 0) before any of its CTAs can have
+// finished a tile, i.e. long before a CTA of this kernel runs; the tag is checked all the same (bounded).  The draw itself is
+// one atomic add: a compare-and-swap loop starves here -- 74 pairs draw ten tickets per microsecond, more than one per
+// load-to-CAS window, and the pairs furthest from the word's L2 slice were measured to lose every attempt for 300 us.
+__device__ __forceinline__ int draw_ticket(unsigned long long *queue, uint32_t epoch, int total, int32_t *status) {
+  const long long t0 = clock64();
+  for (uint32_t spins = 0;; ++spins) {
+    unsigned long long v;
+    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(queue) : "memory");
+    const uint32_t e = (uint32_t)(v >> 32);
+    if (e == epoch) break;
+    if ((int32_t)(e - epoch) > 0) return -1;             // a newer forward owns the word: this one is complete
+    if ((spins & 0x3fu) == 0x3fu) {
+      if (*reinterpret_cast<volatile int32_t *>(status) != 0) return -1;
+      if (clock64() - t0 > kWaitLimitCycles) {
+        if (atomicCAS(status, 0, (int32_t)TMOE_ERR_DEVICE_WAIT) == 0) {
+          status[1] = 4; status[2] = 12; status[3] = (int32_t)blockIdx.x;
+          __threadfence();
+        }
+        return -1;
+      }
+    }
+    __nanosleep(200);
+  }
+  const unsigned long long old = atomicAdd(queue, 1ull);
+  if ((uint32_t)(old >> 32) != epoch) return -1;         // (re-tagged by a newer forward in between: complete)
+  const uint32_t n = (uint32_t)old;
+  return n < (uint32_t)total ? (int)n : -1;
+}
+// Every further draw is the atomic add alone.  Its result is only looked at one tile later (ticket_of), so the trip to
+// L2 runs under the tile's operand loads instead of in front of them.
+__device__ __forceinline__ unsigned long long draw_next(unsigned long long *queue) { return atomicAdd(queue, 1ull); }
+__device__ __forceinline__ int ticket_of(unsigned long long old, uint32_t epoch, int total) {
+  if ((uint32_t)(old >> 32) != epoch) return -1;
+  const uint32_t n = (uint32_t)old;
+  return n < (uint32_t)total ? (int)n : -1;
+}
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(O_THREADS, 1)
 tc_out_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                    const __grid_constant__ CUtensorMap tmY, OutParams p) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bar_full[P_STAGES], bar_empty[P_STAGES], bar_tfull[2], bar_tempty[2];
+  __shared__ __align__(8) uint64_t bar_full[P_STAGES], bar_empty[P_STAGES], bar_tfull[2], bar_tempty[2], bar_sched[P_SCHED];
+  __shared__ int tile_ring[P_SCHED];
   __shared__ uint32_t tmem_base_s;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t rank = cluster_ctarank();
   const int pair_id = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const bool dyn = p.queue != nullptr;
   griddep_launch_dependents();
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < P_STAGES; ++s) { mbar_init(smem_u32(&bar_full[s]), 1); mbar_init(smem_u32(&bar_empty[s]), 1); }
     for (int s = 0; s < 2; ++s) { mbar_init(smem_u32(&bar_tfull[s]), 1); mbar_init(smem_u32(&bar_tempty[s]), 2 * O_EPI_WARPS); }
+    for (int s = 0; s < P_SCHED; ++s) mbar_init(smem_u32(&bar_sched[s]), 1);
     fence_mbar_init();
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmB);
@@ -105,9 +154,13 @@ tc_out_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   cluster_wait();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_s;
-  griddep_wait();   // everything above is independent of the kernel that produces A
-  if (p.ready_clear && blockIdx.x == 0)
-    for (int i = threadIdx.x; i < p.ready_words; i += blockDim.x) p.ready_clear[i] = 0u;
+  // everything above is independent of the kernel that produces A.  With the tile-by-tile hand-over this kernel does not
+  // wait for that kernel to complete: rows of A are released through p.ready, and nothing else of the producer is read.
+  if (!dyn) griddep_wait();
+#ifdef TMOE_TRACE
+  unsigned long long tr_t0; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tr_t0));
+  long long tr_flag = 0, tr_draw = 0; int tr_tiles = 0;
+#endif
 
   const int num_tiles = p.num_m * p.num_n;  // num_m counts 256-row tiles here
   const int KB = (p.K + OKB - 1) / OKB;
@@ -120,9 +173,53 @@ tc_out_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = p.tile_begin + pair_id; tile < num_tiles && ok; tile += num_pairs) {
+      bool all_rows = false;                 // the producing kernel was seen complete: no further per-tile checks
+      unsigned long long pending = 0;        // result of the draw issued one tile ago
+      for (uint32_t i = 0; ok; ++i) {
+        int tile;
+        const uint32_t slot = i % P_SCHED;
+        if (!dyn) {
+          tile = pair_id + (int)i * num_pairs;
+          if (tile >= num_tiles) break;
+        } else if (rank == 0) {
+#ifdef TMOE_TRACE
+          const long long c0_ = clock64();
+#endif
+          tile = i == 0 ? draw_ticket(p.queue, p.epoch, num_tiles, p.status) : ticket_of(pending, p.epoch, num_tiles);
+          if (tile >= 0) pending = draw_next(p.queue);   // the next tile's ticket, on its way while this tile is loaded
+#ifdef TMOE_TRACE
+          tr_draw += clock64() - c0_; tr_tiles += tile >= 0;
+#endif
+          tile_ring[slot] = tile;
+          st_cluster_u32(mapa_u32(smem_u32(&tile_ring[slot]), 1), (uint32_t)tile);
+          mbar_arrive(smem_u32(&bar_sched[slot]));
+          mbar_arrive_cluster(mapa_u32(smem_u32(&bar_sched[slot]), 1));
+          if (tile < 0) break;
+        } else {
+          if (!(ok = mbar_wait_cluster(smem_u32(&bar_sched[slot]), (i / P_SCHED) & 1, p.status, kKernelOutPair, 5))) break;
+          tile = *reinterpret_cast<volatile int *>(&tile_ring[slot]);
+          if (tile < 0) break;
+        }
         const int m0 = (tile / p.num_n) * (2 * OM) + (int)rank * OM;
         const int n0 = (tile % p.num_n) * ON + (int)rank * (ON / 2);
+        // this CTA's 128 rows of A: wait until the CTA that produces them has stored them (rows beyond T do not exist)
+#ifdef TMOE_TRACE
+        const long long c1_ = clock64();
+#endif
+        if (dyn && !all_rows && m0 < p.T) {
+          // one word says whether the whole producing grid is done (true for every pair that becomes resident after it)
+          unsigned long long d;
+          asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(d) : "l"(p.queue + 1) : "memory");
+          if ((uint32_t)(d >> 32) == p.epoch && (uint32_t)d >= (uint32_t)p.n_producers) {
+            all_rows = true;
+            asm volatile("fence.proxy.async;" ::: "memory");
+          } else if (!(ok = rows_ready_wait(p.ready + (m0 / OM) * 8, p.epoch, p.status))) {
+            break;
+          }
+        }
+#ifdef TMOE_TRACE
+        tr_flag += clock64() - c1_;
+#endif
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const uint32_t s = it % P_STAGES, ph = (it / P_STAGES) & 1;
           TMOE_TIC();
@@ -135,13 +232,26 @@ tc_out_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           tma_load_2d_pair(sa + O_A_BYTES, &tmB, kb * OKB, n0, full0);
         }
       }
+#ifdef TMOE_TRACE
+      if (dyn && rank == 0 && pair_id < 120) {   // per pair: start (ns, low bits), end, tiles, cycles in flag waits, cycles in draws
+        unsigned long long t1_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1_));
+        int32_t *o = p.status + 64 + pair_id * 5;
+        o[0] = (int32_t)(uint32_t)tr_t0; o[1] = (int32_t)(uint32_t)t1_; o[2] = tr_tiles; o[3] = (int32_t)tr_flag; o[4] = (int32_t)tr_draw;
+      }
+#endif
     }
   } else if (warp == 1) {
     if (lane == 0 && rank == 0) {
       const uint32_t idesc = umma_idesc_bf16(2 * OM, ON);
       const uint64_t desc0 = umma_desc_k_sw128(ring);
-      uint32_t s = 0, ph = 0, tcount = 0;
-      for (int tile = p.tile_begin + pair_id; tile < num_tiles; tile += num_pairs, ++tcount) {
+      uint32_t s = 0, ph = 0;
+      for (uint32_t tcount = 0;; ++tcount) {
+        if (dyn) {
+          mbar_wait_or_exit(smem_u32(&bar_sched[tcount % P_SCHED]), (tcount / P_SCHED) & 1, p.status, kKernelOutPair, 5);
+          if (*reinterpret_cast<volatile int *>(&tile_ring[tcount % P_SCHED]) < 0) break;
+        } else if (pair_id + (int)tcount * num_pairs >= num_tiles) {
+          break;
+        }
         const uint32_t slot = tcount & 1, aph = (tcount >> 1) & 1;
         TMOE_TIC();
         mbar_wait_or_exit(smem_u32(&bar_tempty[slot]), aph ^ 1, p.status, kKernelOutPair, 4);
@@ -171,9 +281,19 @@ tc_out_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     const int half = ew >> 2;
     const int row_in_tile = quad * 32 + lane;
     const uint32_t stage_buf = ring + P_STAGES * P_STAGE_BYTES + ew * O_Y_BYTES;
-    uint32_t tcount = 0;
     bool ok = true;
-    for (int tile = p.tile_begin + pair_id; tile < num_tiles && ok; tile += num_pairs, ++tcount) {
+    for (uint32_t tcount = 0; ok; ++tcount) {
+      int tile;
+      if (dyn) {
+        ok = mbar_wait_cluster(smem_u32(&bar_sched[tcount % P_SCHED]), (tcount / P_SCHED) & 1, p.status, kKernelOutPair, 5);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tile = *reinterpret_cast<volatile int *>(&tile_ring[tcount % P_SCHED]);
+      } else {
+        tile = pair_id + (int)tcount * num_pairs;
+        if (tile >= num_tiles) tile = -1;
+      }
+      if (tile < 0) break;
       const int m0 = (tile / p.num_n) * (2 * OM) + (int)rank * OM, n0 = (tile % p.num_n) * ON;
       const uint32_t slot = tcount & 1, aph = (tcount >> 1) & 1;
       ok = mbar_wait(smem_u32(&bar_tfull[slot]), aph, p.status, kKernelOutPair, 3);
@@ -236,10 +356,36 @@ static cudaError_t launch_dependent(Kern kern, int grid, int smem, cudaStream_t 
   return cudaLaunchKernelEx(&cfg, kern, a, b, y, p);
 }
 
+// CTA pairs for GEMMs with at least two 256x256 tiles per pair of SMs (each CTA then streams 32 KB instead of 48 KB per
+// k block and the ring is six stages deep: 112 us against 119 us on the prefill configuration); smaller GEMMs keep the
+// single-CTA kernel, whose 128-row tiles cover more SMs.  TMOE_OUT_PAIRS=0 / 1 forces the choice.
+bool tc_gemm_uses_pairs(int64_t M, int N, int sms) {
+  static const int pairs_env = []() { const char *e = getenv("TMOE_OUT_PAIRS"); return e ? (atoi(e) != 0 ? 1 : 0) : -1; }();
+  const int64_t tiles256 = ((M + 2 * OM - 1) / (2 * OM)) * ((N + ON - 1) / ON);
+  return pairs_env >= 0 ? pairs_env == 1 : tiles256 >= 2 * (int64_t)(sms / 2);
+}
+
+// Whether a forward of T tokens hands its z rows to the out-projection tile by tile (see tc_out_pair_kernel): the token
+// tiles need more than one wave of CTAs, the out-projection runs on CTA pairs, programmatic dependent launch is on, and the
+// caller asked for it with TMOE_HANDOFF=1 (read on every call, so a process can switch it).  Off by default: measured on the
+// prefill configuration (256 token tiles on 148 SMs) the hand-over works as designed -- 14 pairs start 45 us early on the
+// SMs of fully free TPCs and finish 5-6 tiles each before the last wave of token tiles ends, the tiles are drawn evenly --
+// but a forward takes 223 us with it against 215 us without: every tile pays for its ticket and its ready words (the
+// producer thread of this GEMM has no slack: 7.1 us per tile against 6.6 us), and the SMs it fills were idle on a
+// power-capped part, where the busy ones clock higher for it.
+bool plan_out_handoff(const tmoe_layer_t &L, int64_t T, int sms) {
+  static const bool pdl_off = []() { const char *e = getenv("TMOE_PDL"); return e && atoi(e) == 0; }();
+  const char *on = getenv("TMOE_HANDOFF");
+  if (!on || atoi(on) != 1 || pdl_off || sms <= 0) return false;
+  const int64_t token_tiles = (T + OM - 1) / OM;
+  return token_tiles > sms && tc_gemm_uses_pairs(T, L.d_out, sms);
+}
+
 // y[M, N] (bf16) = A[M, K] (bf16, row-major) @ B_t[N, K]^T (bf16, K-major) + bias[N] (fp32, optional),
-// then the optional OutEpilogue tail.  N and K multiples of 8.
+// then the optional OutEpilogue tail.  N and K multiples of 8.  `flags` (optional): tile-by-tile hand-over from the kernel
+// that produces A; only honoured on the CTA-pair kernel (the caller asks plan_out_handoff first).
 int launch_tc_gemm_bf16(const void *A, const void *B_t, const float *bias, const OutEpilogue &epi, int64_t M, int N,
-                        int K, void *y, int32_t *status, cudaStream_t st, const OutHandoff *ho) {
+                        int K, void *y, int32_t *status, cudaStream_t st, const OutFlags *flags) {
   CUtensorMap tmA, tmB, tmY;
   int rc = encode_tmap_bf16_2d(&tmY, y, (uint64_t)M, (uint64_t)N, 32);
   if (rc) return rc;
@@ -248,20 +394,17 @@ int launch_tc_gemm_bf16(const void *A, const void *B_t, const float *bias, const
   rc = encode_tmap_bf16_2d(&tmB, B_t, (uint64_t)N, (uint64_t)K, ON);
   if (rc) return rc;
   static bool attr_done[64] = {};
-  int dev = 0, sms = 0;
+  int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return TMOE_ERR_CUDA;
-  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return TMOE_ERR_CUDA;
+  const int sms = current_device_sms();
+  if (sms <= 0) return TMOE_ERR_CUDA;
   if (dev < 64 && !attr_done[dev]) {
     if (cudaFuncSetAttribute(tc_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, O_SMEM_BYTES) != cudaSuccess)
       return TMOE_ERR_CUDA;
     attr_done[dev] = true;
   }
-  // CTA pairs for GEMMs with at least two 256x256 tiles per pair of SMs (each CTA then streams 32 KB instead of 48 KB per
-  // k block and the ring is six stages deep: 112 us against 119 us on the prefill configuration); smaller GEMMs keep the
-  // single-CTA kernel, whose 128-row tiles cover more SMs.  TMOE_OUT_PAIRS=0 / 1 forces the choice.
-  static const int pairs_env = []() { const char *e = getenv("TMOE_OUT_PAIRS"); return e ? (atoi(e) != 0 ? 1 : 0) : -1; }();
-  const int64_t tiles256 = ((M + 2 * OM - 1) / (2 * OM)) * ((N + ON - 1) / ON);
-  const bool use_pairs = pairs_env >= 0 ? pairs_env == 1 : tiles256 >= 2 * (int64_t)(sms / 2);
+  const bool use_pairs = tc_gemm_uses_pairs(M, N, sms);
+  if (flags && !use_pairs) return TMOE_ERR_UNSUPPORTED;
   if (use_pairs) {
     static bool attr2_done[64] = {};
     if (dev < 64 && !attr2_done[dev]) {
@@ -278,8 +421,11 @@ int launch_tc_gemm_bf16(const void *A, const void *B_t, const float *bias, const
     q.T = M; q.N = N; q.K = K;
     q.num_m = (int)((M + 2 * OM - 1) / (2 * OM)); q.num_n = (N + ON - 1) / ON;
     q.status = status;
-    if (ho && ho->n_helpers > 0) { q.tile_begin = (ho->m_tiles / 2) * q.num_n; q.ready_clear = ho->ready; q.ready_words = ho->m_tiles * 8; }
-    const int tiles2 = q.num_m * q.num_n - q.tile_begin;
+    if (flags) {
+      q.ready = flags->ready; q.epoch = flags->epoch; q.queue = flags->queue;
+      q.n_producers = (int)((M + OM - 1) / OM);
+    }
+    const int tiles2 = q.num_m * q.num_n;
     // a persistent grid must be fully co-resident: ask how many 2-CTA clusters the device can hold at once
     static int max_pairs[64] = {};
     if (dev < 64 && max_pairs[dev] == 0) {
@@ -305,17 +451,16 @@ int launch_tc_gemm_bf16(const void *A, const void *B_t, const float *bias, const
   p.T = M; p.N = N; p.K = K;
   p.num_m = (int)((M + OM - 1) / OM); p.num_n = (N + ON - 1) / ON;
   p.on = ON;
-  // few token rows: 128-column tiles put twice as many SMs to work (each CTA then streams half of B per k block)
+  // few token rows: 128-column tiles put twice as many SMs to work (each CTA then streams half of B per k block);
+  // and an output of at most 128 columns (the router-scores GEMM at E <= 128) never needs the wide tile
   static const int narrow_env = [] { const char *e = getenv("TMOE_OUT_NARROW"); return e ? atoi(e) : 1; }();
-  // ... and an output of at most 128 columns (the router-scores GEMM at E <= 128) never needs the wide tile
-  if (narrow_env && !(ho && ho->n_helpers > 0) && (N <= ON / 2 || (int64_t)p.num_m * p.num_n * 2 <= sms)) {
+  if (narrow_env && (N <= ON / 2 || (int64_t)p.num_m * p.num_n * 2 <= sms)) {
     p.on = ON / 2;
     p.num_n = (N + p.on - 1) / p.on;
     if ((rc = encode_tmap_bf16_2d(&tmB, B_t, (uint64_t)N, (uint64_t)K, (uint32_t)p.on))) return rc;
   }
   p.status = status;
-  if (ho && ho->n_helpers > 0) { p.tile_begin = ho->m_tiles * p.num_n; p.ready_clear = ho->ready; p.ready_words = ho->m_tiles * 8; }
-  const int tiles = p.num_m * p.num_n - p.tile_begin;
+  const int tiles = p.num_m * p.num_n;
   const int grid = tiles < sms ? tiles : sms;
   if (launch_dependent(tc_out_kernel, grid, O_SMEM_BYTES, st, tmA, tmB, tmY, p) != cudaSuccess) return TMOE_ERR_CUDA;
   count_launch();
@@ -323,37 +468,8 @@ int launch_tc_gemm_bf16(const void *A, const void *B_t, const float *bias, const
 }
 
 int launch_tc_out(const tmoe_layer_t &L, const void *z, const void *uout_t, const float *bias, const OutEpilogue &epi,
-                  int64_t T_, void *y, int32_t *status, cudaStream_t st, const OutHandoff *ho) {
-  return launch_tc_gemm_bf16(z, uout_t, bias, epi, T_, L.d_out, L.r2, y, status, st, ho);
-}
-
-// A helper CTA has about the time of one token tile of the in/core kernel: the tiles it can take follow from the two
-// kernels' FLOPs per tile, with a margin (measured on the prefill configuration: 3-4 tiles per helper gain 1.5 %, 5 lose
-// it again because the helpers then outlast the last wave; TMOE_HANDOFF_SCALE overrides the margin, TMOE_HANDOFF=0 turns
-// the hand-off off).
-void plan_out_handoff(const tmoe_layer_t &L, int64_t T, int sms, OutHandoff *h) {
-  *h = OutHandoff{};
-  static const bool off = []() { const char *e = getenv("TMOE_HANDOFF"); return e && atoi(e) == 0; }();
-  if (off || sms <= 0) return;
-  const int64_t token_tiles = (T + OM - 1) / OM;
-  const int tail = (int)(token_tiles % sms);
-  if (token_tiles <= sms || tail == 0) return;
-  const int helpers = sms - tail;
-  if (helpers < 4) return;
-  const double e_pad = (double)align_up(L.n_experts, 16);
-  const double f_in = 128.0 * (2.0 * L.d_in * (L.r3 + e_pad) + 2.0 * L.r3 * L.r1 * (double)L.r2);
-  const double f_out = 2.0 * 128.0 * 256.0 * L.r2;
-  static const double scale = []() { const char *e = getenv("TMOE_HANDOFF_SCALE"); return e ? atof(e) : 0.7; }();
-  const int per_helper = (int)(scale * f_in / f_out);
-  const int num_n = (L.d_out + ON - 1) / ON;
-  int m_tiles = (int)((int64_t)helpers * per_helper / num_n);
-  if (m_tiles > sms) m_tiles = sms;                      // only tiles of the first wave
-  if (m_tiles > kMaxHandoffTiles) m_tiles = kMaxHandoffTiles;
-  if (m_tiles > T / OM) m_tiles = (int)(T / OM);         // whole tiles only
-  m_tiles &= ~1;
-  if (m_tiles < 2) return;
-  h->m_tiles = m_tiles;
-  h->n_helpers = helpers;
+                  int64_t T_, void *y, int32_t *status, cudaStream_t st, const OutFlags *flags) {
+  return launch_tc_gemm_bf16(z, uout_t, bias, epi, T_, L.d_out, L.r2, y, status, st, flags);
 }
 
 }  // namespace tmoe

@@ -674,13 +674,59 @@ def fused_out_proj(out_proj: TuckerMoE, mid: torch.Tensor, norm, layer_scale: to
     return out_proj.forward_fused(mid, pre_norm=norm, residual=mid, layer_scale=layer_scale)
 
 
+def _gate_up_one_launch(ffn_gate: TuckerMoE, ffn_up: TuckerMoE, x: torch.Tensor, norm_w: torch.Tensor, norm_eps: float):
+    """``silu(ffn_gate(norm(x))) * ffn_up(norm(x))`` through ``tmoe_ffn_gate_up`` (the two layers' in-projection / core
+    stages in one launch, ``model.py:337-340``), or None when that entry point does not cover the call: other kernel
+    paths (few tokens, fp32), different layer sizes, a router the tensor-core kernel does not run in-kernel."""
+    if not x.is_cuda or x.dtype != torch.bfloat16 or torch.compiler.is_compiling():
+        return None
+    T = x.numel() // max(x.shape[-1], 1)
+    if T == 0 or ffn_gate.path not in (PATH_AUTO, PATH_TENSOR) or ffn_up.path != ffn_gate.path:
+        return None
+    shapes = [tuple(p.shape) for p in ffn_gate._params()]
+    if shapes != [tuple(p.shape) for p in ffn_up._params()] or ffn_gate.top_k != ffn_up.top_k \
+            or ffn_gate.inner_norm.eps != ffn_up.inner_norm.eps or ffn_gate._router() != ffn_up._router():
+        return None
+    if ffn_gate._prenorm_path(x) != PATH_TENSOR or ffn_up._prenorm_path(x) != PATH_TENSOR:
+        return None
+    pg, pu = ffn_gate._prepared_prenorm_for(x, norm_w), ffn_up._prepared_prenorm_for(x, norm_w)
+    if pg is None or pu is None:
+        return None
+    lib = _lib.load()
+    rw, ui, nw, ue, co, uo, b = ffn_gate._params()
+    layer = _layer_struct(x, rw, ui, ue, co, uo, ffn_gate.top_k, ffn_gate.inner_norm.eps, ffn_gate._router())
+    d_in, d_out = ui.shape[0], uo.shape[1]
+    x2 = x.reshape(-1, d_in)
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    dev = x.device
+    with torch.cuda.device(dev):
+        ws_one = _lib.check(lib.tmoe_workspace_bytes(C.byref(layer), T, PATH_TENSOR), "tmoe_workspace_bytes")
+        ws = _workspace(dev, 2 * ((ws_one + 255) // 256 * 256))
+        gate = torch.empty((T, d_out), dtype=x.dtype, device=dev)
+        act = torch.empty((T, d_out), dtype=x.dtype, device=dev)
+        ex = Extras()
+        ex.pre_norm, ex.pre_norm_eps = 1, float(norm_eps)
+        rc = lib.tmoe_ffn_gate_up(C.byref(layer), pg.data_ptr(), pu.data_ptr(), x2.data_ptr(), T, gate.data_ptr(),
+                                  act.data_ptr(), C.byref(ex), ws.data_ptr(), ws.numel(),
+                                  torch.cuda.current_stream(dev).cuda_stream)
+    if rc == -6:     # TMOE_ERR_UNSUPPORTED: the caller composes the two layers itself
+        return None
+    _lib.check(rc, "tmoe_ffn_gate_up")
+    return act.reshape(*x.shape[:-1], d_out)
+
+
 def fused_ffn(ffn_gate: TuckerMoE, ffn_up: TuckerMoE, ffn_down: TuckerMoE, x_res: torch.Tensor, norm,
               layer_scale: torch.Tensor) -> torch.Tensor:
     """``x_res + gamma * ffn_down(silu(ffn_gate(x_f)) * ffn_up(x_f))`` with ``x_f = norm(x_res)`` -- the FFN of the
     reference's transformer block (``model.py:337-341``).  The norm runs inside the gate and up layers' in-projection kernels where those
-    support it (else ``x_f`` is computed once and shared), ``silu(gate) * up`` is the epilogue of the up layer and the residual add is the epilogue of the down
+    support it (else ``x_f`` is computed once and shared); on the tensor-core path the two layers' in-projection / core stages are one
+    launch that reads each tile of ``x_res`` from HBM once, ``silu(gate) * up`` is the epilogue of the up layer and the residual add is the epilogue of the down
     layer, so no element-wise pass over the 6x-wide activations remains."""
     w, e = (norm.weight, norm.eps) if hasattr(norm, "weight") else norm
+    act = _gate_up_one_launch(ffn_gate, ffn_up, x_res, w, e)
+    if act is not None:
+        return ffn_down.forward_fused(act, residual=x_res, layer_scale=layer_scale)
     if ffn_gate._prepared_prenorm_for(x_res, w) is not None and ffn_up._prepared_prenorm_for(x_res, w) is not None:
         # both layers apply the norm inside their in-projection kernels: no separate pass over x_res
         gate = ffn_gate.forward_fused(x_res, pre_norm=(w, e))
