@@ -345,6 +345,62 @@ def run_ffn_pair(args, dev):
         "gpu_launches": int(res["one_launch_gate_up"]["launches_per_block"] * args.steps)}), flush=True)
 
 
+def run_strong_only(args, layer, shape, dtype, seed, T, rank, world, dev, zipf, desc):
+    """The workload's T tokens split over the ranks: forward alone, then forward + NCCL all-gather of y (1 and 4 chunks)."""
+    import torch.distributed as dist
+    from mamba_tuckermoe_b200.sharding import sharded_forward
+    from mamba_tuckermoe_b200.synthetic import make_tokens
+    if T % world:
+        raise SystemExit("--strong-only needs T divisible by the number of ranks")
+    Ts = T // world
+    xs = [make_tokens(Ts, shape.d_in, seed + 17 * rank + 1000 * i, dtype) for i in range(N_INPUT_SETS)]
+    if zipf:
+        for x in xs:
+            x[:, 0] = 1.0
+    xs = [x.to(dev) for x in xs]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    out = {}
+    with torch.no_grad():
+        for i in range(3):
+            layer(xs[i % N_INPUT_SETS])
+        s_ms = timed_steps(lambda i: layer(xs[i % N_INPUT_SETS]), args.steps, barrier, dev, world) / args.steps
+        out["strong"] = {"tokens_per_gpu": Ts, "global_tokens": T, "ms_per_step": s_ms, "tokens_per_s": T / (s_ms * 1e-3)}
+        if world > 1:
+            y_all = torch.empty((T, shape.d_out), dtype=dtype, device=dev)
+            for chunks in (1, 4):
+                if T % (world * chunks):
+                    continue
+                for i in range(2):
+                    sharded_forward(layer, xs[i % N_INPUT_SETS], n_tokens=T, gather=True, chunks=chunks, out=y_all)
+                g_ms = timed_steps(lambda i: sharded_forward(layer, xs[i % N_INPUT_SETS], n_tokens=T, gather=True,
+                                                             chunks=chunks, out=y_all), args.steps, barrier, dev, world) / args.steps
+                out[f"allgather_chunks{chunks}"] = {"ms_per_step": g_ms, "tokens_per_s": T / (g_ms * 1e-3),
+                                                    "ms_over_compute_only": g_ms - s_ms}
+            # the collective alone, for reference: the same in-place all-gather without the kernels
+            mine = y_all[rank * Ts:(rank + 1) * Ts]
+            dist.all_gather_into_tensor(y_all, mine)
+            c_ms = timed_steps(lambda i: dist.all_gather_into_tensor(y_all, mine), args.steps, barrier, dev, world) / args.steps
+            recv = (world - 1) * Ts * shape.d_out * y_all.element_size()
+            out["allgather_alone"] = {"ms": c_ms, "bytes_received_per_gpu": recv, "gbs_received_per_gpu": recv / c_ms / 1e6}
+    if rank == 0:
+        v = out["strong"]["tokens_per_s"]
+        print(json.dumps({"metric": "tucker_moe_layer_tokens_per_sec", "value": v, "unit": "tokens/s", "n_gpus": world,
+                          "steps": args.steps, "warmup": 3, "ms_per_step": out["strong"]["ms_per_step"],
+                          "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                          "dtype": "bf16" if dtype == torch.bfloat16 else "f32", "data": "synthetic",
+                          "config": {"workload": f"{args.workload}: {desc}", "global_tokens": T, "tokens_per_gpu": Ts,
+                                     "sharding": f"{T} tokens split over {world} ranks, factors replicated"},
+                          "layer_frac_of_bf16_peak": v * shape.flops_per_token() / 1e12 / world / load_peaks()["bf16_tflops"],
+                          **out}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def timed_steps(fn, steps, barrier, dev, world):
     """CUDA-event time of `steps` calls of fn(i) bracketed by a barrier + synchronize on both sides; max over ranks (ms)."""
     import torch.distributed as dist
@@ -442,6 +498,9 @@ def main():
                     help="short run for use under ncu: 'forward' = device-resident steps only (no per-kernel, e2e or CPU "
                          "legs); 'router' = the stand-alone router entry point (tmoe_router) on the workload's tokens")
     ap.add_argument("--tokens", type=int, default=0, help="override the workload's token count (profiling of small cases)")
+    ap.add_argument("--strong-only", action="store_true",
+                    help="N > 1: only the strong-sharded legs (the workload's T tokens split over the ranks, without and "
+                         "with the all-gather of y); every rank generates just its own T/N tokens")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
@@ -487,6 +546,10 @@ def main():
                            "U_expert": f["U_expert"], "core": f["core"], "U_out": f["U_out"], "bias": f["bias"]})
     layer = layer.to(device=dev, dtype=dtype)
     layer.path = args.path
+
+    if args.strong_only:
+        run_strong_only(args, layer, shape, dtype, seed, T, rank, world, dev, zipf, desc)
+        return
 
     # this rank's token shard: seeded per rank; two of the host copies stay pinned for the end-to-end leg
     n_pinned = 2

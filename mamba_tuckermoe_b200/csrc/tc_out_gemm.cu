@@ -123,6 +123,8 @@ __device__ __forceinline__ int ticket_of(unsigned long long old, uint32_t epoch,
   return n < (uint32_t)total ? (int)n : -1;
 }
 
+// DYN: tile-by-tile hand-over (the plain instantiation carries none of its code)
+template <bool DYN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(O_THREADS, 1)
 tc_out_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                    const __grid_constant__ CUtensorMap tmY, OutParams p) {
@@ -135,13 +137,14 @@ tc_out_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t rank = cluster_ctarank();
   const int pair_id = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-  const bool dyn = p.queue != nullptr;
+  constexpr bool dyn = DYN;
   griddep_launch_dependents();
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < P_STAGES; ++s) { mbar_init(smem_u32(&bar_full[s]), 1); mbar_init(smem_u32(&bar_empty[s]), 1); }
     for (int s = 0; s < 2; ++s) { mbar_init(smem_u32(&bar_tfull[s]), 1); mbar_init(smem_u32(&bar_tempty[s]), 2 * O_EPI_WARPS); }
-    for (int s = 0; s < P_SCHED; ++s) mbar_init(smem_u32(&bar_sched[s]), 1);
+    if (dyn)
+      for (int s = 0; s < P_SCHED; ++s) mbar_init(smem_u32(&bar_sched[s]), 1);
     fence_mbar_init();
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmB);
@@ -408,7 +411,8 @@ int launch_tc_gemm_bf16(const void *A, const void *B_t, const float *bias, const
   if (use_pairs) {
     static bool attr2_done[64] = {};
     if (dev < 64 && !attr2_done[dev]) {
-      if (cudaFuncSetAttribute(tc_out_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES) != cudaSuccess)
+      if (cudaFuncSetAttribute(tc_out_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES) != cudaSuccess ||
+          cudaFuncSetAttribute(tc_out_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES) != cudaSuccess)
         return TMOE_ERR_CUDA;
       attr2_done[dev] = true;
     }
@@ -436,12 +440,14 @@ int launch_tc_gemm_bf16(const void *A, const void *B_t, const float *bias, const
       at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
       cfg.attrs = at; cfg.numAttrs = 1;
       int n = 0;
-      if (cudaOccupancyMaxActiveClusters(&n, tc_out_pair_kernel, &cfg) != cudaSuccess || n <= 0) return TMOE_ERR_CUDA;
+      if (cudaOccupancyMaxActiveClusters(&n, tc_out_pair_kernel<false>, &cfg) != cudaSuccess || n <= 0) return TMOE_ERR_CUDA;
       max_pairs[dev] = n;
     }
     int pairs = dev < 64 ? max_pairs[dev] : sms / 2;
     if (tiles2 < pairs) pairs = tiles2;
-    if (launch_dependent(tc_out_pair_kernel, 2 * pairs, P_SMEM_BYTES, st, tmA, tmBh, tmY, q) != cudaSuccess) return TMOE_ERR_CUDA;
+    const cudaError_t le = flags ? launch_dependent(tc_out_pair_kernel<true>, 2 * pairs, P_SMEM_BYTES, st, tmA, tmBh, tmY, q)
+                                 : launch_dependent(tc_out_pair_kernel<false>, 2 * pairs, P_SMEM_BYTES, st, tmA, tmBh, tmY, q);
+    if (le != cudaSuccess) return TMOE_ERR_CUDA;
     count_launch();
     return launch_status();
   }
