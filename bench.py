@@ -345,6 +345,57 @@ def run_ffn_pair(args, dev):
         "gpu_launches": int(res["one_launch_gate_up"]["launches_per_block"] * args.steps)}), flush=True)
 
 
+def time_gathers(layer, xs, T, shape, dtype, dev, rank, world, steps, barrier, s_ms):
+    """The T tokens split over the ranks (xs: this rank's inputs), forward + all-gather of y into a [T, d_out] buffer on
+    every rank: NCCL in place per token chunk, and the copy-engine push into mapped peer buffers, 1 and 4 chunks each;
+    then the two exchanges alone."""
+    import torch.distributed as dist
+    from mamba_tuckermoe_b200.sharding import PeerBuffers, sharded_forward
+    Ts = T // world
+    recv = (world - 1) * Ts * shape.d_out * xs[0].element_size()
+    info = {"bytes_received_per_gpu": recv, "compute_only_ms": s_ms}
+
+    def leg(name, fn):
+        for i in range(2):
+            fn(i)
+        ms = timed_steps(fn, steps, barrier, dev, world) / steps
+        info[name] = {"ms_per_step": ms, "tokens_per_s": T / (ms * 1e-3), "ms_over_compute_only": ms - s_ms}
+
+    y_all = torch.empty((T, shape.d_out), dtype=dtype, device=dev)
+    for chunks in (1, 4):
+        if T % (world * chunks) == 0:
+            leg(f"nccl_chunks{chunks}", lambda i: sharded_forward(layer, xs[i % N_INPUT_SETS], n_tokens=T, gather=True,
+                                                                  chunks=chunks, out=y_all))
+    mine = y_all[rank * Ts:(rank + 1) * Ts]
+    leg("nccl_alone", lambda i: dist.all_gather_into_tensor(y_all, mine))
+    info["nccl_alone"]["gbs_received_per_gpu"] = recv / info["nccl_alone"]["ms_per_step"] / 1e6
+    del y_all, mine
+    peers = PeerBuffers(T, shape.d_out, dtype, dev)
+    try:
+        leg("in_kernel", lambda i: sharded_forward(layer, xs[i % N_INPUT_SETS], n_tokens=T, gather=True, peers=peers))
+        for chunks in (1, 2, 4):
+            leg(f"push_chunks{chunks}", lambda i: sharded_forward(layer, xs[i % N_INPUT_SETS], n_tokens=T, gather=True,
+                                                                  chunks=chunks, peers=peers, in_kernel=False))
+        lo = rank * Ts
+
+        def push_alone(i):
+            cur = torch.cuda.current_stream(dev)
+            peers.push_stream.wait_stream(cur)
+            peers.push(lo, lo + Ts)
+            cur.wait_stream(peers.push_stream)
+            peers.rendezvous(cur)
+        leg("push_alone", push_alone)
+        info["push_alone"]["gbs_received_per_gpu"] = recv / info["push_alone"]["ms_per_step"] / 1e6
+    finally:
+        peers.close()
+    info["note"] = ("nccl_*: strong-sharded forward + in-place all_gather_into_tensor per token chunk on a side stream; push_*: "
+                    "the same forward writing into a buffer that every peer has mapped, each finished chunk copied to all peers "
+                    "by the copy engines (tmoe_peer_push), two one-element all-reduces as rendezvous; in_kernel: the out-projection GEMM "
+                    "stores every output tile to its own and to all peers' buffers (tmoe_extras_t.peer_y), same rendezvous "
+                    "(sharding.py)")
+    return info
+
+
 def run_strong_only(args, layer, shape, dtype, seed, T, rank, world, dev, zipf, desc):
     """The workload's T tokens split over the ranks: forward alone, then forward + NCCL all-gather of y (1 and 4 chunks)."""
     import torch.distributed as dist
@@ -371,22 +422,7 @@ def run_strong_only(args, layer, shape, dtype, seed, T, rank, world, dev, zipf, 
         s_ms = timed_steps(lambda i: layer(xs[i % N_INPUT_SETS]), args.steps, barrier, dev, world) / args.steps
         out["strong"] = {"tokens_per_gpu": Ts, "global_tokens": T, "ms_per_step": s_ms, "tokens_per_s": T / (s_ms * 1e-3)}
         if world > 1:
-            y_all = torch.empty((T, shape.d_out), dtype=dtype, device=dev)
-            for chunks in (1, 4):
-                if T % (world * chunks):
-                    continue
-                for i in range(2):
-                    sharded_forward(layer, xs[i % N_INPUT_SETS], n_tokens=T, gather=True, chunks=chunks, out=y_all)
-                g_ms = timed_steps(lambda i: sharded_forward(layer, xs[i % N_INPUT_SETS], n_tokens=T, gather=True,
-                                                             chunks=chunks, out=y_all), args.steps, barrier, dev, world) / args.steps
-                out[f"allgather_chunks{chunks}"] = {"ms_per_step": g_ms, "tokens_per_s": T / (g_ms * 1e-3),
-                                                    "ms_over_compute_only": g_ms - s_ms}
-            # the collective alone, for reference: the same in-place all-gather without the kernels
-            mine = y_all[rank * Ts:(rank + 1) * Ts]
-            dist.all_gather_into_tensor(y_all, mine)
-            c_ms = timed_steps(lambda i: dist.all_gather_into_tensor(y_all, mine), args.steps, barrier, dev, world) / args.steps
-            recv = (world - 1) * Ts * shape.d_out * y_all.element_size()
-            out["allgather_alone"] = {"ms": c_ms, "bytes_received_per_gpu": recv, "gbs_received_per_gpu": recv / c_ms / 1e6}
+            out["allgather"] = time_gathers(layer, xs, T, shape, dtype, dev, rank, world, args.steps, barrier, s_ms)
     if rank == 0:
         v = out["strong"]["tokens_per_s"]
         print(json.dumps({"metric": "tucker_moe_layer_tokens_per_sec", "value": v, "unit": "tokens/s", "n_gpus": world,
@@ -401,19 +437,29 @@ def run_strong_only(args, layer, shape, dtype, seed, T, rank, world, dev, zipf, 
         dist.destroy_process_group()
 
 
-def timed_steps(fn, steps, barrier, dev, world):
-    """CUDA-event time of `steps` calls of fn(i) bracketed by a barrier + synchronize on both sides; max over ranks (ms)."""
+def timed_steps(fn, steps, barrier, dev, world, detail=None):
+    """CUDA-event time of `steps` calls of fn(i) bracketed by a barrier + synchronize on both sides; max over ranks (ms).
+    `detail` (a dict) receives every rank's device time and the host time each rank spent enqueueing the steps."""
     import torch.distributed as dist
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     ev0.record()
+    h0 = time.perf_counter()
     for i in range(steps):
         fn(i)
+    h1 = time.perf_counter()
     ev1.record()
     barrier()
-    t_ms = torch.tensor([ev0.elapsed_time(ev1)], dtype=torch.float64, device=dev)
+    mine = torch.tensor([ev0.elapsed_time(ev1), (h1 - h0) * 1e3], dtype=torch.float64, device=dev)
+    t_ms = mine[:1].clone()
     if world > 1:
         dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
+    if detail is not None:
+        every = [torch.zeros_like(mine) for _ in range(world)] if world > 1 else [mine]
+        if world > 1:
+            dist.all_gather(every, mine)
+        detail["device_ms_per_step_per_rank"] = [round(float(t[0]) / steps, 5) for t in every]
+        detail["host_enqueue_ms_per_step_per_rank"] = [round(float(t[1]) / steps, 5) for t in every]
     return float(t_ms.item())
 
 
@@ -587,8 +633,26 @@ def main():
             sampler.start()
             time.sleep(0.25)
         launches0 = lib.tmoe_launch_count()
-        ms_total = timed_steps(lambda i: layer(x_dev[i % N_INPUT_SETS]), args.steps, barrier, dev, world)
+        per_rank = {}
+        ms_total = timed_steps(lambda i: layer(x_dev[i % N_INPUT_SETS]), args.steps, barrier, dev, world, detail=per_rank)
         launches = lib.tmoe_launch_count() - launches0
+        # the same steps replayed from a CUDA graph (one graph holds a step on each input set): what is left of a step
+        # when the host's part -- Python, tensor-map encoding, four launches -- is taken out
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            layer(x_dev[0])
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for x in x_dev:
+                    layer(x)
+            graph.replay()
+            side.synchronize()
+            replays = max(1, -(-args.steps // N_INPUT_SETS))
+            g_ms = timed_steps(lambda i: graph.replay(), replays, barrier, dev, world) / (replays * N_INPUT_SETS)
+        torch.cuda.current_stream().wait_stream(side)
+        per_rank["graph_replay"] = {"ms_per_step": g_ms, "tokens_per_s": world * T / (g_ms * 1e-3),
+                                    "note": f"{replays} replays of a graph of {N_INPUT_SETS} steps, device-timed, max over ranks"}
         if rank == 0:
             time.sleep(0.15)
             clocks = sampler.stop()
@@ -619,26 +683,7 @@ def main():
                 # ---------------- ... followed by the all-gather of y ----------------
                 want_gather = args.allgather != 0
                 if want_gather:
-                    from mamba_tuckermoe_b200.sharding import sharded_forward
-                    gather_info = {}
-                    y_all = torch.empty((T, shape.d_out), dtype=dtype, device=dev)
-                    for chunks in (1, 4):
-                        if T % (world * chunks):
-                            continue
-                        for i in range(2):
-                            sharded_forward(layer, xs[i % N_INPUT_SETS], n_tokens=T, gather=True, chunks=chunks, out=y_all)
-                        g_ms = timed_steps(lambda i: sharded_forward(layer, xs[i % N_INPUT_SETS], n_tokens=T, gather=True,
-                                                                     chunks=chunks, out=y_all),
-                                           max(5, args.steps // 4), barrier, dev, world) / max(5, args.steps // 4)
-                        recv = (world - 1) * Ts * shape.d_out * y_all.element_size()
-                        gather_info[f"chunks{chunks}"] = {
-                            "ms_per_step": g_ms, "tokens_per_s": T / (g_ms * 1e-3),
-                            "ms_over_compute_only": g_ms - s_ms,
-                            "gather_gbs_per_gpu_if_not_overlapped": recv / max(g_ms - s_ms, 1e-6) / 1e6}
-                    gather_info["bytes_received_per_gpu"] = (world - 1) * Ts * shape.d_out * y_all.element_size()
-                    gather_info["note"] = ("strong-sharded forward + in-place all_gather_into_tensor of y into a [T, d_out] "
-                                           "buffer on every rank, per token chunk on a side stream (sharding.py)")
-                    del y_all
+                    gather_info = time_gathers(layer, xs, T, shape, dtype, dev, rank, world, max(5, args.steps // 4), barrier, s_ms)
 
         # ---------------- per-kernel timing of the two dominant kernels (stage API) ----------------
         kern = per_kernel_times(lib, _lib, layer, shape, dtype, x_dev[0], T, args.path)
@@ -701,6 +746,7 @@ def main():
                 "note": "copy_gbs: each direction alone, all ranks copying at once, pinned buffers"},
         "gpu_launches": int(launches),
         "clocks": clocks,
+        "ranks": per_rank,
     }
     if strong:
         line["strong"] = strong

@@ -111,7 +111,15 @@ typedef struct tmoe_extras {
                             the in-kernel router only (n_experts <= 256, top_k <= 8, r3 <= 256); other
                             combinations return TMOE_ERR_UNSUPPORTED -- use tmoe_rms_norm in front instead. */
   float pre_norm_eps;    /* epsilon of that RMSNorm */
+  int32_t n_peer_y;      /* 0 .. TMOE_MAX_PEERS.  Tensor-core path only (TMOE_ERR_UNSUPPORTED elsewhere): the out-projection
+                            stores every finished output tile to y AND to peer_y[i], i < n_peer_y, each a [T, d_out]
+                            row-major buffer of x's dtype, 16-byte aligned, with rows d_out elements apart -- typically
+                            this rank's rows inside the result buffers of the other GPUs (tmoe_peer_open), so that the
+                            all-gather of y leaves the GPU tile by tile from inside the GEMM; no reference counterpart */
+  int32_t reserved0;
+  void *peer_y[7];
 } tmoe_extras_t;
+#define TMOE_MAX_PEERS 7
 
 /* ABI version of the loaded library (== TMOE_ABI_VERSION of the header it was built from). */
 int tmoe_version(void);
@@ -242,6 +250,26 @@ int64_t tmoe_launch_count(void);
  * take the token tiles that are already finished.  Writes the number of such SMs (0: the hand-over is not used for this
  * call) and the number of token tiles of the waves before the last.  No reference counterpart. */
 int tmoe_handoff_plan(const tmoe_layer_t *layer, int64_t T, int32_t *n_early_sms, int32_t *n_token_tiles);
+
+/* ---- Peer buffers: the all-gather of y across the GPUs of one node (one process per GPU) -------------------------
+ * No reference counterpart (the reference runs on one device).  Every rank allocates its [n_tokens, d_out] result
+ * buffer with tmoe_peer_alloc, the ranks exchange the 64-byte handles through any host channel, each rank opens the
+ * other ranks' buffers with tmoe_peer_open, and after the layer has written a token block into the rank's own buffer
+ * tmoe_peer_push copies that block to the same offset of every peer buffer with the copy engines over NVLink (no SM is
+ * used, so the copies run beside the kernels of the next token block).  Ordering across ranks (every push has landed;
+ * nobody still reads the previous contents) is the caller's: mamba_tuckermoe_b200/sharding.py brackets the pushes
+ * with two one-element NCCL all-reduces.  These four are the only entry points that allocate or map device memory. */
+#define TMOE_PEER_HANDLE_BYTES 64
+/* cudaMalloc of `bytes` (rounded up to 2 MiB) on the current device + its inter-process handle. */
+int tmoe_peer_alloc(int64_t bytes, void **device_ptr, unsigned char handle[TMOE_PEER_HANDLE_BYTES]);
+/* Maps another process's tmoe_peer_alloc buffer (any GPU of the node that the current device can reach over NVLink /
+ * PCIe peer access) into this process; *device_ptr is its base. */
+int tmoe_peer_open(const unsigned char handle[TMOE_PEER_HANDLE_BYTES], void **device_ptr);
+int tmoe_peer_close(void *device_ptr);   /* unmaps a tmoe_peer_open pointer   */
+int tmoe_peer_free(void *device_ptr);    /* frees a tmoe_peer_alloc pointer; synchronises the device */
+/* Enqueues, for i < n_dst, one device-to-device copy of `bytes` bytes from src to dst[i] on streams[i] (cudaStream_t as
+ * void*; the same stream may be given more than once).  Neither waits for nor signals anything else. */
+int tmoe_peer_push(void *const *dst, int32_t n_dst, const void *src, int64_t bytes, void *const *streams);
 
 #ifdef __cplusplus
 }

@@ -12,7 +12,9 @@ LIB_PATH = os.environ.get("TMOE_LIB_PATH") or os.path.join(PKG, "lib", "libtmoe_
 TMOE_F32, TMOE_BF16 = 0, 1
 PATH_AUTO, PATH_SIMT, PATH_TENSOR, PATH_DECODE = 0, 1, 2, 3
 ROUTER_TOPK_SOFTMAX, ROUTER_CAPPED_SOFTMAX = 0, 1
+ERR_UNSUPPORTED = -6
 ERR_DEVICE_WAIT = -9
+MAX_PEERS = 7
 
 # every symbol the header declares; checked when the library is loaded
 EXPORTS = (
@@ -20,7 +22,9 @@ EXPORTS = (
     "tmoe_prepare_factors", "tmoe_workspace_bytes", "tmoe_router", "tmoe_in_core", "tmoe_out",
     "tmoe_forward", "tmoe_read_device_status", "tmoe_launch_count", "tmoe_forward_static_scratch", "tmoe_rms_norm", "tmoe_handoff_plan",
     "tmoe_prepare_factors_prenorm", "tmoe_selftest_bounded_wait", "tmoe_ffn_gate_up",
+    "tmoe_peer_alloc", "tmoe_peer_open", "tmoe_peer_close", "tmoe_peer_free", "tmoe_peer_push",
 )
+PEER_HANDLE_BYTES = 64
 STATIC_SCRATCH_BYTES = 4 << 20
 
 
@@ -39,7 +43,8 @@ class Factors(C.Structure):
 class Extras(C.Structure):
     _fields_ = [("residual", C.c_void_p), ("layer_scale", C.c_void_p), ("idx_out", C.c_void_p),
                 ("gates_out", C.c_void_p), ("c_out", C.c_void_p), ("silu_gate", C.c_void_p),
-                ("pre_norm", C.c_int32), ("pre_norm_eps", C.c_float)]
+                ("pre_norm", C.c_int32), ("pre_norm_eps", C.c_float),
+                ("n_peer_y", C.c_int32), ("reserved0", C.c_int32), ("peer_y", C.c_void_p * 7)]
 
 
 class TmoeError(RuntimeError):
@@ -104,6 +109,17 @@ def load():
         lib.tmoe_selftest_bounded_wait.argtypes = [vp, i64, vp]
         lib.tmoe_handoff_plan.restype = i32
         lib.tmoe_handoff_plan.argtypes = [LP, i64, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]
+        VPP, HP = C.POINTER(vp), C.POINTER(C.c_ubyte)
+        lib.tmoe_peer_alloc.restype = i32
+        lib.tmoe_peer_alloc.argtypes = [i64, VPP, HP]
+        lib.tmoe_peer_open.restype = i32
+        lib.tmoe_peer_open.argtypes = [HP, VPP]
+        lib.tmoe_peer_close.restype = i32
+        lib.tmoe_peer_close.argtypes = [vp]
+        lib.tmoe_peer_free.restype = i32
+        lib.tmoe_peer_free.argtypes = [vp]
+        lib.tmoe_peer_push.restype = i32
+        lib.tmoe_peer_push.argtypes = [VPP, C.c_int32, vp, i64, VPP]
         if lib.tmoe_version() != 1:
             raise RuntimeError("libtmoe_b200.so has an ABI version this binding does not know")
         _lib = lib

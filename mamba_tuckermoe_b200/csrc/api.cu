@@ -111,6 +111,13 @@ int epilogue_from(const tmoe_extras_t *extras, OutEpilogue *epi) {
   epi->residual = extras->residual;
   epi->layer_scale = extras->layer_scale;
   epi->silu_gate = extras->silu_gate;
+  if (extras->n_peer_y < 0 || extras->n_peer_y > TMOE_MAX_PEERS) return TMOE_ERR_SHAPE;
+  epi->n_peers = extras->n_peer_y;
+  for (int i = 0; i < extras->n_peer_y; ++i) {
+    if (!extras->peer_y[i]) return TMOE_ERR_NULL;
+    if (misaligned(extras->peer_y[i])) return TMOE_ERR_ALIGN;
+    epi->peer_y[i] = extras->peer_y[i];
+  }
   return TMOE_OK;
 }
 
@@ -270,6 +277,7 @@ int tmoe_out(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const voi
   if ((rc = epilogue_from(extras, &epi))) return rc;
   int rp = resolve(*layer, T, path, false);
   if (rp < 0) return rp;
+  if (epi.n_peers && rp != TMOE_PATH_TENSOR) return TMOE_ERR_UNSUPPORTED;
   cudaStream_t st = (cudaStream_t)stream;
   if (rp == TMOE_PATH_SIMT)
     return launch_simt_out(*layer, reinterpret_cast<const float *>(z), factors->U_out, factors->bias, epi, T, y, st);
@@ -295,6 +303,7 @@ int tmoe_forward(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const
   const int pre_norm = (extras && extras->pre_norm) ? 1 : 0;
   int rp = resolve(*layer, T, path);
   if (rp < 0) return rp;
+  if (epi.n_peers && rp != TMOE_PATH_TENSOR) return TMOE_ERR_UNSUPPORTED;
   const tmoe_layer_t &L = *layer;
   WsLayout W = ws_layout(L, T, rp);
   if (workspace_bytes < W.total) return TMOE_ERR_WORKSPACE;
@@ -386,7 +395,7 @@ int tmoe_ffn_gate_up(const tmoe_layer_t *layer, const void *prepared_gate, const
   const int64_t half = align_up(W.total, 256);
   if (workspace_bytes < 2 * half) return TMOE_ERR_WORKSPACE;
   if (extras && (extras->residual || extras->layer_scale || extras->silu_gate || extras->idx_out || extras->gates_out ||
-                 extras->c_out))
+                 extras->c_out || extras->n_peer_y))
     return TMOE_ERR_UNSUPPORTED;                             // only the pre-norm applies here
   const int pre_norm = (extras && extras->pre_norm) ? 1 : 0;
   const float pn_eps = pre_norm ? extras->pre_norm_eps : 0.f;

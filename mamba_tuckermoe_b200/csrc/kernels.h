@@ -32,6 +32,8 @@ struct OutEpilogue {
   const void *residual = nullptr;
   const void *layer_scale = nullptr;
   const void *silu_gate = nullptr;
+  int n_peers = 0;                      // tensor-core out-projection only: every tile is also stored to peer_y[i]
+  void *peer_y[TMOE_MAX_PEERS] = {};
 };
 
 // ---- router.cu ----

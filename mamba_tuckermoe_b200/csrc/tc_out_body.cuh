@@ -39,6 +39,20 @@ constexpr int kKernelOut = 3;
 #define TMOE_TOC(i) do { } while (0)
 #endif
 
+// Tensor maps of the further destinations of every output tile (OutParams::n_peers of them are valid): this GPU's rows
+// inside the result buffers of other GPUs, reached through peer mappings.  Same shape and box as the map of y.
+struct PeerMaps {
+  CUtensorMap m[TMOE_MAX_PEERS];
+};
+
+// One finished 32 x 64 staging tile to y and to every peer destination, as one bulk group.
+__device__ __forceinline__ void store_tile_everywhere(const CUtensorMap *tmY, const PeerMaps *pm, int n_peers, uint32_t stage_buf,
+                                                      int c0, int c1) {
+  tma_store_2d(tmY, stage_buf, c0, c1);
+  for (int q = 0; q < n_peers; ++q) tma_store_2d(&pm->m[q], stage_buf, c0, c1);
+  tma_store_commit();
+}
+
 struct OutParams {
   bf16 *y;
   const float *bias;
@@ -51,6 +65,7 @@ struct OutParams {
   // Output columns per tile of the single-CTA kernel: 256 (0 means 256), or 128 when 256-wide tiles would leave more than
   // half of the SMs without one (few token rows); num_n counts tiles of this width and tmB's box has this many rows.
   int on;
+  int n_peers;   // valid entries of the kernel's PeerMaps argument
   int32_t *status;
   // Tile-by-tile hand-over from the kernel that produces A (CTA-pair kernel only; all three null / 0 otherwise).
   //   ready   8 words per 128-row tile of A, each set to `epoch` by one epilogue warp of the producing CTA once its rows
@@ -156,7 +171,7 @@ __device__ __forceinline__ bool rows_ready_wait(const uint32_t *flags, uint32_t 
 // Must be entered by all O_THREADS threads of a CTA that holds O_SMEM_BYTES of dynamic shared memory and no TMEM.
 // A must be complete when `dependent` is false; otherwise the body waits for the kernel before it in the stream.
 __device__ __forceinline__ void tc_out_body(const CUtensorMap *tmA, const CUtensorMap *tmB, const CUtensorMap *tmY,
-                                            const OutParams &p, int tile_first, int tile_step, int tile_end,
+                                            const PeerMaps *pm, const OutParams &p, int tile_first, int tile_step, int tile_end,
                                             uint8_t *smem_raw, bool dependent = false) {
   __shared__ __align__(8) uint64_t bar_full[OSTAGES], bar_empty[OSTAGES], bar_tfull[2], bar_tempty[2];
   __shared__ uint32_t tmem_base_s;
@@ -277,10 +292,7 @@ __device__ __forceinline__ void tc_out_body(const CUtensorMap *tmA, const CUtens
         out_epilogue_chunk(p, r, col0, row, lane, stage_buf);
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0 && col0 < p.N) {
-          tma_store_2d(tmY, stage_buf, col0, m0 + quad * 32);
-          tma_store_commit();
-        }
+        if (lane == 0 && col0 < p.N) store_tile_everywhere(tmY, pm, p.n_peers, stage_buf, col0, m0 + quad * 32);
       }
     }
     if (lane == 0) tma_store_wait_all();

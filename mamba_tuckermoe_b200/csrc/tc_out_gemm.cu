@@ -55,10 +55,10 @@ int encode_tmap_bf16_2d(CUtensorMap *out, const void *base, uint64_t rows, uint6
 
 __global__ void __launch_bounds__(O_THREADS, 1)
 tc_out_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-              const __grid_constant__ CUtensorMap tmY, OutParams p) {
+              const __grid_constant__ CUtensorMap tmY, const __grid_constant__ PeerMaps pm, OutParams p) {
   extern __shared__ uint8_t smem_raw[];
   griddep_launch_dependents();   // all CTAs of this persistent grid are resident: the next kernel may set up on SMs as they free
-  tc_out_body(&tmA, &tmB, &tmY, p, (int)blockIdx.x, (int)gridDim.x, p.num_m * p.num_n, smem_raw, true);
+  tc_out_body(&tmA, &tmB, &tmY, &pm, p, (int)blockIdx.x, (int)gridDim.x, p.num_m * p.num_n, smem_raw, true);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -127,7 +127,7 @@ __device__ __forceinline__ int ticket_of(unsigned long long old, uint32_t epoch,
 template <bool DYN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(O_THREADS, 1)
 tc_out_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                   const __grid_constant__ CUtensorMap tmY, OutParams p) {
+                   const __grid_constant__ CUtensorMap tmY, const __grid_constant__ PeerMaps pm, OutParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[P_STAGES], bar_empty[P_STAGES], bar_tfull[2], bar_tempty[2], bar_sched[P_SCHED];
   __shared__ int tile_ring[P_SCHED];
@@ -322,10 +322,7 @@ tc_out_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         out_epilogue_chunk(p, r, col0, row, lane, stage_buf);
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0 && col0 < p.N) {
-          tma_store_2d(&tmY, stage_buf, col0, m0 + quad * 32);
-          tma_store_commit();
-        }
+        if (lane == 0 && col0 < p.N) store_tile_everywhere(&tmY, &pm, p.n_peers, stage_buf, col0, m0 + quad * 32);
       }
     }
     if (lane == 0) tma_store_wait_all();
@@ -348,7 +345,7 @@ tc_out_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 // kernels do their set-up, then griddep_wait() before they touch anything another kernel produced.
 template <typename Kern>
 static cudaError_t launch_dependent(Kern kern, int grid, int smem, cudaStream_t st, const CUtensorMap &a, const CUtensorMap &b,
-                                    const CUtensorMap &y, const OutParams &p) {
+                                    const CUtensorMap &y, const PeerMaps &pm, const OutParams &p) {
   static const bool off = []() { const char *e = getenv("TMOE_PDL"); return e && atoi(e) == 0; }();
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid); cfg.blockDim = dim3(O_THREADS); cfg.dynamicSmemBytes = (size_t)smem; cfg.stream = st;
@@ -356,7 +353,7 @@ static cudaError_t launch_dependent(Kern kern, int grid, int smem, cudaStream_t 
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at; cfg.numAttrs = off ? 0 : 1;
-  return cudaLaunchKernelEx(&cfg, kern, a, b, y, p);
+  return cudaLaunchKernelEx(&cfg, kern, a, b, y, pm, p);
 }
 
 // CTA pairs for GEMMs with at least two 256x256 tiles per pair of SMs (each CTA then streams 32 KB instead of 48 KB per
@@ -396,6 +393,14 @@ int launch_tc_gemm_bf16(const void *A, const void *B_t, const float *bias, const
   if (rc) return rc;
   rc = encode_tmap_bf16_2d(&tmB, B_t, (uint64_t)N, (uint64_t)K, ON);
   if (rc) return rc;
+  PeerMaps pm;
+  for (int i = 0; i < TMOE_MAX_PEERS; ++i) {   // unused entries repeat y's map: every entry is a valid descriptor
+    if (i < epi.n_peers) {
+      if ((rc = encode_tmap_bf16_2d(&pm.m[i], epi.peer_y[i], (uint64_t)M, (uint64_t)N, 32))) return rc;
+    } else {
+      pm.m[i] = tmY;
+    }
+  }
   static bool attr_done[64] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return TMOE_ERR_CUDA;
@@ -425,6 +430,7 @@ int launch_tc_gemm_bf16(const void *A, const void *B_t, const float *bias, const
     q.T = M; q.N = N; q.K = K;
     q.num_m = (int)((M + 2 * OM - 1) / (2 * OM)); q.num_n = (N + ON - 1) / ON;
     q.status = status;
+    q.n_peers = epi.n_peers;
     if (flags) {
       q.ready = flags->ready; q.epoch = flags->epoch; q.queue = flags->queue;
       q.n_producers = (int)((M + OM - 1) / OM);
@@ -445,8 +451,8 @@ int launch_tc_gemm_bf16(const void *A, const void *B_t, const float *bias, const
     }
     int pairs = dev < 64 ? max_pairs[dev] : sms / 2;
     if (tiles2 < pairs) pairs = tiles2;
-    const cudaError_t le = flags ? launch_dependent(tc_out_pair_kernel<true>, 2 * pairs, P_SMEM_BYTES, st, tmA, tmBh, tmY, q)
-                                 : launch_dependent(tc_out_pair_kernel<false>, 2 * pairs, P_SMEM_BYTES, st, tmA, tmBh, tmY, q);
+    const cudaError_t le = flags ? launch_dependent(tc_out_pair_kernel<true>, 2 * pairs, P_SMEM_BYTES, st, tmA, tmBh, tmY, pm, q)
+                                 : launch_dependent(tc_out_pair_kernel<false>, 2 * pairs, P_SMEM_BYTES, st, tmA, tmBh, tmY, pm, q);
     if (le != cudaSuccess) return TMOE_ERR_CUDA;
     count_launch();
     return launch_status();
@@ -466,9 +472,10 @@ int launch_tc_gemm_bf16(const void *A, const void *B_t, const float *bias, const
     if ((rc = encode_tmap_bf16_2d(&tmB, B_t, (uint64_t)N, (uint64_t)K, (uint32_t)p.on))) return rc;
   }
   p.status = status;
+  p.n_peers = epi.n_peers;
   const int tiles = p.num_m * p.num_n;
   const int grid = tiles < sms ? tiles : sms;
-  if (launch_dependent(tc_out_kernel, grid, O_SMEM_BYTES, st, tmA, tmB, tmY, p) != cudaSuccess) return TMOE_ERR_CUDA;
+  if (launch_dependent(tc_out_kernel, grid, O_SMEM_BYTES, st, tmA, tmB, tmY, pm, p) != cudaSuccess) return TMOE_ERR_CUDA;
   count_launch();
   return launch_status();
 }

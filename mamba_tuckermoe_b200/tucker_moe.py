@@ -431,11 +431,12 @@ class TuckerMoE(nn.Module):
 
     def _fast_forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None,
                       layer_scale: Optional[torch.Tensor] = None, silu_gate: Optional[torch.Tensor] = None,
-                      pre_norm=None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      pre_norm=None, out: Optional[torch.Tensor] = None, peer_ptrs=None) -> torch.Tensor:
         """Eager call without the dispatcher: the same C entry point as the custom op, with the per-call
         Python work cut to a cache lookup (decode-sized calls cost more in Python than on the GPU).
         The optional arguments are those of ``forward_fused`` (``pre_norm`` as a ``(weight, eps)`` pair);
-        ``out`` is an optional contiguous (T, d_out) result buffer."""
+        ``out`` is an optional contiguous (T, d_out) result buffer; ``peer_ptrs`` are device addresses of further
+        (T, d_out) buffers that receive the same result (``tmoe_extras_t.n_peer_y``)."""
         plan = self._plan_for(x)
         if x.shape[-1] != plan.d_in:
             raise RuntimeError(f"tmoe_b200: x has {x.shape[-1]} features, the layer expects {plan.d_in}")
@@ -453,9 +454,15 @@ class TuckerMoE(nn.Module):
         if T:
             lib, dev = plan.lib, plan.dev
             prepared_ptr, force_path, ex_ref, keep = plan.prepared_ptr, None, None, None
-            if residual is not None or silu_gate is not None or pre_norm is not None:
+            if residual is not None or silu_gate is not None or pre_norm is not None or peer_ptrs:
                 ex = Extras()
                 keep = []
+                if peer_ptrs:
+                    if len(peer_ptrs) > _lib.MAX_PEERS:
+                        raise RuntimeError(f"tmoe_b200: at most {_lib.MAX_PEERS} further result buffers")
+                    ex.n_peer_y = len(peer_ptrs)
+                    for i, ptr in enumerate(peer_ptrs):
+                        ex.peer_y[i] = ptr
                 if pre_norm is not None:
                     w, e = pre_norm
                     pn = self._fast_prenorm(plan, x, w, T)
@@ -514,12 +521,15 @@ class TuckerMoE(nn.Module):
         return tucker_moe_forward(x, rw, ui, nw, self.inner_norm.eps, ue, co, uo, b, self.top_k, path=self.path,
                                   prepared=self._prepared_for(x), router=self._router())
 
-    def forward_into(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    def forward_into(self, x: torch.Tensor, out: torch.Tensor, peer_ptrs=None) -> torch.Tensor:
         """``forward`` with the result written into ``out`` (contiguous, (..., d_out), x's dtype and device): lets a
-        caller place the output where the next step wants it, e.g. in its slot of an all-gather buffer."""
+        caller place the output where the next step wants it, e.g. in its slot of an all-gather buffer.  ``peer_ptrs``:
+        device addresses of up to 7 more buffers of out's shape (e.g. the same slot in other GPUs' mapped buffers) that
+        the out-projection writes tile by tile as well; raises ``TmoeError`` with status ``ERR_UNSUPPORTED`` before
+        anything is enqueued when the call does not take the tensor-core path."""
         if not x.is_cuda:
             raise RuntimeError("tmoe_b200: the layer forward runs on CUDA tensors only (no CPU fallback)")
-        self._fast_forward(x, out=out)
+        self._fast_forward(x, out=out, peer_ptrs=peer_ptrs)
         return out
 
     def forward_fused(self, x: torch.Tensor, *, pre_norm=None, residual: Optional[torch.Tensor] = None,

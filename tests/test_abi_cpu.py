@@ -110,6 +110,28 @@ def test_null_and_alignment_errors_before_any_cuda_call():
     assert lib.tmoe_forward(C.byref(L), C.byref(Fbad), None, 4096, 4, 4096, None, 4096, 1 << 20, 1, None) == -4
     ex = _lib.Extras(residual=4096)
     assert lib.tmoe_forward(C.byref(L), C.byref(F), None, 4096, 4, 4096, C.byref(ex), 4096, 1 << 20, 1, None) == -1
+    # further result buffers: count in range, every pointer present and aligned, tensor-core path only
+    ex = _lib.Extras(n_peer_y=8)
+    assert lib.tmoe_forward(C.byref(L), C.byref(F), None, 4096, 4, 4096, C.byref(ex), 4096, 1 << 20, 1, None) == -2
+    ex = _lib.Extras(n_peer_y=2)
+    ex.peer_y[0] = 4096
+    assert lib.tmoe_forward(C.byref(L), C.byref(F), None, 4096, 4, 4096, C.byref(ex), 4096, 1 << 20, 1, None) == -1
+    ex.peer_y[1] = 4100
+    assert lib.tmoe_forward(C.byref(L), C.byref(F), None, 4096, 4, 4096, C.byref(ex), 4096, 1 << 20, 1, None) == -4
+    ex.peer_y[1] = 8192
+    assert lib.tmoe_forward(C.byref(L), C.byref(F), None, 4096, 4, 4096, C.byref(ex), 4096, 1 << 20, 1, None) == -6
+
+
+def test_peer_buffer_entry_points_validate():
+    lib = _lib.load()
+    p, h = C.c_void_p(), (C.c_ubyte * _lib.PEER_HANDLE_BYTES)()
+    assert lib.tmoe_peer_alloc(0, C.byref(p), h) == -2
+    assert lib.tmoe_peer_alloc(1 << 20, None, h) == -1
+    assert lib.tmoe_peer_open(None, C.byref(p)) == -1
+    assert lib.tmoe_peer_close(None) == -1 and lib.tmoe_peer_free(None) == -1
+    assert lib.tmoe_peer_push(None, 0, None, 0, None) == 0
+    assert lib.tmoe_peer_push(None, 2, None, 64, None) == -1
+    assert lib.tmoe_peer_push(None, -1, None, 64, None) == -2
 
 
 def test_path_resolution_and_sizes():

@@ -307,6 +307,39 @@ def test_one_launch_decode_forward(shape, T):
     assert rel_fro(fused.cpu(), expect.cpu()) < 1e-2
 
 
+@pytest.mark.parametrize("shape,T", [
+    (LayerShape(256, 264, 8, 2, 4, 128, 256, 1e-5), 300),       # single-CTA GEMM, ragged last tile, d_out not a multiple of 64
+    (LayerShape(1536, 2304, 64, 2, 4, 256, 1024, 1e-6), 20000),  # CTA pairs, ragged last tile
+])
+def test_out_projection_writes_every_destination(shape, T):
+    """tmoe_extras_t.peer_y: the out-projection stores each tile to y and to the further buffers (here on the same GPU;
+    across GPUs they are the peers' mapped result buffers).  Rows beyond T of a destination stay untouched."""
+    from mamba_tuckermoe_b200 import _lib
+    x, f = _tensor_case(shape, T, seed=31 + T)
+    m = build_module(shape, f, torch.bfloat16, path=PATH_AUTO)
+    xd = x.cuda()
+    ref = m(xd)
+    out = torch.empty_like(ref)
+    big = [torch.full((T + 40, shape.d_out), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(_lib.MAX_PEERS)]
+    for n in (1, 3, _lib.MAX_PEERS):
+        for b in big:
+            b.fill_(float("nan"))
+        m.forward_into(xd, out, peer_ptrs=[b.data_ptr() for b in big[:n]])
+        torch.cuda.synchronize()
+        assert torch.equal(out, ref)
+        for i, b in enumerate(big):
+            if i < n:
+                assert torch.equal(b[:T], ref) and bool(torch.isnan(b[T:]).all())
+            else:
+                assert bool(torch.isnan(b).all())
+    assert read_device_status() == (0, 0, 0, 0)
+    # the other paths refuse before anything is enqueued
+    small = build_module(shape, f, torch.bfloat16, path=PATH_DECODE)
+    with pytest.raises(_lib.TmoeError) as e:
+        small.forward_into(xd[:4], out[:4], peer_ptrs=[big[0].data_ptr()])
+    assert e.value.status == _lib.ERR_UNSUPPORTED
+
+
 @pytest.mark.parametrize("name", BF16_CASES)
 def test_decode_path_matches_reference_golden(name):
     shape, x, f, dtype, g = load_case(name)

@@ -95,3 +95,13 @@ def test_two_rank_shard_and_gather(n_tokens, chunks):
     ret = mgr.dict()
     mp.spawn(_worker, args=(world, port, n_tokens, chunks, ret), nprocs=world, join=True)
     assert all(ret.get(r) for r in range(world)), dict(ret)
+
+
+def test_in_kernel_gather_rule():
+    """The GEMM writes the peers' buffers itself only with one peer and a contraction deep enough to hide the stores."""
+    from types import SimpleNamespace as NS
+    from mamba_tuckermoe_b200.sharding import in_kernel_gather_pays
+    deep, shallow = NS(U_out=torch.empty(2048, 8)), NS(U_out=torch.empty(1024, 8))
+    assert in_kernel_gather_pays(deep, 2) and not in_kernel_gather_pays(deep, 4)
+    assert not in_kernel_gather_pays(shallow, 2)
+    assert not in_kernel_gather_pays(lambda x: x, 2)
