@@ -437,12 +437,20 @@ def run_strong_only(args, layer, shape, dtype, seed, T, rank, world, dev, zipf, 
         dist.destroy_process_group()
 
 
+SPIN_UP_STEPS = 3
+
+
 def timed_steps(fn, steps, barrier, dev, world, detail=None):
     """CUDA-event time of `steps` calls of fn(i) bracketed by a barrier + synchronize on both sides; max over ranks (ms).
-    `detail` (a dict) receives every rank's device time and the host time each rank spent enqueueing the steps."""
+    SPIN_UP_STEPS untimed calls run between the opening barrier and the first event: the GPU leaves the barrier idle, and a
+    region of a few milliseconds otherwise measures its way back to the working clocks (seen on 8 GPUs: 0.29 ms per step
+    over 20 steps against 0.21 ms over 200).  `detail` (a dict) receives every rank's device time and the host time each
+    rank spent enqueueing the steps."""
     import torch.distributed as dist
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    for i in range(SPIN_UP_STEPS):
+        fn(steps - SPIN_UP_STEPS + i)
     ev0.record()
     h0 = time.perf_counter()
     for i in range(steps):
@@ -733,7 +741,9 @@ def main():
                    "sharding": f"tokens x{world}, factors replicated, no collective",
                    "l2": f"{N_INPUT_SETS} rotating input sets; x+z+y per step = "
                          f"{(T * (shape.d_in + 2 * shape.r2 + shape.d_out) * 2) / 1e6:.0f} MB > 126 MB L2",
-                   "path": {0: "auto", 1: "cuda-core", 2: "tensor-core"}[args.path]},
+                   "path": {0: "auto", 1: "cuda-core", 2: "tensor-core"}[args.path],
+                   "timing": f"CUDA events around exactly {args.steps} steps; {SPIN_UP_STEPS} untimed steps run directly in front "
+                             "of the first event, after the barrier"},
         "layer_tflops": value * flops_tok / 1e12 / world,
         "layer_frac_of_bf16_peak": value * flops_tok / 1e12 / world / peak_tf,
         "flops_per_token": flops_tok,
