@@ -677,6 +677,14 @@ class TuckerMoE(nn.Module):
         self._prep_key, self._prep, self._plan = None, None, None
         self._prep_pn_key, self._prep_pn = None, None
 
+    def __getstate__(self):
+        """Copies and pickles carry the parameters, not what was derived from them (C structs, prepared buffers)."""
+        state = self.__dict__.copy()
+        for k in ("_plan", "_prep", "_prep_key", "_prep_pn", "_prep_pn_key"):
+            if k in state:
+                state[k] = None
+        return state
+
 
 def fused_out_proj(out_proj: TuckerMoE, mid: torch.Tensor, norm, layer_scale: torch.Tensor) -> torch.Tensor:
     """``mid + gamma * out_proj(norm(mid))`` -- the tail of the reference's Mamba block (``model.py:258-260``)

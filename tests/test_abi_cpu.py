@@ -189,3 +189,18 @@ def test_fake_kernel_gives_shapes_without_a_gpu():
                                         torch.empty(8, 4), torch.empty(4, 32, 64), torch.empty(64, 96),
                                         torch.empty(96), 2, 0, None, None, None, None, 0, 10.0, 0.5)
     assert y.shape == (2, 5, 96)
+
+
+def test_module_copies_and_pickles_without_its_caches():
+    import copy
+    import pickle
+    import torch
+    from mamba_tuckermoe_b200 import TuckerMoE, TuckerMoEConfig
+    m = TuckerMoE(64, 72, TuckerMoEConfig(8, 2, 4, 64, 64, 1e-5))
+    with torch.no_grad():
+        for q in m.parameters():
+            q.normal_()
+    m._plan = object()          # stands for the C structs a CUDA call leaves behind
+    for c in (copy.deepcopy(m), pickle.loads(pickle.dumps(m))):
+        assert c._plan is None
+        assert all(torch.equal(a, b) for a, b in zip(c.state_dict().values(), m.state_dict().values()))
