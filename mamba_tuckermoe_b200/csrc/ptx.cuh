@@ -162,6 +162,25 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap *m, uint32_t src_
                "r"(src_smem), "r"(c0), "r"(c1)
                : "memory");
 }
+// 256-bit store to global memory (32-byte aligned address): one request for a whole 32-byte sector.
+__device__ __forceinline__ void st_global_256(void *dst, const uint4 &lo, const uint4 &hi) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w),
+               "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w)
+               : "memory");
+}
+// The same store with an L2 eviction-priority hint (a createpolicy value): evict_first for output that nothing on this
+// GPU reads again soon.
+__device__ __forceinline__ void tma_store_2d_hint(const CUtensorMap *m, uint32_t src_smem, int c0, int c1, uint64_t policy) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;" ::"l"(
+                   reinterpret_cast<uint64_t>(m)),
+               "r"(src_smem), "r"(c0), "r"(c1), "l"(policy)
+               : "memory");
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Wait until at most N of this thread's store groups still have to READ their shared-memory source.
 template <int N>

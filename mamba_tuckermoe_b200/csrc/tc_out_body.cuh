@@ -46,9 +46,12 @@ struct PeerMaps {
 };
 
 // One finished 32 x 64 staging tile to y and to every peer destination, as one bulk group.
+// stream_y: y is larger than L2 can hold next to the operands, so its lines are marked evict-first (measured on the
+// 16384 x 512 x 4608 out-projection: 68.9 us against 72.5 us; no difference at K = 1024).
 __device__ __forceinline__ void store_tile_everywhere(const CUtensorMap *tmY, const PeerMaps *pm, int n_peers, uint32_t stage_buf,
-                                                      int c0, int c1) {
-  tma_store_2d(tmY, stage_buf, c0, c1);
+                                                      int c0, int c1, bool stream_y) {
+  if (stream_y) tma_store_2d_hint(tmY, stage_buf, c0, c1, l2_policy_evict_first());
+  else tma_store_2d(tmY, stage_buf, c0, c1);
   for (int q = 0; q < n_peers; ++q) tma_store_2d(&pm->m[q], stage_buf, c0, c1);
   tma_store_commit();
 }
@@ -66,6 +69,7 @@ struct OutParams {
   // half of the SMs without one (few token rows); num_n counts tiles of this width and tmB's box has this many rows.
   int on;
   int n_peers;   // valid entries of the kernel's PeerMaps argument
+  int stream_y;  // y does not fit in L2: store it with the evict-first hint
   int32_t *status;
   // Tile-by-tile hand-over from the kernel that produces A (CTA-pair kernel only; all three null / 0 otherwise).
   //   ready   8 words per 128-row tile of A, each set to `epoch` by one epilogue warp of the producing CTA once its rows
@@ -79,24 +83,37 @@ struct OutParams {
   int n_producers;
 };
 
+// The bias of a warp's share of an output tile, one float4 per lane: lane l holds columns [cbase + 4 l, cbase + 4 l + 4).
+// Loaded once per tile BEFORE the wait for the accumulator, so its trip to L2 (the SM's L1 is almost entirely shared
+// memory here) is off the epilogue's chain; the chunks then fetch their values from the owning lanes by shuffle.
+__device__ __forceinline__ float4 load_bias_lane(const OutParams &p, int cbase, int lane) {
+  const int col = cbase + lane * 4;
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  // volatile: a plain __ldg is sunk by the compiler to its first use, i.e. behind the wait it is meant to overlap
+  if (p.bias && col < p.N)
+    asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p.bias + col));
+  return v;
+}
+
 // Epilogue of one 64-column chunk of an output row: accumulator registers r (two 32-column TMEM loads) + bias, optional
 // silu(gate) * v and residual + layer_scale * v, rounded to bf16 into this lane's 128-byte row of the warp's staging
-// tile (16-byte chunks XOR-swizzled as the TMA box expects).  The shared stores carry no "memory" clobber: the staging
+// tile (16-byte chunks XOR-swizzled as the TMA box expects).  `bias_lane` is load_bias_lane() of the warp's column base
+// and col0 - cbase = `cofs` (a multiple of 64).  The shared stores carry no "memory" clobber: the staging
 // tile is touched by nothing else the compiler sees, volatile asm statements keep their order, and the proxy fence
-// that follows is the barrier.  With the clobber every store pinned the next group's bias loads behind it and the
-// chunk became a chain of sixteen load latencies (out-projection with K = 512: 118 -> measured below in the callers).
+// that follows is the barrier.  Must be entered by all 32 lanes (shuffles).
 __device__ __forceinline__ void out_epilogue_chunk(const OutParams &p, const uint32_t (&r)[2][32], int col0, int64_t row,
-                                                   int lane, uint32_t stage_buf) {
+                                                   int lane, uint32_t stage_buf, const float4 &bias_lane, int cofs) {
   const bool extras = (p.silu_gate != nullptr) | (p.residual != nullptr);
 #pragma unroll
   for (int h2 = 0; h2 < 2; ++h2) {
-    // the half's 32 bias values first, so that their loads are in flight together (N % 8 == 0: a group of 8 columns
-    // is entirely in or out; columns >= N are clipped by the store, their values do not matter)
     float4 b[8];
 #pragma unroll
     for (int g = 0; g < 8; ++g) {
-      const int col = col0 + h2 * 32 + g * 4;
-      b[g] = (p.bias && col < p.N) ? __ldg(reinterpret_cast<const float4 *>(p.bias + col)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      const int src = (cofs >> 2) + h2 * 8 + g;   // the lane that holds this group of four columns
+      b[g].x = __shfl_sync(0xffffffffu, bias_lane.x, src);
+      b[g].y = __shfl_sync(0xffffffffu, bias_lane.y, src);
+      b[g].z = __shfl_sync(0xffffffffu, bias_lane.z, src);
+      b[g].w = __shfl_sync(0xffffffffu, bias_lane.w, src);
     }
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
@@ -264,6 +281,7 @@ __device__ __forceinline__ void tc_out_body(const CUtensorMap *tmA, const CUtens
     for (int tile = tile_first; tile < tile_end && ok; tile += tile_step, ++tcount) {
       const int m0 = (tile / p.num_n) * OM, n0 = (tile % p.num_n) * on;
       const uint32_t slot = tcount & 1, aph = (tcount >> 1) & 1;
+      const float4 bias_lane = load_bias_lane(p, n0 + half * (on >> 1), lane);
       TMOE_TIC();
       ok = mbar_wait(smem_u32(&bar_tfull[slot]), aph, p.status, kKernelOut, 3);
       if (threadIdx.x == 64) TMOE_TOC(3);  // epilogue warp 2 waiting for a finished accumulator
@@ -289,10 +307,10 @@ __device__ __forceinline__ void tc_out_body(const CUtensorMap *tmA, const CUtens
         if (lane == 0) tma_store_wait_read<0>();  // the previous store has finished reading the staging tile
         if (threadIdx.x == 64) TMOE_TOC(4);  // epilogue warp 2 waiting for its previous TMA store
         __syncwarp();
-        out_epilogue_chunk(p, r, col0, row, lane, stage_buf);
+        out_epilogue_chunk(p, r, col0, row, lane, stage_buf, bias_lane, cc * 64);
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0 && col0 < p.N) store_tile_everywhere(tmY, pm, p.n_peers, stage_buf, col0, m0 + quad * 32);
+        if (lane == 0 && col0 < p.N) store_tile_everywhere(tmY, pm, p.n_peers, stage_buf, col0, m0 + quad * 32, p.stream_y != 0);
       }
     }
     if (lane == 0) tma_store_wait_all();

@@ -299,7 +299,10 @@ tc_out_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       if (tile < 0) break;
       const int m0 = (tile / p.num_n) * (2 * OM) + (int)rank * OM, n0 = (tile % p.num_n) * ON;
       const uint32_t slot = tcount & 1, aph = (tcount >> 1) & 1;
+      const float4 bias_lane = load_bias_lane(p, n0 + half * 128, lane);
+      TMOE_TIC();
       ok = mbar_wait(smem_u32(&bar_tfull[slot]), aph, p.status, kKernelOutPair, 3);
+      if (threadIdx.x == 64) TMOE_TOC(5);  // epilogue warp 2 waiting for a finished accumulator
       ok = __all_sync(0xffffffffu, ok);  // the TMEM loads below are warp-collective
       if (!ok) break;
       tc_fence_after();
@@ -309,20 +312,26 @@ tc_out_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       for (int cc = 0; cc < 2; ++cc) {
         const int col0 = n0 + half * 128 + cc * 64;
         uint32_t r[2][32];
+        TMOE_TIC();
         tmem_ld32(t_row + cc * 64, r[0]);
         tmem_ld32(t_row + cc * 64 + 32, r[1]);
         tmem_ld_wait(r[0], r[1]);
+        if (threadIdx.x == 64) TMOE_TOC(3);  // epilogue warp 2: TMEM load round trip
         if (cc == 1) {  // this warp has read its whole share of the accumulator
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&bar_tempty[slot]), 0));  // the MMA thread lives in CTA 0
         }
+        TMOE_TIC();
         if (lane == 0) tma_store_wait_read<0>();  // the previous store has finished reading the staging tile
+        if (threadIdx.x == 64) TMOE_TOC(4);  // epilogue warp 2 waiting for its previous TMA store
         __syncwarp();
-        out_epilogue_chunk(p, r, col0, row, lane, stage_buf);
+        TMOE_TIC();
+        out_epilogue_chunk(p, r, col0, row, lane, stage_buf, bias_lane, cc * 64);
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0 && col0 < p.N) store_tile_everywhere(&tmY, &pm, p.n_peers, stage_buf, col0, m0 + quad * 32);
+        if (threadIdx.x == 64) TMOE_TOC(6);  // epilogue warp 2: bias / tail / staging of one 64-column chunk
+        if (lane == 0 && col0 < p.N) store_tile_everywhere(&tmY, &pm, p.n_peers, stage_buf, col0, m0 + quad * 32, p.stream_y != 0);
       }
     }
     if (lane == 0) tma_store_wait_all();
@@ -359,6 +368,9 @@ static cudaError_t launch_dependent(Kern kern, int grid, int smem, cudaStream_t 
 // CTA pairs for GEMMs with at least two 256x256 tiles per pair of SMs (each CTA then streams 32 KB instead of 48 KB per
 // k block and the ring is six stages deep: 112 us against 119 us on the prefill configuration); smaller GEMMs keep the
 // single-CTA kernel, whose 128-row tiles cover more SMs.  TMOE_OUT_PAIRS=0 / 1 forces the choice.
+// An output beyond this size cannot stay in the 126 MB L2 next to the operands: it is stored with the evict-first hint.
+constexpr int64_t kStreamYBytes = 96ll << 20;
+
 bool tc_gemm_uses_pairs(int64_t M, int N, int sms) {
   static const int pairs_env = []() { const char *e = getenv("TMOE_OUT_PAIRS"); return e ? (atoi(e) != 0 ? 1 : 0) : -1; }();
   const int64_t tiles256 = ((M + 2 * OM - 1) / (2 * OM)) * ((N + ON - 1) / ON);
@@ -431,6 +443,7 @@ int launch_tc_gemm_bf16(const void *A, const void *B_t, const float *bias, const
     q.num_m = (int)((M + 2 * OM - 1) / (2 * OM)); q.num_n = (N + ON - 1) / ON;
     q.status = status;
     q.n_peers = epi.n_peers;
+    q.stream_y = (int64_t)M * N * 2 > kStreamYBytes;
     if (flags) {
       q.ready = flags->ready; q.epoch = flags->epoch; q.queue = flags->queue;
       q.n_producers = (int)((M + OM - 1) / OM);
@@ -473,6 +486,7 @@ int launch_tc_gemm_bf16(const void *A, const void *B_t, const float *bias, const
   }
   p.status = status;
   p.n_peers = epi.n_peers;
+  p.stream_y = (int64_t)M * N * 2 > kStreamYBytes;
   const int tiles = p.num_m * p.num_n;
   const int grid = tiles < sms ? tiles : sms;
   if (launch_dependent(tc_out_kernel, grid, O_SMEM_BYTES, st, tmA, tmB, tmY, pm, p) != cudaSuccess) return TMOE_ERR_CUDA;
