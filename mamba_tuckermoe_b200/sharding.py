@@ -98,21 +98,42 @@ class PeerBuffers:
         self._stride = -(-max(1, n_tokens) * self.row_bytes // 256) * 256     # bytes between the two buffers
         nbytes = self._stride * buffers
         with torch.cuda.device(self.device):
+            # every step that can fail on one rank alone is followed by an agreement of all ranks, so that a failure raises
+            # everywhere instead of leaving the others inside a collective
             own, handle = C.c_void_p(), (C.c_ubyte * _lib.PEER_HANDLE_BYTES)()
-            _lib.check(lib.tmoe_peer_alloc(nbytes, C.byref(own), handle), "tmoe_peer_alloc")
-            self._base = own.value
+            rc = lib.tmoe_peer_alloc(nbytes, C.byref(own), handle)
+            self._base = own.value if rc == 0 else None
             handles = [None] * self.world
-            dist.all_gather_object(handles, bytes(handle), group=group)
+            dist.all_gather_object(handles, bytes(handle) if rc == 0 else None, group=group)
             # the peers in the order rank+1, rank+2, ...: when every rank copies to its peers in this order, one after the
             # other, each GPU receives from one sender at a time.  Measured on 4 B200s (302 MB per copy): 748 GB/s leave
             # every GPU this way, 369-388 GB/s when the copies to all peers run at once or all ranks start with rank 0.
             self.peer_ranks = [(self.rank + k) % self.world for k in range(1, self.world)]
             self._peer_base = []
-            for r in self.peer_ranks:
-                p = C.c_void_p()
-                h = (C.c_ubyte * _lib.PEER_HANDLE_BYTES).from_buffer_copy(handles[r])
-                _lib.check(lib.tmoe_peer_open(h, C.byref(p)), f"tmoe_peer_open(rank {r})")
-                self._peer_base.append(p.value)
+            failed = "tmoe_peer_alloc" if rc else None
+            if all(h is not None for h in handles):
+                for r in self.peer_ranks:
+                    p = C.c_void_p()
+                    h = (C.c_ubyte * _lib.PEER_HANDLE_BYTES).from_buffer_copy(handles[r])
+                    rc = lib.tmoe_peer_open(h, C.byref(p))
+                    if rc:
+                        failed = f"tmoe_peer_open(rank {r})"
+                        break
+                    self._peer_base.append(p.value)
+            elif failed is None:
+                failed = "tmoe_peer_alloc on another rank"
+            verdicts = [None] * self.world
+            dist.all_gather_object(verdicts, failed, group=group)
+            if any(v is not None for v in verdicts):
+                for p in self._peer_base:
+                    lib.tmoe_peer_close(p)
+                self._peer_base = []
+                dist.barrier(group=group)
+                if self._base is not None:
+                    lib.tmoe_peer_free(self._base)
+                    self._base = None
+                raise RuntimeError("PeerBuffers: mapping the result buffers across the ranks failed: " +
+                                   "; ".join(f"rank {r}: {v}" for r, v in enumerate(verdicts) if v is not None))
             flat = torch.as_tensor(_DevicePointer(self._base, nbytes), device=self.device)
             self._outs = [flat[i * self._stride:i * self._stride + n_tokens * self.row_bytes].view(dtype).view(n_tokens, d_out)
                           for i in range(buffers)]
@@ -157,6 +178,17 @@ class PeerBuffers:
         rendezvous has finished."""
         with torch.cuda.stream(stream):
             dist.all_reduce(self._token, group=self.group)
+
+    def __del__(self):
+        # not a substitute for close() (which agrees with the other ranks first): last-resort release of this rank's memory
+        try:
+            if getattr(self, "_base", None) is not None:
+                for p in self._peer_base:
+                    self._lib.tmoe_peer_close(p)
+                self._lib.tmoe_peer_free(self._base)
+                self._base = None
+        except Exception:
+            pass
 
     def close(self) -> None:
         if self._base is None:

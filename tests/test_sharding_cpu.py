@@ -105,3 +105,40 @@ def test_in_kernel_gather_rule():
     assert in_kernel_gather_pays(deep, 2) and not in_kernel_gather_pays(deep, 4)
     assert not in_kernel_gather_pays(shallow, 2)
     assert not in_kernel_gather_pays(lambda x: x, 2)
+
+
+def _peer_failure_worker(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import contextlib
+        from mamba_tuckermoe_b200 import sharding
+        # no GPU here: the allocation fails on every rank; what is checked is that all ranks leave the constructor with
+        # the same error after the same collectives (nobody is left waiting) and that the group still works afterwards
+        real = torch.cuda.device
+        torch.cuda.device = lambda d: contextlib.nullcontext()
+        try:
+            try:
+                sharding.PeerBuffers(64, 96, torch.bfloat16, torch.device("cuda", 0))
+                ret[rank] = "constructed"
+            except RuntimeError as e:
+                ret[rank] = str(e)
+        finally:
+            torch.cuda.device = real
+        t = torch.ones(1)
+        dist.all_reduce(t)
+        ret[f"sum{rank}"] = float(t)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="needs a machine on which the device allocation fails")
+def test_peer_buffers_fail_on_every_rank_alike():
+    world = 2
+    port = 29500 + (os.getpid() + 911) % 2000
+    ret = mp.Manager().dict()
+    mp.spawn(_peer_failure_worker, args=(world, port, ret), nprocs=world, join=True)
+    for r in range(world):
+        assert "tmoe_peer_alloc" in ret[r] and "rank 0" in ret[r] and "rank 1" in ret[r], dict(ret)
+        assert ret[f"sum{r}"] == world
