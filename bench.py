@@ -944,7 +944,7 @@ def per_kernel_times(lib, _lib, layer, shape, dtype, x, T, path, reps=20):
     f_in = T * (2 * shape.d_in * shape.r3 + 2 * shape.r3 * shape.r1 * shape.r2 + 2 * shape.r1 * shape.r2)
     f_out = T * 2 * shape.r2 * shape.d_out
     allk = {
-        "router_cuda_core": {"us": us_router, "bytes": T * shape.d_in * x.element_size(),
+        "router_standalone": {"us": us_router, "bytes": T * shape.d_in * x.element_size(),
                              "gbs": T * shape.d_in * x.element_size() / us_router / 1e3},
         "in_core": {"us": us_incore, "flops": f_in, "tflops": f_in / us_incore / 1e6},
         "out_gemm": {"us": us_out, "flops": f_out, "tflops": f_out / us_out / 1e6},

@@ -365,10 +365,16 @@ int tmoe_forward(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const
                            taps ? extras->idx_out : nullptr,
                            taps ? extras->gates_out : nullptr, taps ? extras->c_out : nullptr, z, status, st, fp);
   } else {
-    // scores = x @ router_w^T on the tensor cores (bf16 out = the reference's rounding), then the select kernel
-    if ((rc = launch_tc_gemm_bf16(x, pb + P.wr_b, nullptr, OutEpilogue{}, T, P.e_pad, L.d_in, scores, status, st)))
-      return rc;
-    if ((rc = launch_select_bf16_scores(L, scores, P.e_pad, factors->U_expert, T, idx, gates, c, st))) return rc;
+    // the router as a kernel of its own.  Up to 256 experts and top-8 (layers whose r3 = 512 leaves no TMEM columns for the
+    // scores next to h): the persistent router kernel, scores never leave the SM.  Beyond that: scores = x @ router_w^T as
+    // a GEMM (bf16 out = the reference's rounding), then the select kernel.
+    rc = launch_tc_router(L, x, factors->router_w, factors->U_expert, T, idx, gates, c, status, st);
+    if (rc == TMOE_ERR_UNSUPPORTED) {
+      if ((rc = launch_tc_gemm_bf16(x, pb + P.wr_b, nullptr, OutEpilogue{}, T, P.e_pad, L.d_in, scores, status, st)))
+        return rc;
+      rc = launch_select_bf16_scores(L, scores, P.e_pad, factors->U_expert, T, idx, gates, c, st);
+    }
+    if (rc) return rc;
     // c_work may alias c: every row is read by its own thread before that thread overwrites it
     rc = launch_tc_in_core(L, x, prepared, P, T, 0, 0.f, 0, c, reinterpret_cast<float *>(ws + W.c), in_core_c_blocks(T), nullptr, nullptr, nullptr, z,
                            status, st, fp);

@@ -104,10 +104,6 @@ __device__ __forceinline__ uint4 ldg_early(const void *ptr) {
   asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr));
   return v;
 }
-// Ask L2 for [ptr, ptr + bytes): one instruction for a whole row piece (ptr 16-byte aligned, bytes a multiple of 16).
-__device__ __forceinline__ void l2_prefetch_bulk(const void *ptr, int bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ptr), "r"(bytes) : "memory");
-}
 __device__ __forceinline__ void cp_async_4(uint32_t smem_addr, const void *g) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_addr), "l"(g) : "memory");
 }
@@ -223,7 +219,7 @@ __global__ void __launch_bounds__(kFThreads, 1) decode_fused_kernel(const FusedP
       for (int n = gw; n < hcols; n += cw) {
         const bf16 *row = (n < p.r3) ? p.uin_t + (int64_t)n * p.d_in : p.wr + (int64_t)(n - p.r3) * p.d_in;
         const int from = (n < gw + NR1 * cw) ? B1 * 256 : 0;   // elements of the row already on their way to registers
-        if (from < p.d_in) l2_prefetch_bulk(row + from, (p.d_in - from) * 2);
+        if (from < p.d_in) ptx::l2_prefetch_bulk(row + from, (p.d_in - from) * 2);
       }
     }
     for (int it = gw; it < kc * G; it += cw) {
@@ -231,9 +227,9 @@ __global__ void __launch_bounds__(kFThreads, 1) decode_fused_kernel(const FusedP
       const int s = k0 + s_loc;
       const int j = s / N2, sl = s - j * N2;
       const bf16 *rows = p.g_t + ((int64_t)j * 256 + sl) * p.r3 + (int64_t)(g * AC) * N2 * p.r3;
-      if (lane < AC) l2_prefetch_bulk(rows + (int64_t)lane * N2 * p.r3, p.r3 * 2);
+      if (lane < AC) ptx::l2_prefetch_bulk(rows + (int64_t)lane * N2 * p.r3, p.r3 * 2);
     }
-    for (int n = n_first; n < n_end; n += kFThreads) l2_prefetch_bulk(p.uout_t + (int64_t)n * p.r2 + k0, kc * 2);
+    for (int n = n_first; n < n_end; n += kFThreads) ptx::l2_prefetch_bulk(p.uout_t + (int64_t)n * p.r2 + k0, kc * 2);
   }
   TMOE_DSTAMP(1);
   ptx::griddep_wait();  // x (and the partial / counter words of the workspace) may belong to the kernel before this one

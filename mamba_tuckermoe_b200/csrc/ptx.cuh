@@ -162,6 +162,10 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap *m, uint32_t src_
                "r"(src_smem), "r"(c0), "r"(c1)
                : "memory");
 }
+// Ask L2 for [ptr, ptr + bytes): one instruction for a whole contiguous piece (ptr 16-byte aligned, bytes a multiple of 16).
+__device__ __forceinline__ void l2_prefetch_bulk(const void *ptr, int bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ptr), "r"(bytes) : "memory");
+}
 // 256-bit store to global memory (32-byte aligned address): one request for a whole 32-byte sector.
 __device__ __forceinline__ void st_global_256(void *dst, const uint4 &lo, const uint4 &hi) {
   asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w),

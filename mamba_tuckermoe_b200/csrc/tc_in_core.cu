@@ -52,7 +52,7 @@ constexpr int IC_EPI_WARPS = 8;
 constexpr int IC_THREADS = (2 + IC_EPI_WARPS) * 32;
 constexpr int IC_RING_BYTES = 224 * 1024;
 constexpr int IC_SMEM_BYTES = IC_RING_BYTES + 1024;
-constexpr int A_STAGES_MAX = 8;   // 4 fit with the U_in tile in the stage; the router-only mode (x + router tile) uses all 8
+constexpr int A_STAGES_MAX = 8;   // 4 stages fit at r3 = 256 (48-56 KB each); layers with a narrower U_in tile get up to 8
 constexpr int SCORE_COL = 256;  // TMEM column of the router scores during phase A
 constexpr int kKernelInCore = 2;
 
@@ -61,8 +61,6 @@ struct InCoreParams {
   int d_in, r3, r2, E, e_pad, top_k, n_tiles2;
   float eps;
   int fuse_router;
-  int router_only;     // 1: stop after the routing (stand-alone router: scores by the tensor cores, idx / gates / c out; no U_in, no core)
-  int uexp_bf16;       // 1: uexp points at the layer's own bf16 U_expert instead of the prepared fp32 copy
   int pre_norm;        // 1: apply the callers' RMSNorm to x in-kernel (its weight is folded into the prepared U_in / router rows)
   float pre_norm_eps;
   RouterCfg rc;  // gate rule (tmoe_layer_t::router_mode)
@@ -92,7 +90,7 @@ struct InCoreParams {
 // stages deep, and starves (measured 2300 cycles per k block against 1024 of tensor-pipe time), so h is made in two passes
 // over K, each streaming x again (from L2) with one 256-row piece of U_in^T: 48 KB stages, four deep.  SCORES: the router
 // tile follows U_in^T in the stage and a second, N = e_pad MMA accumulates the scores at TMEM column SCORE_COL.
-template <bool TWO_BOX, bool SCORES, bool HACC = true>
+template <bool TWO_BOX, bool SCORES>
 __device__ __forceinline__ void issue_phase_a(uint32_t tmem_base, uint64_t desc0, uint32_t stage16, uint32_t u16, int KA, int nA,
                                               int u_box_rows, int e_pad, uint64_t *bar_full, uint64_t *bar_empty, int32_t *status) {
   const uint32_t idescH = umma_idesc_bf16(TM, u_box_rows);
@@ -109,7 +107,7 @@ __device__ __forceinline__ void issue_phase_a(uint32_t tmem_base, uint64_t desc0
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         const uint32_t acc = acc0 | (uint32_t)(k != 0);
-        if (HACC) umma_bf16(d_h, dx + 2 * k, du + 2 * k, idescH, acc);
+        umma_bf16(d_h, dx + 2 * k, du + 2 * k, idescH, acc);
         if (SCORES) umma_bf16(tmem_base + SCORE_COL, dx + 2 * k, dw + 2 * k, idescS, acc);
       }
       umma_commit(smem_u32(&bar_empty[sA]));
@@ -156,7 +154,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
 
   const int u_boxes = (p.r3 + 255) / 256;         // U_in^T is streamed in pieces of <= 256 rows, one pass over K per piece
   const int u_box_rows = p.r3 / u_boxes;
-  const int u_bytes = p.router_only ? 0 : u_box_rows * 128, w_bytes = p.e_pad * 128;
+  const int u_bytes = u_box_rows * 128, w_bytes = p.e_pad * 128;
   const int stageA_bytes = X_TILE_BYTES + u_bytes + w_bytes;
   int nA = IC_RING_BYTES / stageA_bytes;
   nA = nA > A_STAGES_MAX ? A_STAGES_MAX : nA;
@@ -166,8 +164,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
   int nG = (IC_RING_BYTES - h_bytes) / G_STAGE_BYTES;
   nG = nG > G_STAGES_MAX ? G_STAGES_MAX : nG;
 
-  if (!p.router_only)
-    for (int i = threadIdx.x; i < p.r3; i += blockDim.x) wnorm_s[i] = __float2bfloat16_rn(p.normw[i]);
+  for (int i = threadIdx.x; i < p.r3; i += blockDim.x) wnorm_s[i] = __float2bfloat16_rn(p.normw[i]);
   if (threadIdx.x == 0) {
     // a phase-A stage is free once its MMAs have retired and, with the in-kernel pre-norm, the four secondary
     // warps have read its x tile for the row statistics
@@ -182,7 +179,8 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
     for (int s = 0; s < 2; ++s) { mbar_init(smem_u32(&bar_pfull[s]), 1); mbar_init(smem_u32(&bar_pempty[s]), IC_EPI_WARPS); }
     fence_mbar_init();
     prefetch_tmap(&tmX);
-    if (!p.router_only) { prefetch_tmap(tU); prefetch_tmap(tG); }
+    prefetch_tmap(tU);
+    prefetch_tmap(tG);
     if (p.e_pad) prefetch_tmap(tW);
   }
   if (warp == 2) { tmem_alloc(smem_u32(&tmem_base_s), 512); tmem_relinquish(); }  // an epilogue warp: its lanes never retire early
@@ -222,7 +220,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
           mbar_arrive_expect_tx(full, stageA_bytes);
           const uint32_t sa = ring + s * stageA_bytes;
           tma_load_2d(sa, &tmX, kb * 64, m0, full);
-          if (!p.router_only) tma_load_2d(sa + X_TILE_BYTES, tU, kb * 64, pass * u_box_rows, full);
+          tma_load_2d(sa + X_TILE_BYTES, tU, kb * 64, pass * u_box_rows, full);
           if (p.e_pad) tma_load_2d(sa + X_TILE_BYTES + u_bytes, tW, kb * 64, 0, full);
         }
       }
@@ -253,9 +251,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       // reads; the fence is only needed where another thread's tcgen05.ld preceded (accumulator / h hand-offs).
       const uint64_t desc0 = umma_desc_k_sw128(ring);          // descriptor of the ring base; tiles add (bytes >> 4)
       const uint32_t stageA16 = (uint32_t)stageA_bytes >> 4;
-      if (p.router_only)
-        issue_phase_a<false, true, false>(tmem_base, desc0, stageA16, 0u, KA, nA, 16, p.e_pad, bar_fullA, bar_emptyA, p.status);
-      else if (p.e_pad)
+      if (p.e_pad)
         issue_phase_a<false, true>(tmem_base, desc0, stageA16, (uint32_t)u_bytes >> 4, KA, nA, u_box_rows, p.e_pad, bar_fullA, bar_emptyA, p.status);
       else if (u_boxes == 2)
         issue_phase_a<true, false>(tmem_base, desc0, stageA16, (uint32_t)u_bytes >> 4, KA, nA, u_box_rows, 16, bar_fullA, bar_emptyA, p.status);
@@ -263,7 +259,6 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         issue_phase_a<false, false>(tmem_base, desc0, stageA16, (uint32_t)u_bytes >> 4, KA, nA, u_box_rows, 16, bar_fullA, bar_emptyA, p.status);
       umma_commit(smem_u32(&bar_accA));
       TMOE_STAMP(0);  // last phase-A MMA issued
-      if (!p.router_only) {
       mbar_wait_or_exit(smem_u32(&bar_hready), 0, p.status, kKernelInCore, 4);
       tc_fence_after();
       TMOE_STAMP(1);  // MMA thread saw h ready
@@ -288,7 +283,6 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
           if (++sB == (uint32_t)nG) { sB = 0; phB ^= 1; }
         }
         umma_commit(smem_u32(&bar_pfull[slot]));
-      }
       }
     }
   } else {
@@ -418,8 +412,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
               const int e = min(max(si[j], 0), p.E - 1);
 #pragma unroll
               for (int a = 0; a < R1; ++a) {
-                const float ue = p.uexp_bf16 ? __bfloat162float(__ldg(reinterpret_cast<const bf16 *>(p.uexp) + e * R1 + a))
-                                             : __ldg(p.uexp + e * R1 + a);
+                const float ue = __ldg(p.uexp + e * R1 + a);
                 c[a] = fmaf(gate[j], ue, c[a]);
               }
               if (live && sp == 0) {
@@ -444,13 +437,10 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         const float inv_rms = inv_rms_s[row];
 #pragma unroll
         for (int a = 0; a < R1; ++a) c[a] *= inv_rms;
-        if (live && !p.router_only) {
+        if (live) {
 #pragma unroll
           for (int a = 0; a < R1; ++a) c_work[grow * R1 + a] = c[a];
         }
-      } else if (p.router_only) {
-        inv_rms_s[row] = 1.f;          // no h in this mode: c stays unscaled
-        named_bar_sync(3, 256);
       } else {
         // h row: statistics, weight, bf16, swizzled store (16-byte chunk index XOR row%8 inside 128-byte rows)
         float ss = 0.f;
@@ -493,7 +483,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       }
       if (threadIdx.x == 64) TMOE_STAMP(4);  // epilogue A done
       named_bar_sync(4, 256);                // c_work of every row is written
-      if (grp == 1 && !p.router_only) {
+      if (grp == 1) {
 #pragma unroll
         for (int a = 0; a < R1; ++a) c[a] = live ? c_work[grow * R1 + a] : 0.f;
       }
@@ -711,42 +701,5 @@ int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared
   return launch_status();
 }
 
-
-// Stand-alone router on the tensor cores (subsystem 1 for bf16 layers): the kernel above in its router-only mode.  One
-// launch, HBM traffic = one read of x: phase A accumulates only the scores (x tile and router tile per stage, eight stages
-// deep), the primary epilogue warps select and write idx / gates / c.  router_w [E, d_in] as the layer stores it is the
-// K-major operand; rows E .. e_pad of the tile are out of bounds and arrive as zeros.
-int launch_tc_router(const tmoe_layer_t &L, const void *x, const void *router_w, const void *uexp_bf16, int64_t T_, int32_t *idx,
-                     float *gates, float *c, int32_t *status, cudaStream_t st) {
-  const int e_pad = (int)align_up(L.n_experts, 16);
-  if (e_pad > 256 || L.top_k > 8 || (L.d_in % 64) != 0) return TMOE_ERR_UNSUPPORTED;
-  if (!(L.r1 == 2 || L.r1 == 4 || L.r1 == 8 || L.r1 == 16 || L.r1 == 32)) return TMOE_ERR_UNSUPPORTED;
-  CUtensorMap tmX, tmW;
-  int rc = encode_tmap_bf16_2d(&tmX, x, (uint64_t)T_, (uint64_t)L.d_in, TM);
-  if (rc) return rc;
-  if ((rc = encode_tmap_bf16_2d(&tmW, router_w, (uint64_t)L.n_experts, (uint64_t)L.d_in, (uint32_t)e_pad))) return rc;
-  InCoreParams p{};
-  p.T = T_; p.d_in = L.d_in; p.r3 = 64; p.r2 = 0; p.E = L.n_experts; p.top_k = L.top_k; p.e_pad = e_pad;
-  p.n_tiles2 = 0; p.eps = L.eps; p.fuse_router = 1; p.router_only = 1; p.uexp_bf16 = 1; p.rc = router_cfg(L);
-  p.uexp = reinterpret_cast<const float *>(uexp_bf16);
-  p.idx_out = idx; p.gates_out = gates; p.c_out = c; p.status = status; p.j_split = 1;
-  const unsigned grid = (unsigned)((T_ + TM - 1) / TM);
-  cudaError_t e = cudaSuccess;
-#define TMOE_RT(R, K)                                                                                              \
-  do {                                                                                                             \
-    e = cudaFuncSetAttribute(tc_in_core_kernel<R, K>, cudaFuncAttributeMaxDynamicSharedMemorySize, IC_SMEM_BYTES); \
-    if (e == cudaSuccess) e = launch_pdl(tc_in_core_kernel<R, K>, dim3(grid), dim3(IC_THREADS), (size_t)IC_SMEM_BYTES, st, tmX, tmX, tmW, tmX, p, tmX, tmW, tmX, p); \
-  } while (0)
-  const bool small_k = L.top_k <= 2;
-  if (L.r1 == 2) { if (small_k) TMOE_RT(2, 2); else TMOE_RT(2, 8); }
-  else if (L.r1 == 4) { if (small_k) TMOE_RT(4, 2); else TMOE_RT(4, 8); }
-  else if (L.r1 == 8) { if (small_k) TMOE_RT(8, 2); else TMOE_RT(8, 8); }
-  else if (L.r1 == 16) { if (small_k) TMOE_RT(16, 2); else TMOE_RT(16, 8); }
-  else { if (small_k) TMOE_RT(32, 2); else TMOE_RT(32, 8); }
-#undef TMOE_RT
-  if (e != cudaSuccess) return TMOE_ERR_CUDA;
-  count_launch();
-  return launch_status();
-}
 
 }  // namespace tmoe
