@@ -120,8 +120,8 @@ int launch_tc_in_core(const tmoe_layer_t &L, const void *x, const void *prepared
                       int pre_norm, float pre_norm_eps, int fuse_router, const float *c_in, float *c_work, int c_work_blocks, int32_t *idx_out, float *gates_out, float *c_out,
                       void *z, int32_t *status, cudaStream_t st, const OutFlags *flags = nullptr, const InCoreTwin *twin = nullptr);
 
-// Stand-alone router for bf16 layers on the tensor cores (the kernel above in router-only mode): idx / gates / c from x and
-// the layer's own router_w / U_expert.  TMOE_ERR_UNSUPPORTED for E > 256 (padded), top_k > 8, d_in % 64 != 0 or other r1.
+// Stand-alone router for bf16 layers on the tensor cores (tc_router.cu, persistent): idx / gates / c from x and
+// the layer's own router_w / U_expert.  TMOE_ERR_UNSUPPORTED for E > 256 (padded), top_k > 8 or d_in % 64 != 0.
 int launch_tc_router(const tmoe_layer_t &L, const void *x, const void *router_w, const void *uexp_bf16, int64_t T, int32_t *idx,
                      float *gates, float *c, int32_t *status, cudaStream_t st);
 
