@@ -647,7 +647,8 @@ def main():
         launches0 = lib.tmoe_launch_count()
         per_rank = {}
         ms_total = timed_steps(lambda i: layer(x_dev[i % N_INPUT_SETS]), args.steps, barrier, dev, world, detail=per_rank)
-        launches = lib.tmoe_launch_count() - launches0
+        # the counter also saw the untimed steps in front of the first event: every step makes the same launches
+        launches = (lib.tmoe_launch_count() - launches0) * args.steps // (args.steps + SPIN_UP_STEPS)
         # the same steps replayed from a CUDA graph (one graph holds a step on each input set): what is left of a step
         # when the host's part -- Python, tensor-map encoding, four launches -- is taken out
         side = torch.cuda.Stream()
