@@ -55,7 +55,7 @@ def sha(t: torch.Tensor) -> str:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of the reference checkout")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     from pure_torch_mlx.config import Mamba3Config

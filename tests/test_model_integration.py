@@ -21,7 +21,8 @@ sys.path.insert(0, os.path.join(HERE, "golden"))
 from make_model_golden import MAMBA_LAYERS, XFMR_LAYERS, layer_factors, sha  # noqa: E402
 from oracle.tucker_moe_oracle import layer_forward, layer_forward_f64, max_abs, rel_fro, rms_norm as ref_norm  # noqa: E402
 
-REFERENCE = "/root/reference"
+# the reference checkout: TMOE_REFERENCE_DIR, or a directory named "reference" beside this repository
+REFERENCE = os.environ.get("TMOE_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 ALL_LAYERS = MAMBA_LAYERS + XFMR_LAYERS
 
 
