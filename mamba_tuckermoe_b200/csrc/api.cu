@@ -220,7 +220,7 @@ int tmoe_router(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const 
   // select kernel finishes the job.  Needs E % 8 == 0 (16-byte rows of scores) and room for [T, E] bf16 in the workspace.
   const int64_t sc_off = kHeaderBytes;
   if (L.dtype == TMOE_BF16 && T >= 512) {
-    // up to 256 experts and top-8: one launch that accumulates the scores in TMEM and selects from there
+    // up to 1024 experts and top-8: one launch that accumulates the scores in TMEM and selects from there
     rc = launch_tc_router(L, x, factors->router_w, factors->U_expert, T, idx, gates, c, reinterpret_cast<int32_t *>(ws),
                           (cudaStream_t)stream);
     if (rc != TMOE_ERR_UNSUPPORTED) return rc;
@@ -365,8 +365,8 @@ int tmoe_forward(const tmoe_layer_t *layer, const tmoe_factors_t *factors, const
                            taps ? extras->idx_out : nullptr,
                            taps ? extras->gates_out : nullptr, taps ? extras->c_out : nullptr, z, status, st, fp);
   } else {
-    // the router as a kernel of its own.  Up to 256 experts and top-8 (layers whose r3 = 512 leaves no TMEM columns for the
-    // scores next to h): the persistent router kernel, scores never leave the SM.  Beyond that: scores = x @ router_w^T as
+    // the router as a kernel of its own (layers whose r3 = 512 leaves no TMEM columns for the scores next to h, or with more
+    // than 256 experts).  Up to 1024 experts and top-8: the persistent router kernel, scores never leave the SM.  Beyond that: scores = x @ router_w^T as
     // a GEMM (bf16 out = the reference's rounding), then the select kernel.
     rc = launch_tc_router(L, x, factors->router_w, factors->U_expert, T, idx, gates, c, status, st);
     if (rc == TMOE_ERR_UNSUPPORTED) {

@@ -35,6 +35,7 @@ struct RouterParams {
   int64_t T;
   int d_in, E, e_pad, top_k, r1;
   int n_tiles, n_stages;
+  int n_pass;         // expert chunks of e_pad (<= 256) columns per token tile: more than 256 experts take several passes over x
   RouterCfg rc;
   const bf16 *uexp;   // [E, r1], the layer's own table
   int32_t *idx_out;   // [T, top_k]
@@ -77,14 +78,16 @@ tc_router_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     bool ok = true;
     for (int tile = blockIdx.x; tile < p.n_tiles && ok; tile += gridDim.x) {
       if (lane == 0) {
-        for (int kb = 0; kb < KA; ++kb) {
-          if (!(ok = mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1, p.status, kKernelRouter, 2))) break;
-          const uint32_t full = smem_u32(&bar_full[s]);
-          mbar_arrive_expect_tx(full, (uint32_t)stage_bytes);
-          const uint32_t sa = ring + s * (uint32_t)stage_bytes;
-          tma_load_2d(sa, &tmX, kb * 64, tile * RT_TM, full);
-          tma_load_2d(sa + RT_X_BYTES, &tmW, kb * 64, 0, full);
-          if (++s == (uint32_t)p.n_stages) { s = 0; ph ^= 1; }
+        for (int pass = 0; pass < p.n_pass && ok; ++pass) {   // passes after the first find the x tile in L2
+          for (int kb = 0; kb < KA; ++kb) {
+            if (!(ok = mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1, p.status, kKernelRouter, 2))) break;
+            const uint32_t full = smem_u32(&bar_full[s]);
+            mbar_arrive_expect_tx(full, (uint32_t)stage_bytes);
+            const uint32_t sa = ring + s * (uint32_t)stage_bytes;
+            tma_load_2d(sa, &tmX, kb * 64, tile * RT_TM, full);
+            tma_load_2d(sa + RT_X_BYTES, &tmW, kb * 64, pass * p.e_pad, full);
+            if (++s == (uint32_t)p.n_stages) { s = 0; ph ^= 1; }
+          }
         }
       }
       ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
@@ -95,7 +98,8 @@ tc_router_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       const uint64_t desc0 = umma_desc_k_sw128(ring);
       const uint32_t stage16 = (uint32_t)stage_bytes >> 4;
       uint32_t s = 0, ph = 0, tcount = 0;
-      for (int tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x, ++tcount) {
+      const int n_acc = ((p.n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x) * p.n_pass;   // (tile, pass) pairs of this CTA
+      for (int ia = 0; ia < n_acc; ++ia, ++tcount) {
         const uint32_t slot = tcount & 1, aph = (tcount >> 1) & 1;
         mbar_wait_or_exit(smem_u32(&bar_aempty[slot]), aph ^ 1, p.status, kKernelRouter, 4);
         tc_fence_after();
@@ -117,27 +121,32 @@ tc_router_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     const int row = quad * 32 + lane;
     uint32_t tcount = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < p.n_tiles && ok; tile += gridDim.x, ++tcount) {
+    for (int tile = blockIdx.x; tile < p.n_tiles && ok; tile += gridDim.x) {
+      uint32_t key[RK];   // the running top-k list of this thread's token, carried across the expert chunks
+#pragma unroll
+      for (int j = 0; j < RK; ++j) key[j] = 0u;
+      float z_all = 1.f;
+      float sv[RK];
+      int si[RK];
+      for (int pass = 0; pass < p.n_pass; ++pass, ++tcount) {
       const uint32_t slot = tcount & 1, aph = (tcount >> 1) & 1;
       ok = mbar_wait(smem_u32(&bar_afull[slot]), aph, p.status, kKernelRouter, 3);
       ok = __all_sync(0xffffffffu, ok);   // the TMEM loads below are warp-collective
       if (!ok) break;
       tc_fence_after();
       const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + slot * 256;
+      const int e0 = pass * p.e_pad;
       // Running top-k over the score columns, branch-free: a score rounded to bf16 (the reference's rounding of its logits)
       // has 16 significant bits, so (order-preserving map of those bits) << 16 | (0xFFFF - expert) is a 32-bit key whose
       // unsigned order is "higher score first, equal scores -> lower expert index first"; the sorted list is kept with
       // integer max / min only.
-      uint32_t key[RK];
-#pragma unroll
-      for (int j = 0; j < RK; ++j) key[j] = 0u;
       for (int cc = 0; cc < p.e_pad / 16; ++cc) {
         uint32_t r[16];
         tmem_ld16(t_row + cc * 16, r);
         tmem_ld_wait(r);
 #pragma unroll
         for (int q = 0; q < 16; ++q) {
-          const int e = cc * 16 + q;
+          const int e = e0 + cc * 16 + q;
           uint32_t b = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(__uint_as_float(r[q])));
           b = (b == 0x8000u) ? 0u : b;   // -0 and +0 compare equal
           const uint32_t u = (b & 0x8000u) ? (~b & 0xffffu) : (b | 0x8000u);
@@ -150,8 +159,6 @@ tc_router_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           }
         }
       }
-      float sv[RK];
-      int si[RK];
 #pragma unroll
       for (int j = 0; j < RK; ++j) {
         const uint32_t u = key[j] >> 16;
@@ -161,8 +168,7 @@ tc_router_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       }
       // capped-softmax rule only: its denominator runs over ALL experts, relative to the top logit (a second pass over the
       // columns, so that the default rule's scan above stays branch-free)
-      float z_all = 1.f;
-      if (p.rc.mode == 1) {
+      if (p.rc.mode == 1) {   // (one expert chunk only: the launcher sends larger layers with this rule elsewhere)
         const float l0 = p.rc.logit(sv[0]);
         z_all = 0.f;
         for (int cc = 0; cc < p.e_pad / 16; ++cc) {
@@ -180,6 +186,8 @@ tc_router_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_aempty[slot]));
+      }
+      if (!ok) break;
 
       const int64_t grow = (int64_t)tile * RT_TM + row;
       if (grow < p.T) {
@@ -218,11 +226,15 @@ tc_router_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
 }  // namespace
 
 // idx / gates / c for T tokens from x and the layer's own router_w [E, d_in] / U_expert [E, r1] (bf16).
-// TMOE_ERR_UNSUPPORTED for more than 256 experts (padded to 16), top_k > 8 or d_in % 64 != 0.
+// TMOE_ERR_UNSUPPORTED for more than 1024 experts, more than 256 with the capped-softmax rule, top_k > 8 or d_in % 64 != 0.
 int launch_tc_router(const tmoe_layer_t &L, const void *x, const void *router_w, const void *uexp_bf16, int64_t T_, int32_t *idx,
                      float *gates, float *c, int32_t *status, cudaStream_t st) {
-  const int e_pad = (int)align_up(L.n_experts, 16);
-  if (e_pad > 256 || L.top_k > 8 || (L.d_in % 64) != 0) return TMOE_ERR_UNSUPPORTED;
+  // up to 256 experts: one accumulator of e_pad columns per token tile; up to 1024: chunks of 256 experts, one pass over the
+  // tile's x per chunk (the later passes read it from L2), the top-k list carried from chunk to chunk
+  const int e_all = (int)align_up(L.n_experts, 16);
+  const int n_pass = (e_all + 255) / 256;
+  const int e_pad = n_pass == 1 ? e_all : 256;
+  if (n_pass > 4 || (n_pass > 1 && L.router_mode != 0) || L.top_k > 8 || (L.d_in % 64) != 0) return TMOE_ERR_UNSUPPORTED;
   CUtensorMap tmX, tmW;
   int rc = encode_tmap_bf16_2d(&tmX, x, (uint64_t)T_, (uint64_t)L.d_in, RT_TM);
   if (rc) return rc;
@@ -232,6 +244,7 @@ int launch_tc_router(const tmoe_layer_t &L, const void *x, const void *router_w,
   RouterParams p{};
   p.T = T_; p.d_in = L.d_in; p.E = L.n_experts; p.e_pad = e_pad; p.top_k = L.top_k; p.r1 = L.r1;
   p.n_tiles = (int)((T_ + RT_TM - 1) / RT_TM);
+  p.n_pass = n_pass;
   const int stage_bytes = RT_X_BYTES + e_pad * 128;
   p.n_stages = RT_RING_BYTES / stage_bytes < RT_STAGES_MAX ? RT_RING_BYTES / stage_bytes : RT_STAGES_MAX;
   p.rc = router_cfg(L);

@@ -17,11 +17,16 @@ CASES = [
     (LayerShape(256, 384, 1024, 16, 3, 64, 128, 1e-6), 290, torch.float32),  # top-16 of 1024, odd r1
     (LayerShape(1536, 2304, 8, 2, 4, 256, 1024, 1e-6), 8, torch.bfloat16),
     (LayerShape(1536, 2304, 64, 2, 4, 256, 1024, 1e-6), 257, torch.bfloat16),
-    # bf16 with >= 512 tokens: the stand-alone router takes its scores from the tensor-core GEMM kernel (router_w is its
-    # K-major operand as stored) and selects with the keyed kernel
+    # bf16 with >= 512 tokens: the scores come from the tensor cores (router_w is the K-major operand as stored); top-k > 8
+    # through the GEMM kernel + the keyed select kernel
     (LayerShape(1536, 2304, 64, 2, 4, 256, 1024, 1e-6), 2100, torch.bfloat16),
     (LayerShape(256, 384, 1024, 16, 4, 64, 128, 1e-6), 600, torch.bfloat16),   # top-16 of 1024
     (LayerShape(1536, 2304, 8, 2, 4, 256, 1024, 1e-6), 777, torch.bfloat16),   # E = 8: a 128-column tile, 8 of them used
+    # the persistent tensor-core router: one expert chunk (E <= 256) and several (E <= 1024, top-k list carried across)
+    (LayerShape(512, 384, 256, 8, 8, 64, 128, 1e-6), 40000, torch.bfloat16),   # more tiles than SMs: every CTA walks on
+    (LayerShape(512, 384, 1024, 8, 4, 64, 128, 1e-6), 1000, torch.bfloat16),   # four chunks of 256 experts
+    (LayerShape(512, 384, 328, 2, 32, 64, 128, 1e-6), 700, torch.bfloat16),    # two chunks, the second mostly padding
+    (LayerShape(512, 384, 104, 8, 16, 64, 128, 1e-6), 513, torch.bfloat16),    # 104 experts padded to 112 columns
 ]
 
 
@@ -56,10 +61,13 @@ def test_router_stage(shape, T, dtype):
     tol = 2e-6 if dtype == torch.float32 else 4e-3
     assert max_abs(gates.cpu(), own["gates"]) < tol
     assert max_abs(c.cpu(), own["c"]) < tol * 8
-    # descending order of the selected scores, indices distinct per token
+    # descending order of the selected scores (in bf16 the kernel sorts by ITS rounding of a score, which may sit one ulp
+    # from the float64 statement's rounding: neighbours may then appear swapped by at most that ulp), indices distinct
     s_sel = torch.gather(own["scores"], 1, idx.cpu().long())
-    assert bool((s_sel[:, :-1] >= s_sel[:, 1:]).all())
-    assert all(len(set(r.tolist())) == shape.top_k for r in idx.cpu())
+    slack = 0.0 if dtype == torch.float32 else 2.0 ** -7
+    assert bool((s_sel[:, :-1] >= s_sel[:, 1:] - slack * s_sel[:, 1:].abs()).all())
+    srt = torch.sort(idx.cpu(), dim=1).values
+    assert bool((srt[:, 1:] != srt[:, :-1]).all())
 
 
 @pytest.mark.parametrize("shape,T,dtype", CASES)
