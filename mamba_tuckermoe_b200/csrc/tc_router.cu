@@ -129,63 +129,63 @@ tc_router_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       float sv[RK];
       int si[RK];
       for (int pass = 0; pass < p.n_pass; ++pass, ++tcount) {
-      const uint32_t slot = tcount & 1, aph = (tcount >> 1) & 1;
-      ok = mbar_wait(smem_u32(&bar_afull[slot]), aph, p.status, kKernelRouter, 3);
-      ok = __all_sync(0xffffffffu, ok);   // the TMEM loads below are warp-collective
-      if (!ok) break;
-      tc_fence_after();
-      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + slot * 256;
-      const int e0 = pass * p.e_pad;
-      // Running top-k over the score columns, branch-free: a score rounded to bf16 (the reference's rounding of its logits)
-      // has 16 significant bits, so (order-preserving map of those bits) << 16 | (0xFFFF - expert) is a 32-bit key whose
-      // unsigned order is "higher score first, equal scores -> lower expert index first"; the sorted list is kept with
-      // integer max / min only.
-      for (int cc = 0; cc < p.e_pad / 16; ++cc) {
-        uint32_t r[16];
-        tmem_ld16(t_row + cc * 16, r);
-        tmem_ld_wait(r);
-#pragma unroll
-        for (int q = 0; q < 16; ++q) {
-          const int e = e0 + cc * 16 + q;
-          uint32_t b = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(__uint_as_float(r[q])));
-          b = (b == 0x8000u) ? 0u : b;   // -0 and +0 compare equal
-          const uint32_t u = (b & 0x8000u) ? (~b & 0xffffu) : (b | 0x8000u);
-          uint32_t carry = (e < p.E) ? ((u << 16) | (0xffffu - (uint32_t)e)) : 0u;
-#pragma unroll
-          for (int j = 0; j < RK; ++j) {
-            const uint32_t hi = max(key[j], carry);
-            carry = min(key[j], carry);
-            key[j] = hi;
-          }
-        }
-      }
-#pragma unroll
-      for (int j = 0; j < RK; ++j) {
-        const uint32_t u = key[j] >> 16;
-        const uint32_t b = (u & 0x8000u) ? (u & 0x7fffu) : (~u & 0xffffu);
-        sv[j] = __uint_as_float(b << 16);
-        si[j] = (int)(0xffffu - (key[j] & 0xffffu));
-      }
-      // capped-softmax rule only: its denominator runs over ALL experts, relative to the top logit (a second pass over the
-      // columns, so that the default rule's scan above stays branch-free)
-      if (p.rc.mode == 1) {   // (one expert chunk only: the launcher sends larger layers with this rule elsewhere)
-        const float l0 = p.rc.logit(sv[0]);
-        z_all = 0.f;
+        const uint32_t slot = tcount & 1, aph = (tcount >> 1) & 1;
+        ok = mbar_wait(smem_u32(&bar_afull[slot]), aph, p.status, kKernelRouter, 3);
+        ok = __all_sync(0xffffffffu, ok);   // the TMEM loads below are warp-collective
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + slot * 256;
+        const int e0 = pass * p.e_pad;
+        // Running top-k over the score columns, branch-free: a score rounded to bf16 (the reference's rounding of its logits)
+        // has 16 significant bits, so (order-preserving map of those bits) << 16 | (0xFFFF - expert) is a 32-bit key whose
+        // unsigned order is "higher score first, equal scores -> lower expert index first"; the sorted list is kept with
+        // integer max / min only.
         for (int cc = 0; cc < p.e_pad / 16; ++cc) {
           uint32_t r[16];
           tmem_ld16(t_row + cc * 16, r);
           tmem_ld_wait(r);
 #pragma unroll
           for (int q = 0; q < 16; ++q) {
-            const float sc = round_to<bf16>(__uint_as_float(r[q]));
-            if (cc * 16 + q < p.E) z_all += expf(p.rc.logit(sc) - l0);
+            const int e = e0 + cc * 16 + q;
+            uint32_t b = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(__uint_as_float(r[q])));
+            b = (b == 0x8000u) ? 0u : b;   // -0 and +0 compare equal
+            const uint32_t u = (b & 0x8000u) ? (~b & 0xffffu) : (b | 0x8000u);
+            uint32_t carry = (e < p.E) ? ((u << 16) | (0xffffu - (uint32_t)e)) : 0u;
+#pragma unroll
+            for (int j = 0; j < RK; ++j) {
+              const uint32_t hi = max(key[j], carry);
+              carry = min(key[j], carry);
+              key[j] = hi;
+            }
           }
         }
-      }
-      // the accumulator has been read: the MMA thread may start the tile after next in it
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bar_aempty[slot]));
+#pragma unroll
+        for (int j = 0; j < RK; ++j) {
+          const uint32_t u = key[j] >> 16;
+          const uint32_t b = (u & 0x8000u) ? (u & 0x7fffu) : (~u & 0xffffu);
+          sv[j] = __uint_as_float(b << 16);
+          si[j] = (int)(0xffffu - (key[j] & 0xffffu));
+        }
+        // capped-softmax rule only: its denominator runs over ALL experts, relative to the top logit (a second pass over the
+        // columns, so that the default rule's scan above stays branch-free)
+        if (p.rc.mode == 1) {   // (one expert chunk only: the launcher sends larger layers with this rule elsewhere)
+          const float l0 = p.rc.logit(sv[0]);
+          z_all = 0.f;
+          for (int cc = 0; cc < p.e_pad / 16; ++cc) {
+            uint32_t r[16];
+            tmem_ld16(t_row + cc * 16, r);
+            tmem_ld_wait(r);
+#pragma unroll
+            for (int q = 0; q < 16; ++q) {
+              const float sc = round_to<bf16>(__uint_as_float(r[q]));
+              if (cc * 16 + q < p.E) z_all += expf(p.rc.logit(sc) - l0);
+            }
+          }
+        }
+        // the accumulator has been read: the MMA thread may start the tile after next in it
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_aempty[slot]));
       }
       if (!ok) break;
 
