@@ -12,7 +12,8 @@
  *  - every pointer named "device" is a CUDA device pointer on the current device.
  *  - functions return 0 (TMOE_OK) or a negative tmoe_status_t; they never throw, never call
  *    exit(), never synchronise the device (except tmoe_read_device_status) and never allocate
- *    device memory: the caller passes a workspace sized by tmoe_workspace_bytes().
+ *    device memory: the caller passes a workspace sized by tmoe_workspace_bytes().  (The tmoe_peer_*
+ *    functions at the end are the exception: allocating and mapping buffers is their job.)
  *  - all work is enqueued on `stream`; buffers are borrowed until that work has finished.
  *  - tensors are dense row-major.  x, y and the seven factors share one dtype (tmoe_dtype_t).
  */
