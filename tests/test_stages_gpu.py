@@ -131,3 +131,33 @@ def test_bounded_wait_reports_and_returns():
     torch.cuda.synchronize()
     y64, _ = layer_forward_f64(x, f, shape.top_k, shape.eps)
     assert rel_fro(y.cpu(), y64) < 1e-5
+
+
+@pytest.mark.parametrize("shape", [LayerShape(512, 384, 8, 2, 4, 64, 256, 1e-6),     # 64 z columns per core tile and thread
+                                   LayerShape(512, 384, 8, 2, 32, 64, 256, 1e-6)])   # r1 = 32: 8 columns, stores paired up
+def test_in_core_writes_the_same_z_at_any_16_byte_alignment(shape):
+    """The in-projection/core kernel stores z with 256-bit stores when z is 32-byte aligned and with 16-byte stores
+    otherwise (the ABI asks for 16 bytes): same bits either way."""
+    lib = _lib.load()
+    T, dtype = 300, torch.bfloat16
+    L = layer_struct(shape, dtype)
+    x, f, fd = _setup(shape, T, dtype)
+    F = factors_struct(fd)
+    ws, prep = alloc_workspace(lib, L, T, 2), alloc_prepared(lib, L, F)
+    _, taps = layer_forward_f64(x, f, shape.top_k, shape.eps, round_scores_to=torch.bfloat16)
+    c = taps["c"].float().cuda().contiguous()
+    xd = x.cuda()
+    raw = torch.zeros(T * shape.r2 + 64, dtype=dtype, device="cuda")
+    outs = []
+    for off in (0, 8):   # elements: 0 and 16 bytes past a 256-byte aligned address
+        z = raw[off:off + T * shape.r2].view(T, shape.r2)
+        assert z.data_ptr() % 32 == (16 if off else 0)
+        raw.zero_()
+        rc = lib.tmoe_in_core(C.byref(L), C.byref(F), prep.data_ptr(), xd.data_ptr(), T, c.data_ptr(), z.data_ptr(),
+                              ws.data_ptr(), ws.numel(), 2, cuda_stream_ptr())
+        assert rc == 0, _lib.status_string(rc)
+        torch.cuda.synchronize()
+        outs.append(z.clone())
+        assert bool((raw[:off] == 0).all()) and bool((raw[off + T * shape.r2:] == 0).all())
+    assert torch.equal(outs[0], outs[1])
+    assert rel_fro(outs[0].float().cpu(), taps["z"]) < 1e-2
