@@ -154,6 +154,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap
       : "memory");
 }
 
+// The same load with an L2 eviction-priority hint (a createpolicy value).
+__device__ __forceinline__ void tma_load_2d_hint(uint32_t dst_smem, const CUtensorMap *m, int c0, int c1, uint32_t bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;" ::"r"(dst_smem),
+      "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "l"(policy)
+      : "memory");
+}
 // 2-D tiled store shared (this CTA) -> global, tracked by the thread's bulk async-group.
 // Elements of the box that fall outside the tensor are not written.
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap *m, uint32_t src_smem, int c0, int c1) {
@@ -179,6 +186,11 @@ __device__ __forceinline__ void tma_store_2d_hint(const CUtensorMap *m, uint32_t
                    reinterpret_cast<uint64_t>(m)),
                "r"(src_smem), "r"(c0), "r"(c1), "l"(policy)
                : "memory");
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_normal() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
 }
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {
   uint64_t pol;

@@ -211,6 +211,10 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
     if (lane == 0) {
       bool ok = true;
       uint32_t sA = 0, phA = 0, sB = 0, phB = 0;
+      // x is read once (with r3 = 512 twice, the second time from L2: no hint then): its lines are the first to go, so that
+      // z -- which the out-projection reads next -- and the factors stay in L2 (200.9 -> 198.4 us per forward at the prefill
+      // configuration; marking the z stores evict-last on top of that changed nothing)
+      const uint64_t pol_x = u_boxes == 1 ? l2_policy_evict_first() : l2_policy_evict_normal();
       for (int pass = 0; pass < u_boxes && ok; ++pass) {
         for (int kb = 0; kb < KA && ok; ++kb) {
           const uint32_t s = sA, ph = phA;
@@ -219,7 +223,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
           const uint32_t full = smem_u32(&bar_fullA[s]);
           mbar_arrive_expect_tx(full, stageA_bytes);
           const uint32_t sa = ring + s * stageA_bytes;
-          tma_load_2d(sa, &tmX, kb * 64, m0, full);
+          tma_load_2d_hint(sa, &tmX, kb * 64, m0, full, pol_x);
           tma_load_2d(sa + X_TILE_BYTES, tU, kb * 64, pass * u_box_rows, full);
           if (p.e_pad) tma_load_2d(sa + X_TILE_BYTES + u_bytes, tW, kb * 64, 0, full);
         }
