@@ -213,7 +213,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       uint32_t sA = 0, phA = 0, sB = 0, phB = 0;
       // x is read once (with r3 = 512 twice, the second time from L2: no hint then): its lines are the first to go, so that
       // z -- which the out-projection reads next -- and the factors stay in L2 (200.9 -> 198.4 us per forward at the prefill
-      // configuration; marking the z stores evict-last on top of that changed nothing)
+      // configuration; marking the z stores or the factor tiles evict-last on top of that changed nothing)
       const uint64_t pol_x = u_boxes == 1 ? l2_policy_evict_first() : l2_policy_evict_normal();
       for (int pass = 0; pass < u_boxes && ok; ++pass) {
         for (int kb = 0; kb < KA && ok; ++kb) {

@@ -76,6 +76,8 @@ tc_router_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     // against 31 us per launch with L2 flushed; the boxes alone keep HBM busier.)
     uint32_t s = 0, ph = 0;
     bool ok = true;
+    // a single pass reads x once: evict-first, the router rows stay (30.8 -> 28.3 us per launch right after an L2 flush)
+    const uint64_t pol_x = p.n_pass == 1 ? l2_policy_evict_first() : l2_policy_evict_normal();
     for (int tile = blockIdx.x; tile < p.n_tiles && ok; tile += gridDim.x) {
       if (lane == 0) {
         for (int pass = 0; pass < p.n_pass && ok; ++pass) {   // passes after the first find the x tile in L2
@@ -84,7 +86,7 @@ tc_router_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             const uint32_t full = smem_u32(&bar_full[s]);
             mbar_arrive_expect_tx(full, (uint32_t)stage_bytes);
             const uint32_t sa = ring + s * (uint32_t)stage_bytes;
-            tma_load_2d(sa, &tmX, kb * 64, tile * RT_TM, full);
+            tma_load_2d_hint(sa, &tmX, kb * 64, tile * RT_TM, full, pol_x);
             tma_load_2d(sa + RT_X_BYTES, &tmW, kb * 64, pass * p.e_pad, full);
             if (++s == (uint32_t)p.n_stages) { s = 0; ph ^= 1; }
           }
