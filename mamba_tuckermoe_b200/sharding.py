@@ -205,6 +205,13 @@ class PeerBuffers:
         self._base = None
 
 
+def push_chunks(local_tokens: int) -> int:
+    """Chunks of the copy-engine push when the caller leaves the choice open: about 8192 tokens per chunk, at most 4 -- below
+    that a chunk's copies are too short to stay ahead of the host's per-chunk work (measured optimum at 4096 ... 65536
+    tokens per GPU on 2, 4 and 8 GPUs: 1, 1, 2, 4, 4)."""
+    return max(1, min(4, local_tokens // 8192))
+
+
 def in_kernel_gather_pays(layer, world: int) -> bool:
     """Whether the out-projection GEMM should write the peers' buffers itself.  It produces 2 * d_out bytes of y per
     2 * r2 * d_out flops, i.e. (world - 1) / r2 bytes per flop have to leave through NVLink while it runs: at ~1.4 PFLOP/s
@@ -285,7 +292,7 @@ def _into(layer, x: torch.Tensor, dst: torch.Tensor) -> None:
 
 
 def sharded_forward(layer: Callable[[torch.Tensor], torch.Tensor], x_local: torch.Tensor, *, n_tokens: int,
-                    gather: bool = False, chunks: int = 1, group=None, out: Optional[torch.Tensor] = None,
+                    gather: bool = False, chunks: Optional[int] = None, group=None, out: Optional[torch.Tensor] = None,
                     d_out: Optional[int] = None, peers: Optional[PeerBuffers] = None, in_kernel: Optional[bool] = None) -> torch.Tensor:
     """Runs `layer` on this rank's tokens ``x_local`` ([T_local, d_in]).
 
@@ -300,12 +307,17 @@ def sharded_forward(layer: Callable[[torch.Tensor], torch.Tensor], x_local: torc
     contiguous ``shard_bounds`` range for any n_tokens, and the result is ``peers.out`` (see ``PeerBuffers`` for how long
     it stays valid).  With in_kernel=True the out-projection GEMM itself stores every output tile to all ranks' buffers
     when the call takes the tensor-core path; in_kernel=False, or a call on another path, copies finished chunks with the
-    copy engines instead (`chunks` applies to this form only); None (default) decides by ``in_kernel_gather_pays``.
+    copy engines instead (`chunks` applies to this form only; None = ``push_chunks``); None (default) decides by
+    ``in_kernel_gather_pays``.  With NCCL `chunks` defaults to 1.
     """
     if peers is not None:
         if not gather or out is not None:
             raise ValueError("`peers` is the gathered result buffer: pass gather=True and no `out`")
+        if chunks is None:
+            chunks = push_chunks(x_local.shape[0])
         return _push_gather(layer, x_local, n_tokens, chunks, peers, in_kernel)
+    if chunks is None:
+        chunks = 1
     if not gather or not dist.is_initialized() or dist.get_world_size(group) == 1:
         if gather and n_tokens != x_local.shape[0]:
             raise ValueError("single-rank gather needs the whole token range")

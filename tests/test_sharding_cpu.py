@@ -105,6 +105,8 @@ def test_in_kernel_gather_rule():
     assert in_kernel_gather_pays(deep, 2) and not in_kernel_gather_pays(deep, 4)
     assert not in_kernel_gather_pays(shallow, 2)
     assert not in_kernel_gather_pays(lambda x: x, 2)
+    from mamba_tuckermoe_b200.sharding import push_chunks
+    assert [push_chunks(t) for t in (1, 4096, 8192, 16384, 32768, 65536, 1 << 20)] == [1, 1, 1, 2, 4, 4, 4]
 
 
 def _peer_failure_worker(rank, world, port, ret):
