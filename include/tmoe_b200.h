@@ -26,7 +26,8 @@
 extern "C" {
 #endif
 
-#define TMOE_ABI_VERSION 1
+/* 2: tmoe_extras_t grew (n_peer_y, peer_y); the tmoe_peer_* entry points */
+#define TMOE_ABI_VERSION 2
 #define TMOE_MAX_TOPK 16
 #define TMOE_MAX_R1 64
 

@@ -12,6 +12,7 @@ LIB_PATH = os.environ.get("TMOE_LIB_PATH") or os.path.join(PKG, "lib", "libtmoe_
 TMOE_F32, TMOE_BF16 = 0, 1
 PATH_AUTO, PATH_SIMT, PATH_TENSOR, PATH_DECODE = 0, 1, 2, 3
 ROUTER_TOPK_SOFTMAX, ROUTER_CAPPED_SOFTMAX = 0, 1
+ABI_VERSION = 2   # TMOE_ABI_VERSION of the header this binding mirrors
 ERR_UNSUPPORTED = -6
 ERR_DEVICE_WAIT = -9
 MAX_PEERS = 7
@@ -120,7 +121,7 @@ def load():
         lib.tmoe_peer_free.argtypes = [vp]
         lib.tmoe_peer_push.restype = i32
         lib.tmoe_peer_push.argtypes = [VPP, C.c_int32, vp, i64, VPP]
-        if lib.tmoe_version() != 1:
+        if lib.tmoe_version() != ABI_VERSION:
             raise RuntimeError("libtmoe_b200.so has an ABI version this binding does not know")
         _lib = lib
     return _lib

@@ -27,7 +27,7 @@ def test_header_symbols_are_exported():
     lib = _lib.load()
     for s in declared:
         assert hasattr(lib, s), s
-    assert lib.tmoe_version() == 1
+    assert lib.tmoe_version() == _lib.ABI_VERSION == 2
 
 
 def test_status_strings():
