@@ -476,7 +476,8 @@ def timed_steps(fn, steps, barrier, dev, world, detail=None):
 
 
 def copy_rates(x_host, y_host, x_dev, dev, world, reps=4):
-    """Host<->device copy rate of each direction alone (GB/s, this rank), all ranks copying at the same time."""
+    """Host<->device copy rates of this rank in GB/s, all ranks copying at the same time: [H2D alone, D2H alone, H2D and
+    D2H while the other direction is busy too]."""
     import torch.distributed as dist
     y_dev = torch.empty(y_host.shape, dtype=y_host.dtype, device=dev)
     out = []
@@ -492,6 +493,22 @@ def copy_rates(x_host, y_host, x_dev, dev, world, reps=4):
         b.record()
         torch.cuda.synchronize()
         out.append(src.numel() * src.element_size() * reps / (a.elapsed_time(b) * 1e-3) / 1e9)
+    # both directions at once, on two streams: what a pipelined step actually gets from a full-duplex link
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ev = []
+    for st, src, dst in ((s_in, x_host, x_dev), (s_out, y_dev, y_host)):
+        with torch.cuda.stream(st):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(reps):
+                dst.copy_(src, non_blocking=True)
+            b.record()
+            ev.append((a, b, src.numel() * src.element_size() * reps))
+    torch.cuda.synchronize()
+    out += [n / (a.elapsed_time(b) * 1e-3) / 1e9 for a, b, n in ev]
     rates = torch.tensor(out, dtype=torch.float64, device=dev)
     if world > 1:
         allr = [torch.zeros_like(rates) for _ in range(world)]
@@ -756,9 +773,10 @@ def main():
         "kernels": kern["all"],
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": T * shape.d_in * x_pin[0].element_size(),
                 "d2h_bytes_per_step": T * shape.d_out * y_host.element_size(), "steps": e2e_steps,
-                "copy_gbs_per_rank_h2d_d2h": rates,
+                "copy_gbs_per_rank_h2d_d2h": [r[:2] for r in rates],
+                "copy_gbs_per_rank_h2d_d2h_both_at_once": [r[2:] for r in rates],
                 "copy_gbs_all_ranks": [round(sum(r[0] for r in rates), 1), round(sum(r[1] for r in rates), 1)],
-                "note": "copy_gbs: each direction alone, all ranks copying at once, pinned buffers"},
+                "note": "copy_gbs: each direction alone / both at once, all ranks copying at once, pinned buffers"},
         "gpu_launches": int(launches),
         "clocks": clocks,
         "ranks": per_rank,
