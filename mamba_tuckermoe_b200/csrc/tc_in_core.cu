@@ -171,11 +171,11 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
     for (int s = 0; s < A_STAGES_MAX; ++s) { mbar_init(smem_u32(&bar_fullA[s]), 1); mbar_init(smem_u32(&bar_emptyA[s]), p.pre_norm ? 5 : 1); }
     for (int s = 0; s < G_STAGES_MAX; ++s) { mbar_init(smem_u32(&bar_fullB[s]), 1); mbar_init(smem_u32(&bar_emptyB[s]), 1); }
     mbar_init(smem_u32(&bar_accA), 1);
-    // h is staged (and its TMEM columns free) once the four secondary warps say so; the score columns, which lie in
+    // h is staged (and its TMEM columns free) once all eight warps have said so (each stages half of a row's columns); the score columns, which lie in
     // accumulator slot 1, are released through bar_pempty[1] (see the MMA thread's wait).  An accumulator slot is handed
     // back by all eight warps: the four that read it, and the four that only watched its 'full' barrier, so that the MMA
     // thread can never complete that barrier twice before a slow watcher has seen the first completion
-    mbar_init(smem_u32(&bar_hready), IC_EPI_WARPS / 2);
+    mbar_init(smem_u32(&bar_hready), IC_EPI_WARPS);
     for (int s = 0; s < 2; ++s) { mbar_init(smem_u32(&bar_pfull[s]), 1); mbar_init(smem_u32(&bar_pempty[s]), IC_EPI_WARPS); }
     fence_mbar_init();
     prefetch_tmap(&tmX);
@@ -293,9 +293,10 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
     // ------------------------------- epilogue warps -------------------------------
     // Eight warps: warp w may read TMEM lanes 32*(w%4)..+31, so each row quadrant has a "primary" warp
     // (2-5) and a "secondary" warp (6-9); thread = token row in both.
-    //   epilogue A: primary = routing (scores -> top-k -> gates -> c), secondary = h row (sum of squares,
-    //               h*w -> bf16 -> shared memory); they meet at a named barrier, the primary scales c by the
-    //               row's 1/rms and publishes it through the workspace for its secondary twin.
+    //   epilogue A: both warps of a row stage half of its h columns each (sum of squares, h*w -> bf16 -> shared
+    //               memory); then primary = routing (scores -> top-k -> gates -> c) while the first core tile runs; they
+    //               meet at a named barrier, the primary scales c by the row's 1/rms and publishes it through the
+    //               workspace for its secondary twin.
     //   epilogue B: the 64-column units of z alternate between the two groups, so each group has two MMA
     //               tile times per unit; each thread stores its row's columns as 16-byte pieces.
     const int quad = warp & 3;
@@ -307,6 +308,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
     float c[R1];
     bool ok = true;
     float inv_x = 1.f;  // 1 / rms(x row) when the callers' pre-norm is applied here
+    float ss_half = 0.f;  // this warp's half of the row's sum of squares of h
     if (p.pre_norm && grp == 1) {
       // The secondary warps are idle during phase A: they follow the x tiles through the ring and accumulate
       // each row's sum of squares (the swizzle permutes 16-byte chunks inside a row, which a sum does not see).
@@ -346,6 +348,48 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         if (grp == 1 && live) c_work[grow * R1] = inv_x;
         named_bar_sync(5, 256);
         if (grp == 0) inv_x = live ? c_work[grow * R1] : 1.f;
+      }
+      // h rows: both warps of a row quadrant stage half of the r3 columns each (statistics, weight, bf16, swizzled store:
+      // 16-byte chunk index XOR row % 8 inside 128-byte rows), so that phase B can start after half the time one warp
+      // would need; the primary warps do the routing afterwards, while the first core tile is already running.
+      {
+        const int ncc = p.r3 / 32, cc_lo = grp * (ncc / 2), cc_hi = cc_lo + ncc / 2;
+        float ss = 0.f;
+        for (int cc = cc_lo; cc < cc_hi; ++cc) {
+          uint32_t r[32];
+          tmem_ld32(t_lane + cc * 32, r);
+          tmem_ld_wait(r);
+          const uint32_t kblk_base = ring + (cc >> 1) * H_KBLOCK_BYTES + row * 128;
+          // the 32 weights of this column group as four 16-byte broadcast loads, all ahead of the stores
+          uint4 wq[4];
+#pragma unroll
+          for (int g = 0; g < 4; ++g) wq[g] = *reinterpret_cast<const uint4 *>(&wnorm_s[cc * 32 + g * 8]);
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            float v[8];
+            const uint32_t ww[4] = {wq[g].x, wq[g].y, wq[g].z, wq[g].w};
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const float a = __uint_as_float(r[g * 8 + q]);
+              ss = fmaf(a, a, ss);
+              v[q] = a * __uint_as_float((q & 1) ? (ww[q >> 1] & 0xffff0000u) : (ww[q >> 1] << 16));
+            }
+            const uint32_t chunk = (uint32_t)((cc & 1) * 4 + g) ^ (uint32_t)(row & 7);
+            const uint32_t addr = kblk_base + chunk * 16;
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pack_bf16x2(v[0], v[1])),
+                         "r"(pack_bf16x2(v[2], v[3])), "r"(pack_bf16x2(v[4], v[5])), "r"(pack_bf16x2(v[6], v[7])));
+            // no "memory" clobber: nothing the compiler sees touches the h tile, and the proxy fence below orders it
+          }
+        }
+        ss_half = ss;
+        if (grp == 1) inv_rms_s[row] = ss;   // the secondary warp's half of the sum of squares, for its primary twin
+        fence_proxy_async_smem();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(smem_u32(&bar_hready));   // 8 arrivals: h is in shared memory, its TMEM columns are free
+          if (grp == 1) mbar_arrive(smem_u32(&bar_pempty[1]));  // this warp does not read the score columns
+        }
       }
       if (grp == 0) {
         if (p.fuse_router) {
@@ -437,8 +481,10 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         }
         if (threadIdx.x == 64) TMOE_STAMP(3);  // routing done
         tc_fence_before();                      // score columns are free for the core-tile accumulators
-        named_bar_sync(3, 256);                 // the secondary warps have written inv_rms_s
-        const float inv_rms = inv_rms_s[row];
+        named_bar_sync(3, 256);                 // the secondary warps have written their halves of the sums of squares
+        // h = inv_x * h_raw: RMSNorm(h) = h_raw * inv_x / sqrt(inv_x^2 * mean(h_raw^2) + eps)
+        const float ss_row = ss_half + inv_rms_s[row];
+        const float inv_rms = inv_x / sqrtf(inv_x * inv_x * ss_row / (float)p.r3 + p.eps);
 #pragma unroll
         for (int a = 0; a < R1; ++a) c[a] *= inv_rms;
         if (live) {
@@ -446,43 +492,6 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
           for (int a = 0; a < R1; ++a) c_work[grow * R1 + a] = c[a];
         }
       } else {
-        // h row: statistics, weight, bf16, swizzled store (16-byte chunk index XOR row%8 inside 128-byte rows)
-        float ss = 0.f;
-        for (int cc = 0; cc < p.r3 / 32; ++cc) {
-          uint32_t r[32];
-          tmem_ld32(t_lane + cc * 32, r);
-          tmem_ld_wait(r);
-          const uint32_t kblk_base = ring + (cc >> 1) * H_KBLOCK_BYTES + row * 128;
-          // the 32 weights of this column group as four 16-byte broadcast loads, all ahead of the stores
-          uint4 wq[4];
-#pragma unroll
-          for (int g = 0; g < 4; ++g) wq[g] = *reinterpret_cast<const uint4 *>(&wnorm_s[cc * 32 + g * 8]);
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            float v[8];
-            const uint32_t ww[4] = {wq[g].x, wq[g].y, wq[g].z, wq[g].w};
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              const float a = __uint_as_float(r[g * 8 + q]);
-              ss = fmaf(a, a, ss);
-              v[q] = a * __uint_as_float((q & 1) ? (ww[q >> 1] & 0xffff0000u) : (ww[q >> 1] << 16));
-            }
-            const uint32_t chunk = (uint32_t)((cc & 1) * 4 + g) ^ (uint32_t)(row & 7);
-            const uint32_t addr = kblk_base + chunk * 16;
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pack_bf16x2(v[0], v[1])),
-                         "r"(pack_bf16x2(v[2], v[3])), "r"(pack_bf16x2(v[4], v[5])), "r"(pack_bf16x2(v[6], v[7])));
-            // no "memory" clobber: nothing the compiler sees touches the h tile, and the proxy fence below orders it
-          }
-        }
-        // h = inv_x * h_raw: RMSNorm(h) = h_raw * inv_x / sqrt(inv_x^2 * mean(h_raw^2) + eps)
-        inv_rms_s[row] = inv_x / sqrtf(inv_x * inv_x * ss / (float)p.r3 + p.eps);
-        fence_proxy_async_smem();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(smem_u32(&bar_hready));     // 4 arrivals: h is in shared memory, its TMEM columns are free
-          mbar_arrive(smem_u32(&bar_pempty[1]));  // this warp does not read the score columns
-        }
         named_bar_sync(3, 256);
       }
       if (threadIdx.x == 64) TMOE_STAMP(4);  // epilogue A done
