@@ -35,3 +35,17 @@ def test_traffic_figures_come_from_the_profile_summaries():
     peaks = bench.load_peaks()
     assert peaks["source"] in ("measured", "fallback") and 3000 < peaks["hbm_gbs"] < 9000 and 800 < peaks["bf16_tflops"] < 2500
     assert bench.SPIN_UP_STEPS >= 0 and "cfg2" in bench.WORKLOADS and "cfg4" in bench.WORKLOADS
+
+
+def test_reference_arm_under_a_two_rank_launch_prints_once():
+    """Launched the way the multi-GPU arm is (one process per rank), rank 0 alone times and prints; the others exit 0."""
+    port = 29600 + os.getpid() % 300
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                          "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "bench.py"),
+                          "--impl", "reference", "--gpus", "2", "--workload", "cfg0", "--steps", "1", "--warmup", "0"],
+                         capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert out.returncode == 0, out.stderr[-2000:]
+    lines = [l for l in out.stdout.splitlines() if l.startswith("{")]
+    assert len(lines) == 1
+    line = json.loads(lines[0])
+    assert line["impl"] == "reference" and line["n_gpus"] == 2 and line["value"] > 0
