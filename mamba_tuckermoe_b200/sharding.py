@@ -82,7 +82,8 @@ class PeerBuffers:
     the ranks (after its last write) instead of two: when rank r starts writing buffer A again in call k+2 it has passed
     the rendezvous of call k+1, which every rank q enqueued behind its reads of call k's result in A.  The result of a
     call therefore stays valid until the call after next.  ``buffers=1`` keeps one buffer (valid until the next call) and
-    adds a rendezvous in front of the first write.  ``.out`` is the buffer of the latest call.
+    adds a rendezvous in front of the first write.  ``.out`` is the buffer of the latest call.  The buffers belong to this
+    object: ``close()`` (or dropping the object) frees them, tensors obtained from ``.out`` must not be used afterwards.
     """
 
     def __init__(self, n_tokens: int, d_out: int, dtype: torch.dtype, device: torch.device, group=None, buffers: int = 2):
