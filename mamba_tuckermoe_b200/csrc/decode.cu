@@ -181,7 +181,7 @@ decode_core_kernel(const float *__restrict__ h_raw, const float *__restrict__ sc
       const float inv_rms = inv_x / sqrtf(inv_x * inv_x * ss / (float)r3 + eps);
       TopList<KMAX> sel;
       sel.init();
-      warp_select_topk<bf16, KMAX>(scores + (int64_t)t * E, E, top_k, lane, sel, inv_x);
+      warp_select_topk<bf16, KMAX>(scores + (int64_t)t * E, E, top_k, lane, sel, inv_x, &rc);
       const bool tap = (blockIdx.x == 0);
       const float z_all = rc.mode == 1 ? warp_softmax_denominator<bf16, float>(scores + (int64_t)t * E, E, lane, rc, sel.v[0], inv_x) : 1.f;
       emit_token<bf16, KMAX, float>(sel, top_k, E, R1, uexp, 0, lane, tap && idx_out ? idx_out + (int64_t)t * top_k : nullptr,

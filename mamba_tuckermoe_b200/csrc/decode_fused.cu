@@ -113,12 +113,14 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 // 0xFFFF - expert: unsigned order = "higher score first, equal scores -> lower expert index first", the rule of
 // ranks_before()): k rounds of register maximum + one warp-wide integer maximum + removal of the winner.
 template <int KMAX, int NK>
-__device__ __forceinline__ void warp_select_topk_keys(const float *sc, int E, int k, int lane, float scale, TopList<KMAX> &sel) {
+__device__ __forceinline__ void warp_select_topk_keys(const float *sc, int E, int k, int lane, float scale, TopList<KMAX> &sel,
+                                                      const RouterCfg &rc) {
   uint32_t key[NK];
 #pragma unroll
   for (int i = 0; i < NK; ++i) {
     const int e = i * 32 + lane;
     uint32_t b = e < E ? (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(sc[e] * scale)) : 0u;
+    if (rc.mode == 1) b = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(rc.logit(__uint_as_float(b << 16))));
     b = (b == 0x8000u) ? 0u : b;                                   // -0 and +0 compare equal
     const uint32_t u = (b & 0x8000u) ? (~b & 0xffffu) : (b | 0x8000u);
     key[i] = e < E ? ((u << 16) | (0xffffu - (uint32_t)e)) : 0u;
@@ -342,9 +344,9 @@ __global__ void __launch_bounds__(kFThreads, 1) decode_fused_kernel(const FusedP
       const float *sc = hs + t * hcols + p.r3;
       TopList<KMAX> sel;
       sel.init();
-      if (p.E <= 32) warp_select_topk_keys<KMAX, 1>(sc, p.E, p.top_k, lane, inv_x, sel);
-      else if (p.E <= 128) warp_select_topk_keys<KMAX, 4>(sc, p.E, p.top_k, lane, inv_x, sel);
-      else warp_select_topk<bf16, KMAX>(sc, p.E, p.top_k, lane, sel, inv_x);
+      if (p.E <= 32) warp_select_topk_keys<KMAX, 1>(sc, p.E, p.top_k, lane, inv_x, sel, p.rc);
+      else if (p.E <= 128) warp_select_topk_keys<KMAX, 4>(sc, p.E, p.top_k, lane, inv_x, sel, p.rc);
+      else warp_select_topk<bf16, KMAX>(sc, p.E, p.top_k, lane, sel, inv_x, &p.rc);
       const bool tap = (blockIdx.x == 0);
       const float z_all = p.rc.mode == 1 ? warp_softmax_denominator<bf16, float>(sc, p.E, lane, p.rc, sel.v[0], inv_x) : 1.f;
       emit_token<bf16, KMAX, float>(sel, p.top_k, p.E, R1, uexp, 0, lane, tap && p.idx_out ? p.idx_out + (int64_t)t * p.top_k : nullptr,

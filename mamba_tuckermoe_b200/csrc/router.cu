@@ -55,7 +55,7 @@ router_fused_kernel(const T *__restrict__ x, const T *__restrict__ wr, const T *
       float s = warp_sum(acc[g]);
       if (e0 + g < E) {
         const float sr = round_to<T>(s);
-        sel.insert(sr, e0 + g, k);
+        sel.insert(rc.order_value(sr), e0 + g, k);
         if (rc.mode == 1) {
           const float l = rc.logit(sr);
           if (l > run_max) { run_sum = run_sum * expf(run_max - l) + 1.f; run_max = l; }
@@ -91,6 +91,7 @@ select_bf16_keys_kernel(const bf16 *__restrict__ scores, int ld, const bf16 *__r
     for (int q = 0; q < 8; ++q) {
       const int e = e0 + q;
       uint32_t b = (q & 1) ? (w[q >> 1] >> 16) : (w[q >> 1] & 0xffffu);
+      if (rc.mode == 1) b = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(rc.logit(__uint_as_float(b << 16))));
       b = (b == 0x8000u) ? 0u : b;                                   // -0 and +0 compare equal
       const uint32_t u = (b & 0x8000u) ? (~b & 0xffffu) : (b | 0x8000u);
       key[i * 8 + q] = (e < E) ? ((u << 16) | (0xffffu - (uint32_t)e)) : 0u;
@@ -128,7 +129,7 @@ select_kernel(const TS *__restrict__ scores, int ld, const T *__restrict__ uexp,
   const TS *sr = scores + t * ld;
   TopList<KMAX> sel;
   sel.init();
-  warp_select_topk<T, KMAX, TS>(sr, E, k, lane, sel);
+  warp_select_topk<T, KMAX, TS>(sr, E, k, lane, sel, 1.f, &rc);
   const float z_all = rc.mode == 1 ? warp_softmax_denominator<T, TS>(sr, E, lane, rc, sel.v[0]) : 1.f;
   emit_token<T, KMAX>(sel, k, E, r1, uexp, t, lane, idx, gates, c, rc, z_all);
 }

@@ -13,13 +13,28 @@ struct RouterCfg {
   int mode;        // 0: softmax over the k winners' raw scores; 1: capped / tempered softmax over all experts
   float cap;
   float inv_temp;
-  __device__ __forceinline__ float logit(float score) const { return cap * tanhf(score / cap) * inv_temp; }
+  int bf16;        // bf16 layer: the capped score and the logit are rounded to bf16, as the reference's bf16 tensors are
+  // logit of one score: cap * tanh(score / cap) in fp32, stored in the layer dtype (sft_cot_bundle/scripts/model.py:32-40,
+  // 320), then divided by the temperature in the layer dtype (model.py:324).  At logits of 10-20 a bf16 step is 0.06-0.12,
+  // i.e. several per cent of a probability: the rounding points have to be the reference's.
+  __device__ __forceinline__ float logit(float score) const {
+    float c = cap * tanhf(score / cap);
+    if (bf16) c = __bfloat162float(__float2bfloat16_rn(c));
+    float l = c * inv_temp;
+    if (bf16) l = __bfloat162float(__float2bfloat16_rn(l));
+    return l;
+  }
+  // What the top-k orders by: the raw score, or (rule 1) the tempered capped logit, as the reference's torch.topk does
+  // (model.py:327).  In bf16 the two orders differ: where the cap saturates, different scores become the same logit and
+  // the lower expert index wins.
+  __device__ __forceinline__ float order_value(float score) const { return mode == 1 ? logit(score) : score; }
 };
 inline RouterCfg router_cfg(const tmoe_layer_t &L) {
   RouterCfg rc;
   rc.mode = L.router_mode;
   rc.cap = L.router_cap > 0.f ? L.router_cap : 10.f;
   rc.inv_temp = 1.f / (L.router_temperature > 0.f ? L.router_temperature : 0.5f);
+  rc.bf16 = L.dtype == TMOE_BF16 ? 1 : 0;
   return rc;
 }
 
@@ -47,7 +62,8 @@ struct TopList {
 // Writes idx / gates / c for one token from a finished selection list (all lanes hold it).
 // T: storage type the gates are rounded to; TU: element type of the U_expert table.
 // Gate weights of the k selected experts (sel_v sorted descending), rounded to the storage type T.
-// mode 0: softmax over the k raw scores.  mode 1: p_j = exp(l_j - l_0) / z_all with l = rc.logit(score) and
+// mode 0: softmax over the k raw scores (sel_v).  mode 1: sel_v holds the selected LOGITS (RouterCfg::order_value);
+// p_j = exp(l_j - l_0) / z_all and
 // z_all = sum over ALL experts of exp(l_e - l_0); gate_j = p_j / (sum_j p_j + 1e-6).
 template <typename T, int KMAX>
 __device__ __forceinline__ void gates_of(const float (&sel_v)[KMAX], int k, const RouterCfg &rc, float z_all,
@@ -61,10 +77,10 @@ __device__ __forceinline__ void gates_of(const float (&sel_v)[KMAX], int k, cons
 #pragma unroll
     for (int j = 0; j < KMAX; ++j) gate[j] = round_to<T>(gate[j] * inv);
   } else {
-    const float l0 = rc.logit(sel_v[0]);
+    const float l0 = sel_v[0];
     float den = 0.f;
 #pragma unroll
-    for (int j = 0; j < KMAX; ++j) { gate[j] = (j < k) ? expf(rc.logit(sel_v[j]) - l0) / z_all : 0.f; den += gate[j]; }
+    for (int j = 0; j < KMAX; ++j) { gate[j] = (j < k) ? expf(sel_v[j] - l0) / z_all : 0.f; den += gate[j]; }
     const float inv = 1.f / (den + 1e-6f);
 #pragma unroll
     for (int j = 0; j < KMAX; ++j) gate[j] = round_to<T>(gate[j] * inv);
@@ -75,7 +91,7 @@ template <typename T, int KMAX, typename TU = T>
 __device__ __forceinline__ void emit_token(const TopList<KMAX> &sel, int k, int E, int r1, const TU *__restrict__ uexp,
                                            int64_t t, int lane, int32_t *__restrict__ idx,
                                            float *__restrict__ gates, float *__restrict__ c,
-                                           const RouterCfg &rc = RouterCfg{0, 10.f, 2.f}, float z_all = 1.f) {
+                                           const RouterCfg &rc = RouterCfg{0, 10.f, 2.f, 0}, float z_all = 1.f) {
   float gate[KMAX];
   gates_of<T, KMAX>(sel.v, k, rc, z_all, gate);
 #pragma unroll
@@ -122,10 +138,10 @@ template <> struct Vec16<bf16> {
 
 // Top-k of one token's scores [E] by k passes over the row (all lanes end with the same list).
 // Scores are multiplied by `scale` (1/rms(x) when the callers' pre-norm is applied in-kernel) and rounded to the storage
-// type T before they are compared.
+// type T before they are compared; with `rc` they are compared as rc->order_value() of that (the list then holds those).
 template <typename T, int KMAX, typename TS = float>
 __device__ __forceinline__ void warp_select_topk(const TS *__restrict__ sr, int E, int k, int lane, TopList<KMAX> &sel,
-                                                 float scale = 1.f) {
+                                                 float scale = 1.f, const RouterCfg *rc = nullptr) {
   float pv = INFINITY; int pi = -1;
 #pragma unroll
   for (int j = 0; j < KMAX; ++j) {
@@ -133,6 +149,7 @@ __device__ __forceinline__ void warp_select_topk(const TS *__restrict__ sr, int 
       float bv = -INFINITY; int bi = 0x7fffffff;
       for (int e = lane; e < E; e += 32) {
         float v = round_to<T>(to_f32(sr[e]) * scale);
+        if (rc) v = rc->order_value(v);
         if (ranks_before(pv, pi, v, e) && ranks_before(v, e, bv, bi)) { bv = v; bi = e; }
       }
 #pragma unroll
@@ -146,11 +163,11 @@ __device__ __forceinline__ void warp_select_topk(const TS *__restrict__ sr, int 
   }
 }
 
-// sum over all experts of exp(logit(score_e) - logit(top score)) for one token's score row (mode 1 only)
+// sum over all experts of exp(logit(score_e) - top logit) for one token's score row (mode 1 only)
 template <typename T, typename TS>
 __device__ __forceinline__ float warp_softmax_denominator(const TS *__restrict__ sr, int E, int lane, const RouterCfg &rc,
-                                                          float top_score, float scale = 1.f) {
-  const float l0 = rc.logit(top_score);
+                                                          float top_logit, float scale = 1.f) {
+  const float l0 = top_logit;
   float z = 0.f;
   for (int e = lane; e < E; e += 32) z += expf(rc.logit(round_to<T>(to_f32(sr[e]) * scale)) - l0);
   return warp_sum(z);

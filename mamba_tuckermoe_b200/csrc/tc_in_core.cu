@@ -399,6 +399,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
           // list is then maintained with integer max/min only (no data-dependent branches, independent
           // scores pipeline through the levels).
           uint32_t key[RK];
+          const bool rule1 = p.rc.mode == 1;   // the top-k then orders by the tempered capped logit (RouterCfg::order_value)
 #pragma unroll
           for (int j = 0; j < RK; ++j) key[j] = 0u;
           for (int cc = 0; cc < p.e_pad / 16; ++cc) {
@@ -409,6 +410,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
             for (int q = 0; q < 16; ++q) {
               const int e = cc * 16 + q;
               uint32_t b = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(__uint_as_float(r[q]) * inv_x));
+              if (rule1) b = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(p.rc.logit(__uint_as_float(b << 16))));
               b = (b == 0x8000u) ? 0u : b;                                   // -0 and +0 compare equal
               const uint32_t u = (b & 0x8000u) ? (~b & 0xffffu) : (b | 0x8000u);
               uint32_t carry = (e < p.E) ? ((u << 16) | (0xffffu - (uint32_t)e)) : 0u;
@@ -433,7 +435,7 @@ tc_in_core_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
           // scan above (a second pass over the score columns) so that the default rule's loop stays branch-free.
           float z_all = 1.f;
           if (p.rc.mode == 1) {
-            const float l0 = p.rc.logit(sv[0]);
+            const float l0 = sv[0];   // the list holds logits under this rule
             z_all = 0.f;
             for (int cc = 0; cc < p.e_pad / 16; ++cc) {
               uint32_t r[16];

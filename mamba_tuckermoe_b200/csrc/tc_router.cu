@@ -121,6 +121,7 @@ tc_router_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   } else {
     const int quad = warp & 3;
     const int row = quad * 32 + lane;
+    const bool rule1 = p.rc.mode == 1;   // the top-k then orders by the tempered capped logit (RouterCfg::order_value)
     uint32_t tcount = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < p.n_tiles && ok; tile += gridDim.x) {
@@ -150,6 +151,7 @@ tc_router_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           for (int q = 0; q < 16; ++q) {
             const int e = e0 + cc * 16 + q;
             uint32_t b = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(__uint_as_float(r[q])));
+            if (rule1) b = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(p.rc.logit(__uint_as_float(b << 16))));
             b = (b == 0x8000u) ? 0u : b;   // -0 and +0 compare equal
             const uint32_t u = (b & 0x8000u) ? (~b & 0xffffu) : (b | 0x8000u);
             uint32_t carry = (e < p.E) ? ((u << 16) | (0xffffu - (uint32_t)e)) : 0u;
@@ -171,7 +173,7 @@ tc_router_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         // capped-softmax rule only: its denominator runs over ALL experts, relative to the top logit (a second pass over the
         // columns, so that the default rule's scan above stays branch-free)
         if (p.rc.mode == 1) {   // (one expert chunk only: the launcher sends larger layers with this rule elsewhere)
-          const float l0 = p.rc.logit(sv[0]);
+          const float l0 = sv[0];   // the list holds logits under this rule
           z_all = 0.f;
           for (int cc = 0; cc < p.e_pad / 16; ++cc) {
             uint32_t r[16];

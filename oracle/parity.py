@@ -56,8 +56,10 @@ def parity_report(y: torch.Tensor, idx: torch.Tensor, x: torch.Tensor, factors: 
                 "topk_tie_explained": 0, "topk_unexplained": 0, "tie_tokens_rel_fro": 0.0, "tol": tol, "ok": True}
     y_ref, taps = layer_forward(x, factors, top_k, eps, chunk_tokens=chunk_tokens, return_taps=True, router=router)
     y_ref = y_ref.float()
-    gap = gap_ulps * score_ulp(taps["scores"].float(), dtype)
-    rep = classify_topk(idx, taps["idx"], taps["scores"].float(), gap)
+    # a differing selection is explained by a near-tie of what the reference's top-k compared: its scores, or under rule 1
+    # its tempered capped logits (which tie exactly where the cap saturates in bf16)
+    gap = gap_ulps * score_ulp(taps["order"].float(), dtype)
+    rep = classify_topk(idx, taps["idx"], taps["order"].float(), gap)
     keep = torch.ones(n, dtype=torch.bool)
     keep[rep.mismatch_tokens] = False
     yk, rk = y[keep].double(), y_ref[keep].double()

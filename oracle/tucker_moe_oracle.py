@@ -49,14 +49,23 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     return (x / denom) * weight
 
 
+def router_logits(scores: torch.Tensor, cap: float, temperature: float) -> torch.Tensor:
+    """Tempered capped logits of the trained checkpoints' router (``sft_cot_bundle/scripts/model.py:320-324``): what their
+    softmax and their top-k see.  Both steps are stored in the scores' dtype; in bf16 scores beyond about twice the cap all
+    become the same logit."""
+    capped = ((2.0 * torch.sigmoid(2.0 * (scores.float() * (1.0 / cap))) - 1.0) * cap).to(scores.dtype)
+    return capped / temperature
+
+
 def capped_softmax_gates(scores: torch.Tensor, top_k: int, cap: float, temperature: float):
     """The trained checkpoints' gate rule, restated from ``sft_cot_bundle/scripts/model.py:318-329`` (same math in
-    ``mamba3_mlx/mlx_model/tucker_moe.py:107-114``): soft cap ``cap*tanh(s/cap)``, temperature, softmax over ALL
-    experts, top-k of the tempered logits, renormalise the k selected probabilities with ``+1e-6``.
-    PARITY UNPINNED for this rule: that file needs a Triton GPU driver to import and its fused kernels to run, so no
-    golden vectors could be produced from the reference itself; this restatement is the only oracle for it."""
-    capped = cap * torch.tanh(scores / cap)
-    logits = capped / temperature
+    ``mamba3_mlx/mlx_model/tucker_moe.py:107-114``): soft cap ``cap*tanh(s/cap)`` -- computed in fp32 as
+    ``(2*sigmoid(2*s/cap) - 1)*cap`` and stored in the scores' dtype, as the reference's kernel does
+    (``model.py:15-18, 32-40``) --, temperature, softmax over ALL experts, top-k of the tempered logits, renormalise the k
+    selected probabilities with ``+1e-6``; every step after the cap in the scores' dtype, as in the reference.
+    Pinned by ``tests/golden/variant_*.npz``, made by running the reference module itself (its two Triton kernel launches
+    replaced by torch statements of their arithmetic: ``tests/golden/make_variant_golden.py``)."""
+    logits = router_logits(scores, cap, temperature)
     probs = torch.softmax(logits, dim=-1)
     _, idx = torch.topk(logits, top_k, dim=-1)
     raw = probs.gather(-1, idx)
@@ -70,8 +79,10 @@ def _forward_chunk(x_flat: torch.Tensor, f: Dict[str, torch.Tensor], top_k: int,
         # model.py:75-77 -- raw scores, top-k on the raw scores, softmax over the k winners only
         sel_val, sel_idx = torch.topk(scores, top_k, dim=-1)
         gates = F.softmax(sel_val, dim=-1)
+        order = scores
     else:
         sel_idx, gates = capped_softmax_gates(scores, top_k, router[1], router[2])
+        order = router_logits(scores, router[1], router[2])
     # model.py:80-81 -- shared in-projection, then the inner RMSNorm
     h = rms_norm(x_flat @ f["U_in"], f["inner_norm_w"], eps)
     # model.py:87-98 -- per selected expert: mix the core slices, contract, weight, accumulate
@@ -85,7 +96,8 @@ def _forward_chunk(x_flat: torch.Tensor, f: Dict[str, torch.Tensor], top_k: int,
     # model.py:101
     y = acc @ f["U_out"] + f["bias"]
     if taps is not None:
-        for name, val in (("scores", scores), ("idx", sel_idx), ("gates", gates), ("h", h),
+        # "order": the values the top-k compared (scores under rule 0, tempered capped logits under rule 1)
+        for name, val in (("scores", scores), ("order", order), ("idx", sel_idx), ("gates", gates), ("h", h),
                           ("z", acc), ("y", y)):
             taps.setdefault(name, []).append(val)
     return y
@@ -140,15 +152,23 @@ def layer_forward_f64(x: torch.Tensor, factors: Dict[str, torch.Tensor], top_k: 
         scores = xc @ f["router_w"].t()
         if round_scores_to is not None:
             scores = scores.to(round_scores_to).double()
-        if idx is None:
-            sel_val, sel_idx = torch.topk(scores, top_k, dim=-1)
+        order = scores
+        if router[0] != 0:
+            capped = router[1] * torch.tanh(scores / router[1])
+            if round_scores_to is not None:   # the reference keeps the capped scores and the logits in the layer dtype
+                capped = capped.to(round_scores_to).double()
+            logits = capped / router[2]
+            if round_scores_to is not None:
+                logits = logits.to(round_scores_to).double()
+            order = logits                    # its top-k runs on the logits (model.py:327)
+        if idx is None:   # higher value first, equal values -> lower expert index first
+            sel_idx = torch.sort(order, dim=-1, descending=True, stable=True).indices[:, :top_k]
         else:
             sel_idx = idx[t0:t0 + chunk_tokens].long()
-            sel_val = torch.gather(scores, 1, sel_idx)
+        sel_val = torch.gather(scores, 1, sel_idx)
         if router[0] == 0:
             gates = torch.softmax(sel_val, -1)
         else:  # capped / tempered softmax over all experts, renormalised over the selection (+1e-6)
-            logits = router[1] * torch.tanh(scores / router[1]) / router[2]
             raw = torch.softmax(logits, -1).gather(-1, sel_idx)
             gates = raw / (raw.sum(-1, keepdim=True) + 1e-6)
         c = torch.einsum("tk,tkr->tr", gates, f["U_expert"][sel_idx])         # [t, r1]
