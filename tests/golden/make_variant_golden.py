@@ -38,6 +38,8 @@ CASES = {
     "variant_shipped_f32": (LayerShape(768, 768, 8, 2, 32, 256, 512, 1e-5), 6, "float32", 2103, 0.3),
     "variant_e64_k2_bf16": (LayerShape(256, 384, 64, 2, 4, 128, 256, 1e-5), 300, "bfloat16", 2104, 0.5),
     "variant_shipped_bf16": (LayerShape(768, 768, 8, 2, 32, 256, 512, 1e-5), 64, "bfloat16", 2105, 0.3),
+    # 512 tokens or more in bf16: the stand-alone router runs on the tensor cores
+    "variant_e256_k8_bf16": (LayerShape(256, 128, 256, 8, 8, 64, 128, 1e-5), 600, "bfloat16", 2106, 0.3),
 }
 
 
