@@ -44,7 +44,11 @@ struct RouterParams {
   int32_t *status;
 };
 
-template <int RK>
+// PAIR: launched as clusters of two CTAs on neighbouring token tiles; the even CTA issues every MMA for both (tcgen05
+// cta_group::2, M = 256) and each CTA loads only half of the rows of a router tile.  The kernel's bandwidth is the bytes of x
+// it keeps in flight per SM, and a stage that holds half a router tile leaves room for more of them (E = 256: 6 stages of
+// 32 KB instead of 4 of 48 KB).
+template <int RK, bool PAIR>
 __global__ void __launch_bounds__(RT_THREADS, 1)
 tc_router_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, const RouterParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -54,19 +58,34 @@ tc_router_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const int stage_bytes = RT_X_BYTES + p.e_pad * 128;
+  constexpr int NB = PAIR ? 2 : 1;   // CTAs that share one MMA
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+  const int w_rows = p.e_pad / NB;   // rows of a router tile in this CTA's stage
+  const int stage_bytes = RT_X_BYTES + w_rows * 128;
   const int KA = p.d_in / 64;
+  // token tiles of this CTA: first, first + step, ... (PAIR: the pair walks over tile pairs; the odd CTA of the last pair may
+  // stand on a tile beyond the last one -- its loads return zeros and its rows are never stored)
+  const int first = PAIR ? (int)(blockIdx.x >> 1) * 2 + (int)rank : (int)blockIdx.x;
+  const int step = (int)gridDim.x;
+  const int tile_end = PAIR ? ((p.n_tiles + 1) & ~1) : p.n_tiles;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < RT_STAGES_MAX; ++s) { mbar_init(smem_u32(&bar_full[s]), 1); mbar_init(smem_u32(&bar_empty[s]), 1); }
-    for (int s = 0; s < 2; ++s) { mbar_init(smem_u32(&bar_afull[s]), 1); mbar_init(smem_u32(&bar_aempty[s]), RT_EPI_WARPS); }
+    for (int s = 0; s < 2; ++s) { mbar_init(smem_u32(&bar_afull[s]), 1); mbar_init(smem_u32(&bar_aempty[s]), NB * RT_EPI_WARPS); }
     fence_mbar_init();
     prefetch_tmap(&tmX);
     prefetch_tmap(&tmW);
   }
-  if (warp == 2) { tmem_alloc(smem_u32(&tmem_base_s), 512); tmem_relinquish(); }
+  if (warp == 2) {
+    if constexpr (PAIR) { tmem_alloc_pair(smem_u32(&tmem_base_s), 512); tmem_relinquish_pair(); }
+    else { tmem_alloc(smem_u32(&tmem_base_s), 512); tmem_relinquish(); }
+  }
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) {   // both CTAs' barriers are initialised before anyone signals across the pair
+    cluster_arrive();
+    cluster_wait();
+  }
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_s;
   griddep_wait();   // x may come from the kernel before this one in the stream
@@ -78,16 +97,23 @@ tc_router_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     bool ok = true;
     // a single pass reads x once: evict-first, the router rows stay (30.8 -> 28.3 us per launch right after an L2 flush)
     const uint64_t pol_x = p.n_pass == 1 ? l2_policy_evict_first() : l2_policy_evict_normal();
-    for (int tile = blockIdx.x; tile < p.n_tiles && ok; tile += gridDim.x) {
+    for (int tile = first; tile < tile_end && ok; tile += step) {
       if (lane == 0) {
         for (int pass = 0; pass < p.n_pass && ok; ++pass) {   // passes after the first find the x tile in L2
           for (int kb = 0; kb < KA; ++kb) {
             if (!(ok = mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1, p.status, kKernelRouter, 2))) break;
             const uint32_t full = smem_u32(&bar_full[s]);
-            mbar_arrive_expect_tx(full, (uint32_t)stage_bytes);
             const uint32_t sa = ring + s * (uint32_t)stage_bytes;
-            tma_load_2d_hint(sa, &tmX, kb * 64, tile * RT_TM, full, pol_x);
-            tma_load_2d(sa + RT_X_BYTES, &tmW, kb * 64, pass * p.e_pad, full);
+            if constexpr (PAIR) {   // both CTAs' bytes are counted on the barrier of the CTA that issues the MMAs
+              if (rank == 0) mbar_arrive_expect_tx(full, 2u * (uint32_t)stage_bytes);
+              const uint32_t full0 = mapa_u32(full, 0);
+              tma_load_2d_pair_hint(sa, &tmX, kb * 64, tile * RT_TM, full0, pol_x);
+              tma_load_2d_pair(sa + RT_X_BYTES, &tmW, kb * 64, pass * p.e_pad + (int)rank * w_rows, full0);
+            } else {
+              mbar_arrive_expect_tx(full, (uint32_t)stage_bytes);
+              tma_load_2d_hint(sa, &tmX, kb * 64, tile * RT_TM, full, pol_x);
+              tma_load_2d(sa + RT_X_BYTES, &tmW, kb * 64, pass * p.e_pad, full);
+            }
             if (++s == (uint32_t)p.n_stages) { s = 0; ph ^= 1; }
           }
         }
@@ -95,12 +121,12 @@ tc_router_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc = umma_idesc_bf16(RT_TM, p.e_pad);
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = umma_idesc_bf16(NB * RT_TM, p.e_pad);
       const uint64_t desc0 = umma_desc_k_sw128(ring);
       const uint32_t stage16 = (uint32_t)stage_bytes >> 4;
       uint32_t s = 0, ph = 0, tcount = 0;
-      const int n_acc = ((p.n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x) * p.n_pass;   // (tile, pass) pairs of this CTA
+      const int n_acc = ((tile_end - first + step - 1) / step) * p.n_pass;   // (tile, pass) pairs of this CTA
       for (int ia = 0; ia < n_acc; ++ia, ++tcount) {
         const uint32_t slot = tcount & 1, aph = (tcount >> 1) & 1;
         mbar_wait_or_exit(smem_u32(&bar_aempty[slot]), aph ^ 1, p.status, kKernelRouter, 4);
@@ -111,11 +137,14 @@ tc_router_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           const uint64_t dx = desc0 + s * stage16, dw = dx + (RT_X_BYTES >> 4);
           const uint32_t acc0 = kb != 0;
 #pragma unroll
-          for (int k = 0; k < 4; ++k) umma_bf16(d_tmem, dx + 2 * k, dw + 2 * k, idesc, acc0 | (uint32_t)(k != 0));
-          umma_commit(smem_u32(&bar_empty[s]));
+          for (int k = 0; k < 4; ++k) {
+            if constexpr (PAIR) umma_bf16_pair(d_tmem, dx + 2 * k, dw + 2 * k, idesc, acc0 | (uint32_t)(k != 0));
+            else umma_bf16(d_tmem, dx + 2 * k, dw + 2 * k, idesc, acc0 | (uint32_t)(k != 0));
+          }
+          if constexpr (PAIR) umma_commit_pair(smem_u32(&bar_empty[s]), 3); else umma_commit(smem_u32(&bar_empty[s]));
           if (++s == (uint32_t)p.n_stages) { s = 0; ph ^= 1; }
         }
-        umma_commit(smem_u32(&bar_afull[slot]));
+        if constexpr (PAIR) umma_commit_pair(smem_u32(&bar_afull[slot]), 3); else umma_commit(smem_u32(&bar_afull[slot]));
       }
     }
   } else {
@@ -124,7 +153,7 @@ tc_router_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     const bool rule1 = p.rc.mode == 1;   // the top-k then orders by the tempered capped logit (RouterCfg::order_value)
     uint32_t tcount = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < p.n_tiles && ok; tile += gridDim.x) {
+    for (int tile = first; tile < tile_end && ok; tile += step) {
       uint32_t key[RK];   // the running top-k list of this thread's token, carried across the expert chunks
 #pragma unroll
       for (int j = 0; j < RK; ++j) key[j] = 0u;
@@ -189,7 +218,9 @@ tc_router_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         // the accumulator has been read: the MMA thread may start the tile after next in it
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&bar_aempty[slot]));
+        if (lane == 0) {
+          if constexpr (PAIR) mbar_arrive_cluster(mapa_u32(smem_u32(&bar_aempty[slot]), 0)); else mbar_arrive(smem_u32(&bar_aempty[slot]));
+        }
       }
       if (!ok) break;
 
@@ -220,10 +251,14 @@ tc_router_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) {   // the other CTA may still be signalling this CTA's barriers, or its MMAs reading this CTA's tiles
+    cluster_arrive();
+    cluster_wait();
+  }
   if (warp == 2) {
     __syncwarp();
     tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    if constexpr (PAIR) tmem_dealloc_pair(tmem_base, 512); else tmem_dealloc(tmem_base, 512);
   }
 }
 
@@ -242,27 +277,39 @@ int launch_tc_router(const tmoe_layer_t &L, const void *x, const void *router_w,
   CUtensorMap tmX, tmW;
   int rc = encode_tmap_bf16_2d(&tmX, x, (uint64_t)T_, (uint64_t)L.d_in, RT_TM);
   if (rc) return rc;
-  if ((rc = encode_tmap_bf16_2d(&tmW, router_w, (uint64_t)L.n_experts, (uint64_t)L.d_in, (uint32_t)e_pad))) return rc;
+  // CTA pairs where the router tile is at least as large as the x tile (128 experts or more per chunk): there the ring is
+  // only 4 stages deep and half a router tile per CTA makes it 6 (805 MB of x at E = 256: 162 us against 180 us; at E = 64,
+  // 10 stages against 9, pairs are 4 % slower).  TMOE_ROUTER_PAIRS=0 / 1 forces the choice.
+  static const int pairs_env = [] { const char *s = getenv("TMOE_ROUTER_PAIRS"); return s ? (atoi(s) != 0 ? 1 : 0) : -1; }();
+  const bool pairs = T_ > RT_TM && (pairs_env >= 0 ? pairs_env == 1 : e_pad >= 128);
+  const int nb = pairs ? 2 : 1;
+  if ((rc = encode_tmap_bf16_2d(&tmW, router_w, (uint64_t)L.n_experts, (uint64_t)L.d_in, (uint32_t)(e_pad / nb)))) return rc;
   const int sms = current_device_sms();
   if (sms <= 0) return TMOE_ERR_CUDA;
   RouterParams p{};
   p.T = T_; p.d_in = L.d_in; p.E = L.n_experts; p.e_pad = e_pad; p.top_k = L.top_k; p.r1 = L.r1;
   p.n_tiles = (int)((T_ + RT_TM - 1) / RT_TM);
   p.n_pass = n_pass;
-  const int stage_bytes = RT_X_BYTES + e_pad * 128;
+  const int stage_bytes = RT_X_BYTES + e_pad / nb * 128;
   p.n_stages = RT_RING_BYTES / stage_bytes < RT_STAGES_MAX ? RT_RING_BYTES / stage_bytes : RT_STAGES_MAX;
   p.rc = router_cfg(L);
   p.uexp = reinterpret_cast<const bf16 *>(uexp_bf16);
   p.idx_out = idx; p.gates_out = gates; p.c_out = c; p.status = status;
-  const unsigned grid = (unsigned)(p.n_tiles < sms ? p.n_tiles : sms);
-  cudaError_t e;
-  if (L.top_k <= 2) {
-    e = cudaFuncSetAttribute(tc_router_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, RT_SMEM_BYTES);
-    if (e == cudaSuccess) e = launch_pdl(tc_router_kernel<2>, dim3(grid), dim3(RT_THREADS), (size_t)RT_SMEM_BYTES, st, tmX, tmW, p);
-  } else {
-    e = cudaFuncSetAttribute(tc_router_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, RT_SMEM_BYTES);
-    if (e == cudaSuccess) e = launch_pdl(tc_router_kernel<8>, dim3(grid), dim3(RT_THREADS), (size_t)RT_SMEM_BYTES, st, tmX, tmW, p);
+  unsigned grid = (unsigned)(p.n_tiles < sms ? p.n_tiles : sms);
+  if (pairs) {   // whole pairs: as many as there are tile pairs, at most one per two SMs
+    const unsigned want = (unsigned)((p.n_tiles + 1) / 2), have = (unsigned)(sms / 2);
+    grid = 2u * (want < have ? want : have);
   }
+  cudaError_t e;
+#define TMOE_RT(K, PR)                                                                                                     \
+  do {                                                                                                                     \
+    e = cudaFuncSetAttribute(tc_router_kernel<K, PR>, cudaFuncAttributeMaxDynamicSharedMemorySize, RT_SMEM_BYTES);         \
+    if (e == cudaSuccess)                                                                                                  \
+      e = launch_pdl_cluster(tc_router_kernel<K, PR>, dim3(grid), dim3(RT_THREADS), (size_t)RT_SMEM_BYTES, st, PR ? 2u : 1u, tmX, tmW, p); \
+  } while (0)
+  if (L.top_k <= 2) { if (pairs) TMOE_RT(2, true); else TMOE_RT(2, false); }
+  else { if (pairs) TMOE_RT(8, true); else TMOE_RT(8, false); }
+#undef TMOE_RT
   if (e != cudaSuccess) return TMOE_ERR_CUDA;
   count_launch();
   return launch_status();
